@@ -1,0 +1,156 @@
+// Shared device helpers for the sm_100a kernels of this package.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define B2_MAX_TP 8
+#define B2_MAX_ROWS 8          // token rows one decode-path launch can carry
+
+#define B2_API extern "C" __attribute__((visibility("default")))
+
+// Error/status codes written to CommCtx::status by kernels whose bounded waits expire.
+#define B2_STATUS_OK 0
+#define B2_STATUS_WAIT_TIMEOUT 1
+
+// ---------------------------------------------------------------------------
+// Symmetric-memory communicator as the kernels see it.  Every rank allocates
+// the same buffers; part[r] / sig[r] are this process's mappings of rank r's
+// copies.  mc_part is the NVSwitch multicast mapping of the partial buffer
+// (null when multimem is not used).
+// ---------------------------------------------------------------------------
+struct CommCtx {
+    int tp;                       // ranks
+    int rank;                     // this rank
+    int part_stride;              // floats per parity half of the partial buffer
+    int pad0;
+    float* part[B2_MAX_TP];       // [2][part_stride] fp32 partial sums, per rank
+    uint32_t* sig[B2_MAX_TP];     // [B2_MAX_TP] arrival words, per rank: sig[dst][src]
+    float* mc_part;               // multicast address of part (or null)
+    uint32_t* epoch;              // local: number of collective calls completed
+    int* status;                  // local: [0]=code [1]=kernel id [2]=peer [3]=epoch
+    long long wait_ns;            // bound of every spin-wait
+};
+
+// Device-resident description of one token row of a decode/verify step.  A
+// captured CUDA graph reads these instead of host-patched kernel arguments.
+struct RowMeta {
+    int seq;                      // sequence slot (KV cache / DeltaNet state index)
+    int pos;                      // RoPE position
+    int slot;                     // KV cache slot this row's K/V is written to
+    int ctx;                      // cache slots [0, ctx) are visible to this row
+    unsigned long long mask;      // bit j: slot ctx+j is visible (self and draft ancestors)
+};
+
+struct SeqState {
+    int len;                      // committed tokens in the cache
+    int token;                    // last sampled token (input of the next step)
+    int pad[2];
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum; `red` needs 32 floats of shared memory.  All threads get the result.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (l == 0) red[w] = v;
+    __syncthreads();
+    float t = (l < nw) ? red[l] : 0.f;
+    t = warp_sum(t);
+    return t;
+}
+
+__device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
+__device__ __forceinline__ uint2 ldg_nc_v2(const void* p) {
+    uint2 r;
+    asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p));
+    return r;
+}
+// Loads that must observe another GPU's (or another CTA's) fresh writes.
+__device__ __forceinline__ float4 ld_relaxed_sys_v4(const float* p) {
+    float4 r;
+    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(p) : "memory");
+    return r;
+}
+__device__ __forceinline__ float4 ld_cg_v4(const float* p) {
+    float4 r;
+    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(p) : "memory");
+    return r;
+}
+__device__ __forceinline__ float ld_cg_f32(const float* p) {
+    float r;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(r) : "l"(p) : "memory");
+    return r;
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float4 multimem_ld_reduce_v4(const float* mc) {
+    float4 r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(mc) : "memory");
+    return r;
+}
+__device__ __forceinline__ void multimem_st_v4(float* mc, float4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+                 :: "l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ long long globaltimer_ns() {
+    long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Spin until *p has reached `target` (wrap-safe) or `budget_ns` has passed.
+// Never unbounded: on expiry the caller records a status and carries on.
+__device__ __forceinline__ bool wait_reached(const uint32_t* p, uint32_t target, long long budget_ns) {
+    if ((int)(ld_acquire_sys_u32(p) - target) >= 0) return true;
+    long long t0 = globaltimer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if ((int)(ld_acquire_sys_u32(p) - target) >= 0) return true;
+        if (globaltimer_ns() - t0 > budget_ns) return false;
+    }
+}
+
+__device__ __forceinline__ void report_timeout(const CommCtx& c, int kernel_id, int peer, uint32_t epoch) {
+    if (atomicCAS(c.status, B2_STATUS_OK, B2_STATUS_WAIT_TIMEOUT) == B2_STATUS_OK) {
+        c.status[1] = kernel_id;
+        c.status[2] = peer;
+        c.status[3] = (int)epoch;
+    }
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
+
+#define B2_KID_GEMV_FIN 1
+#define B2_KID_ALLREDUCE 2
+#define B2_KID_ARGMAX 3
+#define B2_KID_BARRIER 4
+#define B2_KID_TEST 5
+#define B2_KID_GEMM_RS 6

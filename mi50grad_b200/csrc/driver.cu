@@ -1,0 +1,258 @@
+// Decode step driver: owns the per-token launch sequence of one rank and its
+// CUDA-graph capture/replay.
+//
+// It is the counterpart of the reference's C dispatch loops (reference:
+// src/runtime/c_dispatch.c:975-1213, c_dispatch_v2.c:501, c_graph_dispatch.c:458-540):
+// Python flattens the model into plain structs once, then one C call issues a
+// whole token.  What is different on purpose:
+//  * one process drives one GPU, so there is no device switching and no
+//    host-side event choreography between GPUs: cross-GPU ordering lives inside
+//    the kernels (flags in symmetric memory);
+//  * nothing is patched between tokens.  Positions, cache slots and the input
+//    token live in device memory (SeqState / RowMeta), so the whole step,
+//    embedding gather to arg-max, is ONE graph that is replayed unchanged (the
+//    reference re-writes kernel-node parameters of 2 graphs per layer per token:
+//    c_graph_dispatch.c:389-431);
+//  * a replay loop can run any number of tokens without returning to the host.
+#include <cstdio>
+#include <cstring>
+#include <vector>
+#include "kernels.cuh"
+
+#define LIN_INT4 0
+#define LIN_F16 1
+#define LIN_NONE 2
+
+struct LinearDesc {
+    int kind;
+    int K, N;                     // logical in/out features (N: valid outputs)
+    int KB, NTL, G, off32, gshift;
+    int k_splits, L;              // int4 launch shape
+    int ldw, kslice;              // f16 launch shape
+    int pad;
+    const void* w;                // qfrag or fp16 weights
+    const void* sz;               // szfrag
+};
+
+struct LayerDesc {
+    int type;                     // 0 gated full attention, 1 gated DeltaNet
+    int pad;
+    LinearDesc in_proj;           // [Q|gate|K|V] or [q|k|v|z(|a|b)]
+    LinearDesc out_proj;          // row-parallel
+    LinearDesc gate_up;           // gate/up interleaved by 8
+    LinearDesc down;              // row-parallel
+    const void* ffn_norm;         // RMSNorm applied after the attention block
+    const void* next_norm;        // RMSNorm applied after the FFN (next layer's input norm / final norm)
+    // full attention
+    const void* q_norm; const void* k_norm;
+    void* kcache; void* vcache;
+    // DeltaNet
+    const void* wa; const void* wb; const void* conv_w; void* conv_state; float* state;
+    const float* A_log; const void* dt_bias; const void* la_norm;
+    int off_q, off_k, off_v, off_z, off_a, off_b;
+};
+
+struct ModelDesc {
+    int n_layers, H, vocab, vocab_local, vocab_offset;
+    int nq, nkv, hd, rot, rope_interleaved;
+    int la_nk, la_nv, la_dk, la_dv;
+    int max_seq, max_rows, ar_mode;        // 0 exact, 1 deferred_ref, 2 deferred_consistent
+    int attn_splits, argmax_blocks, n_seqs_max;
+    float eps;
+    int F_pad;                             // padded local FFN width (row stride of the SiLU buffer)
+    const void* embed; const void* first_norm;
+    LinearDesc lm_head;
+    const float* cos_tab; const float* sin_tab;
+    // work buffers
+    float* h; void* xn; void* proj; int ld_proj; int pad0;
+    void* attn_out; int ld_attn; int pad1;
+    void* act; float* logits; int ld_logits; int pad2;
+    float* gemv_scratch; int* gemv_counters;
+    float* attn_scratch; int* attn_counters;
+    float* argmax_scratch; int* argmax_counters;
+    float* extra; float* local_part;
+    void* rows; void* rows_tmpl; void* seqs; int* row_tokens; int* seq_rows; int* out_tokens;
+    CommCtx comm;
+};
+
+struct Driver {
+    ModelDesc m;
+    std::vector<LayerDesc> layers;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    int graph_rows = 0, graph_flags = 0;
+    long long launches = 0;               // kernels issued by the last eager step
+};
+
+#define STEP_EMBED_TOKENS 1     // gather embeddings from tokens (else: h/xn were loaded by the caller)
+#define STEP_LM_HEAD 2          // compute logits
+#define STEP_ARGMAX 4           // arg-max into out_tokens (and SeqState.token)
+#define STEP_ADVANCE 8          // len += 1 for every row's sequence (plain decode)
+#define STEP_NO_COMMIT_DELTA 16 // DeltaNet state dry run
+
+#define CK(x) do { int e_ = (x); if (e_ != 0) return e_; } while (0)
+
+static int run_linear(Driver* d, const LinearDesc& L, const void* x, int ldx, int rows, const GemvEpi& epi,
+                      cudaStream_t s) {
+    d->launches++;
+    if (L.kind == LIN_INT4) {
+        GemvInt4Params p;
+        memset(&p, 0, sizeof(p));
+        p.qfrag = (const uint4*)L.w; p.szfrag = (const uint2*)L.sz; p.x = (const __half*)x;
+        p.ldx = ldx; p.rows = rows; p.K = L.K; p.KB = L.KB; p.NTL = L.NTL; p.G = L.G;
+        p.off32 = L.off32; p.gshift = L.gshift; p.k_splits = L.k_splits; p.L = L.L;
+        p.scratch = d->m.gemv_scratch; p.counters = d->m.gemv_counters; p.epi = epi; p.comm = d->m.comm;
+        return b2_gemv_int4(&p, s);
+    }
+    GemvF16Params p;
+    memset(&p, 0, sizeof(p));
+    p.w = (const __half*)L.w; p.x = (const __half*)x; p.ldw = L.ldw; p.ldx = ldx; p.rows = rows;
+    p.K = L.K; p.N = L.N; p.k_splits = L.k_splits; p.kslice = L.kslice;
+    p.scratch = d->m.gemv_scratch; p.counters = d->m.gemv_counters; p.epi = epi; p.comm = d->m.comm;
+    return b2_gemv_f16(&p, s);
+}
+
+static GemvEpi epi_store(void* out, int ldo, int n_valid, int mode) {
+    GemvEpi e;
+    memset(&e, 0, sizeof(e));
+    e.mode = mode; e.out = out; e.ldo = ldo; e.n_valid = n_valid;
+    return e;
+}
+
+static GemvEpi epi_finish(Driver* d, const void* norm_w, int flags) {
+    GemvEpi e;
+    memset(&e, 0, sizeof(e));
+    e.mode = EPI_FINISH; e.n_valid = d->m.H; e.fin_flags = flags;
+    e.h = d->m.h; e.norm_w = (const __half*)norm_w; e.xn = (__half*)d->m.xn;
+    e.extra = d->m.extra; e.local_part = d->m.local_part; e.eps = d->m.eps;
+    return e;
+}
+
+static int step_impl(Driver* d, int rows, int n_seqs, int flags, cudaStream_t s) {
+    const ModelDesc& m = d->m;
+    if (rows < 1 || rows > m.max_rows || rows > B2_MAX_ROWS) return cudaErrorInvalidValue;
+    d->launches = 0;
+    const bool tp = m.comm.tp > 1;
+    CK(b2_prepare_rows(m.rows_tmpl, m.seqs, m.rows, rows, s)); d->launches++;
+    if (flags & STEP_EMBED_TOKENS) {
+        CK(b2_embed_rmsnorm(m.embed, m.row_tokens, m.rows, m.seqs, m.first_norm, m.h, m.xn, rows, m.H, m.eps,
+                            m.vocab, s));
+        d->launches++;
+    }
+    for (int li = 0; li < m.n_layers; ++li) {
+        const LayerDesc& L = d->layers[li];
+        // ---- token mixer
+        CK(run_linear(d, L.in_proj, m.xn, m.H, rows, epi_store(m.proj, m.ld_proj, L.in_proj.N, EPI_STORE_F16), s));
+        if (L.type == 0) {
+            CK(b2_qknorm_rope_cachew(m.proj, m.ld_proj, m.rows, L.q_norm, L.k_norm, m.cos_tab, m.sin_tab, L.kcache,
+                                     L.vcache, rows, m.nq, m.nkv, m.hd, m.rot, m.max_seq, m.rope_interleaved,
+                                     m.eps, s));
+            AttnParams a;
+            memset(&a, 0, sizeof(a));
+            a.q = (const __half*)m.proj; a.ldq = m.ld_proj; a.gate_off = m.nq * m.hd;
+            a.kcache = (const __half*)L.kcache; a.vcache = (const __half*)L.vcache; a.rows = (const RowMeta*)m.rows;
+            a.out = (__half*)m.attn_out; a.ldo = m.ld_attn; a.n_rows = rows; a.nq = m.nq; a.nkv = m.nkv;
+            a.max_seq = m.max_seq; a.splits = m.attn_splits; a.scale = 1.0f / sqrtf((float)m.hd);
+            a.scratch = m.attn_scratch; a.counters = m.attn_counters;
+            CK(b2_decode_attn(&a, m.hd, s));
+            d->launches += 2;
+        } else {
+            DeltaParams q;
+            memset(&q, 0, sizeof(q));
+            q.proj = (const __half*)m.proj; q.ld = m.ld_proj;
+            q.off_q = L.off_q; q.off_k = L.off_k; q.off_v = L.off_v; q.off_z = L.off_z; q.off_a = L.off_a; q.off_b = L.off_b;
+            q.xn = (const __half*)m.xn; q.ldx = m.H; q.H = m.H; q.wa = (const __half*)L.wa; q.wb = (const __half*)L.wb;
+            q.conv_w = (const __half*)L.conv_w; q.conv_state = (__half*)L.conv_state; q.state = L.state;
+            q.A_log = L.A_log; q.dt_bias = (const __half*)L.dt_bias; q.norm_w = (const __half*)L.la_norm;
+            q.seq_rows = m.seq_rows; q.rows = (const RowMeta*)m.rows; q.out = (__half*)m.attn_out; q.ldo = m.ld_attn;
+            q.nk = m.la_nk; q.nv = m.la_nv; q.n_seqs = n_seqs; q.eps = 1e-6f;
+            q.commit = (flags & STEP_NO_COMMIT_DELTA) ? 0 : 1;
+            CK(b2_deltanet_step(&q, m.la_dk, m.la_dv, s));
+            d->launches++;
+        }
+        int f_attn = 0, f_ffn = 0;
+        if (!tp) { f_attn = FIN_NO_COMM; f_ffn = FIN_NO_COMM; }
+        else if (m.ar_mode == 1) { f_attn = FIN_NO_COMM; }
+        else if (m.ar_mode == 2) { f_attn = FIN_NO_COMM | FIN_NO_H_WRITE | FIN_SAVE_EXTRA; f_ffn = FIN_ADD_EXTRA; }
+        CK(run_linear(d, L.out_proj, m.attn_out, m.ld_attn, rows, epi_finish(d, L.ffn_norm, f_attn), s));
+        // ---- FFN
+        CK(run_linear(d, L.gate_up, m.xn, m.H, rows, epi_store(m.act, m.F_pad, m.F_pad, EPI_SILU_PAIR), s));
+        CK(run_linear(d, L.down, m.act, m.F_pad, rows, epi_finish(d, L.next_norm, f_ffn), s));
+    }
+    if (flags & STEP_LM_HEAD) {
+        CK(run_linear(d, m.lm_head, m.xn, m.H, rows, epi_store(m.logits, m.ld_logits, m.vocab_local, EPI_STORE_F32), s));
+    }
+    if (flags & STEP_ARGMAX) {
+        ArgmaxParams a;
+        memset(&a, 0, sizeof(a));
+        a.logits = m.logits; a.ld = m.ld_logits; a.n_rows = rows; a.vocab_local = m.vocab_local;
+        a.vocab_offset = m.vocab_offset; a.blocks = m.argmax_blocks; a.scratch = m.argmax_scratch;
+        a.counters = m.argmax_counters; a.out_tokens = m.out_tokens;
+        a.seqs = (flags & STEP_ADVANCE) ? (SeqState*)m.seqs : nullptr; a.rows = (const RowMeta*)m.rows; a.comm = m.comm;
+        CK(b2_argmax(&a, s));
+        d->launches++;
+    }
+    if (flags & STEP_ADVANCE) {
+        CK(b2_advance(m.seqs, nullptr, n_seqs, 1, s));
+        d->launches++;
+    }
+    return 0;
+}
+
+B2_API void* b2_driver_create(const ModelDesc* m, const LayerDesc* layers) {
+    Driver* d = new Driver();
+    d->m = *m;
+    d->layers.assign(layers, layers + m->n_layers);
+    return d;
+}
+B2_API void b2_driver_destroy(void* h) {
+    Driver* d = (Driver*)h;
+    if (!d) return;
+    if (d->exec) cudaGraphExecDestroy(d->exec);
+    if (d->graph) cudaGraphDestroy(d->graph);
+    delete d;
+}
+B2_API int b2_driver_step(void* h, int rows, int n_seqs, int flags, cudaStream_t s) {
+    return step_impl((Driver*)h, rows, n_seqs, flags, s);
+}
+B2_API long long b2_driver_launches(void* h) { return ((Driver*)h)->launches; }
+
+// Capture one step into a graph (the stream must be a non-default stream).
+B2_API int b2_driver_capture(void* h, int rows, int n_seqs, int flags, cudaStream_t s) {
+    Driver* d = (Driver*)h;
+    if (d->exec) { cudaGraphExecDestroy(d->exec); d->exec = nullptr; }
+    if (d->graph) { cudaGraphDestroy(d->graph); d->graph = nullptr; }
+    cudaError_t e = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) return e;
+    int r = step_impl(d, rows, n_seqs, flags, s);
+    cudaGraph_t g = nullptr;
+    e = cudaStreamEndCapture(s, &g);
+    if (r != 0) { if (g) cudaGraphDestroy(g); return r; }
+    if (e != cudaSuccess) return e;
+    d->graph = g;
+    e = cudaGraphInstantiate(&d->exec, g, 0);
+    if (e != cudaSuccess) return e;
+    d->graph_rows = rows; d->graph_flags = flags;
+    return 0;
+}
+// Replay the captured step `n` times back to back.
+B2_API int b2_driver_replay(void* h, int n, cudaStream_t s) {
+    Driver* d = (Driver*)h;
+    if (!d->exec) return cudaErrorInvalidValue;
+    for (int i = 0; i < n; ++i) {
+        cudaError_t e = cudaGraphLaunch(d->exec, s);
+        if (e != cudaSuccess) return e;
+    }
+    return 0;
+}
+B2_API int b2_driver_graph_nodes(void* h) {
+    Driver* d = (Driver*)h;
+    size_t n = 0;
+    if (!d->graph || cudaGraphGetNodes(d->graph, nullptr, &n) != cudaSuccess) return -1;
+    return (int)n;
+}
+B2_API int b2_sizeof_linear_desc() { return (int)sizeof(LinearDesc); }
+B2_API int b2_sizeof_layer_desc() { return (int)sizeof(LayerDesc); }
+B2_API int b2_sizeof_model_desc() { return (int)sizeof(ModelDesc); }
+B2_API int b2_sizeof_row_meta() { return (int)sizeof(RowMeta); }
+B2_API int b2_sizeof_seq_state() { return (int)sizeof(SeqState); }

@@ -1,0 +1,491 @@
+// Decode-path matrix-vector kernels (1..8 token rows) for sm_100a.
+//
+// gemv_int4: weight-only INT4 (group-wise scale and zero) times fp16
+// activations, fp32 accumulation.  It replaces the reference's whole family of
+// INT4 GEMV kernels (reference: src/kernels/gemv_int4_v2.hip ... gemv_int4_v8.hip,
+// gemv_int4_v5_awq.hip, gemv_int4_dual.hip, gemv_int4_dual_awq.hip,
+// gemv_int4_qkv_fused.hip) and the fused communication kernels
+// (reference: src/kernels/gemv_int4_p2p_allreduce_rmsnorm.hip,
+// kernel_p2p_allreduce_rmsnorm*.hip) with one kernel and four epilogues.
+//
+// Design, B200-first:
+//  * Weights are re-packed once at load time into tensor-core fragment order:
+//    a warp's 512-byte load is a [16 outputs x 64 k] tile whose nibbles already
+//    sit where mma.m16n8k16 wants them, so decode costs two logic ops per four
+//    weights: (w & 0x000f000f) | 0x6400 reads nibble pairs as the fp16 numbers
+//    1024+q, and (w & 0x00f000f0) | 0x6400 as 1024+16q.  The second form
+//    multiplies activations pre-scaled by 1/16.  Nothing is subtracted per
+//    weight: the tensor core accumulates sum((1024+q)*x) in fp32 and the bias
+//    1024*sum(x) + zero*sum(x) is removed once per quantisation group.
+//  * With 6.5 TB/s of HBM per 148 SMs an SM has ~30 issue slots per 512 bytes,
+//    which rules out per-weight SIMT arithmetic; the tensor core is used as an
+//    fp32-accumulating dot-product engine, the token rows ride in the 8-wide n
+//    dimension of the MMA.
+//  * Split-K inside the CTA (4 warps) and across CTAs (deterministic scratch +
+//    last-arriver reduction, no atomics on data).
+//  * EPI_FINISH: the CTA that completes the last tile publishes this rank's
+//    partial sums, signals its peers with st.release.sys, waits (bounded) for
+//    theirs, reads the peers' partials over NVLink (plain peer loads or one
+//    multimem.ld_reduce), adds the residual and applies the next RMSNorm.  It
+//    writes both the updated residual stream and the normalised vector.
+#include "gemv.cuh"
+
+#define GEMV_THREADS 256
+#define GEMV_WN 2            // warps along n
+#define GEMV_WK 4            // warps along k
+#define GEMV_NT 4            // 16-wide n-tiles per warp
+#define GEMV_TILE_N (GEMV_WN * GEMV_NT * 16)   // 128
+
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t nib_lo(uint32_t w) {      // halves: 1024 + q
+    uint32_t r;
+    asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(r) : "r"(w));
+    return r;
+}
+__device__ __forceinline__ uint32_t nib_hi(uint32_t w) {      // halves: 1024 + 16 q
+    uint32_t r;
+    asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(r) : "r"(w));
+    return r;
+}
+
+// ---------------------------------------------------------------------------
+// Tile completion shared by the INT4 and fp16 kernels.  `ybuf` holds the CTA's
+// [B2_MAX_ROWS][128] fp32 tile (this CTA's K-slice only when k_splits > 1).
+// ---------------------------------------------------------------------------
+struct TileCtx {
+    int rows, n0, n_pad;     // token rows, first output column, padded N (scratch stride)
+    int k_splits;
+    float* scratch;
+    int* counters;
+};
+
+__device__ void finish_rows(const GemvEpi& e, const CommCtx& c, int rows, uint32_t epoch_next,
+                            float* red);
+
+__device__ void complete_tile(float* ybuf, const TileCtx& t, const GemvEpi& e, const CommCtx& c,
+                              uint32_t epoch_next, float* red, int* s_flag) {
+    const int tid = threadIdx.x;
+    // ---- cross-CTA split-K: publish, count, last arriver sums in a fixed order
+    if (t.k_splits > 1) {
+        for (int i = tid; i < t.rows * GEMV_TILE_N; i += GEMV_THREADS) {
+            int r = i / GEMV_TILE_N, nl = i % GEMV_TILE_N;
+            t.scratch[((size_t)blockIdx.y * t.rows + r) * t.n_pad + t.n0 + nl] = ybuf[r * GEMV_TILE_N + nl];
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            int old = atomicAdd(&t.counters[blockIdx.x], 1);
+            int last = (old == t.k_splits - 1);
+            if (last) t.counters[blockIdx.x] = 0;
+            *s_flag = last;
+            __threadfence();
+        }
+        __syncthreads();
+        if (!*s_flag) return;
+        for (int i = tid; i < t.rows * GEMV_TILE_N; i += GEMV_THREADS) {
+            int r = i / GEMV_TILE_N, nl = i % GEMV_TILE_N;
+            float s = 0.f;
+            for (int ks = 0; ks < t.k_splits; ++ks)
+                s += ld_cg_f32(&t.scratch[((size_t)ks * t.rows + r) * t.n_pad + t.n0 + nl]);
+            ybuf[r * GEMV_TILE_N + nl] = s;
+        }
+        __syncthreads();
+    }
+    // ---- epilogues
+    if (e.mode == EPI_STORE_F16) {
+        __half* out = (__half*)e.out;
+        for (int i = tid; i < t.rows * GEMV_TILE_N; i += GEMV_THREADS) {
+            int r = i / GEMV_TILE_N, n = t.n0 + i % GEMV_TILE_N;
+            if (n < e.n_valid) out[(size_t)r * e.ldo + n] = __float2half(ybuf[i]);
+        }
+    } else if (e.mode == EPI_STORE_F32) {
+        float* out = (float*)e.out;
+        for (int i = tid; i < t.rows * GEMV_TILE_N; i += GEMV_THREADS) {
+            int r = i / GEMV_TILE_N, n = t.n0 + i % GEMV_TILE_N;
+            if (n < e.n_valid) out[(size_t)r * e.ldo + n] = ybuf[i];
+        }
+    } else if (e.mode == EPI_SILU_PAIR) {
+        __half* out = (__half*)e.out;
+        for (int i = tid; i < t.rows * (GEMV_TILE_N / 2); i += GEMV_THREADS) {
+            int r = i / (GEMV_TILE_N / 2), j = i % (GEMV_TILE_N / 2);
+            int base = r * GEMV_TILE_N + (j >> 3) * 16 + (j & 7);
+            int o = t.n0 / 2 + j;
+            if (o < e.n_valid) out[(size_t)r * e.ldo + o] = __float2half(silu_f(ybuf[base]) * ybuf[base + 8]);
+        }
+    } else {   // EPI_FINISH
+        const bool local = (e.fin_flags & FIN_NO_COMM) || c.tp <= 1;
+        float* part = local ? e.local_part
+                            : c.part[c.rank] + (size_t)(epoch_next & 1) * c.part_stride;
+        for (int i = tid; i < t.rows * GEMV_TILE_N; i += GEMV_THREADS) {
+            int r = i / GEMV_TILE_N, n = t.n0 + i % GEMV_TILE_N;
+            if (n < e.n_valid) {
+                float v = ybuf[i];
+                if (e.fin_flags & FIN_ADD_EXTRA) v += e.extra[(size_t)r * e.n_valid + n];
+                part[(size_t)r * e.n_valid + n] = v;
+            }
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            int old = atomicAdd(&t.counters[gridDim.x], 1);
+            int last = (old == (int)gridDim.x - 1);
+            if (last) t.counters[gridDim.x] = 0;
+            *s_flag = last;
+            __threadfence();
+        }
+        __syncthreads();
+        if (!*s_flag) return;
+        finish_rows(e, c, t.rows, epoch_next, red);
+    }
+}
+
+// One CTA: exchange partials, residual add, RMSNorm.  n_valid <= 8192.
+__device__ void finish_rows(const GemvEpi& e, const CommCtx& c, int rows, uint32_t epoch_next,
+                            float* red) {
+    const int tid = threadIdx.x;
+    const int H = e.n_valid;
+    const bool local = (e.fin_flags & FIN_NO_COMM) || c.tp <= 1;
+    __shared__ int s_fail;
+    if (tid == 0) s_fail = 0;
+    __syncthreads();
+    if (!local) {
+        if (tid == 0) *c.epoch = epoch_next;
+        if (tid < c.tp && tid != c.rank && !(e.fin_flags & FIN_TEST_WITHHOLD_SIGNAL))
+            st_release_sys_u32(c.sig[tid] + c.rank, epoch_next);
+        if (tid < c.tp && tid != c.rank) {
+            if (!wait_reached(c.sig[c.rank] + tid, epoch_next, c.wait_ns)) {
+                report_timeout(c, B2_KID_GEMV_FIN, tid, epoch_next);
+                s_fail = 1;
+            }
+        }
+        __syncthreads();
+    }
+    const bool exchange = !local && !s_fail;
+    const size_t poff = local ? 0 : (size_t)(epoch_next & 1) * c.part_stride;
+    const float* mine = local ? e.local_part : c.part[c.rank] + poff;
+    for (int r = 0; r < rows; ++r) {
+        float4 hv[8];
+        float ss = 0.f;
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            int n = (it * GEMV_THREADS + tid) * 4;
+            if (n < H) {
+                size_t off = (size_t)r * H + n;
+                float4 y;
+                if (exchange && c.mc_part) {
+                    y = multimem_ld_reduce_v4(c.mc_part + poff + off);
+                } else if (exchange) {
+                    y = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int pr = 0; pr < c.tp; ++pr) {
+                        float4 v = ld_relaxed_sys_v4(c.part[pr] + poff + off);
+                        y.x += v.x; y.y += v.y; y.z += v.z; y.w += v.w;
+                    }
+                } else {
+                    y = ld_cg_v4(mine + off);
+                }
+                if (e.fin_flags & FIN_SAVE_EXTRA) *(float4*)(e.extra + off) = y;
+                float4 h = *(const float4*)(e.h + off);
+                h.x += y.x; h.y += y.y; h.z += y.z; h.w += y.w;
+                if (!(e.fin_flags & FIN_NO_H_WRITE)) *(float4*)(e.h + off) = h;
+                hv[it] = h;
+                ss += h.x * h.x + h.y * h.y + h.z * h.z + h.w * h.w;
+            }
+        }
+        if (e.fin_flags & FIN_NO_NORM) continue;
+        float tot = block_sum(ss, red);
+        float inv = rsqrtf(tot / (float)H + e.eps);
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            int n = (it * GEMV_THREADS + tid) * 4;
+            if (n < H) {
+                const __half2* w2 = (const __half2*)(e.norm_w + n);
+                float2 w01 = __half22float2(w2[0]), w23 = __half22float2(w2[1]);
+                __half2 o0 = __floats2half2_rn(hv[it].x * inv * w01.x, hv[it].y * inv * w01.y);
+                __half2 o1 = __floats2half2_rn(hv[it].z * inv * w23.x, hv[it].w * inv * w23.y);
+                __half2* dst = (__half2*)(e.xn + (size_t)r * H + n);
+                dst[0] = o0;
+                dst[1] = o1;
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// INT4 kernel
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_int4_kernel(const GemvInt4Params p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wn = warp % GEMV_WN, wk = warp / GEMV_WN;
+    const int g = lane >> 2, t = lane & 3;
+    const int M = p.rows;
+    const int maxCh = 2 * GEMV_WK * p.L;
+    const int cta_b0 = blockIdx.y * (GEMV_WK * p.L);
+    const int cta_b1 = min(p.KB, cta_b0 + GEMV_WK * p.L);
+    const int nCh = max(0, cta_b1 - cta_b0) * 2;
+    const uint32_t epoch_next = (p.epi.mode == EPI_FINISH && p.comm.tp > 1) ? (*p.comm.epoch + 1u) : 0u;
+
+    uint4* xf = (uint4*)smem;                                        // [maxCh][M][4]
+    float2* cs = (float2*)(smem + (size_t)maxCh * M * 4 * 16);       // [maxCh][8]
+    float* redbuf = (float*)((unsigned char*)cs + (size_t)maxCh * 8 * 8);   // [WK*WN*NT*128]
+    float* ybuf = redbuf + GEMV_WK * GEMV_WN * GEMV_NT * 128;        // [8][128]
+    float* red32 = ybuf + B2_MAX_ROWS * GEMV_TILE_N;                 // [32]
+    int* s_flag = (int*)(red32 + 32);
+
+    // ---- stage activations in MMA B-fragment order, with per-chunk bias sums
+    for (int i = tid; i < nCh * 8; i += GEMV_THREADS)
+        if ((i & 7) >= M) cs[i] = make_float2(0.f, 0.f);
+    const int items = nCh * M * 4;
+    for (int base = 0; base < items; base += GEMV_THREADS) {
+        int item = base + tid;
+        bool valid = item < items;
+        int tt = item & 3, m = (item >> 2) % M, cl = (item >> 2) / M;
+        int k0 = (cta_b0 * 2 + cl) * 32 + 2 * tt;
+        __half2 a0, a1, b0, b1;
+        a0 = a1 = b0 = b1 = __float2half2_rn(0.f);
+        if (valid) {
+            const __half* xr = p.x + (size_t)m * p.ldx;
+            if (k0 < p.K) a0 = *(const __half2*)(xr + k0);
+            if (k0 + 8 < p.K) a1 = *(const __half2*)(xr + k0 + 8);
+            if (k0 + 16 < p.K) b0 = *(const __half2*)(xr + k0 + 16);
+            if (k0 + 24 < p.K) b1 = *(const __half2*)(xr + k0 + 24);
+        }
+        const __half2 sixteenth = __float2half2_rn(0.0625f);
+        b0 = __hmul2(b0, sixteenth);
+        b1 = __hmul2(b1, sixteenth);
+        float2 fa0 = __half22float2(a0), fa1 = __half22float2(a1);
+        float2 fb0 = __half22float2(b0), fb1 = __half22float2(b1);
+        float sa = fa0.x + fa0.y + fa1.x + fa1.y;
+        float sb = fb0.x + fb0.y + fb1.x + fb1.y;
+        sa += __shfl_xor_sync(0xffffffffu, sa, 1);
+        sb += __shfl_xor_sync(0xffffffffu, sb, 1);
+        sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+        sb += __shfl_xor_sync(0xffffffffu, sb, 2);
+        if (valid) {
+            uint4 v;
+            v.x = *(uint32_t*)&a0; v.y = *(uint32_t*)&a1; v.z = *(uint32_t*)&b0; v.w = *(uint32_t*)&b1;
+            xf[(cl * M + m) * 4 + tt] = v;
+            if (tt == 0) cs[cl * 8 + m] = make_float2(1024.f * (sa + sb), sa + 16.f * sb);
+        }
+    }
+    __syncthreads();
+
+    // ---- main loop: this warp owns GEMV_NT n-tiles over blocks [wb0, wb1)
+    const int tile0 = (blockIdx.x * GEMV_WN + wn) * GEMV_NT;
+    const int wb0 = cta_b0 + wk * p.L, wb1 = min(cta_b1, wb0 + p.L);
+    float acc[GEMV_NT][4], tot[GEMV_NT][4];
+#pragma unroll
+    for (int i = 0; i < GEMV_NT; ++i)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) acc[i][r] = tot[i][r] = 0.f;
+    float c1r0 = 0.f, c1r1 = 0.f, c2r0 = 0.f, c2r1 = 0.f;
+    int cur = -1;
+
+    auto flush = [&](int grp) {
+#pragma unroll
+        for (int i = 0; i < GEMV_NT; ++i) {
+            uint2 sz = ldg_nc_v2(p.szfrag + ((size_t)(tile0 + i) * p.G + grp) * 8 + g);
+            float2 s = __half22float2(*(__half2*)&sz.x), z = __half22float2(*(__half2*)&sz.y);
+            tot[i][0] += s.x * (acc[i][0] - c1r0 - z.x * c2r0);
+            tot[i][1] += s.x * (acc[i][1] - c1r1 - z.x * c2r1);
+            tot[i][2] += s.y * (acc[i][2] - c1r0 - z.y * c2r0);
+            tot[i][3] += s.y * (acc[i][3] - c1r1 - z.y * c2r1);
+            acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+        }
+        c1r0 = c1r1 = c2r0 = c2r1 = 0.f;
+    };
+
+    uint4 w[GEMV_NT], wnext[GEMV_NT];
+    if (wb0 < wb1) {
+#pragma unroll
+        for (int i = 0; i < GEMV_NT; ++i)
+            w[i] = ldg_nc_v4(p.qfrag + ((size_t)(tile0 + i) * p.KB + wb0) * 32 + lane);
+    }
+    for (int b = wb0; b < wb1; ++b) {
+        if (b + 1 < wb1) {
+#pragma unroll
+            for (int i = 0; i < GEMV_NT; ++i)
+                wnext[i] = ldg_nc_v4(p.qfrag + ((size_t)(tile0 + i) * p.KB + b + 1) * 32 + lane);
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int c = 2 * b + j;
+            const int grp = (c + p.off32) >> p.gshift;
+            if (grp != cur) {
+                if (cur >= 0) flush(cur);
+                cur = grp;
+            }
+            const int cl = c - 2 * cta_b0;
+            uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+            if (g < M) xv = xf[(cl * M + g) * 4 + t];
+            float4 cv = *(const float4*)&cs[cl * 8 + 2 * t];
+            c1r0 += cv.x; c2r0 += cv.y; c1r1 += cv.z; c2r1 += cv.w;
+#pragma unroll
+            for (int i = 0; i < GEMV_NT; ++i) {
+                uint32_t w0 = j ? w[i].z : w[i].x, w1 = j ? w[i].w : w[i].y;
+                uint32_t w0s = w0 >> 8, w1s = w1 >> 8;
+                mma16816(acc[i], nib_lo(w0), nib_lo(w0s), nib_lo(w1), nib_lo(w1s), xv.x, xv.y);
+                mma16816(acc[i], nib_hi(w0), nib_hi(w0s), nib_hi(w1), nib_hi(w1s), xv.z, xv.w);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < GEMV_NT; ++i) w[i] = wnext[i];
+    }
+    if (cur >= 0) flush(cur);
+
+    // ---- in-CTA reduction over the k-warps into ybuf[row][n_local]
+#pragma unroll
+    for (int i = 0; i < GEMV_NT; ++i)
+        *(float4*)&redbuf[(((wk * GEMV_WN + wn) * GEMV_NT + i) * 32 + lane) * 4] =
+            make_float4(tot[i][0], tot[i][1], tot[i][2], tot[i][3]);
+    __syncthreads();
+    for (int e = tid; e < GEMV_WN * GEMV_NT * 128; e += GEMV_THREADS) {
+        int wne = e / (GEMV_NT * 128), rem = e % (GEMV_NT * 128);
+        int i = rem >> 7, ln = (rem >> 2) & 31, r = rem & 3;
+        float s = 0.f;
+#pragma unroll
+        for (int k = 0; k < GEMV_WK; ++k) s += redbuf[((k * GEMV_WN + wne) * GEMV_NT + i) * 128 + (rem & 127)];
+        int nl = wne * GEMV_NT * 16 + i * 16 + (ln >> 2) + 8 * (r >> 1);
+        int row = 2 * (ln & 3) + (r & 1);
+        ybuf[row * GEMV_TILE_N + nl] = s;
+    }
+    __syncthreads();
+
+    TileCtx tc;
+    tc.rows = M; tc.n0 = blockIdx.x * GEMV_TILE_N; tc.n_pad = p.NTL * 16;
+    tc.k_splits = p.k_splits; tc.scratch = p.scratch; tc.counters = p.counters;
+    complete_tile(ybuf, tc, p.epi, p.comm, epoch_next, red32, s_flag);
+}
+
+// ---------------------------------------------------------------------------
+// fp16-weight kernel (lm_head, fp16-attention checkpoints).  Replaces the
+// reference's gemv_fp16_v2 (reference: src/kernels/gemv_fp16_v2.hip:22-88).
+// CTA tile: 128 outputs x kslice; each warp owns 16 outputs, 4 at a time.
+// ---------------------------------------------------------------------------
+template <int MR>
+__global__ void __launch_bounds__(GEMV_THREADS) gemv_f16_kernel(const GemvF16Params p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int M = p.rows;
+    const int k0 = blockIdx.y * p.kslice;
+    const int klen = min(p.kslice, p.K - k0);
+    const uint32_t epoch_next = (p.epi.mode == EPI_FINISH && p.comm.tp > 1) ? (*p.comm.epoch + 1u) : 0u;
+    __half* xs = (__half*)smem;                                      // [MR][kslice]
+    float* ybuf = (float*)(smem + (size_t)MR * p.kslice * 2);        // [8][128]
+    float* red32 = ybuf + B2_MAX_ROWS * GEMV_TILE_N;
+    int* s_flag = (int*)(red32 + 32);
+
+    for (int i = tid * 8; i < MR * p.kslice; i += GEMV_THREADS * 8) {
+        int m = i / p.kslice, kk = i % p.kslice;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (m < M && kk < klen) v = *(const uint4*)(p.x + (size_t)m * p.ldx + k0 + kk);
+        *(uint4*)(xs + i) = v;
+    }
+    for (int i = tid; i < B2_MAX_ROWS * GEMV_TILE_N; i += GEMV_THREADS) ybuf[i] = 0.f;
+    __syncthreads();
+
+    const int n_base = blockIdx.x * GEMV_TILE_N + warp * 16;
+#pragma unroll 1
+    for (int rb = 0; rb < 16; rb += 4) {
+        float acc[4][MR];
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int m = 0; m < MR; ++m) acc[r][m] = 0.f;
+        const __half* wr[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            int n = min(n_base + rb + r, p.N - 1);
+            wr[r] = p.w + (size_t)n * p.ldw + k0;
+        }
+        for (int kk = lane * 8; kk < klen; kk += 256) {
+            uint4 wv[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) wv[r] = ldg_nc_v4(wr[r] + kk);
+#pragma unroll
+            for (int m = 0; m < MR; ++m) {
+                uint4 xv = *(const uint4*)(xs + m * p.kslice + kk);
+                const __half2* x2 = (const __half2*)&xv;
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const __half2* w2 = (const __half2*)&wv[r];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        float2 a = __half22float2(w2[q]), b = __half22float2(x2[q]);
+                        acc[r][m] = fmaf(a.x, b.x, acc[r][m]);
+                        acc[r][m] = fmaf(a.y, b.y, acc[r][m]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int m = 0; m < MR; ++m) {
+                float v = warp_sum(acc[r][m]);
+                if (lane == 0 && m < M) ybuf[m * GEMV_TILE_N + warp * 16 + rb + r] = v;
+            }
+    }
+    __syncthreads();
+    TileCtx tc;
+    tc.rows = M; tc.n0 = blockIdx.x * GEMV_TILE_N; tc.n_pad = (int)gridDim.x * GEMV_TILE_N;
+    tc.k_splits = p.k_splits; tc.scratch = p.scratch; tc.counters = p.counters;
+    complete_tile(ybuf, tc, p.epi, p.comm, epoch_next, red32, s_flag);
+}
+
+// ---------------------------------------------------------------------------
+// Host launchers
+// ---------------------------------------------------------------------------
+B2_API size_t b2_gemv_int4_smem(int rows, int L) {
+    size_t maxCh = 2 * GEMV_WK * (size_t)L;
+    return maxCh * rows * 64 + maxCh * 64 + (GEMV_WK * GEMV_WN * GEMV_NT * 128 + B2_MAX_ROWS * GEMV_TILE_N + 32 + 4) * 4;
+}
+
+B2_API int b2_gemv_int4(const GemvInt4Params* p, cudaStream_t stream) {
+    if (p->rows < 1 || p->rows > B2_MAX_ROWS) return cudaErrorInvalidValue;
+    if (p->epi.mode == EPI_FINISH && p->epi.n_valid > 8192) return cudaErrorInvalidValue;
+    size_t smem = b2_gemv_int4_smem(p->rows, p->L);
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_int4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = smem;
+    }
+    dim3 grid(p->NTL * 16 / GEMV_TILE_N, p->k_splits);
+    gemv_int4_kernel<<<grid, GEMV_THREADS, smem, stream>>>(*p);
+    return cudaGetLastError();
+}
+
+template <int MR>
+static int launch_f16(const GemvF16Params* p, cudaStream_t stream) {
+    size_t smem = (size_t)MR * p->kslice * 2 + (B2_MAX_ROWS * GEMV_TILE_N + 32 + 4) * 4;
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_f16_kernel<MR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = smem;
+    }
+    dim3 grid((p->N + GEMV_TILE_N - 1) / GEMV_TILE_N, p->k_splits);
+    gemv_f16_kernel<MR><<<grid, GEMV_THREADS, smem, stream>>>(*p);
+    return cudaGetLastError();
+}
+
+B2_API int b2_gemv_f16(const GemvF16Params* p, cudaStream_t stream) {
+    if (p->rows < 1 || p->rows > B2_MAX_ROWS || (p->kslice & 255)) return cudaErrorInvalidValue;
+    if (p->epi.mode == EPI_FINISH && p->epi.n_valid > 8192) return cudaErrorInvalidValue;
+    if (p->rows == 1) return launch_f16<1>(p, stream);
+    if (p->rows == 2) return launch_f16<2>(p, stream);
+    if (p->rows <= 4) return launch_f16<4>(p, stream);
+    return launch_f16<8>(p, stream);
+}
+
+B2_API int b2_sizeof_gemv_int4_params() { return (int)sizeof(GemvInt4Params); }
+B2_API int b2_sizeof_gemv_f16_params() { return (int)sizeof(GemvF16Params); }
+B2_API int b2_sizeof_comm_ctx() { return (int)sizeof(CommCtx); }

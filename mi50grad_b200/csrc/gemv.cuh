@@ -1,0 +1,56 @@
+// Parameter blocks of the decode-path GEMV kernels (shared with the step driver).
+#pragma once
+#include "common.cuh"
+
+// Epilogue modes: what happens to a finished [rows x 128] output tile.
+#define EPI_STORE_F16 0      // out16[row][n]  = y
+#define EPI_SILU_PAIR 1      // out16[row][j]  = silu(y[gate_j]) * y[up_j]  (gate/up interleaved by 8)
+#define EPI_STORE_F32 2      // out32[row][n]  = y
+#define EPI_FINISH    3      // row-parallel: all-reduce + residual add + next RMSNorm
+
+// Flags of EPI_FINISH.
+#define FIN_NO_COMM     1    // keep the sum local (tp == 1, or a deferred attention partial)
+#define FIN_NO_H_WRITE  2    // do not update the residual stream (deferred_consistent attention)
+#define FIN_SAVE_EXTRA  4    // save this rank's partial into `extra`
+#define FIN_ADD_EXTRA   8    // add `extra` to the partial before it is exchanged
+#define FIN_NO_NORM     16   // skip the RMSNorm (xn not written)
+#define FIN_TEST_WITHHOLD_SIGNAL 32  // test hook: do not signal peers, so the bounded wait runs out
+
+struct GemvEpi {
+    int mode;
+    int ldo;                 // row stride of out (elements)
+    int n_valid;             // real number of outputs (columns beyond are padding)
+    int fin_flags;
+    void* out;               // f16 / f32 output for the STORE / SILU modes
+    float* h;                // [rows][n_valid] fp32 residual stream (FINISH)
+    const __half* norm_w;    // [n_valid] multiplier of the following RMSNorm
+    __half* xn;              // [rows][n_valid] normalised output
+    float* extra;            // [rows][n_valid] saved / added partial
+    float* local_part;       // [rows][n_valid] staging when FIN_NO_COMM
+    float eps;
+    int pad;
+};
+
+struct GemvInt4Params {
+    const uint4* qfrag;      // [NTL][KB][32] fragment-ordered nibbles
+    const uint2* szfrag;     // [NTL][G][8] (scale_lo, scale_hi, zero_lo, zero_hi) halves
+    const __half* x;         // [rows][ldx]
+    int ldx, rows, K, KB, NTL, G;
+    int off32, gshift;       // group of chunk c = (c + off32) >> gshift   (chunk = 32 k)
+    int k_splits, L;         // CTAs along K, k64-blocks per warp
+    float* scratch;          // [k_splits][rows][NTL*16] split-K partials
+    int* counters;           // [gridDim.x + 1], zero between launches
+    GemvEpi epi;
+    CommCtx comm;
+};
+
+struct GemvF16Params {
+    const __half* w;         // [N][ldw] row-major (out_features x in_features)
+    const __half* x;         // [rows][ldx]
+    int ldw, ldx, rows, K, N;
+    int k_splits, kslice;    // kslice: multiple of 256
+    float* scratch;
+    int* counters;
+    GemvEpi epi;
+    CommCtx comm;
+};

@@ -1,0 +1,66 @@
+// Parameter blocks and host launchers of every kernel in this library.
+#pragma once
+#include "gemv.cuh"
+
+struct AttnParams {
+    const __half* q;         // [rows][ldq]: Q heads at column h*hd, gates at gate_off + h*hd
+    int ldq, gate_off;       // gate_off < 0: no output gate
+    const __half* kcache;    // [seq][max_seq][nkv][hd]
+    const __half* vcache;
+    const RowMeta* rows;
+    __half* out;             // [rows][ldo], head h at column h*hd
+    int ldo, n_rows, nq, nkv, max_seq, splits;
+    float scale;
+    float* scratch;          // [rows][nkv][splits][G][hd+2]
+    int* counters;           // [rows*nkv], zero between launches
+};
+
+struct DeltaParams {
+    const __half* proj;      // [rows][ld] in-projection outputs
+    int ld, off_q, off_k, off_v, off_z, off_a, off_b;   // off_a < 0: compute a,b here
+    const __half* xn;        // [rows][ldx] normalised layer input (for in-kernel a,b)
+    int ldx, H;
+    const __half* wa;        // [nv][H]
+    const __half* wb;        // [nv][H]
+    const __half* conv_w;    // [2*nk*dk + nv*dv][4], channel order q | k | v
+    __half* conv_state;      // [seq][nv][dv/32][2*dk+32][3] private histories (oldest first)
+    float* state;            // [seq][nv][dk][dv]
+    const float* A_log;      // [nv]
+    const __half* dt_bias;   // [nv]
+    const __half* norm_w;    // [dv]
+    const int* seq_rows;     // [n_seqs+1] row range of each launched sequence
+    const RowMeta* rows;     // rows[seq_rows[i]].seq = state slot of launched sequence i
+    __half* out;             // [rows][ldo], head j at column j*dv
+    int ldo, nk, nv, n_seqs;
+    float eps;
+    int commit;              // 0: leave state and conv history untouched (dry run for tree verification)
+};
+
+struct ArgmaxParams {
+    const float* logits;     // [rows][ld] this rank's vocabulary slice
+    int ld, n_rows, vocab_local, vocab_offset;
+    int blocks;              // CTAs per row
+    float* scratch;          // [rows][blocks][2]
+    int* counters;           // [rows]
+    int* out_tokens;         // [rows]
+    SeqState* seqs;          // if non-null: seqs[rows[r].seq].token = token of row r
+    const RowMeta* rows;
+    CommCtx comm;
+};
+
+B2_API int b2_gemv_int4(const GemvInt4Params* p, cudaStream_t stream);
+B2_API int b2_gemv_f16(const GemvF16Params* p, cudaStream_t stream);
+B2_API int b2_decode_attn(const AttnParams* p, int hd, cudaStream_t s);
+B2_API int b2_deltanet_step(const DeltaParams* p, int dk, int dv, cudaStream_t s);
+B2_API int b2_argmax(const ArgmaxParams* p, cudaStream_t s);
+B2_API int b2_prepare_rows(const void* tmpl, const void* seqs, void* rows, int n, cudaStream_t s);
+B2_API int b2_advance(void* seqs, const int* add, int n, int add_const, cudaStream_t s);
+B2_API int b2_embed_rmsnorm(const void* embed, const int* row_tokens, const void* rows, const void* seqs,
+                            const void* w, float* h, void* xn, int n_rows, int H, float eps, int vocab,
+                            cudaStream_t s);
+B2_API int b2_load_rmsnorm(const void* emb16, const float* emb32, const void* w, float* h, void* xn,
+                           int n_rows, int H, float eps, cudaStream_t s);
+B2_API int b2_qknorm_rope_cachew(void* qkv, int ld, const void* rows, const void* q_norm, const void* k_norm,
+                                 const float* cos_tab, const float* sin_tab, void* kcache, void* vcache,
+                                 int n_rows, int nq, int nkv, int hd, int rot, int max_seq, int interleaved,
+                                 float eps, cudaStream_t s);

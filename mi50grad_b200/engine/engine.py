@@ -1,0 +1,587 @@
+"""Single-GPU engine and per-rank worker of the tensor-parallel engine.
+
+Same role and public surface as the reference's `InferenceEngine` (reference:
+src/inference/engine.py:458-3785: embedding-in / hidden-out `decode_step`,
+`prefill_step`, `compute_logits`, `load_layer_weights`, launch counters), built
+differently:
+
+* weights are packed into tensor-core fragment order and fused at load
+  (Q|gate|K|V, q|k|v|z, gate/up interleaved) -- ops/packing.py;
+* a C++ driver issues the whole step (csrc/driver.cu); the step reads positions
+  and tokens from device memory, so ONE captured CUDA graph replays every token
+  and `generate_tokens` can run many tokens without a host round trip;
+* the token-level interface (`step_tokens`, `generate_tokens`) keeps embedding
+  lookup, lm_head and arg-max on the device; the reference does those three on
+  the host per token (reference: src/inference/generate.py:55-72,126-145);
+* sequences have independent lengths; state can be snapshotted and restored.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import logging
+import math
+from typing import Dict, List, Optional, Sequence, Union
+
+import numpy as np
+import torch
+
+from ..config import EngineConfig, QwenConfig
+from ..models.weights import LayerWeights, ModelWeights
+from ..ops import lib as L
+from ..ops.packing import (PackedInt4, concat_out, concat_out_dense, interleave_gate_up, launch_shape,
+                           pack_int4, random_packed_int4)
+from ..parallel.sharding import ShardSpec, make_shard_spec
+from ..utils.quant import DenseLinear, Int4Linear
+from .state import SequenceStates
+
+log = logging.getLogger(__name__)
+AR_MODE_ID = {"exact": 0, "deferred_ref": 1, "deferred_consistent": 2}
+
+
+class DeviceLinear:
+    """A projection resident on the GPU: packed INT4 or dense fp16 [N, K]."""
+
+    def __init__(self, packed: Optional[PackedInt4] = None, dense: Optional[torch.Tensor] = None):
+        self.packed, self.dense = packed, dense
+        if dense is not None:
+            self.N, self.K = dense.shape
+            ctas_n = -(-self.N // 128)
+            ks = 1 if ctas_n >= 148 else max(1, min(296 // ctas_n, self.K // 512))
+            self.kslice = min(8192, -(-(-(-self.K // ks)) // 256) * 256)
+            self.k_splits = -(-self.K // self.kslice)
+        else:
+            self.N, self.K = packed.N, packed.K
+
+    @property
+    def n_pad(self) -> int:
+        return self.packed.n_pad if self.packed is not None else -(-self.N // 128) * 128
+
+    def scratch_floats(self, rows: int) -> int:
+        ks = self.packed.k_splits if self.packed is not None else self.k_splits
+        return ks * rows * self.n_pad if ks > 1 else 0
+
+    def desc(self) -> L.LinearDesc:
+        d = L.LinearDesc()
+        if self.packed is not None:
+            p = self.packed
+            d.kind, d.K, d.N, d.KB, d.NTL, d.G = L.LIN_INT4, p.K, p.N, p.KB, p.NTL, p.G
+            d.off32, d.gshift, d.k_splits, d.L = p.off32, p.gshift, p.k_splits, p.L
+            d.w, d.sz = p.qfrag.data_ptr(), p.szfrag.data_ptr()
+        else:
+            d.kind, d.K, d.N = L.LIN_F16, self.K, self.N
+            d.ldw, d.kslice, d.k_splits = self.dense.stride(0), self.kslice, self.k_splits
+            d.w = self.dense.data_ptr()
+        return d
+
+    def nbytes(self) -> int:
+        return self.packed.nbytes() if self.packed is not None else self.dense.numel() * 2
+
+
+def _to_device_linear(lins: Sequence, device, rows_hint: int) -> DeviceLinear:
+    if all(isinstance(l, Int4Linear) for l in lins):
+        lin = lins[0] if len(lins) == 1 else concat_out(list(lins))
+        return DeviceLinear(packed=pack_int4(lin.to(device), device, rows_hint))
+    if all(isinstance(l, DenseLinear) for l in lins):
+        w = torch.cat([l.weight for l in lins], dim=0).to(device=device, dtype=torch.float16).contiguous()
+        if w.shape[1] % 8:
+            raise ValueError("dense projections need in_features % 8 == 0")
+        return DeviceLinear(dense=w)
+    raise ValueError("cannot fuse INT4 and fp16 projections into one launch")
+
+
+class DeviceLayer:
+    def __init__(self):
+        self.type = 0
+        self.in_proj = self.out_proj = self.gate_up = self.down = None
+        self.ffn_norm = self.attn_norm = None
+        self.q_norm = self.k_norm = None
+        self.wa = self.wb = self.conv_w = self.A_log = self.dt_bias = self.la_norm = None
+        self.off = (0, 0, 0, 0, -1, -1)
+
+
+class InferenceEngine:
+    def __init__(self, config: QwenConfig, device_id: int = 0, max_seq_len: int = 2048,
+                 tp_size: int = 1, tp_rank: int = 0, quant_format: str = "w4a16",
+                 use_int4_attention: bool = False, engine_config: Optional[EngineConfig] = None,
+                 comm=None, max_batch: int = 1):
+        if not torch.cuda.is_available():
+            raise RuntimeError("InferenceEngine needs a CUDA device; use models.oracle.OracleEngine on CPU")
+        if quant_format != "w4a16":
+            raise NotImplementedError("the decode path runs w4a16; w8a8/w4a8 are converter-only here")
+        self.config = config
+        self.ecfg = (engine_config or EngineConfig()).replace(
+            tp_size=tp_size, tp_rank=tp_rank, max_seq_len=max_seq_len, max_batch=max_batch)
+        self.device = torch.device("cuda", device_id)
+        torch.cuda.set_device(self.device)
+        self.lib = L.lib()
+        self.tp_size, self.tp_rank = tp_size, tp_rank
+        self.spec: ShardSpec = make_shard_spec(config, tp_size, tp_rank)
+        self.max_seq_len, self.max_batch = max_seq_len, max_batch
+        self.max_rows = L.MAX_ROWS
+        self.comm = comm
+        self.use_int4_attention = use_int4_attention
+        self.layers: List[Optional[DeviceLayer]] = [None] * config.num_hidden_layers
+        self.embed: Optional[torch.Tensor] = None
+        self.lm_head: Optional[DeviceLinear] = None
+        self.final_norm: Optional[torch.Tensor] = None
+        self.states = SequenceStates(config, self.spec, max_seq_len, max_batch, self.device)
+        self._driver = None
+        self._graph_key = None
+        self._tmpl_key = None
+        self._launch_counts: Dict[int, int] = {}
+        self._steps = 0
+        self._init_rope_tables()
+
+    # ------------------------------------------------------------------ set-up
+    @property
+    def kv_cache(self):
+        return self.states.kv
+
+    @property
+    def deltanet_state(self):
+        return self.states.dn
+
+    def _init_rope_tables(self):
+        cfg = self.config
+        half = cfg.rotary_dim // 2
+        freqs = 1.0 / (cfg.rope_theta ** (torch.arange(half, dtype=torch.float64) * 2.0 / cfg.rotary_dim))
+        ang = torch.arange(self.max_seq_len, dtype=torch.float64)[:, None] * freqs[None, :]
+        self.cos_tab = torch.cos(ang).float().to(self.device).contiguous()
+        self.sin_tab = torch.sin(ang).float().to(self.device).contiguous()
+
+    def _h16(self, t: torch.Tensor) -> torch.Tensor:
+        return t.to(device=self.device, dtype=torch.float16).contiguous()
+
+    def load_layer_weights(self, layer_idx: int, lw: Union[LayerWeights, dict]):
+        """`lw` is this rank's shard in engine format (loaders and
+        parallel.sharding produce it)."""
+        if isinstance(lw, dict):
+            lw = LayerWeights(**lw)
+        cfg, dev, rh = self.config, self.device, 1
+        dl = DeviceLayer()
+        dl.attn_norm, dl.ffn_norm = self._h16(lw.attn_norm), self._h16(lw.ffn_norm)
+        if lw.is_full:
+            dl.type = 0
+            dl.in_proj = _to_device_linear([lw.q, lw.q_gate, lw.k, lw.v], dev, rh)
+            dl.out_proj = _to_device_linear([lw.o], dev, rh)
+            dl.q_norm, dl.k_norm = self._h16(lw.q_norm), self._h16(lw.k_norm)
+        else:
+            dl.type = 1
+            sp = self.spec
+            kd = sp.n_la_k * cfg.linear_key_head_dim
+            vd = sp.n_la_v * cfg.linear_value_head_dim
+            parts = [lw.la_qkv, lw.la_z]
+            off_a = off_b = -1
+            if isinstance(lw.la_a, Int4Linear) and isinstance(lw.la_qkv, Int4Linear):
+                parts += [lw.la_a, lw.la_b]
+                off_a, off_b = 2 * kd + 2 * vd, 2 * kd + 2 * vd + sp.n_la_v
+            elif isinstance(lw.la_a, DenseLinear) and isinstance(lw.la_qkv, DenseLinear):
+                parts += [lw.la_a, lw.la_b]
+                off_a, off_b = 2 * kd + 2 * vd, 2 * kd + 2 * vd + sp.n_la_v
+            else:
+                dl.wa, dl.wb = self._h16(lw.la_a.dense(torch.float16)), self._h16(lw.la_b.dense(torch.float16))
+            dl.in_proj = _to_device_linear(parts, dev, rh)
+            dl.off = (0, kd, 2 * kd, 2 * kd + vd, off_a, off_b)
+            dl.out_proj = _to_device_linear([lw.la_out], dev, rh)
+            dl.conv_w = self._h16(lw.la_conv1d)
+            dl.A_log = lw.la_A_log.to(device=dev, dtype=torch.float32).contiguous()
+            dl.dt_bias, dl.la_norm = self._h16(lw.la_dt_bias), self._h16(lw.la_norm)
+        if not (isinstance(lw.gate, Int4Linear) and isinstance(lw.up, Int4Linear)):
+            raise NotImplementedError("FFN projections must be INT4 (w4a16)")
+        dl.gate_up = DeviceLinear(packed=pack_int4(interleave_gate_up(lw.gate.to(dev), lw.up.to(dev)), dev, rh))
+        dl.down = _to_device_linear([lw.down], dev, rh)
+        self.layers[layer_idx] = dl
+        self._driver = None
+
+    def load_final_norm(self, w: torch.Tensor):
+        self.final_norm = self._h16(torch.as_tensor(w))
+        self._driver = None
+
+    def load_lm_head(self, w: torch.Tensor):
+        """`w` is this rank's vocabulary slice [vocab_local, hidden]."""
+        self.lm_head = DeviceLinear(dense=self._h16(torch.as_tensor(w)))
+        self._driver = None
+
+    def load_embedding(self, w: torch.Tensor):
+        self.embed = self._h16(torch.as_tensor(w))
+        self._driver = None
+
+    def load_model(self, mw: ModelWeights):
+        """`mw` must already be this rank's shard."""
+        for i, lw in enumerate(mw.layers):
+            self.load_layer_weights(i, lw)
+        self.load_embedding(mw.embed)
+        self.load_lm_head(mw.lm_head)
+        self.load_final_norm(mw.final_norm)
+
+    def init_random(self, seed: int = 0, int4_attention: bool = True, embed_std: float = 0.05):
+        """Random-init weights of the benchmark's form created directly on the
+        device in packed layout (no checkpoint, no host copy)."""
+        cfg, sp, dev = self.config, self.spec, self.device
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(seed + 1000 * self.tp_rank)
+        H, g = cfg.hidden_size, cfg.group_size
+        ones = lambda n: torch.ones(n, dtype=torch.float16, device=dev)
+        rnd = lambda K, N: DeviceLinear(packed=random_packed_int4(K, N, g, dev, gen))
+        dense = lambda N, K: DeviceLinear(dense=(torch.randn(N, K, device=dev, generator=gen) * 0.02).half())
+        Fp = -(-sp.ffn_local // 64) * 64
+        for i in range(cfg.num_hidden_layers):
+            dl = DeviceLayer()
+            dl.attn_norm, dl.ffn_norm = ones(H), ones(H)
+            if cfg.is_full_attention(i):
+                dl.type = 0
+                qd, kvd = sp.n_q * cfg.head_dim, sp.n_kv * cfg.head_dim
+                dl.in_proj = rnd(H, 2 * qd + 2 * kvd) if int4_attention else dense(2 * qd + 2 * kvd, H)
+                dl.out_proj = rnd(qd, H) if int4_attention else dense(H, qd)
+                dl.q_norm, dl.k_norm = ones(cfg.head_dim), ones(cfg.head_dim)
+            else:
+                dl.type = 1
+                kd = sp.n_la_k * cfg.linear_key_head_dim
+                vd = sp.n_la_v * cfg.linear_value_head_dim
+                dl.in_proj = rnd(H, 2 * kd + 2 * vd) if int4_attention else dense(2 * kd + 2 * vd, H)
+                dl.out_proj = rnd(vd, H) if int4_attention else dense(H, vd)
+                dl.off = (0, kd, 2 * kd, 2 * kd + vd, -1, -1)
+                dl.wa = (torch.randn(sp.n_la_v, H, device=dev, generator=gen) * 0.02).half()
+                dl.wb = (torch.randn(sp.n_la_v, H, device=dev, generator=gen) * 0.02).half()
+                dl.conv_w = (torch.randn(2 * kd + vd, cfg.linear_conv_kernel_dim, device=dev, generator=gen) * 0.3).half()
+                dl.A_log = (torch.rand(sp.n_la_v, device=dev, generator=gen) * 1.5 - 1.0).float()
+                dl.dt_bias = (torch.randn(sp.n_la_v, device=dev, generator=gen) * 0.5).half()
+                dl.la_norm = ones(cfg.linear_value_head_dim)
+            dl.gate_up = rnd(H, 2 * Fp)
+            if Fp != sp.ffn_local:
+                raise NotImplementedError("random init needs ffn_local % 64 == 0")
+            dl.down = rnd(sp.ffn_local, H)
+            self.layers[i] = dl
+        # replicated tensors use a rank-independent generator so every rank holds the same values
+        g2 = torch.Generator(device=dev)
+        g2.manual_seed(seed + 7)
+        self.embed = (torch.randn(cfg.vocab_size, H, device=dev, generator=g2) * embed_std).half()
+        vl = sp.vocab_local
+        self.lm_head = DeviceLinear(dense=(torch.randn(vl, H, device=dev, generator=gen) * embed_std).half())
+        self.final_norm = ones(H)
+        self._driver = None
+
+    def weight_bytes(self) -> int:
+        n = sum(l.nbytes() for dl in self.layers for l in (dl.in_proj, dl.out_proj, dl.gate_up, dl.down))
+        return n + self.lm_head.nbytes()
+
+    def streamed_bytes_per_token(self) -> int:
+        """Weight bytes one decode step must read (embedding row excluded)."""
+        return self.weight_bytes()
+
+    # ------------------------------------------------------------------ driver
+    def _comm_ctx(self) -> L.CommCtx:
+        if self.comm is not None and self.tp_size > 1:
+            return self.comm.ctx()
+        return L.null_comm()
+
+    def _ensure_driver(self):
+        if self._driver is not None:
+            return
+        if any(l is None for l in self.layers) or self.embed is None or self.lm_head is None \
+                or self.final_norm is None:
+            raise RuntimeError("weights are not fully loaded")
+        cfg, sp, dev, R = self.config, self.spec, self.device, self.max_rows
+        H = cfg.hidden_size
+        lins = [l for dl in self.layers for l in (dl.in_proj, dl.out_proj, dl.gate_up, dl.down)] + [self.lm_head]
+        f32 = lambda *s: torch.zeros(*s, dtype=torch.float32, device=dev)
+        f16 = lambda *s: torch.zeros(*s, dtype=torch.float16, device=dev)
+        i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
+        self.F_pad = self.layers[0].gate_up.n_pad // 2
+        b = self.buf = {}
+        b["h"], b["xn"] = f32(R, H), f16(R, H)
+        b["ld_proj"] = max(dl.in_proj.N for dl in self.layers)
+        b["proj"] = f16(R, b["ld_proj"])
+        b["ld_attn"] = max(dl.out_proj.K for dl in self.layers)
+        b["attn_out"] = f16(R, b["ld_attn"])
+        b["act"] = f16(R, self.F_pad)
+        b["ld_logits"] = -(-sp.vocab_local // 4) * 4
+        b["logits"] = f32(R, b["ld_logits"])
+        b["gemv_scratch"] = f32(max(1, max(l.scratch_floats(R) for l in lins)))
+        b["gemv_counters"] = i32(8192)
+        self.attn_splits = 8 if self.max_seq_len <= 4096 else 16
+        G = sp.n_q // sp.n_kv
+        b["attn_scratch"] = f32(R * sp.n_kv * self.attn_splits * G * (cfg.head_dim + 2))
+        b["attn_counters"] = i32(R * sp.n_kv + 8)
+        self.argmax_blocks = max(1, min(64, sp.vocab_local // 2048))
+        b["argmax_scratch"] = f32(R * self.argmax_blocks * 2)
+        b["argmax_counters"] = i32(R + 8)
+        b["extra"], b["local_part"] = f32(R, H), f32(R, H)
+        b["rows"], b["rows_tmpl"] = i32(R, 6), i32(R, 6)
+        b["row_tokens"] = torch.full((R,), -1, dtype=torch.int32, device=dev)
+        b["seq_rows"] = i32(self.max_batch + 1 + R)
+        b["out_tokens"] = i32(R)
+        b["emb_in"] = f32(R, H)
+
+        m = L.ModelDesc()
+        m.n_layers, m.H, m.vocab = cfg.num_hidden_layers, H, cfg.vocab_size
+        m.vocab_local, m.vocab_offset = sp.vocab_local, sp.vocab[0]
+        m.nq, m.nkv, m.hd, m.rot = sp.n_q, sp.n_kv, cfg.head_dim, cfg.rotary_dim
+        m.rope_interleaved = 1 if cfg.rope_style == "interleaved" else 0
+        m.la_nk, m.la_nv = sp.n_la_k, sp.n_la_v
+        m.la_dk, m.la_dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        m.max_seq, m.max_rows = self.max_seq_len, R
+        m.ar_mode = AR_MODE_ID[self.ecfg.ar_mode]
+        m.attn_splits, m.argmax_blocks, m.n_seqs_max = self.attn_splits, self.argmax_blocks, self.max_batch
+        m.eps, m.F_pad = cfg.rms_norm_eps, self.F_pad
+        m.embed, m.first_norm = self.embed.data_ptr(), self.layers[0].attn_norm.data_ptr()
+        m.lm_head = self.lm_head.desc()
+        m.cos_tab, m.sin_tab = self.cos_tab.data_ptr(), self.sin_tab.data_ptr()
+        for k in ("h", "xn", "proj", "attn_out", "act", "logits", "gemv_scratch", "gemv_counters",
+                  "attn_scratch", "attn_counters", "argmax_scratch", "argmax_counters", "extra",
+                  "local_part", "rows", "rows_tmpl", "row_tokens", "seq_rows", "out_tokens"):
+            setattr(m, k, b[k].data_ptr())
+        m.ld_proj, m.ld_attn, m.ld_logits = b["ld_proj"], b["ld_attn"], b["ld_logits"]
+        m.seqs = self.states.seqs.data_ptr()
+        m.comm = self._comm_ctx()
+        descs = (L.LayerDesc * cfg.num_hidden_layers)()
+        for i, dl in enumerate(self.layers):
+            d = descs[i]
+            d.type = dl.type
+            d.in_proj, d.out_proj = dl.in_proj.desc(), dl.out_proj.desc()
+            d.gate_up, d.down = dl.gate_up.desc(), dl.down.desc()
+            d.ffn_norm = dl.ffn_norm.data_ptr()
+            nxt = self.layers[i + 1].attn_norm if i + 1 < len(self.layers) else self.final_norm
+            d.next_norm = nxt.data_ptr()
+            if dl.type == 0:
+                d.q_norm, d.k_norm = dl.q_norm.data_ptr(), dl.k_norm.data_ptr()
+                d.kcache = self.states.kv.layer_k(i).data_ptr()
+                d.vcache = self.states.kv.layer_v(i).data_ptr()
+            else:
+                d.wa = None if dl.wa is None else dl.wa.data_ptr()
+                d.wb = None if dl.wb is None else dl.wb.data_ptr()
+                d.conv_w, d.A_log = dl.conv_w.data_ptr(), dl.A_log.data_ptr()
+                d.dt_bias, d.la_norm = dl.dt_bias.data_ptr(), dl.la_norm.data_ptr()
+                d.conv_state = self.states.dn.layer_conv(i).data_ptr()
+                d.state = self.states.dn.layer_S(i).data_ptr()
+                d.off_q, d.off_k, d.off_v, d.off_z, d.off_a, d.off_b = dl.off
+        self._model_desc, self._layer_descs = m, descs
+        self._driver = self.lib.b2_driver_create(C.byref(m), descs)
+        self._graph_key = None
+        self._tmpl_key = None
+        self._stream = torch.cuda.Stream(device=dev)
+
+    def build_decode_launch_cache(self):
+        """Reference-compatible name (src/inference/engine.py:3309): builds the
+        driver plan."""
+        self._ensure_driver()
+
+    # ------------------------------------------------------------------ rows
+    def _set_template(self, key, rows: List[tuple], seq_rows: List[int]):
+        """rows: (seq, depth, slot_offset, mask) per row."""
+        if key is not None and key == self._tmpl_key:
+            return
+        t = torch.zeros(self.max_rows, 6, dtype=torch.int32)
+        for r, (seq, depth, slot, mask) in enumerate(rows):
+            t[r, 0], t[r, 1], t[r, 2] = seq, depth, slot
+            t[r, 4] = (mask & 0xFFFFFFFF) - (1 << 32 if mask & 0x80000000 else 0)
+            hi = (mask >> 32) & 0xFFFFFFFF
+            t[r, 5] = hi - (1 << 32 if hi & 0x80000000 else 0)
+        self.buf["rows_tmpl"].copy_(t.to(self.device))
+        sr = torch.zeros(self.buf["seq_rows"].shape[0], dtype=torch.int32)
+        sr[:len(seq_rows)] = torch.tensor(seq_rows, dtype=torch.int32)
+        self.buf["seq_rows"].copy_(sr.to(self.device))
+        self._tmpl_key = key
+
+    def _template_decode(self, seqs: Sequence[int]):
+        self._set_template(("decode", tuple(seqs)), [(s, 0, 0, 1) for s in seqs],
+                           list(range(len(seqs) + 1)))
+
+    def _template_chain(self, seq: int, n: int):
+        self._set_template(("chain", seq, n), [(seq, i, i, (1 << (i + 1)) - 1) for i in range(n)], [0, n])
+
+    def _run(self, rows: int, n_seqs: int, flags: int):
+        self._ensure_driver()
+        L.check(self.lib.b2_driver_step(C.c_void_p(self._driver), rows, n_seqs, flags, L.stream()), "driver step")
+        self._steps += 1
+
+    # ------------------------------------------------------------------ token-level API
+    def step_tokens(self, tokens: Sequence[int], seq: int = 0, logits: bool = True,
+                    commit: bool = True) -> torch.Tensor:
+        """Feed `tokens` (<= 8) of one sequence as a chain; returns the arg-max
+        token after every fed token (device int32 [n])."""
+        n = len(tokens)
+        if not 1 <= n <= self.max_rows:
+            raise ValueError(f"1..{self.max_rows} tokens per step")
+        self._ensure_driver()
+        self._template_chain(seq, n)
+        rt = torch.full((self.max_rows,), -1, dtype=torch.int32)
+        rt[:n] = torch.as_tensor(list(tokens), dtype=torch.int32)
+        self.buf["row_tokens"].copy_(rt.to(self.device))
+        flags = L.STEP_EMBED_TOKENS | ((L.STEP_LM_HEAD | L.STEP_ARGMAX) if logits else 0)
+        if not commit:
+            flags |= L.STEP_NO_COMMIT_DELTA
+        self._run(n, 1, flags)
+        if commit:
+            self.states.seqs[seq, 0] += n
+        self.buf["row_tokens"].fill_(-1)
+        return self.buf["out_tokens"][:n]
+
+    def prefill_tokens(self, tokens: Sequence[int], seq: int = 0) -> int:
+        """Consume a prompt; returns the first generated token and stores it as
+        the sequence's next input."""
+        tokens = list(tokens)
+        out = None
+        for i in range(0, len(tokens), self.max_rows):
+            chunk = tokens[i:i + self.max_rows]
+            last = i + self.max_rows >= len(tokens)
+            out = self.step_tokens(chunk, seq, logits=last)
+        tok = out[len(chunk) - 1]
+        self.states.seqs[seq, 1] = tok
+        return int(tok.item())
+
+    def decode_tokens(self, n_steps: int, seqs: Optional[Sequence[int]] = None, graph: Optional[bool] = None,
+                      collect: bool = True) -> Optional[torch.Tensor]:
+        """Greedy-decode `n_steps` tokens for the given sequence slots; each step
+        consumes SeqState.token and writes the next one.  Returns int32
+        [n_steps, len(seqs)] when `collect`."""
+        seqs = list(seqs) if seqs is not None else [0]
+        self._ensure_driver()
+        self._template_decode(seqs)
+        rows = len(seqs)
+        flags = L.STEP_EMBED_TOKENS | L.STEP_LM_HEAD | L.STEP_ARGMAX | L.STEP_ADVANCE
+        use_graph = self.ecfg.use_graph if graph is None else graph
+        outs = []
+        if use_graph:
+            key = ("decode", tuple(seqs), flags)
+            if self._graph_key != key:
+                torch.cuda.synchronize()
+                with torch.cuda.stream(self._stream):
+                    L.check(self.lib.b2_driver_capture(C.c_void_p(self._driver), rows, rows, flags,
+                                                       C.c_void_p(self._stream.cuda_stream)), "graph capture")
+                torch.cuda.synchronize()
+                self._graph_key = key
+            if collect:
+                for _ in range(n_steps):
+                    L.check(self.lib.b2_driver_replay(C.c_void_p(self._driver), 1, L.stream()), "graph replay")
+                    outs.append(self.buf["out_tokens"][:rows].clone())
+            else:
+                L.check(self.lib.b2_driver_replay(C.c_void_p(self._driver), n_steps, L.stream()), "graph replay")
+        else:
+            for _ in range(n_steps):
+                self._run(rows, rows, flags)
+                if collect:
+                    outs.append(self.buf["out_tokens"][:rows].clone())
+        self._steps += n_steps
+        return torch.stack(outs) if collect else None
+
+    def generate_tokens(self, prompt: Sequence[int], n_new: int, seq: int = 0, graph: Optional[bool] = None):
+        """Greedy generation entirely on the device: returns n_new token ids."""
+        self.states.reset(seq)
+        first = self.prefill_tokens(prompt, seq)
+        if n_new <= 1:
+            return [first][:n_new]
+        rest = self.decode_tokens(n_new - 1, [seq], graph=graph)
+        return [first] + rest[:, 0].tolist()
+
+    def step_host(self, token: int, seq: int = 0) -> int:
+        """One greedy decode step driven from the host: the input token is
+        uploaded from pinned memory, the step graph is replayed, the next token is
+        downloaded.  This is the per-token path of the generation API."""
+        self._ensure_driver()
+        if not hasattr(self, "_pin_in"):
+            self._pin_in = torch.zeros(1, dtype=torch.int32).pin_memory()
+            self._pin_out = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._pin_in[0] = int(token)
+        self.states.seqs[seq, 1:2].copy_(self._pin_in, non_blocking=True)
+        self.decode_tokens(1, [seq], collect=False)
+        self._pin_out.copy_(self.buf["out_tokens"][:1], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return int(self._pin_out[0])
+
+    def logits(self, rows: int = 1) -> torch.Tensor:
+        """fp32 logits of the last step, this rank's vocabulary slice."""
+        return self.buf["logits"][:rows, :self.spec.vocab_local]
+
+    # ------------------------------------------------------------------ embedding-in API
+    def _as_dev(self, x) -> torch.Tensor:
+        if isinstance(x, np.ndarray):
+            x = torch.from_numpy(x)
+        return x.to(device=self.device, dtype=torch.float32)
+
+    def forward_embeddings(self, embs, seq: int = 0, commit: bool = True) -> torch.Tensor:
+        """Run n <= 8 rows given as embeddings; returns the final-normed hidden
+        states fp16 [n, hidden] (device)."""
+        self._ensure_driver()
+        e = self._as_dev(embs).reshape(-1, self.config.hidden_size)
+        n = e.shape[0]
+        self._template_chain(seq, n)
+        self.buf["emb_in"][:n].copy_(e)
+        L.check(self.lib.b2_load_rmsnorm(None, C.c_void_p(self.buf["emb_in"].data_ptr()),
+                                         C.c_void_p(self.layers[0].attn_norm.data_ptr()),
+                                         C.c_void_p(self.buf["h"].data_ptr()),
+                                         C.c_void_p(self.buf["xn"].data_ptr()), n, self.config.hidden_size,
+                                         C.c_float(self.config.rms_norm_eps), L.stream()), "load_rmsnorm")
+        self._run(n, 1, 0 if commit else L.STEP_NO_COMMIT_DELTA)
+        if commit:
+            self.states.seqs[seq, 0] += n
+        return self.buf["xn"][:n]
+
+    def decode_step(self, token_embedding, position: Optional[int] = None, seq: int = 0):
+        """Reference signature (src/inference/engine.py:1417): embedding [hidden]
+        in, final-normed hidden state out (numpy fp16 if numpy came in)."""
+        if position is not None and position != self.states.length(seq):
+            self.states.set_length(seq, position)
+        out = self.forward_embeddings(token_embedding, seq)[0]
+        return out.cpu().numpy() if isinstance(token_embedding, np.ndarray) else out.clone()
+
+    def prefill_step(self, token_embeddings, seq: int = 0):
+        """Whole prompt [S, hidden] in, hidden state of the last token out
+        (reference: src/inference/engine.py:3009-3294)."""
+        e = self._as_dev(token_embeddings).reshape(-1, self.config.hidden_size)
+        out = None
+        for i in range(0, e.shape[0], self.max_rows):
+            out = self.forward_embeddings(e[i:i + self.max_rows], seq)
+        out = out[-1]
+        return out.cpu().numpy() if isinstance(token_embeddings, np.ndarray) else out.clone()
+
+    def residual_stream(self, rows: int = 1) -> torch.Tensor:
+        """fp32 residual stream after the last step (before the final norm)."""
+        return self.buf["h"][:rows]
+
+    def compute_logits(self, hidden=None) -> torch.Tensor:
+        """Logits (fp32, this rank's vocabulary slice) of a final-normed hidden
+        state; None = the last step's (reference: src/inference/engine.py:1123-1143)."""
+        self._ensure_driver()
+        if hidden is not None:
+            hdn = self._as_dev(hidden).reshape(1, -1)
+            self.buf["xn"][:1].copy_(hdn.half())
+        from ..ops import kernels as K
+        K.gemv(self.lm_head, self.buf["xn"][:1], out=self.buf["logits"][:1], mode=L.EPI_STORE_F32,
+               scratch=self.buf["gemv_scratch"], counters=self.buf["gemv_counters"])
+        out = self.buf["logits"][0, :self.spec.vocab_local]
+        return out.cpu().numpy() if isinstance(hidden, np.ndarray) else out.clone()
+
+    # ------------------------------------------------------------------ misc reference-compatible
+    def set_awq_mode(self, enabled: bool = True):
+        """AWQ weights are the same packed layout with zero = 0; nothing to switch."""
+
+    def set_direct_kv_write(self, enabled: bool = True):
+        """K/V are always written straight into the cache by qknorm_rope_cachew."""
+
+    def reset_launch_counters(self):
+        self._launch_counts.clear()
+
+    def get_layer_launch_count(self, layer_idx: int) -> int:
+        """Kernels issued per layer and step (reference: src/inference/engine.py:993-1023)."""
+        return 6 if self.layers[layer_idx].type == 0 else 5
+
+    def launches_per_step(self) -> int:
+        self._ensure_driver()
+        return int(self.lib.b2_driver_launches(C.c_void_p(self._driver)))
+
+    def synchronize(self):
+        torch.cuda.synchronize(self.device)
+
+    def reset(self, seq: Optional[int] = None):
+        self.states.reset(seq)
+
+    def check_status(self):
+        if self.comm is not None:
+            self.comm.check_status()
+
+    def cleanup(self):
+        if self._driver is not None:
+            self.lib.b2_driver_destroy(C.c_void_p(self._driver))
+            self._driver = None
+        self.buf = {}

@@ -1,0 +1,180 @@
+"""Python entry points of the individual CUDA kernels (used by the tests, the
+micro-benchmarks and the parts of the engines that run outside the step driver).
+Every function launches on the current CUDA stream and raises if the launch
+fails; there is no PyTorch fallback."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import lib as L
+
+
+def _vp(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def make_rows(entries, device) -> torch.Tensor:
+    """entries: (seq, pos, slot, ctx, mask) per row -> device RowMeta array."""
+    t = torch.zeros(len(entries), 6, dtype=torch.int32)
+    for r, (seq, pos, slot, ctx, mask) in enumerate(entries):
+        t[r, 0], t[r, 1], t[r, 2], t[r, 3] = seq, pos, slot, ctx
+        lo, hi = mask & 0xFFFFFFFF, (mask >> 32) & 0xFFFFFFFF
+        t[r, 4] = lo - (1 << 32 if lo & 0x80000000 else 0)
+        t[r, 5] = hi - (1 << 32 if hi & 0x80000000 else 0)
+    return t.to(device)
+
+
+def _epi(mode, out=None, ldo=0, n_valid=0, fin_flags=0, h=None, norm_w=None, xn=None, extra=None,
+         local_part=None, eps=1e-6) -> L.GemvEpi:
+    e = L.GemvEpi()
+    e.mode, e.ldo, e.n_valid, e.fin_flags = mode, ldo, n_valid, fin_flags
+    e.out, e.h, e.norm_w, e.xn = L.ptr(out), L.ptr(h), L.ptr(norm_w), L.ptr(xn)
+    e.extra, e.local_part, e.eps = L.ptr(extra), L.ptr(local_part), eps
+    return e
+
+
+def gemv(lin, x: torch.Tensor, out: Optional[torch.Tensor] = None, mode: int = L.EPI_STORE_F16,
+         scratch: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None,
+         comm: Optional[L.CommCtx] = None, fin_flags: int = 0, h=None, norm_w=None, xn=None,
+         extra=None, local_part=None, eps: float = 1e-6, n_valid: Optional[int] = None,
+         k_splits: Optional[int] = None, Lblocks: Optional[int] = None):
+    """y = x W^T for x[rows, K] fp16 with a `DeviceLinear`-like object (`.packed`
+    PackedInt4 or `.dense` fp16 [N, K]) and one of the four epilogues."""
+    lib = L.lib()
+    rows = x.shape[0]
+    dev = x.device
+    pk, dense = getattr(lin, "packed", None), getattr(lin, "dense", None)
+    if pk is None and dense is None:
+        pk = lin
+    ks = k_splits or (pk.k_splits if pk is not None else lin.k_splits)
+    n_pad = pk.n_pad if pk is not None else -(-dense.shape[0] // 128) * 128
+    if scratch is None:
+        scratch = torch.empty(max(1, ks * rows * n_pad), dtype=torch.float32, device=dev)
+    if counters is None:
+        counters = torch.zeros(n_pad // 128 + 2, dtype=torch.int32, device=dev)
+    N = pk.N if pk is not None else dense.shape[0]
+    if mode == L.EPI_SILU_PAIR:
+        nv = n_valid if n_valid is not None else n_pad // 2
+    elif mode == L.EPI_FINISH:
+        nv = N
+    else:
+        nv = n_valid if n_valid is not None else N
+    epi = _epi(mode, out, out.stride(0) if out is not None else 0, nv, fin_flags, h, norm_w, xn, extra,
+               local_part, eps)
+    cm = comm if comm is not None else L.null_comm()
+    if pk is not None:
+        p = L.GemvInt4Params()
+        p.qfrag, p.szfrag, p.x = pk.qfrag.data_ptr(), pk.szfrag.data_ptr(), x.data_ptr()
+        p.ldx, p.rows, p.K, p.KB, p.NTL, p.G = x.stride(0), rows, pk.K, pk.KB, pk.NTL, pk.G
+        p.off32, p.gshift, p.k_splits, p.L = pk.off32, pk.gshift, ks, Lblocks or pk.L
+        if k_splits and not Lblocks:
+            p.L = -(-pk.KB // (4 * ks))
+        p.scratch, p.counters, p.epi, p.comm = scratch.data_ptr(), counters.data_ptr(), epi, cm
+        L.check(lib.b2_gemv_int4(C.byref(p), L.stream()), "gemv_int4")
+    else:
+        p = L.GemvF16Params()
+        p.w, p.x, p.ldw, p.ldx, p.rows = dense.data_ptr(), x.data_ptr(), dense.stride(0), x.stride(0), rows
+        p.K, p.N, p.k_splits, p.kslice = dense.shape[1], dense.shape[0], ks, lin.kslice
+        p.scratch, p.counters, p.epi, p.comm = scratch.data_ptr(), counters.data_ptr(), epi, cm
+        L.check(lib.b2_gemv_f16(C.byref(p), L.stream()), "gemv_f16")
+    return out
+
+
+def add_rmsnorm(h: torch.Tensor, w: torch.Tensor, delta: Optional[torch.Tensor] = None, eps: float = 1e-6,
+                out32: bool = False):
+    """h (fp32 [rows, H]) += delta; returns rmsnorm(h)*w as fp16 (or fp32)."""
+    rows, H = h.shape
+    xn = torch.empty(rows, H, dtype=torch.float32 if out32 else torch.float16, device=h.device)
+    d32 = delta if delta is not None and delta.dtype == torch.float32 else None
+    d16 = delta if delta is not None and delta.dtype == torch.float16 else None
+    L.check(L.lib().b2_add_rmsnorm(_vp(h), _vp(d32), _vp(d16), _vp(w), None if out32 else _vp(xn),
+                                   _vp(xn) if out32 else None, rows, H, C.c_float(eps), L.stream()), "add_rmsnorm")
+    return xn
+
+
+def embed_rmsnorm(embed, row_tokens, rows_meta, seqs, w, h, xn, eps=1e-6):
+    n, H = h.shape
+    L.check(L.lib().b2_embed_rmsnorm(_vp(embed), _vp(row_tokens), _vp(rows_meta), _vp(seqs), _vp(w), _vp(h),
+                                     _vp(xn), n, H, C.c_float(eps), embed.shape[0], L.stream()), "embed_rmsnorm")
+
+
+def qknorm_rope_cachew(qkv, rows_meta, q_norm, k_norm, cos_tab, sin_tab, kcache, vcache, nq, nkv, hd, rot,
+                       interleaved=True, eps=1e-6):
+    """kcache/vcache: [seqs, max_seq, nkv, hd] fp16."""
+    L.check(L.lib().b2_qknorm_rope_cachew(_vp(qkv), qkv.stride(0), _vp(rows_meta), _vp(q_norm), _vp(k_norm),
+                                          _vp(cos_tab), _vp(sin_tab), _vp(kcache), _vp(vcache), qkv.shape[0], nq,
+                                          nkv, hd, rot, kcache.shape[1], 1 if interleaved else 0, C.c_float(eps),
+                                          L.stream()), "qknorm_rope_cachew")
+
+
+def decode_attn(q, rows_meta, kcache, vcache, nq, nkv, hd, gate_off=-1, splits=4, out=None):
+    n = q.shape[0]
+    dev = q.device
+    if out is None:
+        out = torch.empty(n, nq * hd, dtype=torch.float16, device=dev)
+    G = nq // nkv
+    p = L.AttnParams()
+    p.q, p.ldq, p.gate_off = q.data_ptr(), q.stride(0), gate_off
+    p.kcache, p.vcache, p.rows = kcache.data_ptr(), vcache.data_ptr(), rows_meta.data_ptr()
+    p.out, p.ldo, p.n_rows, p.nq, p.nkv = out.data_ptr(), out.stride(0), n, nq, nkv
+    p.max_seq, p.splits, p.scale = kcache.shape[1], splits, 1.0 / hd ** 0.5
+    scratch = torch.empty(n * nkv * splits * G * (hd + 2), dtype=torch.float32, device=dev)
+    counters = torch.zeros(n * nkv + 1, dtype=torch.int32, device=dev)
+    p.scratch, p.counters = scratch.data_ptr(), counters.data_ptr()
+    L.check(L.lib().b2_decode_attn(C.byref(p), hd, L.stream()), "decode_attn")
+    return out
+
+
+def deltanet_step(proj, offs, conv_w, conv_state, state, A_log, dt_bias, norm_w, rows_meta, seq_rows, nk, nv,
+                  dk, dv, xn=None, wa=None, wb=None, out=None, commit=True, eps=1e-6):
+    """offs = (off_q, off_k, off_v, off_z, off_a, off_b)."""
+    n = proj.shape[0]
+    if out is None:
+        out = torch.empty(n, nv * dv, dtype=torch.float16, device=proj.device)
+    p = L.DeltaParams()
+    p.proj, p.ld = proj.data_ptr(), proj.stride(0)
+    p.off_q, p.off_k, p.off_v, p.off_z, p.off_a, p.off_b = offs
+    if xn is not None:
+        p.xn, p.ldx, p.H = xn.data_ptr(), xn.stride(0), xn.shape[1]
+        p.wa, p.wb = wa.data_ptr(), wb.data_ptr()
+    p.conv_w, p.conv_state, p.state = conv_w.data_ptr(), conv_state.data_ptr(), state.data_ptr()
+    p.A_log, p.dt_bias, p.norm_w = A_log.data_ptr(), dt_bias.data_ptr(), norm_w.data_ptr()
+    p.seq_rows, p.rows, p.out, p.ldo = seq_rows.data_ptr(), rows_meta.data_ptr(), out.data_ptr(), out.stride(0)
+    p.nk, p.nv, p.n_seqs, p.eps, p.commit = nk, nv, seq_rows.shape[0] - 1, eps, 1 if commit else 0
+    L.check(L.lib().b2_deltanet_step(C.byref(p), dk, dv, L.stream()), "deltanet_step")
+    return out
+
+
+def argmax(logits: torch.Tensor, vocab_offset: int = 0, blocks: int = 16, comm: Optional[L.CommCtx] = None):
+    n, V = logits.shape
+    dev = logits.device
+    out = torch.empty(n, dtype=torch.int32, device=dev)
+    p = L.ArgmaxParams()
+    p.logits, p.ld, p.n_rows, p.vocab_local, p.vocab_offset, p.blocks = logits.data_ptr(), logits.stride(0), n, V, vocab_offset, blocks
+    scratch = torch.empty(n * blocks * 2, dtype=torch.float32, device=dev)
+    counters = torch.zeros(n + 2, dtype=torch.int32, device=dev)
+    p.scratch, p.counters, p.out_tokens = scratch.data_ptr(), counters.data_ptr(), out.data_ptr()
+    p.comm = comm if comm is not None else L.null_comm()
+    L.check(L.lib().b2_argmax(C.byref(p), L.stream()), "argmax")
+    return out
+
+
+def silu_mul(gate, up):
+    out = torch.empty_like(gate)
+    L.check(L.lib().b2_silu_mul(_vp(gate), _vp(up), _vp(out), C.c_size_t(gate.numel()), L.stream()), "silu_mul")
+    return out
+
+
+def sigmoid_mul_(x, gate):
+    L.check(L.lib().b2_sigmoid_mul(_vp(x), _vp(gate), C.c_size_t(x.numel()), L.stream()), "sigmoid_mul")
+    return x
+
+
+def residual_add_(h, delta):
+    d32 = delta if delta.dtype == torch.float32 else None
+    d16 = delta if delta.dtype == torch.float16 else None
+    L.check(L.lib().b2_residual_add(_vp(h), _vp(d32), _vp(d16), C.c_size_t(h.numel()), L.stream()), "residual_add")
+    return h

@@ -1,0 +1,176 @@
+"""ctypes binding of libb200grad.so.
+
+The reference reaches its kernels through a ctypes wrapper of the HIP runtime
+plus by-name kernel lookup in code objects (reference:
+src/runtime/hip_dispatch.py:100-587, src/kernels/launcher.py:26-130).  Here the
+library exports one C launcher per kernel and a step driver; tensors come from
+PyTorch and are passed as raw device pointers with the current CUDA stream.
+
+There is no silent fallback: importing an op on a machine with a GPU but without
+the built library raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libb200grad.so"
+MAX_TP = 8
+MAX_ROWS = 8
+
+EPI_STORE_F16, EPI_SILU_PAIR, EPI_STORE_F32, EPI_FINISH = 0, 1, 2, 3
+FIN_NO_COMM, FIN_NO_H_WRITE, FIN_SAVE_EXTRA, FIN_ADD_EXTRA, FIN_NO_NORM = 1, 2, 4, 8, 16
+FIN_TEST_WITHHOLD_SIGNAL = 32
+LIN_INT4, LIN_F16, LIN_NONE = 0, 1, 2
+STEP_EMBED_TOKENS, STEP_LM_HEAD, STEP_ARGMAX, STEP_ADVANCE, STEP_NO_COMMIT_DELTA = 1, 2, 4, 8, 16
+
+vp, i32, f32, i64 = C.c_void_p, C.c_int, C.c_float, C.c_longlong
+
+
+class CommCtx(C.Structure):
+    _fields_ = [("tp", i32), ("rank", i32), ("part_stride", i32), ("pad0", i32),
+                ("part", vp * MAX_TP), ("sig", vp * MAX_TP), ("mc_part", vp),
+                ("epoch", vp), ("status", vp), ("wait_ns", i64)]
+
+
+class RowMeta(C.Structure):
+    _fields_ = [("seq", i32), ("pos", i32), ("slot", i32), ("ctx", i32), ("mask", C.c_ulonglong)]
+
+
+class SeqState(C.Structure):
+    _fields_ = [("len", i32), ("token", i32), ("pad", i32 * 2)]
+
+
+class GemvEpi(C.Structure):
+    _fields_ = [("mode", i32), ("ldo", i32), ("n_valid", i32), ("fin_flags", i32), ("out", vp),
+                ("h", vp), ("norm_w", vp), ("xn", vp), ("extra", vp), ("local_part", vp),
+                ("eps", f32), ("pad", i32)]
+
+
+class GemvInt4Params(C.Structure):
+    _fields_ = [("qfrag", vp), ("szfrag", vp), ("x", vp),
+                ("ldx", i32), ("rows", i32), ("K", i32), ("KB", i32), ("NTL", i32), ("G", i32),
+                ("off32", i32), ("gshift", i32), ("k_splits", i32), ("L", i32),
+                ("scratch", vp), ("counters", vp), ("epi", GemvEpi), ("comm", CommCtx)]
+
+
+class GemvF16Params(C.Structure):
+    _fields_ = [("w", vp), ("x", vp), ("ldw", i32), ("ldx", i32), ("rows", i32), ("K", i32), ("N", i32),
+                ("k_splits", i32), ("kslice", i32), ("scratch", vp), ("counters", vp),
+                ("epi", GemvEpi), ("comm", CommCtx)]
+
+
+class AttnParams(C.Structure):
+    _fields_ = [("q", vp), ("ldq", i32), ("gate_off", i32), ("kcache", vp), ("vcache", vp), ("rows", vp),
+                ("out", vp), ("ldo", i32), ("n_rows", i32), ("nq", i32), ("nkv", i32), ("max_seq", i32),
+                ("splits", i32), ("scale", f32), ("scratch", vp), ("counters", vp)]
+
+
+class DeltaParams(C.Structure):
+    _fields_ = [("proj", vp), ("ld", i32), ("off_q", i32), ("off_k", i32), ("off_v", i32), ("off_z", i32),
+                ("off_a", i32), ("off_b", i32), ("xn", vp), ("ldx", i32), ("H", i32), ("wa", vp), ("wb", vp),
+                ("conv_w", vp), ("conv_state", vp), ("state", vp), ("A_log", vp), ("dt_bias", vp),
+                ("norm_w", vp), ("seq_rows", vp), ("rows", vp), ("out", vp), ("ldo", i32), ("nk", i32),
+                ("nv", i32), ("n_seqs", i32), ("eps", f32), ("commit", i32)]
+
+
+class ArgmaxParams(C.Structure):
+    _fields_ = [("logits", vp), ("ld", i32), ("n_rows", i32), ("vocab_local", i32), ("vocab_offset", i32),
+                ("blocks", i32), ("scratch", vp), ("counters", vp), ("out_tokens", vp), ("seqs", vp),
+                ("rows", vp), ("comm", CommCtx)]
+
+
+class LinearDesc(C.Structure):
+    _fields_ = [("kind", i32), ("K", i32), ("N", i32), ("KB", i32), ("NTL", i32), ("G", i32), ("off32", i32),
+                ("gshift", i32), ("k_splits", i32), ("L", i32), ("ldw", i32), ("kslice", i32), ("pad", i32),
+                ("w", vp), ("sz", vp)]
+
+
+class LayerDesc(C.Structure):
+    _fields_ = [("type", i32), ("pad", i32), ("in_proj", LinearDesc), ("out_proj", LinearDesc),
+                ("gate_up", LinearDesc), ("down", LinearDesc), ("ffn_norm", vp), ("next_norm", vp),
+                ("q_norm", vp), ("k_norm", vp), ("kcache", vp), ("vcache", vp),
+                ("wa", vp), ("wb", vp), ("conv_w", vp), ("conv_state", vp), ("state", vp),
+                ("A_log", vp), ("dt_bias", vp), ("la_norm", vp),
+                ("off_q", i32), ("off_k", i32), ("off_v", i32), ("off_z", i32), ("off_a", i32), ("off_b", i32)]
+
+
+class ModelDesc(C.Structure):
+    _fields_ = [("n_layers", i32), ("H", i32), ("vocab", i32), ("vocab_local", i32), ("vocab_offset", i32),
+                ("nq", i32), ("nkv", i32), ("hd", i32), ("rot", i32), ("rope_interleaved", i32),
+                ("la_nk", i32), ("la_nv", i32), ("la_dk", i32), ("la_dv", i32),
+                ("max_seq", i32), ("max_rows", i32), ("ar_mode", i32),
+                ("attn_splits", i32), ("argmax_blocks", i32), ("n_seqs_max", i32),
+                ("eps", f32), ("F_pad", i32),
+                ("embed", vp), ("first_norm", vp), ("lm_head", LinearDesc),
+                ("cos_tab", vp), ("sin_tab", vp),
+                ("h", vp), ("xn", vp), ("proj", vp), ("ld_proj", i32), ("pad0", i32),
+                ("attn_out", vp), ("ld_attn", i32), ("pad1", i32),
+                ("act", vp), ("logits", vp), ("ld_logits", i32), ("pad2", i32),
+                ("gemv_scratch", vp), ("gemv_counters", vp), ("attn_scratch", vp), ("attn_counters", vp),
+                ("argmax_scratch", vp), ("argmax_counters", vp), ("extra", vp), ("local_part", vp),
+                ("rows", vp), ("rows_tmpl", vp), ("seqs", vp), ("row_tokens", vp), ("seq_rows", vp),
+                ("out_tokens", vp), ("comm", CommCtx)]
+
+
+_SIZE_CHECKS = {
+    "b2_sizeof_comm_ctx": CommCtx, "b2_sizeof_gemv_int4_params": GemvInt4Params,
+    "b2_sizeof_gemv_f16_params": GemvF16Params, "b2_sizeof_attn_params": AttnParams,
+    "b2_sizeof_delta_params": DeltaParams, "b2_sizeof_argmax_params": ArgmaxParams,
+    "b2_sizeof_linear_desc": LinearDesc, "b2_sizeof_layer_desc": LayerDesc,
+    "b2_sizeof_model_desc": ModelDesc, "b2_sizeof_row_meta": RowMeta, "b2_sizeof_seq_state": SeqState,
+}
+
+_lib: Optional[C.CDLL] = None
+
+
+class NativeLibraryMissing(RuntimeError):
+    pass
+
+
+def lib() -> C.CDLL:
+    """The loaded library (built on first use when nvcc is present)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        if os.environ.get("B200GRAD_NO_AUTOBUILD"):
+            raise NativeLibraryMissing(f"{LIB_PATH} is missing: run `python -m mi50grad_b200.build`")
+        from ..build import build_all
+        build_all()
+    _lib = C.CDLL(str(LIB_PATH))
+    for fn, st in _SIZE_CHECKS.items():
+        f = getattr(_lib, fn)
+        f.restype = i32
+        if f() != C.sizeof(st):
+            raise RuntimeError(f"struct layout mismatch for {st.__name__}: C {f()} vs ctypes {C.sizeof(st)}")
+    _lib.b2_driver_create.restype = vp
+    _lib.b2_driver_launches.restype = i64
+    _lib.b2_gemv_int4_smem.restype = C.c_size_t
+    return _lib
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    return t.data_ptr()
+
+
+def stream() -> vp:
+    return vp(torch.cuda.current_stream().cuda_stream)
+
+
+def check(code: int, what: str = "kernel launch"):
+    if code != 0:
+        name = f"cudaError {code}"
+        raise RuntimeError(f"{what} failed: {name}")
+
+
+def null_comm() -> CommCtx:
+    c = CommCtx()
+    c.tp, c.rank = 1, 0
+    return c
