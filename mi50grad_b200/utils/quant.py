@@ -36,7 +36,7 @@ def pack_int4_rows(q: torch.Tensor) -> torch.Tensor:
     if K % NIBBLES:
         raise ValueError("K must be a multiple of 8")
     q = q.to(torch.int64).reshape(K // NIBBLES, NIBBLES, N)
-    shifts = (torch.arange(NIBBLES, dtype=torch.int64) * 4).view(1, NIBBLES, 1)
+    shifts = (torch.arange(NIBBLES, dtype=torch.int64, device=q.device) * 4).view(1, NIBBLES, 1)
     word = (q << shifts).sum(dim=1)
     return _to_i32(word)
 
@@ -45,7 +45,7 @@ def unpack_int4_rows(qweight: torch.Tensor) -> torch.Tensor:
     """[K/8, N] int32 -> [K, N] uint8."""
     R, N = qweight.shape
     w = qweight.to(torch.int64) & 0xFFFFFFFF
-    shifts = (torch.arange(NIBBLES, dtype=torch.int64) * 4).view(1, NIBBLES, 1)
+    shifts = (torch.arange(NIBBLES, dtype=torch.int64, device=qweight.device) * 4).view(1, NIBBLES, 1)
     q = (w.unsqueeze(1) >> shifts) & 0xF
     return q.reshape(R * NIBBLES, N).to(torch.uint8)
 
