@@ -1,0 +1,112 @@
+"""Kernel micro-benchmarks with roofline fractions.
+
+    python -m mi50grad_b200.bench.microbench gemv [--tp 1] [--rows 1] [--iters 20]
+
+Each shape is timed with CUDA events over `iters` launches that rotate through
+enough independent weight copies to exceed the 126 MB L2, after 3 warm-ups;
+achieved bandwidth is weight bytes / time and the fraction is taken against the
+measured copy bandwidth in MEASURED_PEAKS.json (fallback 6.65 TB/s).
+(reference counterparts: bench/micro/*.hip.cpp, tests/bench_*.py)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+
+def measured_peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                     "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def time_launches(fn, n_variants: int, iters: int, warmup: int = 3) -> float:
+    """Mean microseconds per launch of fn(i % n_variants)."""
+    for i in range(warmup):
+        fn(i % n_variants)
+    torch.cuda.synchronize()
+    # the launches are captured in a CUDA graph so that host launch cost is not what is timed
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(iters):
+            fn(i % n_variants)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / iters
+
+
+def bench_gemv(tp: int, rows: int, iters: int, only=None):
+    from ..config import qwen35_27b
+    from ..ops import kernels as K
+    from ..ops import lib as L
+    from ..ops.packing import random_packed_int4
+    cfg = qwen35_27b()
+    H, F = cfg.hidden_size, cfg.intermediate_size // tp
+    qd, kvd = cfg.full_attn_q_dim // tp, max(cfg.head_dim, cfg.full_attn_kv_dim // tp)
+    shapes = {
+        "ffn_gate_up(silu)": (H, 2 * F, L.EPI_SILU_PAIR),
+        "ffn_down(finish)": (F, H, L.EPI_FINISH),
+        "attn_qkv": (H, 2 * qd + 2 * kvd, L.EPI_STORE_F16),
+        "deltanet_in_proj": (H, (2 * cfg.linear_attn_key_dim + 2 * cfg.linear_attn_value_dim) // tp, L.EPI_STORE_F16),
+        "attn_o_proj(finish)": (qd, H, L.EPI_FINISH),
+    }
+    hbm, _, src = measured_peaks()
+    dev = torch.device("cuda")
+    out = []
+    for name, (Kd, N, mode) in shapes.items():
+        if only and only not in name:
+            continue
+        one = random_packed_int4(Kd, N, 128, dev)
+        nvar = max(2, int(300e6 // one.nbytes()) + 1)
+        pks = [one] + [random_packed_int4(Kd, N, 128, dev) for _ in range(nvar - 1)]
+        x = torch.randn(rows, Kd, device=dev).half()
+        o16 = torch.zeros(rows, one.n_pad, dtype=torch.float16, device=dev)
+        h = torch.zeros(rows, N, device=dev)
+        xn = torch.zeros(rows, N, dtype=torch.float16, device=dev)
+        lp = torch.zeros(rows, N, device=dev)
+        w = torch.ones(N, dtype=torch.float16, device=dev)
+        scratch = torch.empty(max(1, one.k_splits * rows * one.n_pad), device=dev)
+        counters = torch.zeros(one.n_pad // 128 + 2, dtype=torch.int32, device=dev)
+
+        def run(i):
+            if mode == L.EPI_FINISH:
+                K.gemv(pks[i], x, mode=mode, fin_flags=L.FIN_NO_COMM, h=h, norm_w=w,
+                       scratch=scratch, counters=counters)
+            else:
+                K.gemv(pks[i], x, out=o16, mode=mode, scratch=scratch, counters=counters)
+        us = time_launches(run, nvar, iters)
+        gbs = one.nbytes() / us / 1e3
+        out.append({"kernel": "gemv_int4", "shape": name, "K": Kd, "N": N, "rows": rows, "tp": tp,
+                    "grid": [one.n_pad // 128, one.k_splits], "L": one.L, "us": round(us, 2),
+                    "weight_mb": round(one.nbytes() / 1e6, 2), "gb_s": round(gbs, 1),
+                    "frac_of_hbm": round(gbs / hbm, 3), "peak_source": src})
+        print(json.dumps(out[-1]), flush=True)
+    return out
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemv"])
+    ap.add_argument("--tp", type=int, default=1)
+    ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--only", default=None)
+    a = ap.parse_args(argv)
+    if a.what == "gemv":
+        bench_gemv(a.tp, a.rows, a.iters, a.only)
+
+
+if __name__ == "__main__":
+    main()

@@ -24,6 +24,7 @@ template <int HD>
 __global__ void __launch_bounds__(ATT_THREADS) decode_attn_kernel(const AttnParams p) {
     constexpr int EPL = HD / 32;                 // elements per lane
     const int kvh = blockIdx.x, r = blockIdx.y, sp = blockIdx.z;
+    pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int G = p.nq / p.nkv;
     const RowMeta rm = p.rows[r];

@@ -1,0 +1,212 @@
+// Stand-alone collectives over NVLink symmetric memory, issued from our own
+// kernels: one-shot and two-shot all-reduce (optionally fused with the residual
+// add), a device barrier, and peer-memory probes.
+//
+// They replace the reference's five host-orchestrated all-reduce variants
+// (reference: src/kernels/kernel_p2p_allreduce.hip:45-105 one-shot peer reads,
+// src/kernels/gemv_p2p_reduce.hip:187-227 prefill-sized payloads,
+// src/kernels/p2p_allreduce.hip:228-303 root reduce of gathered copies,
+// src/kernels/ring_allreduce.hip:142-225 ring chunks, src/runtime/fast_allreduce.c
+// host AVX sums).  The reference orders GPUs with host-recorded events and has no
+// device-side signalling; here each kernel publishes its data, raises a flag in
+// every peer's memory with st.release.sys and waits, with a time bound, on the
+// flags the peers raise in its own memory.  Flags carry a monotonically
+// increasing epoch, so nothing is ever reset, and inputs are double-buffered by
+// epoch parity, so no trailing barrier is needed.
+//
+// one-shot : every rank reads all peers' copies (or one multimem.ld_reduce) --
+//            lowest latency, tp x traffic; used for small payloads.
+// two-shot : rank r reduces slice r and stores it to every rank (plain peer
+//            stores or one multimem.st), second flag round, then the local
+//            epilogue -- 2(tp-1)/tp x traffic; used for prefill-sized payloads.
+#include "kernels.cuh"
+
+struct CollParams {
+    CommCtx comm;
+    const float* in;         // local input [n] fp32 (may be null when in16 is given)
+    const __half* in16;      // local input [n] fp16
+    float* out;              // local output [n]: out = sum (+ out if residual)
+    __half* out16;           // optional fp16 copy of the result
+    float* gather[B2_MAX_TP];// two-shot: per-rank symmetric result buffers [n]
+    float* mc_gather;        // multicast mapping of gather (or null)
+    size_t n;                // elements, multiple of 4
+    int residual;            // 1: out += sum
+    int twoshot;
+    int* counters;           // [4] local, zero between launches
+    int test_withhold;       // test hook: never signal, so that the bounded wait expires
+};
+
+__device__ __forceinline__ bool wait_all(const CommCtx& c, int base, uint32_t epoch, int kid) {
+    // every thread < tp polls one peer's flag (its own rank's flag included)
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < c.tp) {
+        if (!wait_reached(c.sig[c.rank] + base + threadIdx.x, epoch, c.wait_ns)) {
+            report_timeout(c, kid, threadIdx.x, epoch);
+            s_ok = 0;
+        }
+    }
+    __syncthreads();
+    return s_ok != 0;
+}
+
+__device__ __forceinline__ void signal_all(const CommCtx& c, int base, uint32_t epoch) {
+    if (threadIdx.x < c.tp) st_release_sys_u32(c.sig[threadIdx.x] + base + c.rank, epoch);
+}
+
+// grid must be fully resident (host clamps it): CTAs wait for work done by other CTAs.
+__global__ void __launch_bounds__(512) allreduce_kernel(const CollParams p) {
+    const CommCtx& c = p.comm;
+    const int tp = c.tp, rank = c.rank;
+    const uint32_t epoch = *c.epoch + 1u;
+    const size_t poff = (size_t)(epoch & 1) * c.part_stride;
+    __shared__ int s_last;
+    const size_t n4 = p.n / 4;
+    const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, gsz = (size_t)gridDim.x * blockDim.x;
+
+    // ---- 1. publish the local input in this rank's symmetric staging buffer
+    float4* mine = (float4*)(c.part[rank] + poff);
+    for (size_t i = gtid; i < n4; i += gsz) {
+        float4 v;
+        if (p.in) v = ((const float4*)p.in)[i];
+        else {
+            uint2 h = ((const uint2*)p.in16)[i];
+            float2 a = __half22float2(*(__half2*)&h.x), b = __half22float2(*(__half2*)&h.y);
+            v = make_float4(a.x, a.y, b.x, b.y);
+        }
+        mine[i] = v;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        s_last = (atomicAdd(&p.counters[0], 1) == (int)gridDim.x - 1);
+        if (s_last) p.counters[0] = 0;
+        __threadfence();
+    }
+    __syncthreads();
+    if (s_last && !p.test_withhold) signal_all(c, 0, epoch);
+    const bool ok = wait_all(c, 0, epoch, B2_KID_ALLREDUCE);
+
+    auto emit = [&](size_t i, float4 s) {
+        float4* o = (float4*)p.out + i;
+        if (p.residual) { float4 h = *o; s.x += h.x; s.y += h.y; s.z += h.z; s.w += h.w; }
+        *o = s;
+        if (p.out16) {
+            __half2 a = __floats2half2_rn(s.x, s.y), b = __floats2half2_rn(s.z, s.w);
+            uint2 h; h.x = *(uint32_t*)&a; h.y = *(uint32_t*)&b;
+            ((uint2*)p.out16)[i] = h;
+        }
+    };
+    auto reduce_at = [&](size_t i) -> float4 {
+        if (!ok) return mine[i];
+        if (c.mc_part) return multimem_ld_reduce_v4(c.mc_part + poff + 4 * i);
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < tp; ++r) {
+            float4 v = ld_relaxed_sys_v4(c.part[r] + poff + 4 * i);
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        return s;
+    };
+
+    if (!p.twoshot) {
+        for (size_t i = gtid; i < n4; i += gsz) emit(i, reduce_at(i));
+    } else {
+        // ---- 2. reduce this rank's slice and store it into every rank's gather buffer
+        const size_t per = (n4 + tp - 1) / tp, lo = per * rank, hi = min(n4, lo + per);
+        for (size_t i = lo + gtid; i < hi; i += gsz) {
+            float4 s = reduce_at(i);
+            if (p.mc_gather) multimem_st_v4(p.mc_gather + 4 * i, s);
+            else for (int r = 0; r < tp; ++r) ((float4*)p.gather[r])[i] = s;
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            s_last = (atomicAdd(&p.counters[1], 1) == (int)gridDim.x - 1);
+            if (s_last) p.counters[1] = 0;
+            __threadfence_system();
+        }
+        __syncthreads();
+        if (s_last && !p.test_withhold) signal_all(c, B2_MAX_TP, epoch);
+        const bool ok2 = wait_all(c, B2_MAX_TP, epoch, B2_KID_ALLREDUCE);
+        const float* mygather = p.gather[rank];
+        for (size_t i = gtid; i < n4; i += gsz) {
+            float4 s = ok2 ? ld_relaxed_sys_v4(mygather + 4 * i) : mine[i];
+            emit(i, s);
+        }
+    }
+    // ---- the last CTA to finish advances the epoch
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (atomicAdd(&p.counters[2], 1) == (int)gridDim.x - 1) {
+            p.counters[2] = 0;
+            *c.epoch = epoch;
+        }
+    }
+}
+
+B2_API int b2_allreduce(const CollParams* p, int max_ctas, cudaStream_t s) {
+    if (p->n % 4 || p->n > (size_t)p->comm.part_stride) return cudaErrorInvalidValue;
+    size_t n4 = p->n / 4;
+    int ctas = (int)((n4 + 511) / 512);
+    if (ctas > max_ctas) ctas = max_ctas;
+    if (ctas < 1) ctas = 1;
+    allreduce_kernel<<<ctas, 512, 0, s>>>(*p);
+    return cudaGetLastError();
+}
+B2_API int b2_sizeof_coll_params() { return (int)sizeof(CollParams); }
+
+// ---------------------------------------------------------------------------
+// Device barrier across ranks (one CTA): flags only, bounded.
+// ---------------------------------------------------------------------------
+__global__ void barrier_kernel(const CommCtx c, int withhold) {
+    const uint32_t epoch = *c.epoch + 1u;
+    if (!withhold) signal_all(c, 0, epoch);
+    wait_all(c, 0, epoch, B2_KID_BARRIER);
+    if (threadIdx.x == 0) *c.epoch = epoch;
+}
+B2_API int b2_barrier(const CommCtx* c, int withhold, cudaStream_t s) {
+    barrier_kernel<<<1, 32, 0, s>>>(*c, withhold);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// Probes: copy bandwidth (local or peer source, plain or multimem) and
+// dependent-load latency.  (reference: src/kernels/p2p_bandwidth_kernels.hip)
+// ---------------------------------------------------------------------------
+__global__ void probe_read_kernel(const float4* __restrict__ src, float4* __restrict__ dst, size_t n4, int mode) {
+    const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, gsz = (size_t)gridDim.x * blockDim.x;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (size_t i = gtid; i < n4; i += gsz) {
+        float4 v = (mode == 1) ? multimem_ld_reduce_v4((const float*)(src + i)) : ld_relaxed_sys_v4((const float*)(src + i));
+        if (dst) dst[i] = v;
+        else { acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w; }
+    }
+    if (!dst && acc.x == 1.2345e38f) ((float4*)src)[0] = acc;    // keep the loads alive
+}
+B2_API int b2_probe_read(const void* src, void* dst, size_t nbytes, int mode, int ctas, cudaStream_t s) {
+    probe_read_kernel<<<ctas, 512, 0, s>>>((const float4*)src, (float4*)dst, nbytes / 16, mode);
+    return cudaGetLastError();
+}
+
+__global__ void probe_latency_kernel(const uint32_t* __restrict__ chain, int hops, long long* out_ns) {
+    uint32_t idx = 0;
+    long long t0 = globaltimer_ns();
+    for (int i = 0; i < hops; ++i) idx = ld_acquire_sys_u32(chain + idx);
+    long long t1 = globaltimer_ns();
+    out_ns[0] = t1 - t0;
+    out_ns[1] = idx;
+}
+B2_API int b2_probe_latency(const void* chain, int hops, void* out_ns, cudaStream_t s) {
+    probe_latency_kernel<<<1, 1, 0, s>>>((const uint32_t*)chain, hops, (long long*)out_ns);
+    return cudaGetLastError();
+}
+
+// Bounded-wait self test: waits on a flag that nothing sets; returns with a status.
+__global__ void wait_test_kernel(const CommCtx c, uint32_t* flag) {
+    if (threadIdx.x == 0 && !wait_reached(flag, 1u, c.wait_ns)) report_timeout(c, B2_KID_TEST, -1, 1u);
+}
+B2_API int b2_wait_test(const CommCtx* c, void* flag, cudaStream_t s) {
+    wait_test_kernel<<<1, 32, 0, s>>>(*c, (uint32_t*)flag);
+    return cudaGetLastError();
+}

@@ -86,20 +86,20 @@ __device__ __forceinline__ uint2 ldg_nc_v2(const void* p) {
 __device__ __forceinline__ float4 ld_relaxed_sys_v4(const float* p) {
     float4 r;
     asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
-                 : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(p) : "memory");
+                 : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(p));
     return r;
 }
-__device__ __forceinline__ float4 ld_cg_v4(const float* p) {
-    float4 r;
-    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];"
-                 : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(p) : "memory");
-    return r;
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    uint32_t s = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(s), "l"(gmem_src) : "memory");
 }
-__device__ __forceinline__ float ld_cg_f32(const float* p) {
-    float r;
-    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(r) : "l"(p) : "memory");
-    return r;
-}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
+// L2 loads (bypass L1) of data another CTA of this kernel wrote before a fence
+// + counter handshake.  Not volatile, so independent loads pipeline.
+__device__ __forceinline__ float4 ld_cg_v4(const float* p) { return __ldcg((const float4*)p); }
+__device__ __forceinline__ float ld_cg_f32(const float* p) { return __ldcg(p); }
 __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -144,6 +144,14 @@ __device__ __forceinline__ void report_timeout(const CommCtx& c, int kernel_id, 
         c.status[3] = (int)epoch;
     }
 }
+
+// Programmatic dependent launch.  A kernel that calls pdl_launch_dependents() lets the
+// next kernel in the stream start (if that one was launched with the programmatic
+// stream-serialisation attribute); the dependent must call pdl_wait() before it touches
+// anything its predecessors produce.  pdl_wait() returns once every predecessor grid has
+// completed and its memory is visible.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }

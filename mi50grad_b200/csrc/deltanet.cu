@@ -32,6 +32,7 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_step_kernel(const DeltaPa
     constexpr int RPT = DK / 8;                  // state rows per thread
     constexpr int NCH = 2 * DK + DN_COLS;        // conv channels this CTA consumes
     cg::cluster_group cluster = cg::this_cluster();
+    pdl_launch_dependents();
     const int cb = blockIdx.x, j = blockIdx.y, si = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, kr = tid >> 5, vcol = lane;
     const int kh = j / (p.nv / p.nk);
@@ -86,8 +87,21 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_step_kernel(const DeltaPa
             const __half* wa = p.wa + (size_t)j * p.H;
             const __half* wb = p.wb + (size_t)j * p.H;
             float sa = 0.f, sb = 0.f;
+            float inv = 0.f;
+            if (p.ln.h) {
+                if (kr == 0) { float v = lazy_inv_rms(p.ln, r, lane); if (lane == 0) red32[31] = v; }
+                __syncthreads();
+                inv = red32[31];
+            }
             for (int i = tid * 2; i < p.H; i += DN_THREADS * 2) {
-                float2 xv = __half22float2(*(const __half2*)(x + i));
+                float2 xv;
+                if (p.ln.h) {
+                    float2 hv = *(const float2*)(p.ln.h + (size_t)r * p.ln.H + i);
+                    float2 ww = __half22float2(*(const __half2*)(p.ln.w + i));
+                    xv = __half22float2(__floats2half2_rn(hv.x * inv * ww.x, hv.y * inv * ww.y));
+                } else {
+                    xv = __half22float2(*(const __half2*)(x + i));
+                }
                 float2 av = __half22float2(*(const __half2*)(wa + i));
                 float2 bv = __half22float2(*(const __half2*)(wb + i));
                 sa += xv.x * av.x + xv.y * av.y;

@@ -41,6 +41,7 @@ struct LayerDesc {
     LinearDesc out_proj;          // row-parallel
     LinearDesc gate_up;           // gate/up interleaved by 8
     LinearDesc down;              // row-parallel
+    const void* attn_norm;        // RMSNorm applied to this layer's input
     const void* ffn_norm;         // RMSNorm applied after the attention block
     const void* next_norm;        // RMSNorm applied after the FFN (next layer's input norm / final norm)
     // full attention
@@ -70,7 +71,8 @@ struct ModelDesc {
     float* gemv_scratch; int* gemv_counters;
     float* attn_scratch; int* attn_counters;
     float* argmax_scratch; int* argmax_counters;
-    float* extra; float* local_part;
+    float* extra; float* h_tmp;            // saved attention partial; uncommitted h + partial (deferred_consistent)
+    float* ss; int np; int pad3;           // [rows][np] sums of squares for the lazy RMSNorm
     void* rows; void* rows_tmpl; void* seqs; int* row_tokens; int* seq_rows; int* out_tokens;
     CommCtx comm;
 };
@@ -89,11 +91,20 @@ struct Driver {
 #define STEP_ARGMAX 4           // arg-max into out_tokens (and SeqState.token)
 #define STEP_ADVANCE 8          // len += 1 for every row's sequence (plain decode)
 #define STEP_NO_COMMIT_DELTA 16 // DeltaNet state dry run
+#define STEP_MATERIALIZE_XN 32  // write the final-normed hidden states to xn (hidden-out interface)
 
 #define CK(x) do { int e_ = (x); if (e_ != 0) return e_; } while (0)
 
-static int run_linear(Driver* d, const LinearDesc& L, const void* x, int ldx, int rows, const GemvEpi& epi,
-                      cudaStream_t s) {
+static LazyNorm lazy(const Driver* d, const float* h, const void* w) {
+    LazyNorm ln;
+    memset(&ln, 0, sizeof(ln));
+    ln.h = h; ln.ss = d->m.ss; ln.w = (const __half*)w; ln.np = d->m.np; ln.H = d->m.H; ln.eps = d->m.eps;
+    return ln;
+}
+static LazyNorm no_lazy() { LazyNorm ln; memset(&ln, 0, sizeof(ln)); return ln; }
+
+static int run_linear(Driver* d, const LinearDesc& L, const void* x, int ldx, const LazyNorm& ln, int rows,
+                      const GemvEpi& epi, cudaStream_t s) {
     d->launches++;
     if (L.kind == LIN_INT4) {
         GemvInt4Params p;
@@ -101,14 +112,14 @@ static int run_linear(Driver* d, const LinearDesc& L, const void* x, int ldx, in
         p.qfrag = (const uint4*)L.w; p.szfrag = (const uint2*)L.sz; p.x = (const __half*)x;
         p.ldx = ldx; p.rows = rows; p.K = L.K; p.KB = L.KB; p.NTL = L.NTL; p.G = L.G;
         p.off32 = L.off32; p.gshift = L.gshift; p.k_splits = L.k_splits; p.L = L.L;
-        p.scratch = d->m.gemv_scratch; p.counters = d->m.gemv_counters; p.epi = epi; p.comm = d->m.comm;
+        p.scratch = d->m.gemv_scratch; p.counters = d->m.gemv_counters; p.ln = ln; p.epi = epi; p.comm = d->m.comm;
         return b2_gemv_int4(&p, s);
     }
     GemvF16Params p;
     memset(&p, 0, sizeof(p));
     p.w = (const __half*)L.w; p.x = (const __half*)x; p.ldw = L.ldw; p.ldx = ldx; p.rows = rows;
     p.K = L.K; p.N = L.N; p.k_splits = L.k_splits; p.kslice = L.kslice;
-    p.scratch = d->m.gemv_scratch; p.counters = d->m.gemv_counters; p.epi = epi; p.comm = d->m.comm;
+    p.scratch = d->m.gemv_scratch; p.counters = d->m.gemv_counters; p.ln = ln; p.epi = epi; p.comm = d->m.comm;
     return b2_gemv_f16(&p, s);
 }
 
@@ -119,12 +130,11 @@ static GemvEpi epi_store(void* out, int ldo, int n_valid, int mode) {
     return e;
 }
 
-static GemvEpi epi_finish(Driver* d, const void* norm_w, int flags) {
+static GemvEpi epi_finish(Driver* d, int flags, float* hout) {
     GemvEpi e;
     memset(&e, 0, sizeof(e));
     e.mode = EPI_FINISH; e.n_valid = d->m.H; e.fin_flags = flags;
-    e.h = d->m.h; e.norm_w = (const __half*)norm_w; e.xn = (__half*)d->m.xn;
-    e.extra = d->m.extra; e.local_part = d->m.local_part; e.eps = d->m.eps;
+    e.h = d->m.h; e.hout = hout; e.ss_part = d->m.ss; e.extra = d->m.extra; e.eps = d->m.eps;
     return e;
 }
 
@@ -135,14 +145,16 @@ static int step_impl(Driver* d, int rows, int n_seqs, int flags, cudaStream_t s)
     const bool tp = m.comm.tp > 1;
     CK(b2_prepare_rows(m.rows_tmpl, m.seqs, m.rows, rows, s)); d->launches++;
     if (flags & STEP_EMBED_TOKENS) {
-        CK(b2_embed_rmsnorm(m.embed, m.row_tokens, m.rows, m.seqs, m.first_norm, m.h, m.xn, rows, m.H, m.eps,
-                            m.vocab, s));
+        CK(b2_embed_rmsnorm(m.embed, m.row_tokens, m.rows, m.seqs, m.first_norm, m.h, nullptr, m.ss, m.np, rows,
+                            m.H, m.eps, m.vocab, s));
         d->launches++;
     }
+    const void* last_norm = m.first_norm;
     for (int li = 0; li < m.n_layers; ++li) {
         const LayerDesc& L = d->layers[li];
+        const LazyNorm ln_in = lazy(d, m.h, L.attn_norm);
         // ---- token mixer
-        CK(run_linear(d, L.in_proj, m.xn, m.H, rows, epi_store(m.proj, m.ld_proj, L.in_proj.N, EPI_STORE_F16), s));
+        CK(run_linear(d, L.in_proj, nullptr, 0, ln_in, rows, epi_store(m.proj, m.ld_proj, L.in_proj.N, EPI_STORE_F16), s));
         if (L.type == 0) {
             CK(b2_qknorm_rope_cachew(m.proj, m.ld_proj, m.rows, L.q_norm, L.k_norm, m.cos_tab, m.sin_tab, L.kcache,
                                      L.vcache, rows, m.nq, m.nkv, m.hd, m.rot, m.max_seq, m.rope_interleaved,
@@ -161,7 +173,8 @@ static int step_impl(Driver* d, int rows, int n_seqs, int flags, cudaStream_t s)
             memset(&q, 0, sizeof(q));
             q.proj = (const __half*)m.proj; q.ld = m.ld_proj;
             q.off_q = L.off_q; q.off_k = L.off_k; q.off_v = L.off_v; q.off_z = L.off_z; q.off_a = L.off_a; q.off_b = L.off_b;
-            q.xn = (const __half*)m.xn; q.ldx = m.H; q.H = m.H; q.wa = (const __half*)L.wa; q.wb = (const __half*)L.wb;
+            q.xn = nullptr; q.ldx = m.H; q.H = m.H; q.wa = (const __half*)L.wa; q.wb = (const __half*)L.wb;
+            q.ln = ln_in;
             q.conv_w = (const __half*)L.conv_w; q.conv_state = (__half*)L.conv_state; q.state = L.state;
             q.A_log = L.A_log; q.dt_bias = (const __half*)L.dt_bias; q.norm_w = (const __half*)L.la_norm;
             q.seq_rows = m.seq_rows; q.rows = (const RowMeta*)m.rows; q.out = (__half*)m.attn_out; q.ldo = m.ld_attn;
@@ -171,16 +184,24 @@ static int step_impl(Driver* d, int rows, int n_seqs, int flags, cudaStream_t s)
             d->launches++;
         }
         int f_attn = 0, f_ffn = 0;
+        float* h_mid = m.h;                      // residual stream the FFN reads
         if (!tp) { f_attn = FIN_NO_COMM; f_ffn = FIN_NO_COMM; }
         else if (m.ar_mode == 1) { f_attn = FIN_NO_COMM; }
-        else if (m.ar_mode == 2) { f_attn = FIN_NO_COMM | FIN_NO_H_WRITE | FIN_SAVE_EXTRA; f_ffn = FIN_ADD_EXTRA; }
-        CK(run_linear(d, L.out_proj, m.attn_out, m.ld_attn, rows, epi_finish(d, L.ffn_norm, f_attn), s));
+        else if (m.ar_mode == 2) { f_attn = FIN_NO_COMM | FIN_NO_H_WRITE | FIN_SAVE_EXTRA; f_ffn = FIN_ADD_EXTRA; h_mid = m.h_tmp; }
+        CK(run_linear(d, L.out_proj, m.attn_out, m.ld_attn, no_lazy(), rows, epi_finish(d, f_attn, h_mid), s));
         // ---- FFN
-        CK(run_linear(d, L.gate_up, m.xn, m.H, rows, epi_store(m.act, m.F_pad, m.F_pad, EPI_SILU_PAIR), s));
-        CK(run_linear(d, L.down, m.act, m.F_pad, rows, epi_finish(d, L.next_norm, f_ffn), s));
+        CK(run_linear(d, L.gate_up, nullptr, 0, lazy(d, h_mid, L.ffn_norm), rows,
+                      epi_store(m.act, m.F_pad, m.F_pad, EPI_SILU_PAIR), s));
+        CK(run_linear(d, L.down, m.act, m.F_pad, no_lazy(), rows, epi_finish(d, f_ffn, m.h), s));
+        last_norm = L.next_norm;
     }
     if (flags & STEP_LM_HEAD) {
-        CK(run_linear(d, m.lm_head, m.xn, m.H, rows, epi_store(m.logits, m.ld_logits, m.vocab_local, EPI_STORE_F32), s));
+        CK(run_linear(d, m.lm_head, nullptr, 0, lazy(d, m.h, last_norm), rows,
+                      epi_store(m.logits, m.ld_logits, m.vocab_local, EPI_STORE_F32), s));
+    }
+    if (flags & STEP_MATERIALIZE_XN) {
+        CK(b2_add_rmsnorm(m.h, nullptr, nullptr, last_norm, m.xn, nullptr, rows, m.H, m.eps, s));
+        d->launches++;
     }
     if (flags & STEP_ARGMAX) {
         ArgmaxParams a;

@@ -9,7 +9,7 @@
 // sigmoid_mul.hip:10).  Differences: positions, cache slots and sequence ids
 // come from a device-resident RowMeta array, so a captured CUDA graph replays
 // unchanged; the residual stream is fp32.
-#include "common.cuh"
+#include "gemv.cuh"
 
 // ---------------------------------------------------------------------------
 // prepare_rows: fill RowMeta from the per-sequence state and a static template.
@@ -17,6 +17,7 @@
 // ---------------------------------------------------------------------------
 __global__ void prepare_rows_kernel(const RowMeta* __restrict__ tmpl, const SeqState* __restrict__ seqs,
                                     RowMeta* __restrict__ rows, int n) {
+    pdl_launch_dependents();
     int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= n) return;
     RowMeta t = tmpl[r];
@@ -37,6 +38,7 @@ B2_API int b2_prepare_rows(const void* tmpl, const void* seqs, void* rows, int n
 
 // advance: len += add[seq] for every sequence (after a step has been committed)
 __global__ void advance_kernel(SeqState* seqs, const int* __restrict__ add, int n, int add_const) {
+    pdl_launch_dependents();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) seqs[i].len += add ? add[i] : add_const;
 }
@@ -52,8 +54,10 @@ B2_API int b2_advance(void* seqs, const int* add, int n, int add_const, cudaStre
 __global__ void embed_rmsnorm_kernel(const __half* __restrict__ embed, const int* __restrict__ row_tokens,
                                      const RowMeta* __restrict__ rows, const SeqState* __restrict__ seqs,
                                      const __half* __restrict__ w, float* __restrict__ h,
-                                     __half* __restrict__ xn, int H, float eps, int vocab) {
+                                     __half* __restrict__ xn, float* __restrict__ ss_part, int np,
+                                     int H, float eps, int vocab) {
     __shared__ float red[32];
+    pdl_launch_dependents();
     int r = blockIdx.x;
     int tok = row_tokens ? row_tokens[r] : -1;
     if (tok < 0) tok = seqs[rows[r].seq].token;
@@ -65,7 +69,10 @@ __global__ void embed_rmsnorm_kernel(const __half* __restrict__ embed, const int
         *(float2*)(h + (size_t)r * H + i) = v;
         ss += v.x * v.x + v.y * v.y;
     }
-    float inv = rsqrtf(block_sum(ss, red) / (float)H + eps);
+    float tot = block_sum(ss, red);
+    if (ss_part) for (int i = threadIdx.x; i < np; i += blockDim.x) ss_part[(size_t)r * np + i] = i ? 0.f : tot;
+    if (!xn) return;
+    float inv = rsqrtf(tot / (float)H + eps);
     for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
         float2 v = *(const float2*)(h + (size_t)r * H + i);
         float2 ww = __half22float2(*(const __half2*)(w + i));
@@ -73,10 +80,11 @@ __global__ void embed_rmsnorm_kernel(const __half* __restrict__ embed, const int
     }
 }
 B2_API int b2_embed_rmsnorm(const void* embed, const int* row_tokens, const void* rows, const void* seqs,
-                            const void* w, float* h, void* xn, int n_rows, int H, float eps, int vocab,
-                            cudaStream_t s) {
+                            const void* w, float* h, void* xn, float* ss_part, int np, int n_rows, int H,
+                            float eps, int vocab, cudaStream_t s) {
     embed_rmsnorm_kernel<<<n_rows, 256, 0, s>>>((const __half*)embed, row_tokens, (const RowMeta*)rows,
-                                                (const SeqState*)seqs, (const __half*)w, h, (__half*)xn, H, eps, vocab);
+                                                (const SeqState*)seqs, (const __half*)w, h, (__half*)xn, ss_part, np,
+                                                H, eps, vocab);
     return cudaGetLastError();
 }
 
@@ -84,7 +92,7 @@ B2_API int b2_embed_rmsnorm(const void* embed, const int* row_tokens, const void
 // embedding-in interface): h = emb (fp16 or fp32 input), xn = rmsnorm(h)*w.
 __global__ void load_rmsnorm_kernel(const __half* __restrict__ emb16, const float* __restrict__ emb32,
                                     const __half* __restrict__ w, float* __restrict__ h,
-                                    __half* __restrict__ xn, int H, float eps) {
+                                    __half* __restrict__ xn, float* __restrict__ ss_part, int np, int H, float eps) {
     __shared__ float red[32];
     int r = blockIdx.x;
     float ss = 0.f;
@@ -93,13 +101,16 @@ __global__ void load_rmsnorm_kernel(const __half* __restrict__ emb16, const floa
         h[(size_t)r * H + i] = v;
         ss += v * v;
     }
-    float inv = rsqrtf(block_sum(ss, red) / (float)H + eps);
+    float tot = block_sum(ss, red);
+    if (ss_part) for (int i = threadIdx.x; i < np; i += blockDim.x) ss_part[(size_t)r * np + i] = i ? 0.f : tot;
+    if (!xn) return;
+    float inv = rsqrtf(tot / (float)H + eps);
     for (int i = threadIdx.x; i < H; i += blockDim.x)
         xn[(size_t)r * H + i] = __float2half(h[(size_t)r * H + i] * inv * __half2float(w[i]));
 }
 B2_API int b2_load_rmsnorm(const void* emb16, const float* emb32, const void* w, float* h, void* xn,
-                           int n_rows, int H, float eps, cudaStream_t s) {
-    load_rmsnorm_kernel<<<n_rows, 256, 0, s>>>((const __half*)emb16, emb32, (const __half*)w, h, (__half*)xn, H, eps);
+                           float* ss_part, int np, int n_rows, int H, float eps, cudaStream_t s) {
+    load_rmsnorm_kernel<<<n_rows, 256, 0, s>>>((const __half*)emb16, emb32, (const __half*)w, h, (__half*)xn, ss_part, np, H, eps);
     return cudaGetLastError();
 }
 
@@ -151,6 +162,7 @@ __global__ void qknorm_rope_cachew_kernel(__half* __restrict__ qkv, int ld, cons
     extern __shared__ float sv[];           // [hd]
     __shared__ float red[32];
     const int hidx = blockIdx.x, r = blockIdx.y, i = threadIdx.x;
+    pdl_launch_dependents();
     const RowMeta rm = rows[r];
     __half* row = qkv + (size_t)r * ld;
     const size_t cache_off = (((size_t)rm.seq * max_seq + rm.slot) * nkv) * hd;

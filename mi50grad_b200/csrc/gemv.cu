@@ -35,6 +35,7 @@
 #define GEMV_WK 4            // warps along k
 #define GEMV_NT 4            // 16-wide n-tiles per warp
 #define GEMV_TILE_N (GEMV_WN * GEMV_NT * 16)   // 128
+#define GEMV_STAGES 4        // cp.async ring depth per warp (k64-blocks in flight)
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -121,8 +122,31 @@ __device__ void complete_tile(float* ybuf, const TileCtx& t, const GemvEpi& e, c
         }
     } else {   // EPI_FINISH
         const bool local = (e.fin_flags & FIN_NO_COMM) || c.tp <= 1;
-        float* part = local ? e.local_part
-                            : c.part[c.rank] + (size_t)(epoch_next & 1) * c.part_stride;
+        const int np = (e.n_valid + GEMV_TILE_N - 1) / GEMV_TILE_N;
+        if (local) {
+            // No exchange: every tile adds the residual for its own 128 columns and leaves the
+            // sum of squares of what it wrote; the consumer applies the RMSNorm lazily.  No
+            // counter, no fence, no serial tail.
+            for (int r = 0; r < t.rows; ++r) {
+                float sq = 0.f;
+                if (tid < GEMV_TILE_N) {
+                    int n = t.n0 + tid;
+                    if (n < e.n_valid) {
+                        size_t off = (size_t)r * e.n_valid + n;
+                        float v = ybuf[r * GEMV_TILE_N + tid];
+                        if (e.fin_flags & FIN_ADD_EXTRA) v += e.extra[off];
+                        if (e.fin_flags & FIN_SAVE_EXTRA) e.extra[off] = v;
+                        float hv = e.h[off] + v;
+                        e.hout[off] = hv;
+                        sq = hv * hv;
+                    }
+                }
+                float tot = block_sum(sq, red);
+                if (tid == 0) e.ss_part[(size_t)r * np + blockIdx.x] = tot;
+            }
+            return;
+        }
+        float* part = c.part[c.rank] + (size_t)(epoch_next & 1) * c.part_stride;
         for (int i = tid; i < t.rows * GEMV_TILE_N; i += GEMV_THREADS) {
             int r = i / GEMV_TILE_N, n = t.n0 + i % GEMV_TILE_N;
             if (n < e.n_valid) {
@@ -146,30 +170,30 @@ __device__ void complete_tile(float* ybuf, const TileCtx& t, const GemvEpi& e, c
     }
 }
 
-// One CTA: exchange partials, residual add, RMSNorm.  n_valid <= 8192.
+// One CTA: exchange the ranks' partial sums over NVLink, add the residual, leave the sum
+// of squares for the consumer's lazy RMSNorm (and, if asked, the normalised vector).
+// n_valid <= 8192.
 __device__ void finish_rows(const GemvEpi& e, const CommCtx& c, int rows, uint32_t epoch_next,
                             float* red) {
     const int tid = threadIdx.x;
     const int H = e.n_valid;
-    const bool local = (e.fin_flags & FIN_NO_COMM) || c.tp <= 1;
+    const int np = (H + GEMV_TILE_N - 1) / GEMV_TILE_N;
     __shared__ int s_fail;
     if (tid == 0) s_fail = 0;
     __syncthreads();
-    if (!local) {
-        if (tid == 0) *c.epoch = epoch_next;
-        if (tid < c.tp && tid != c.rank && !(e.fin_flags & FIN_TEST_WITHHOLD_SIGNAL))
-            st_release_sys_u32(c.sig[tid] + c.rank, epoch_next);
-        if (tid < c.tp && tid != c.rank) {
-            if (!wait_reached(c.sig[c.rank] + tid, epoch_next, c.wait_ns)) {
-                report_timeout(c, B2_KID_GEMV_FIN, tid, epoch_next);
-                s_fail = 1;
-            }
+    if (tid == 0) *c.epoch = epoch_next;
+    if (tid < c.tp && tid != c.rank && !(e.fin_flags & FIN_TEST_WITHHOLD_SIGNAL))
+        st_release_sys_u32(c.sig[tid] + c.rank, epoch_next);
+    if (tid < c.tp && tid != c.rank) {
+        if (!wait_reached(c.sig[c.rank] + tid, epoch_next, c.wait_ns)) {
+            report_timeout(c, B2_KID_GEMV_FIN, tid, epoch_next);
+            s_fail = 1;
         }
-        __syncthreads();
     }
-    const bool exchange = !local && !s_fail;
-    const size_t poff = local ? 0 : (size_t)(epoch_next & 1) * c.part_stride;
-    const float* mine = local ? e.local_part : c.part[c.rank] + poff;
+    __syncthreads();
+    const bool exchange = !s_fail;
+    const size_t poff = (size_t)(epoch_next & 1) * c.part_stride;
+    const float* mine = c.part[c.rank] + poff;
     for (int r = 0; r < rows; ++r) {
         float4 hv[8];
         float ss = 0.f;
@@ -190,16 +214,16 @@ __device__ void finish_rows(const GemvEpi& e, const CommCtx& c, int rows, uint32
                 } else {
                     y = ld_cg_v4(mine + off);
                 }
-                if (e.fin_flags & FIN_SAVE_EXTRA) *(float4*)(e.extra + off) = y;
                 float4 h = *(const float4*)(e.h + off);
                 h.x += y.x; h.y += y.y; h.z += y.z; h.w += y.w;
-                if (!(e.fin_flags & FIN_NO_H_WRITE)) *(float4*)(e.h + off) = h;
+                *(float4*)(e.hout + off) = h;
                 hv[it] = h;
                 ss += h.x * h.x + h.y * h.y + h.z * h.z + h.w * h.w;
             }
         }
-        if (e.fin_flags & FIN_NO_NORM) continue;
         float tot = block_sum(ss, red);
+        for (int i = tid; i < np; i += GEMV_THREADS) e.ss_part[(size_t)r * np + i] = (i == 0) ? tot : 0.f;
+        if (e.xn == nullptr || (e.fin_flags & FIN_NO_NORM)) continue;
         float inv = rsqrtf(tot / (float)H + e.eps);
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
@@ -220,6 +244,7 @@ __device__ void finish_rows(const GemvEpi& e, const CommCtx& c, int rows, uint32
 // ---------------------------------------------------------------------------
 // INT4 kernel
 // ---------------------------------------------------------------------------
+template <bool FAST>
 __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_int4_kernel(const GemvInt4Params p) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -230,56 +255,96 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_int4_kernel(const GemvIn
     const int cta_b0 = blockIdx.y * (GEMV_WK * p.L);
     const int cta_b1 = min(p.KB, cta_b0 + GEMV_WK * p.L);
     const int nCh = max(0, cta_b1 - cta_b0) * 2;
-    const uint32_t epoch_next = (p.epi.mode == EPI_FINISH && p.comm.tp > 1) ? (*p.comm.epoch + 1u) : 0u;
+    pdl_launch_dependents();
 
-    uint4* xf = (uint4*)smem;                                        // [maxCh][M][4]
-    float2* cs = (float2*)(smem + (size_t)maxCh * M * 4 * 16);       // [maxCh][8]
+    uint4* xf = (uint4*)smem;                                        // [maxCh][M][4] (+1 zero entry)
+    float2* cs = (float2*)(smem + ((size_t)maxCh * M * 4 + 4) * 16); // [maxCh][8]
     float* redbuf = (float*)((unsigned char*)cs + (size_t)maxCh * 8 * 8);   // [WK*WN*NT*128]
     float* ybuf = redbuf + GEMV_WK * GEMV_WN * GEMV_NT * 128;        // [8][128]
     float* red32 = ybuf + B2_MAX_ROWS * GEMV_TILE_N;                 // [32]
-    int* s_flag = (int*)(red32 + 32);
+    int* s_flag = (int*)(red32 + 32);          // 4 ints, then the weight ring (16-byte aligned)
+
+    // ---- this warp owns GEMV_NT n-tiles (contiguous in memory per k-block) over blocks [wb0, wb1).
+    // Weights stream through a per-warp cp.async ring: GEMV_STAGES-1 blocks of 2 KB are in
+    // flight per warp at all times (each lane copies and later reads only its own 16 bytes,
+    // so no cross-lane synchronisation).  The ring is primed before anything else so that
+    // HBM is busy while the activations are staged.
+    const int wt = blockIdx.x * GEMV_WN + wn;
+    const int wb0 = cta_b0 + wk * p.L, wb1 = min(cta_b1, wb0 + p.L);
+    const int nb = max(0, wb1 - wb0);
+    uint4* rp = (uint4*)(s_flag + 4) + (size_t)warp * (GEMV_STAGES * GEMV_NT * 32) + lane;
+    const uint4* gp = p.qfrag + ((size_t)wt * p.KB + wb0) * (GEMV_NT * 32) + lane;
+#pragma unroll
+    for (int s = 0; s < GEMV_STAGES - 1; ++s) {
+        if (s < nb) {
+#pragma unroll
+            for (int i = 0; i < GEMV_NT; ++i) cp_async16(rp + (s * GEMV_NT + i) * 32, gp + (s * GEMV_NT + i) * 32);
+        }
+        cp_async_commit();
+    }
+    gp += (GEMV_STAGES - 1) * GEMV_NT * 32;    // next block to prefetch
+    // Weights do not depend on earlier kernels; everything below does.
+    pdl_wait();
+    const uint32_t epoch_next = (p.epi.mode == EPI_FINISH && p.comm.tp > 1) ? (*p.comm.epoch + 1u) : 0u;
 
     // ---- stage activations in MMA B-fragment order, with per-chunk bias sums
     for (int i = tid; i < nCh * 8; i += GEMV_THREADS)
         if ((i & 7) >= M) cs[i] = make_float2(0.f, 0.f);
-    const int items = nCh * M * 4;
-    for (int base = 0; base < items; base += GEMV_THREADS) {
-        int item = base + tid;
-        bool valid = item < items;
-        int tt = item & 3, m = (item >> 2) % M, cl = (item >> 2) / M;
-        int k0 = (cta_b0 * 2 + cl) * 32 + 2 * tt;
-        __half2 a0, a1, b0, b1;
-        a0 = a1 = b0 = b1 = __float2half2_rn(0.f);
-        if (valid) {
-            const __half* xr = p.x + (size_t)m * p.ldx;
-            if (k0 < p.K) a0 = *(const __half2*)(xr + k0);
-            if (k0 + 8 < p.K) a1 = *(const __half2*)(xr + k0 + 8);
-            if (k0 + 16 < p.K) b0 = *(const __half2*)(xr + k0 + 16);
-            if (k0 + 24 < p.K) b1 = *(const __half2*)(xr + k0 + 24);
-        }
-        const __half2 sixteenth = __float2half2_rn(0.0625f);
-        b0 = __hmul2(b0, sixteenth);
-        b1 = __hmul2(b1, sixteenth);
-        float2 fa0 = __half22float2(a0), fa1 = __half22float2(a1);
-        float2 fb0 = __half22float2(b0), fb1 = __half22float2(b1);
-        float sa = fa0.x + fa0.y + fa1.x + fa1.y;
-        float sb = fb0.x + fb0.y + fb1.x + fb1.y;
-        sa += __shfl_xor_sync(0xffffffffu, sa, 1);
-        sb += __shfl_xor_sync(0xffffffffu, sb, 1);
-        sa += __shfl_xor_sync(0xffffffffu, sa, 2);
-        sb += __shfl_xor_sync(0xffffffffu, sb, 2);
-        if (valid) {
-            uint4 v;
-            v.x = *(uint32_t*)&a0; v.y = *(uint32_t*)&a1; v.z = *(uint32_t*)&b0; v.w = *(uint32_t*)&b1;
-            xf[(cl * M + m) * 4 + tt] = v;
-            if (tt == 0) cs[cl * 8 + m] = make_float2(1024.f * (sa + sb), sa + 16.f * sb);
+    if (tid < 4) xf[(size_t)maxCh * M * 4 + tid] = make_uint4(0u, 0u, 0u, 0u);
+    const int items = nCh * 4;
+    float* s_inv = red32;                       // [rows] 1/rms per row when the input is lazy-normed
+    if (p.ln.h) {
+        if (warp < M) { float v = lazy_inv_rms(p.ln, warp, lane); if (lane == 0) s_inv[warp] = v; }
+        __syncthreads();
+    }
+    for (int m = 0; m < M; ++m) {
+        const __half* xr = p.x + (size_t)m * p.ldx;
+        const float* hr = p.ln.h ? p.ln.h + (size_t)m * p.ln.H : nullptr;
+        const float inv = p.ln.h ? s_inv[m] : 0.f;
+        for (int base = 0; base < items; base += GEMV_THREADS) {
+            int item = base + tid;
+            bool valid = item < items;
+            int tt = item & 3, cl = item >> 2;
+            int k0 = (cta_b0 * 2 + cl) * 32 + 2 * tt;
+            __half2 a0, a1, b0, b1;
+            a0 = a1 = b0 = b1 = __float2half2_rn(0.f);
+            if (valid && hr) {
+                auto ld = [&](int k) -> __half2 {
+                    float2 hv = *(const float2*)(hr + k);
+                    float2 wv = __half22float2(*(const __half2*)(p.ln.w + k));
+                    return __floats2half2_rn(hv.x * inv * wv.x, hv.y * inv * wv.y);
+                };
+                if (k0 < p.K) a0 = ld(k0);
+                if (k0 + 8 < p.K) a1 = ld(k0 + 8);
+                if (k0 + 16 < p.K) b0 = ld(k0 + 16);
+                if (k0 + 24 < p.K) b1 = ld(k0 + 24);
+            } else if (valid) {
+                if (k0 < p.K) a0 = *(const __half2*)(xr + k0);
+                if (k0 + 8 < p.K) a1 = *(const __half2*)(xr + k0 + 8);
+                if (k0 + 16 < p.K) b0 = *(const __half2*)(xr + k0 + 16);
+                if (k0 + 24 < p.K) b1 = *(const __half2*)(xr + k0 + 24);
+            }
+            const __half2 sixteenth = __float2half2_rn(0.0625f);
+            b0 = __hmul2(b0, sixteenth);
+            b1 = __hmul2(b1, sixteenth);
+            float2 fa0 = __half22float2(a0), fa1 = __half22float2(a1);
+            float2 fb0 = __half22float2(b0), fb1 = __half22float2(b1);
+            float sa = fa0.x + fa0.y + fa1.x + fa1.y;
+            float sb = fb0.x + fb0.y + fb1.x + fb1.y;
+            sa += __shfl_xor_sync(0xffffffffu, sa, 1);
+            sb += __shfl_xor_sync(0xffffffffu, sb, 1);
+            sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+            sb += __shfl_xor_sync(0xffffffffu, sb, 2);
+            if (valid) {
+                uint4 v;
+                v.x = *(uint32_t*)&a0; v.y = *(uint32_t*)&a1; v.z = *(uint32_t*)&b0; v.w = *(uint32_t*)&b1;
+                xf[(cl * M + m) * 4 + tt] = v;
+                if (tt == 0) cs[cl * 8 + m] = make_float2(1024.f * (sa + sb), sa + 16.f * sb);
+            }
         }
     }
     __syncthreads();
 
-    // ---- main loop: this warp owns GEMV_NT n-tiles over blocks [wb0, wb1)
-    const int tile0 = (blockIdx.x * GEMV_WN + wn) * GEMV_NT;
-    const int wb0 = cta_b0 + wk * p.L, wb1 = min(cta_b1, wb0 + p.L);
     float acc[GEMV_NT][4], tot[GEMV_NT][4];
 #pragma unroll
     for (int i = 0; i < GEMV_NT; ++i)
@@ -287,11 +352,12 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_int4_kernel(const GemvIn
         for (int r = 0; r < 4; ++r) acc[i][r] = tot[i][r] = 0.f;
     float c1r0 = 0.f, c1r1 = 0.f, c2r0 = 0.f, c2r1 = 0.f;
     int cur = -1;
+    const uint2* szp = p.szfrag + (size_t)wt * GEMV_NT * p.G * 8 + g;
 
     auto flush = [&](int grp) {
 #pragma unroll
         for (int i = 0; i < GEMV_NT; ++i) {
-            uint2 sz = ldg_nc_v2(p.szfrag + ((size_t)(tile0 + i) * p.G + grp) * 8 + g);
+            uint2 sz = ldg_nc_v2(szp + ((size_t)i * p.G + grp) * 8);
             float2 s = __half22float2(*(__half2*)&sz.x), z = __half22float2(*(__half2*)&sz.y);
             tot[i][0] += s.x * (acc[i][0] - c1r0 - z.x * c2r0);
             tot[i][1] += s.x * (acc[i][1] - c1r1 - z.x * c2r1);
@@ -302,43 +368,58 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_int4_kernel(const GemvIn
         c1r0 = c1r1 = c2r0 = c2r1 = 0.f;
     };
 
-    uint4 w[GEMV_NT], wnext[GEMV_NT];
-    if (wb0 < wb1) {
+    // per-lane activation pointer: lanes whose token row does not exist read a zero entry with stride 0
+    const int cl0 = 2 * (wb0 - cta_b0);
+    const uint4* xp = (g < M) ? xf + ((size_t)cl0 * M + g) * 4 + t : xf + (size_t)maxCh * M * 4 + t;
+    const int xstride = (g < M) ? M * 4 : 0;
+    const float4* cp4 = (const float4*)(cs + (size_t)cl0 * 8 + 2 * t);
+
+    for (int bb = 0; bb < nb; bb += GEMV_STAGES) {
 #pragma unroll
-        for (int i = 0; i < GEMV_NT; ++i)
-            w[i] = ldg_nc_v4(p.qfrag + ((size_t)(tile0 + i) * p.KB + wb0) * 32 + lane);
-    }
-    for (int b = wb0; b < wb1; ++b) {
-        if (b + 1 < wb1) {
+        for (int s = 0; s < GEMV_STAGES; ++s) {
+            const int br = bb + s;
+            if (br < nb) {
+                if (br + GEMV_STAGES - 1 < nb) {
 #pragma unroll
-            for (int i = 0; i < GEMV_NT; ++i)
-                wnext[i] = ldg_nc_v4(p.qfrag + ((size_t)(tile0 + i) * p.KB + b + 1) * 32 + lane);
-        }
+                    for (int i = 0; i < GEMV_NT; ++i)
+                        cp_async16(rp + (((s + GEMV_STAGES - 1) % GEMV_STAGES) * GEMV_NT + i) * 32, gp + i * 32);
+                    gp += GEMV_NT * 32;
+                }
+                cp_async_commit();
+                cp_async_wait<GEMV_STAGES - 1>();
+                uint4 w[GEMV_NT];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int c = 2 * b + j;
-            const int grp = (c + p.off32) >> p.gshift;
-            if (grp != cur) {
-                if (cur >= 0) flush(cur);
-                cur = grp;
+                for (int i = 0; i < GEMV_NT; ++i) w[i] = rp[(s * GEMV_NT + i) * 32];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    if (!FAST) {
+                        const int grp = (2 * (wb0 + br) + j + p.off32) >> p.gshift;
+                        if (grp != cur) {
+                            if (cur >= 0) flush(cur);
+                            cur = grp;
+                        }
+                    }
+                    const uint4 xv = *xp;
+                    xp += xstride;
+                    const float4 cv = cp4[j * 4];
+                    c1r0 += cv.x; c2r0 += cv.y; c1r1 += cv.z; c2r1 += cv.w;
+#pragma unroll
+                    for (int i = 0; i < GEMV_NT; ++i) {
+                        uint32_t w0 = j ? w[i].z : w[i].x, w1 = j ? w[i].w : w[i].y;
+                        uint32_t w0s = w0 >> 8, w1s = w1 >> 8;
+                        mma16816(acc[i], nib_lo(w0), nib_lo(w0s), nib_lo(w1), nib_lo(w1s), xv.x, xv.y);
+                        mma16816(acc[i], nib_hi(w0), nib_hi(w0s), nib_hi(w1), nib_hi(w1s), xv.z, xv.w);
+                    }
+                }
+                cp4 += 8;
+                // FAST: groups of 128 k aligned to even blocks, so a group ends after every odd block
+                if (FAST && (s & 1)) flush((wb0 + br) >> 1);
             }
-            const int cl = c - 2 * cta_b0;
-            uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-            if (g < M) xv = xf[(cl * M + g) * 4 + t];
-            float4 cv = *(const float4*)&cs[cl * 8 + 2 * t];
-            c1r0 += cv.x; c2r0 += cv.y; c1r1 += cv.z; c2r1 += cv.w;
-#pragma unroll
-            for (int i = 0; i < GEMV_NT; ++i) {
-                uint32_t w0 = j ? w[i].z : w[i].x, w1 = j ? w[i].w : w[i].y;
-                uint32_t w0s = w0 >> 8, w1s = w1 >> 8;
-                mma16816(acc[i], nib_lo(w0), nib_lo(w0s), nib_lo(w1), nib_lo(w1s), xv.x, xv.y);
-                mma16816(acc[i], nib_hi(w0), nib_hi(w0s), nib_hi(w1), nib_hi(w1s), xv.z, xv.w);
-            }
         }
-#pragma unroll
-        for (int i = 0; i < GEMV_NT; ++i) w[i] = wnext[i];
     }
-    if (cur >= 0) flush(cur);
+    cp_async_wait<0>();
+    if (FAST) { if (nb & 1) flush((wb0 + nb - 1) >> 1); }
+    else if (cur >= 0) flush(cur);
 
     // ---- in-CTA reduction over the k-warps into ybuf[row][n_local]
 #pragma unroll
@@ -376,16 +457,35 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_f16_kernel(const GemvF16Par
     const int M = p.rows;
     const int k0 = blockIdx.y * p.kslice;
     const int klen = min(p.kslice, p.K - k0);
+    pdl_launch_dependents();
     const uint32_t epoch_next = (p.epi.mode == EPI_FINISH && p.comm.tp > 1) ? (*p.comm.epoch + 1u) : 0u;
     __half* xs = (__half*)smem;                                      // [MR][kslice]
     float* ybuf = (float*)(smem + (size_t)MR * p.kslice * 2);        // [8][128]
     float* red32 = ybuf + B2_MAX_ROWS * GEMV_TILE_N;
     int* s_flag = (int*)(red32 + 32);
 
+    if (p.ln.h) {
+        if (warp < M) { float v = lazy_inv_rms(p.ln, warp, lane); if (lane == 0) red32[warp] = v; }
+        __syncthreads();
+    }
     for (int i = tid * 8; i < MR * p.kslice; i += GEMV_THREADS * 8) {
         int m = i / p.kslice, kk = i % p.kslice;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (m < M && kk < klen) v = *(const uint4*)(p.x + (size_t)m * p.ldx + k0 + kk);
+        if (m < M && kk < klen) {
+            if (p.ln.h) {
+                const float* hr = p.ln.h + (size_t)m * p.ln.H + k0 + kk;
+                const __half2* wv = (const __half2*)(p.ln.w + k0 + kk);
+                const float inv = red32[m];
+                __half2* o = (__half2*)&v;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float2 hv = *(const float2*)(hr + 2 * q), ww = __half22float2(wv[q]);
+                    o[q] = __floats2half2_rn(hv.x * inv * ww.x, hv.y * inv * ww.y);
+                }
+            } else {
+                v = *(const uint4*)(p.x + (size_t)m * p.ldx + k0 + kk);
+            }
+        }
         *(uint4*)(xs + i) = v;
     }
     for (int i = tid; i < B2_MAX_ROWS * GEMV_TILE_N; i += GEMV_THREADS) ybuf[i] = 0.f;
@@ -445,22 +545,35 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_f16_kernel(const GemvF16Par
 // ---------------------------------------------------------------------------
 B2_API size_t b2_gemv_int4_smem(int rows, int L) {
     size_t maxCh = 2 * GEMV_WK * (size_t)L;
-    return maxCh * rows * 64 + maxCh * 64 + (GEMV_WK * GEMV_WN * GEMV_NT * 128 + B2_MAX_ROWS * GEMV_TILE_N + 32 + 4) * 4;
+    return (maxCh * rows + 1) * 64 + maxCh * 64 + (GEMV_WK * GEMV_WN * GEMV_NT * 128 + B2_MAX_ROWS * GEMV_TILE_N + 32 + 4) * 4
+           + (size_t)(GEMV_THREADS / 32) * GEMV_STAGES * GEMV_NT * 512;
 }
 
 B2_API int b2_gemv_int4(const GemvInt4Params* p, cudaStream_t stream) {
     if (p->rows < 1 || p->rows > B2_MAX_ROWS) return cudaErrorInvalidValue;
     if (p->epi.mode == EPI_FINISH && p->epi.n_valid > 8192) return cudaErrorInvalidValue;
     size_t smem = b2_gemv_int4_smem(p->rows, p->L);
-    static size_t configured = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_int4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    // groups of 128 aligned to even k-blocks let the kernel drop all per-chunk group bookkeeping
+    const bool fast = p->gshift == 2 && p->off32 == 0 && (p->L % 2 == 0);
+    static size_t configured[2] = {0, 0};
+    if (smem > configured[fast]) {
+        cudaError_t e = fast ? cudaFuncSetAttribute(gemv_int4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                             : cudaFuncSetAttribute(gemv_int4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        configured = smem;
+        configured[fast] = smem;
     }
-    dim3 grid(p->NTL * 16 / GEMV_TILE_N, p->k_splits);
-    gemv_int4_kernel<<<grid, GEMV_THREADS, smem, stream>>>(*p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p->NTL * 16 / GEMV_TILE_N, p->k_splits);
+    cfg.blockDim = dim3(GEMV_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (fast) return cudaLaunchKernelEx(&cfg, gemv_int4_kernel<true>, *p);
+    return cudaLaunchKernelEx(&cfg, gemv_int4_kernel<false>, *p);
 }
 
 template <int MR>

@@ -16,6 +16,29 @@
 #define FIN_NO_NORM     16   // skip the RMSNorm (xn not written)
 #define FIN_TEST_WITHHOLD_SIGNAL 32  // test hook: do not signal peers, so the bounded wait runs out
 
+// "Lazy" RMSNorm input: instead of a materialised fp16 vector a consumer kernel can be
+// given the fp32 residual stream, the per-tile sums of squares its producer left behind
+// and the norm weights; it then forms x[k] = h[k] * rsqrt(sum(ss)/H + eps) * w[k] while
+// staging its activations.  This removes the serial normalise-and-store tail between a
+// row-parallel projection and its consumer.
+struct LazyNorm {
+    const float* h;          // [rows][H] residual stream (null: use the fp16 x instead)
+    const float* ss;         // [rows][np] partial sums of squares
+    const __half* w;         // [H]
+    int np, H;
+    float eps;
+    int pad;
+};
+
+__device__ __forceinline__ float lazy_inv_rms(const LazyNorm& ln, int row, int lane) {
+    // one warp: sum the partials in a fixed order
+    float s = 0.f;
+    for (int i = lane; i < ln.np; i += 32) s += ln.ss[(size_t)row * ln.np + i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    return rsqrtf(s / (float)ln.H + ln.eps);
+}
+
 struct GemvEpi {
     int mode;
     int ldo;                 // row stride of out (elements)
@@ -26,7 +49,10 @@ struct GemvEpi {
     const __half* norm_w;    // [n_valid] multiplier of the following RMSNorm
     __half* xn;              // [rows][n_valid] normalised output
     float* extra;            // [rows][n_valid] saved / added partial
-    float* local_part;       // [rows][n_valid] staging when FIN_NO_COMM
+    float* local_part;       // unused (kept for layout stability)
+    float* hout;             // [rows][n_valid] where h + sum is written (h itself, or a scratch row
+                             // buffer when FIN_NO_H_WRITE)
+    float* ss_part;          // [rows][ceil(n_valid/128)] per-tile sums of squares of hout
     float eps;
     int pad;
 };
@@ -40,6 +66,7 @@ struct GemvInt4Params {
     int k_splits, L;         // CTAs along K, k64-blocks per warp
     float* scratch;          // [k_splits][rows][NTL*16] split-K partials
     int* counters;           // [gridDim.x + 1], zero between launches
+    LazyNorm ln;
     GemvEpi epi;
     CommCtx comm;
 };
@@ -51,6 +78,7 @@ struct GemvF16Params {
     int k_splits, kslice;    // kslice: multiple of 256
     float* scratch;
     int* counters;
+    LazyNorm ln;
     GemvEpi epi;
     CommCtx comm;
 };

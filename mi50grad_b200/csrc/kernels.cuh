@@ -34,6 +34,7 @@ struct DeltaParams {
     int ldo, nk, nv, n_seqs;
     float eps;
     int commit;              // 0: leave state and conv history untouched (dry run for tree verification)
+    LazyNorm ln;             // if ln.h: the a/b projections read the lazily normalised residual stream
 };
 
 struct ArgmaxParams {
@@ -56,10 +57,12 @@ B2_API int b2_argmax(const ArgmaxParams* p, cudaStream_t s);
 B2_API int b2_prepare_rows(const void* tmpl, const void* seqs, void* rows, int n, cudaStream_t s);
 B2_API int b2_advance(void* seqs, const int* add, int n, int add_const, cudaStream_t s);
 B2_API int b2_embed_rmsnorm(const void* embed, const int* row_tokens, const void* rows, const void* seqs,
-                            const void* w, float* h, void* xn, int n_rows, int H, float eps, int vocab,
-                            cudaStream_t s);
+                            const void* w, float* h, void* xn, float* ss_part, int np, int n_rows, int H,
+                            float eps, int vocab, cudaStream_t s);
 B2_API int b2_load_rmsnorm(const void* emb16, const float* emb32, const void* w, float* h, void* xn,
-                           int n_rows, int H, float eps, cudaStream_t s);
+                           float* ss_part, int np, int n_rows, int H, float eps, cudaStream_t s);
+B2_API int b2_add_rmsnorm(float* h, const float* delta32, const void* delta16, const void* w, void* xn,
+                          float* xn32, int n_rows, int H, float eps, cudaStream_t s);
 B2_API int b2_qknorm_rope_cachew(void* qkv, int ld, const void* rows, const void* q_norm, const void* k_norm,
                                  const float* cos_tab, const float* sin_tab, void* kcache, void* vcache,
                                  int n_rows, int nq, int nkv, int hd, int rot, int max_seq, int interleaved,

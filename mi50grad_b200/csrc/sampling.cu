@@ -12,6 +12,7 @@ __device__ __forceinline__ void arg_better(float& v, int& i, float v2, int i2) {
 
 __global__ void __launch_bounds__(256) argmax_kernel(const ArgmaxParams p) {
     const int r = blockIdx.y, b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_launch_dependents();
     __shared__ float sv[8];
     __shared__ int si[8];
     __shared__ int s_last, s_fail;

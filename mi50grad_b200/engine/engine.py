@@ -306,7 +306,9 @@ class InferenceEngine:
         self.argmax_blocks = max(1, min(64, sp.vocab_local // 2048))
         b["argmax_scratch"] = f32(R * self.argmax_blocks * 2)
         b["argmax_counters"] = i32(R + 8)
-        b["extra"], b["local_part"] = f32(R, H), f32(R, H)
+        b["extra"], b["h_tmp"] = f32(R, H), f32(R, H)
+        self.np = -(-H // 128)
+        b["ss"] = f32(R, self.np)
         b["rows"], b["rows_tmpl"] = i32(R, 6), i32(R, 6)
         b["row_tokens"] = torch.full((R,), -1, dtype=torch.int32, device=dev)
         b["seq_rows"] = i32(self.max_batch + 1 + R)
@@ -329,9 +331,10 @@ class InferenceEngine:
         m.cos_tab, m.sin_tab = self.cos_tab.data_ptr(), self.sin_tab.data_ptr()
         for k in ("h", "xn", "proj", "attn_out", "act", "logits", "gemv_scratch", "gemv_counters",
                   "attn_scratch", "attn_counters", "argmax_scratch", "argmax_counters", "extra",
-                  "local_part", "rows", "rows_tmpl", "row_tokens", "seq_rows", "out_tokens"):
+                  "h_tmp", "ss", "rows", "rows_tmpl", "row_tokens", "seq_rows", "out_tokens"):
             setattr(m, k, b[k].data_ptr())
         m.ld_proj, m.ld_attn, m.ld_logits = b["ld_proj"], b["ld_attn"], b["ld_logits"]
+        m.np = self.np
         m.seqs = self.states.seqs.data_ptr()
         m.comm = self._comm_ctx()
         descs = (L.LayerDesc * cfg.num_hidden_layers)()
@@ -340,6 +343,7 @@ class InferenceEngine:
             d.type = dl.type
             d.in_proj, d.out_proj = dl.in_proj.desc(), dl.out_proj.desc()
             d.gate_up, d.down = dl.gate_up.desc(), dl.down.desc()
+            d.attn_norm = dl.attn_norm.data_ptr()
             d.ffn_norm = dl.ffn_norm.data_ptr()
             nxt = self.layers[i + 1].attn_norm if i + 1 < len(self.layers) else self.final_norm
             d.next_norm = nxt.data_ptr()
@@ -509,10 +513,11 @@ class InferenceEngine:
         self.buf["emb_in"][:n].copy_(e)
         L.check(self.lib.b2_load_rmsnorm(None, C.c_void_p(self.buf["emb_in"].data_ptr()),
                                          C.c_void_p(self.layers[0].attn_norm.data_ptr()),
-                                         C.c_void_p(self.buf["h"].data_ptr()),
-                                         C.c_void_p(self.buf["xn"].data_ptr()), n, self.config.hidden_size,
-                                         C.c_float(self.config.rms_norm_eps), L.stream()), "load_rmsnorm")
-        self._run(n, 1, 0 if commit else L.STEP_NO_COMMIT_DELTA)
+                                         C.c_void_p(self.buf["h"].data_ptr()), None,
+                                         C.c_void_p(self.buf["ss"].data_ptr()), self.np, n,
+                                         self.config.hidden_size, C.c_float(self.config.rms_norm_eps),
+                                         L.stream()), "load_rmsnorm")
+        self._run(n, 1, L.STEP_MATERIALIZE_XN | (0 if commit else L.STEP_NO_COMMIT_DELTA))
         if commit:
             self.states.seqs[seq, 0] += n
         return self.buf["xn"][:n]
@@ -543,11 +548,14 @@ class InferenceEngine:
         """Logits (fp32, this rank's vocabulary slice) of a final-normed hidden
         state; None = the last step's (reference: src/inference/engine.py:1123-1143)."""
         self._ensure_driver()
+        from ..ops import kernels as K
         if hidden is not None:
             hdn = self._as_dev(hidden).reshape(1, -1)
             self.buf["xn"][:1].copy_(hdn.half())
-        from ..ops import kernels as K
-        K.gemv(self.lm_head, self.buf["xn"][:1], out=self.buf["logits"][:1], mode=L.EPI_STORE_F32,
+            x, ln = self.buf["xn"][:1], None
+        else:
+            x, ln = None, K.lazy_norm(self.buf["h"], self.buf["ss"], self.final_norm, self.config.rms_norm_eps)
+        K.gemv(self.lm_head, x, out=self.buf["logits"][:1], mode=L.EPI_STORE_F32, ln=ln, rows=1,
                scratch=self.buf["gemv_scratch"], counters=self.buf["gemv_counters"])
         out = self.buf["logits"][0, :self.spec.vocab_local]
         return out.cpu().numpy() if isinstance(hidden, np.ndarray) else out.clone()

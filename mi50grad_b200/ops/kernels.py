@@ -28,24 +28,37 @@ def make_rows(entries, device) -> torch.Tensor:
 
 
 def _epi(mode, out=None, ldo=0, n_valid=0, fin_flags=0, h=None, norm_w=None, xn=None, extra=None,
-         local_part=None, eps=1e-6) -> L.GemvEpi:
+         hout=None, ss_part=None, eps=1e-6) -> L.GemvEpi:
     e = L.GemvEpi()
     e.mode, e.ldo, e.n_valid, e.fin_flags = mode, ldo, n_valid, fin_flags
     e.out, e.h, e.norm_w, e.xn = L.ptr(out), L.ptr(h), L.ptr(norm_w), L.ptr(xn)
-    e.extra, e.local_part, e.eps = L.ptr(extra), L.ptr(local_part), eps
+    e.extra, e.eps = L.ptr(extra), eps
+    e.hout = L.ptr(hout if hout is not None else h)
+    e.ss_part = L.ptr(ss_part)
     return e
 
 
-def gemv(lin, x: torch.Tensor, out: Optional[torch.Tensor] = None, mode: int = L.EPI_STORE_F16,
+def lazy_norm(h: torch.Tensor, ss: torch.Tensor, w: torch.Tensor, eps: float = 1e-6) -> L.LazyNorm:
+    """Input descriptor: x = h * rsqrt(sum(ss[row]) / H + eps) * w, formed by the consumer."""
+    ln = L.LazyNorm()
+    ln.h, ln.ss, ln.w = h.data_ptr(), ss.data_ptr(), w.data_ptr()
+    ln.np, ln.H, ln.eps = ss.shape[1], h.shape[1], eps
+    return ln
+
+
+def gemv(lin, x: Optional[torch.Tensor], out: Optional[torch.Tensor] = None, mode: int = L.EPI_STORE_F16,
          scratch: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None,
          comm: Optional[L.CommCtx] = None, fin_flags: int = 0, h=None, norm_w=None, xn=None,
-         extra=None, local_part=None, eps: float = 1e-6, n_valid: Optional[int] = None,
-         k_splits: Optional[int] = None, Lblocks: Optional[int] = None):
-    """y = x W^T for x[rows, K] fp16 with a `DeviceLinear`-like object (`.packed`
-    PackedInt4 or `.dense` fp16 [N, K]) and one of the four epilogues."""
+         extra=None, hout=None, ss_part=None, eps: float = 1e-6, n_valid: Optional[int] = None,
+         k_splits: Optional[int] = None, Lblocks: Optional[int] = None, ln: Optional[L.LazyNorm] = None,
+         rows: Optional[int] = None):
+    """y = x W^T for x[rows, K] fp16 (or a lazily normalised fp32 stream `ln`) with a
+    `DeviceLinear`-like object (`.packed` PackedInt4 or `.dense` fp16 [N, K]) and one of
+    the four epilogues.  EPI_FINISH: hout = h + y (+ all-reduce), ss_part = per-tile
+    sums of squares of hout (one total and zeros after an exchange)."""
     lib = L.lib()
-    rows = x.shape[0]
-    dev = x.device
+    rows = x.shape[0] if x is not None else rows
+    dev = x.device if x is not None else (out if out is not None else h).device
     pk, dense = getattr(lin, "packed", None), getattr(lin, "dense", None)
     if pk is None and dense is None:
         pk = lin
@@ -62,13 +75,19 @@ def gemv(lin, x: torch.Tensor, out: Optional[torch.Tensor] = None, mode: int = L
         nv = N
     else:
         nv = n_valid if n_valid is not None else N
+    if mode == L.EPI_FINISH and ss_part is None:
+        ss_part = torch.zeros(rows, -(-N // 128), dtype=torch.float32, device=dev)
     epi = _epi(mode, out, out.stride(0) if out is not None else 0, nv, fin_flags, h, norm_w, xn, extra,
-               local_part, eps)
+               hout, ss_part, eps)
+    xptr = x.data_ptr() if x is not None else None
+    ldx = x.stride(0) if x is not None else 0
     cm = comm if comm is not None else L.null_comm()
     if pk is not None:
         p = L.GemvInt4Params()
-        p.qfrag, p.szfrag, p.x = pk.qfrag.data_ptr(), pk.szfrag.data_ptr(), x.data_ptr()
-        p.ldx, p.rows, p.K, p.KB, p.NTL, p.G = x.stride(0), rows, pk.K, pk.KB, pk.NTL, pk.G
+        p.qfrag, p.szfrag, p.x = pk.qfrag.data_ptr(), pk.szfrag.data_ptr(), xptr
+        p.ldx, p.rows, p.K, p.KB, p.NTL, p.G = ldx, rows, pk.K, pk.KB, pk.NTL, pk.G
+        if ln is not None:
+            p.ln = ln
         p.off32, p.gshift, p.k_splits, p.L = pk.off32, pk.gshift, ks, Lblocks or pk.L
         if k_splits and not Lblocks:
             p.L = -(-pk.KB // (4 * ks))
@@ -76,11 +95,13 @@ def gemv(lin, x: torch.Tensor, out: Optional[torch.Tensor] = None, mode: int = L
         L.check(lib.b2_gemv_int4(C.byref(p), L.stream()), "gemv_int4")
     else:
         p = L.GemvF16Params()
-        p.w, p.x, p.ldw, p.ldx, p.rows = dense.data_ptr(), x.data_ptr(), dense.stride(0), x.stride(0), rows
+        p.w, p.x, p.ldw, p.ldx, p.rows = dense.data_ptr(), xptr, dense.stride(0), ldx, rows
+        if ln is not None:
+            p.ln = ln
         p.K, p.N, p.k_splits, p.kslice = dense.shape[1], dense.shape[0], ks, lin.kslice
         p.scratch, p.counters, p.epi, p.comm = scratch.data_ptr(), counters.data_ptr(), epi, cm
         L.check(lib.b2_gemv_f16(C.byref(p), L.stream()), "gemv_f16")
-    return out
+    return ss_part if mode == L.EPI_FINISH else out
 
 
 def add_rmsnorm(h: torch.Tensor, w: torch.Tensor, delta: Optional[torch.Tensor] = None, eps: float = 1e-6,
@@ -95,10 +116,12 @@ def add_rmsnorm(h: torch.Tensor, w: torch.Tensor, delta: Optional[torch.Tensor] 
     return xn
 
 
-def embed_rmsnorm(embed, row_tokens, rows_meta, seqs, w, h, xn, eps=1e-6):
+def embed_rmsnorm(embed, row_tokens, rows_meta, seqs, w, h, xn=None, ss_part=None, eps=1e-6):
     n, H = h.shape
+    np_ = ss_part.shape[1] if ss_part is not None else 0
     L.check(L.lib().b2_embed_rmsnorm(_vp(embed), _vp(row_tokens), _vp(rows_meta), _vp(seqs), _vp(w), _vp(h),
-                                     _vp(xn), n, H, C.c_float(eps), embed.shape[0], L.stream()), "embed_rmsnorm")
+                                     _vp(xn), _vp(ss_part), np_, n, H, C.c_float(eps), embed.shape[0],
+                                     L.stream()), "embed_rmsnorm")
 
 
 def qknorm_rope_cachew(qkv, rows_meta, q_norm, k_norm, cos_tab, sin_tab, kcache, vcache, nq, nkv, hd, rot,
@@ -129,7 +152,7 @@ def decode_attn(q, rows_meta, kcache, vcache, nq, nkv, hd, gate_off=-1, splits=4
 
 
 def deltanet_step(proj, offs, conv_w, conv_state, state, A_log, dt_bias, norm_w, rows_meta, seq_rows, nk, nv,
-                  dk, dv, xn=None, wa=None, wb=None, out=None, commit=True, eps=1e-6):
+                  dk, dv, xn=None, wa=None, wb=None, out=None, commit=True, eps=1e-6, ln=None):
     """offs = (off_q, off_k, off_v, off_z, off_a, off_b)."""
     n = proj.shape[0]
     if out is None:
@@ -139,6 +162,9 @@ def deltanet_step(proj, offs, conv_w, conv_state, state, A_log, dt_bias, norm_w,
     p.off_q, p.off_k, p.off_v, p.off_z, p.off_a, p.off_b = offs
     if xn is not None:
         p.xn, p.ldx, p.H = xn.data_ptr(), xn.stride(0), xn.shape[1]
+        p.wa, p.wb = wa.data_ptr(), wb.data_ptr()
+    if ln is not None:
+        p.ln, p.H = ln, ln.H
         p.wa, p.wb = wa.data_ptr(), wb.data_ptr()
     p.conv_w, p.conv_state, p.state = conv_w.data_ptr(), conv_state.data_ptr(), state.data_ptr()
     p.A_log, p.dt_bias, p.norm_w = A_log.data_ptr(), dt_bias.data_ptr(), norm_w.data_ptr()

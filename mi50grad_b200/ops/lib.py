@@ -27,6 +27,7 @@ FIN_NO_COMM, FIN_NO_H_WRITE, FIN_SAVE_EXTRA, FIN_ADD_EXTRA, FIN_NO_NORM = 1, 2, 
 FIN_TEST_WITHHOLD_SIGNAL = 32
 LIN_INT4, LIN_F16, LIN_NONE = 0, 1, 2
 STEP_EMBED_TOKENS, STEP_LM_HEAD, STEP_ARGMAX, STEP_ADVANCE, STEP_NO_COMMIT_DELTA = 1, 2, 4, 8, 16
+STEP_MATERIALIZE_XN = 32
 
 vp, i32, f32, i64 = C.c_void_p, C.c_int, C.c_float, C.c_longlong
 
@@ -45,23 +46,27 @@ class SeqState(C.Structure):
     _fields_ = [("len", i32), ("token", i32), ("pad", i32 * 2)]
 
 
+class LazyNorm(C.Structure):
+    _fields_ = [("h", vp), ("ss", vp), ("w", vp), ("np", i32), ("H", i32), ("eps", f32), ("pad", i32)]
+
+
 class GemvEpi(C.Structure):
     _fields_ = [("mode", i32), ("ldo", i32), ("n_valid", i32), ("fin_flags", i32), ("out", vp),
                 ("h", vp), ("norm_w", vp), ("xn", vp), ("extra", vp), ("local_part", vp),
-                ("eps", f32), ("pad", i32)]
+                ("hout", vp), ("ss_part", vp), ("eps", f32), ("pad", i32)]
 
 
 class GemvInt4Params(C.Structure):
     _fields_ = [("qfrag", vp), ("szfrag", vp), ("x", vp),
                 ("ldx", i32), ("rows", i32), ("K", i32), ("KB", i32), ("NTL", i32), ("G", i32),
                 ("off32", i32), ("gshift", i32), ("k_splits", i32), ("L", i32),
-                ("scratch", vp), ("counters", vp), ("epi", GemvEpi), ("comm", CommCtx)]
+                ("scratch", vp), ("counters", vp), ("ln", LazyNorm), ("epi", GemvEpi), ("comm", CommCtx)]
 
 
 class GemvF16Params(C.Structure):
     _fields_ = [("w", vp), ("x", vp), ("ldw", i32), ("ldx", i32), ("rows", i32), ("K", i32), ("N", i32),
                 ("k_splits", i32), ("kslice", i32), ("scratch", vp), ("counters", vp),
-                ("epi", GemvEpi), ("comm", CommCtx)]
+                ("ln", LazyNorm), ("epi", GemvEpi), ("comm", CommCtx)]
 
 
 class AttnParams(C.Structure):
@@ -75,7 +80,7 @@ class DeltaParams(C.Structure):
                 ("off_a", i32), ("off_b", i32), ("xn", vp), ("ldx", i32), ("H", i32), ("wa", vp), ("wb", vp),
                 ("conv_w", vp), ("conv_state", vp), ("state", vp), ("A_log", vp), ("dt_bias", vp),
                 ("norm_w", vp), ("seq_rows", vp), ("rows", vp), ("out", vp), ("ldo", i32), ("nk", i32),
-                ("nv", i32), ("n_seqs", i32), ("eps", f32), ("commit", i32)]
+                ("nv", i32), ("n_seqs", i32), ("eps", f32), ("commit", i32), ("ln", LazyNorm)]
 
 
 class ArgmaxParams(C.Structure):
@@ -92,7 +97,7 @@ class LinearDesc(C.Structure):
 
 class LayerDesc(C.Structure):
     _fields_ = [("type", i32), ("pad", i32), ("in_proj", LinearDesc), ("out_proj", LinearDesc),
-                ("gate_up", LinearDesc), ("down", LinearDesc), ("ffn_norm", vp), ("next_norm", vp),
+                ("gate_up", LinearDesc), ("down", LinearDesc), ("attn_norm", vp), ("ffn_norm", vp), ("next_norm", vp),
                 ("q_norm", vp), ("k_norm", vp), ("kcache", vp), ("vcache", vp),
                 ("wa", vp), ("wb", vp), ("conv_w", vp), ("conv_state", vp), ("state", vp),
                 ("A_log", vp), ("dt_bias", vp), ("la_norm", vp),
@@ -112,7 +117,8 @@ class ModelDesc(C.Structure):
                 ("attn_out", vp), ("ld_attn", i32), ("pad1", i32),
                 ("act", vp), ("logits", vp), ("ld_logits", i32), ("pad2", i32),
                 ("gemv_scratch", vp), ("gemv_counters", vp), ("attn_scratch", vp), ("attn_counters", vp),
-                ("argmax_scratch", vp), ("argmax_counters", vp), ("extra", vp), ("local_part", vp),
+                ("argmax_scratch", vp), ("argmax_counters", vp), ("extra", vp), ("h_tmp", vp),
+                ("ss", vp), ("np", i32), ("pad3", i32),
                 ("rows", vp), ("rows_tmpl", vp), ("seqs", vp), ("row_tokens", vp), ("seq_rows", vp),
                 ("out_tokens", vp), ("comm", CommCtx)]
 

@@ -3,7 +3,7 @@
 INT4 projections are re-packed once, at load time, from the checkpoint's
 K-packed `qweight[K/8, N]` into tensor-core fragment order (see csrc/gemv.cu):
 
-    qfrag [NTL][KB][32 lanes][4 words]   int32
+    qfrag [NTL/4][KB][4 tiles][32 lanes][4 words]   int32   (a warp's 2 KB per k-block is contiguous)
     szfrag[NTL][G ][8][4]                 fp16  (scale n, scale n+8, zero n, zero n+8)
 
 where an n-tile is 16 output features, a k-block 64 input features (two chunks
@@ -30,7 +30,7 @@ GEMV_WK = 4
 
 @dataclass
 class PackedInt4:
-    qfrag: torch.Tensor       # int32 [NTL, KB, 32, 4]
+    qfrag: torch.Tensor       # int32 [NTL/4, KB, 4, 32, 4]
     szfrag: torch.Tensor      # fp16  [NTL, G, 8, 4]
     K: int                    # real input features
     N: int                    # real output features
@@ -59,11 +59,12 @@ def launch_shape(KB: int, NTL: int, rows: int = 1, slots: int = 2 * NUM_SMS) -> 
     fills the 148 SMs (two resident CTAs each) in one wave."""
     ctas_n = NTL * 16 // TILE_N
     k_splits = max(1, min(slots // max(ctas_n, 1), -(-KB // GEMV_WK)))
-    L = -(-KB // (GEMV_WK * k_splits))
+    even = lambda v: v + (v & 1) if KB >= 2 * GEMV_WK else v      # even L enables the aligned-group fast path
+    L = even(-(-KB // (GEMV_WK * k_splits)))
     # shared-memory bound: activation fragments are 64 bytes per chunk per row
-    while 2 * GEMV_WK * L * (rows + 1) * 64 > 150_000:
+    while 2 * GEMV_WK * L * (rows + 1) * 64 > 40_000:
         k_splits += 1
-        L = -(-KB // (GEMV_WK * k_splits))
+        L = even(-(-KB // (GEMV_WK * k_splits)))
     k_splits = -(-KB // (GEMV_WK * L))
     return k_splits, L
 
@@ -104,6 +105,7 @@ def pack_int4(lin: Int4Linear, device=None, rows_hint: int = 1, chunk_tiles: int
         words = (v << shifts).sum(dim=-1)                                          # [tile,KB,j,lane,wi]
         words = torch.where(words >= 2**31, words - 2**32, words).to(torch.int32)
         qfrag[t0:t1] = words.permute(0, 1, 3, 2, 4).reshape(t1 - t0, KB, 32, 4)
+    qfrag = qfrag.reshape(NTL // 4, 4, KB, 32, 4).permute(0, 2, 1, 3, 4).contiguous()
     sc = torch.zeros(G, Np, dtype=torch.float16, device=dev)
     zr = torch.zeros(G, Np, dtype=torch.float16, device=dev)
     sc[:lin.num_groups, :N] = lin.scales.to(dev)
@@ -125,7 +127,7 @@ def random_packed_int4(K: int, N: int, group_size: int = 128, device="cuda",
     KB = -(-K // 64)
     NTL = -(-N // TILE_N) * (TILE_N // 16)
     G = -(-(KB * 64) // group_size)
-    qfrag = torch.randint(-2**31, 2**31 - 1, (NTL, KB, 32, 4), dtype=torch.int64, device=device,
+    qfrag = torch.randint(-2**31, 2**31 - 1, (NTL // 4, KB, 4, 32, 4), dtype=torch.int64, device=device,
                           generator=generator).to(torch.int32)
     sc = torch.rand(NTL, G, 8, 2, device=device, generator=generator) * (scale_hi - scale_lo) + scale_lo
     n_idx = (torch.arange(NTL, device=device)[:, None, None] * 16
@@ -146,7 +148,7 @@ def unpack_fragments(pk: PackedInt4) -> Int4Linear:
     dev = pk.qfrag.device
     idx = _frag_index(dev)
     shifts = (torch.arange(8, device=dev, dtype=torch.int64) * 4)
-    w = pk.qfrag.to(torch.int64) & 0xFFFFFFFF                                      # [NTL,KB,32,4]
+    w = pk.qfrag.permute(0, 2, 1, 3, 4).reshape(pk.NTL, pk.KB, 32, 4).to(torch.int64) & 0xFFFFFFFF
     w = w.reshape(pk.NTL, pk.KB, 32, 2, 2).permute(0, 1, 3, 2, 4)                  # [NTL,KB,j,lane,wi]
     v = ((w.unsqueeze(-1) >> shifts) & 0xF).to(torch.uint8).reshape(pk.NTL, pk.KB, 2, 512)
     w5 = torch.empty_like(v)

@@ -1,0 +1,158 @@
+"""Symmetric-memory communicator over NVLink / NVSwitch.
+
+Every rank allocates the same buffers through PyTorch's symmetric-memory
+allocator (CUDA VMM allocations whose handles are exchanged once at rendezvous),
+maps all peers' copies, and -- when the fabric offers it -- gets a multicast
+mapping so kernels can issue `multimem.ld_reduce` / `multimem.st`.  PyTorch does
+the allocation and the handle exchange; every byte that moves afterwards is
+moved by this package's kernels (csrc/gemv.cu finisher, csrc/comm.cu).
+
+Replaces the reference's single-process peer plumbing: `hipDeviceEnablePeerAccess`
+between all pairs, gather buffers on GPU 0, per-GPU all-reduce streams and
+host-recorded events (reference: src/runtime/tensor_parallel.py:47-58,
+src/runtime/p2p_allreduce.py:73-104, :257-332).
+
+Layout of the symmetric block (bytes):
+    [0, 2*part_floats*4)            partial-sum staging, double-buffered by epoch parity
+    [+0, +gather_floats*4)          two-shot gather area
+    [.., +256)                      flag words: [0,8) phase A, [8,16) phase B (uint32, by source rank)
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import lib as L
+from .comm import CommTimeout, Communicator
+
+KERNEL_NAMES = {1: "gemv finisher", 2: "all-reduce", 3: "arg-max", 4: "barrier", 5: "wait self-test", 6: "gemm reduce-scatter"}
+
+
+class CollParams(C.Structure):
+    _fields_ = [("comm", L.CommCtx), ("in_", C.c_void_p), ("in16", C.c_void_p), ("out", C.c_void_p),
+                ("out16", C.c_void_p), ("gather", C.c_void_p * L.MAX_TP), ("mc_gather", C.c_void_p),
+                ("n", C.c_size_t), ("residual", C.c_int), ("twoshot", C.c_int), ("counters", C.c_void_p),
+                ("test_withhold", C.c_int)]
+
+
+class SymmComm(Communicator):
+    def __init__(self, max_rows: int = 8, hidden: int = 5120, part_floats: Optional[int] = None,
+                 use_multimem: bool = True, wait_us: int = 2_000_000, group=None):
+        super().__init__()
+        import torch.distributed._symmetric_memory as symm_mem
+        if not dist.is_initialized():
+            raise RuntimeError("torch.distributed is not initialised")
+        self.group = group or dist.group.WORLD
+        self.tp_size, self.tp_rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if self.tp_size > L.MAX_TP:
+            raise ValueError(f"at most {L.MAX_TP} ranks")
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.lib = L.lib()
+        if self.lib.b2_sizeof_coll_params() != C.sizeof(CollParams):
+            raise RuntimeError("CollParams layout mismatch")
+        self.part_floats = int(part_floats or max(max_rows * hidden, 4096))
+        self.part_floats = -(-self.part_floats // 64) * 64
+        self.gather_floats = self.part_floats
+        self.off_gather = 2 * self.part_floats * 4
+        self.off_sig = self.off_gather + self.gather_floats * 4
+        nbytes = self.off_sig + 256
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.buf.zero_()
+        self.hdl = symm_mem.rendezvous(self.buf, self.group)
+        self.peer_ptrs: List[int] = [int(p) for p in self.hdl.buffer_ptrs]
+        mc = int(getattr(self.hdl, "multicast_ptr", 0) or 0)
+        self.multicast_ptr = mc if use_multimem else 0
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.counters = torch.zeros(8, dtype=torch.int32, device=self.device)
+        self.wait_ns = int(wait_us) * 1000
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+
+    # -- what kernels see -------------------------------------------------------
+    def ctx(self) -> L.CommCtx:
+        c = L.CommCtx()
+        c.tp, c.rank, c.part_stride = self.tp_size, self.tp_rank, self.part_floats
+        for r in range(self.tp_size):
+            c.part[r] = self.peer_ptrs[r]
+            c.sig[r] = self.peer_ptrs[r] + self.off_sig
+        c.mc_part = self.multicast_ptr or None
+        c.epoch, c.status, c.wait_ns = self.epoch.data_ptr(), self.status.data_ptr(), self.wait_ns
+        return c
+
+    @property
+    def has_multimem(self) -> bool:
+        return bool(self.multicast_ptr)
+
+    def check_status(self):
+        """Raise CommTimeout if any kernel's bounded wait expired since the last check."""
+        st = self.status.tolist()
+        if st[0] != 0:
+            self.status.zero_()
+            raise CommTimeout(f"rank {self.tp_rank}: bounded wait expired in {KERNEL_NAMES.get(st[1], st[1])} "
+                              f"waiting for rank {st[2]} at epoch {st[3]}")
+
+    # -- collectives --------------------------------------------------------------
+    def _params(self, n: int, residual: bool, twoshot: bool) -> CollParams:
+        p = CollParams()
+        p.comm = self.ctx()
+        for r in range(self.tp_size):
+            p.gather[r] = self.peer_ptrs[r] + self.off_gather
+        p.mc_gather = (self.multicast_ptr + self.off_gather) if self.multicast_ptr else None
+        p.n, p.residual, p.twoshot = n, int(residual), int(twoshot)
+        p.counters = self.counters.data_ptr()
+        return p
+
+    def all_reduce_into(self, src: torch.Tensor, out: torch.Tensor, residual: bool = False,
+                        twoshot: Optional[bool] = None, out16: Optional[torch.Tensor] = None,
+                        withhold_signal: bool = False) -> torch.Tensor:
+        """out (fp32) = [out +] sum over ranks of src (fp32 or fp16), in one kernel."""
+        n = src.numel()
+        if n % 4 or n > self.part_floats:
+            raise ValueError(f"payload of {n} elements: need a multiple of 4 and <= {self.part_floats}")
+        if twoshot is None:
+            twoshot = n * 4 > 512 * 1024
+        p = self._params(n, residual, twoshot)
+        if src.dtype == torch.float32:
+            p.in_ = src.data_ptr()
+        elif src.dtype == torch.float16:
+            p.in16 = src.data_ptr()
+        else:
+            raise TypeError("fp32 or fp16 input")
+        p.out = out.data_ptr()
+        p.out16 = None if out16 is None else out16.data_ptr()
+        p.test_withhold = int(withhold_signal)
+        L.check(self.lib.b2_allreduce(C.byref(p), 2 * 148, L.stream()), "allreduce")
+        self.allreduce_calls += 1
+        return out
+
+    def all_reduce_sum(self, t: torch.Tensor) -> torch.Tensor:
+        out = torch.empty(t.shape, dtype=torch.float32, device=t.device)
+        self.all_reduce_into(t.contiguous(), out)
+        return out if t.dtype == torch.float32 else out.to(t.dtype)
+
+    def allreduce_residual(self, partial: torch.Tensor, hidden: torch.Tensor) -> torch.Tensor:
+        return self.all_reduce_into(partial.contiguous(), hidden, residual=True)
+
+    def device_barrier(self, withhold_signal: bool = False):
+        c = self.ctx()
+        L.check(self.lib.b2_barrier(C.byref(c), int(withhold_signal), L.stream()), "barrier")
+
+    def barrier(self):
+        self.device_barrier()
+
+    def all_gather(self, t):
+        outs = [torch.empty_like(t) for _ in range(self.tp_size)]
+        dist.all_gather(outs, t.contiguous(), group=self.group)
+        return outs
+
+    def broadcast(self, t, src=0):
+        dist.broadcast(t, src=src, group=self.group)
+        return t
+
+    def close(self):
+        self.buf = None
+        self.hdl = None

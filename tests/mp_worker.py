@@ -1,0 +1,133 @@
+"""Multi-GPU test worker: run under torch.distributed.run, one rank per GPU.
+    python -m torch.distributed.run --nproc-per-node 2 ... tests/mp_worker.py <scenario> [args]
+Exits non-zero on failure; rank 0 prints 'WORKER-OK <scenario>'."""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import torch
+import torch.distributed as dist
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-12))
+
+
+def scenario_allreduce(multimem: bool):
+    from mi50grad_b200.parallel.symm import SymmComm
+    rank, world = dist.get_rank(), dist.get_world_size()
+    comm = SymmComm(part_floats=512 * 5120, use_multimem=multimem)
+    dev = comm.device
+    for n, twoshot in [(5120, False), (5120, True), (512 * 5120, False), (512 * 5120, True), (40960, None)]:
+        for dtype in (torch.float32, torch.float16):
+            gens = [torch.Generator().manual_seed(100 + r) for r in range(world)]
+            xs = [torch.randn(n, generator=g).to(dtype) for g in gens]
+            ref = sum(x.float() for x in xs)
+            h0 = torch.randn(n, generator=torch.Generator().manual_seed(7))
+            out = h0.to(dev).clone()
+            o16 = torch.zeros(n, dtype=torch.float16, device=dev)
+            for rep in range(3):                      # epochs advance, parity alternates
+                out.copy_(h0)
+                comm.all_reduce_into(xs[rank].to(dev), out, residual=True, twoshot=twoshot, out16=o16)
+            torch.cuda.synchronize()
+            comm.check_status()
+            assert _rel(out.cpu(), h0 + ref) < 1e-5, (n, twoshot, dtype)
+            assert _rel(o16.cpu(), h0 + ref) < 2e-3
+    s = comm.all_reduce_sum(torch.full((64,), float(rank + 1), device=dev))
+    assert torch.allclose(s.cpu(), torch.full((64,), world * (world + 1) / 2.0))
+    comm.device_barrier()
+    torch.cuda.synchronize()
+    comm.check_status()
+    return comm.has_multimem
+
+
+def scenario_tp_engine(ar_mode: str, multimem: bool):
+    """Tiny hybrid model at TP=world on GPUs vs the CPU oracle running the same
+    placement of all-reduces (single process emulation of every rank)."""
+    from mi50grad_b200.config import EngineConfig, tiny_config
+    from mi50grad_b200.engine.tp_engine import TPInferenceEngine
+    from mi50grad_b200.models.oracle import OracleEngine
+    from mi50grad_b200.models.weights import random_model
+    rank, world = dist.get_rank(), dist.get_world_size()
+    cfg = tiny_config()
+    mw = random_model(cfg, 0)
+    eng = TPInferenceEngine(cfg, list(range(world)), max_seq_len=128,
+                            engine_config=EngineConfig(ar_mode=ar_mode, use_multimem=multimem))
+    eng.load_model(mw)
+    ids = torch.randint(0, cfg.vocab_size, (16,), generator=torch.Generator().manual_seed(0)).tolist()
+    toks = eng.generate_tokens(ids, 8, graph=False)
+    toks_g = eng.generate_tokens(ids, 8, graph=True)
+    torch.cuda.synchronize()
+    eng.check_status()
+    assert toks == toks_g, (toks, toks_g)
+    if ar_mode == "exact":
+        ref, _ = OracleEngine(mw, max_seq_len=128).greedy_generate(ids, 8)
+        assert toks == ref, (toks, ref)
+    # every rank must have produced the same tokens
+    t = torch.tensor(toks, device="cuda")
+    ts = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(ts, t)
+    assert all(torch.equal(ts[0], x) for x in ts)
+    lg = eng.compute_logits(None)
+    assert lg.shape[0] == cfg.vocab_size
+    assert eng.get_allreduce_call_count() > 0
+    eng.cleanup()
+
+
+def scenario_wait_timeout():
+    """A flag that nobody raises: the bounded wait must return with a status and
+    leave the context usable.  Plain peer loads, no multicast."""
+    from mi50grad_b200.parallel.comm import CommTimeout
+    from mi50grad_b200.parallel.symm import SymmComm
+    comm = SymmComm(use_multimem=False, wait_us=200_000)
+    dev = comm.device
+    x = torch.ones(4096, device=dev)
+    out = torch.zeros(4096, device=dev)
+    comm.all_reduce_into(x, out, withhold_signal=True)      # every rank withholds: all time out
+    torch.cuda.synchronize()
+    try:
+        comm.check_status()
+    except CommTimeout as e:
+        msg = str(e)
+    else:
+        raise AssertionError("expected CommTimeout")
+    assert "all-reduce" in msg
+    # the context is still usable, and after a host-side re-synchronisation so is the communicator
+    y = (torch.ones(8, device=dev) * 2).sum().item()
+    assert y == 16
+    dist.barrier()
+    comm2 = SymmComm(use_multimem=False)
+    comm2.all_reduce_into(x, out)
+    torch.cuda.synchronize()
+    comm2.check_status()
+    assert float(out[0]) == dist.get_world_size()
+
+
+def main():
+    scenario = sys.argv[1]
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    try:
+        if scenario == "allreduce":
+            mm = scenario_allreduce(sys.argv[2] == "multimem")
+            extra = f"multimem={mm}"
+        elif scenario == "tp_engine":
+            scenario_tp_engine(sys.argv[2], sys.argv[3] == "multimem")
+            extra = sys.argv[2]
+        elif scenario == "wait_timeout":
+            scenario_wait_timeout()
+            extra = ""
+        else:
+            raise SystemExit(f"unknown scenario {scenario}")
+        dist.barrier()
+        if dist.get_rank() == 0:
+            print(f"WORKER-OK {scenario} {extra}", flush=True)
+    finally:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

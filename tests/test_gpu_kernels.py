@@ -88,7 +88,9 @@ def test_gemv_silu_pair(K, rows, F):
 
 
 @pytest.mark.parametrize("rows,ks", [(1, None), (3, 4)])
-def test_gemv_finish_local_residual_rmsnorm(K, rows, ks):
+def test_gemv_finish_local_residual_and_lazy_norm(K, rows, ks):
+    """Row-parallel epilogue without exchange: h += y per tile, per-tile sums of squares;
+    the consumer GEMV applies the RMSNorm while staging its input."""
     from mi50grad_b200.ops import lib as L
     from mi50grad_b200.ops.packing import pack_int4
     from mi50grad_b200.utils.quant import random_int4_linear
@@ -102,22 +104,32 @@ def test_gemv_finish_local_residual_rmsnorm(K, rows, ks):
     h_ref = h0 + y
     xn_ref = h_ref * torch.rsqrt(h_ref.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
     d = _dev()
+    pk = pack_int4(lin, d)
     h = h0.to(d).clone()
-    xn = torch.zeros(rows, H, dtype=torch.float16, device=d)
-    lp = torch.zeros(rows, H, dtype=torch.float32, device=d)
-    K.gemv(pack_int4(lin, d), x.to(d), mode=L.EPI_FINISH, fin_flags=L.FIN_NO_COMM, h=h, norm_w=w.to(d), xn=xn,
-           local_part=lp, k_splits=ks)
+    ss = K.gemv(pk, x.to(d), mode=L.EPI_FINISH, fin_flags=L.FIN_NO_COMM, h=h, k_splits=ks)
     assert _rel(h.cpu(), h_ref) < 1e-4
-    assert _rel(xn.cpu(), xn_ref) < 2e-3
-    # deferred_consistent attention form: h untouched, partial saved, then added to the next partial
+    assert ss.shape == (rows, 40)
+    assert torch.allclose(ss.sum(-1).cpu(), h_ref.pow(2).sum(-1), rtol=1e-4)
+    # consumer: INT4 and fp16 GEMVs reading the lazily normalised stream
+    lin2 = random_int4_linear(H, 256, 128, gen)
+    out = torch.zeros(rows, 256, dtype=torch.float16, device=d)
+    K.gemv(pack_int4(lin2, d), None, out=out, ln=K.lazy_norm(h, ss, w.to(d)), rows=rows)
+    assert _rel(out.cpu(), xn_ref.half().float() @ lin2.dense().t()) < 3e-3
+    from mi50grad_b200.engine.engine import DeviceLinear
+    wd = (torch.randn(300, H, generator=gen) * 0.05).half()
+    out32 = torch.zeros(rows, 300, dtype=torch.float32, device=d)
+    K.gemv(DeviceLinear(dense=wd.to(d)), None, out=out32, mode=L.EPI_STORE_F32, ln=K.lazy_norm(h, ss, w.to(d)),
+           rows=rows)
+    assert _rel(out32.cpu(), xn_ref.half().float() @ wd.float().t()) < 2e-3
+    # deferred_consistent attention form: h untouched, h+y goes to a scratch stream, partial saved;
+    # the following projection adds the saved partial to its own
     h2 = h0.to(d).clone()
+    h_tmp = torch.zeros_like(h2)
     extra = torch.zeros(rows, H, dtype=torch.float32, device=d)
-    K.gemv(pack_int4(lin, d), x.to(d), mode=L.EPI_FINISH,
-           fin_flags=L.FIN_NO_COMM | L.FIN_NO_H_WRITE | L.FIN_SAVE_EXTRA, h=h2, norm_w=w.to(d), xn=xn,
-           local_part=lp, extra=extra)
-    assert torch.equal(h2.cpu(), h0) and _rel(extra.cpu(), y) < 1e-4 and _rel(xn.cpu(), xn_ref) < 2e-3
-    K.gemv(pack_int4(lin, d), x.to(d), mode=L.EPI_FINISH, fin_flags=L.FIN_NO_COMM | L.FIN_ADD_EXTRA, h=h2,
-           norm_w=w.to(d), xn=xn, local_part=lp, extra=extra)
+    K.gemv(pk, x.to(d), mode=L.EPI_FINISH, fin_flags=L.FIN_NO_COMM | L.FIN_NO_H_WRITE | L.FIN_SAVE_EXTRA,
+           h=h2, hout=h_tmp, extra=extra)
+    assert torch.equal(h2.cpu(), h0) and _rel(extra.cpu(), y) < 1e-4 and _rel(h_tmp.cpu(), h_ref) < 1e-4
+    K.gemv(pk, x.to(d), mode=L.EPI_FINISH, fin_flags=L.FIN_NO_COMM | L.FIN_ADD_EXTRA, h=h2, extra=extra)
     assert _rel(h2.cpu(), h0 + 2 * y) < 1e-4
 
 
@@ -155,9 +167,11 @@ def test_add_rmsnorm_and_embed(K):
     row_tokens = torch.tensor([-1, 33], dtype=torch.int32, device=d)
     hh = torch.zeros(2, H, device=d)
     xx = torch.zeros(2, H, dtype=torch.float16, device=d)
-    K.embed_rmsnorm(embed.to(d), row_tokens, rows, seqs, w.to(d), hh, xx)
+    ssp = torch.full((2, 40), 7.0, device=d)
+    K.embed_rmsnorm(embed.to(d), row_tokens, rows, seqs, w.to(d), hh, xx, ssp)
     e = embed[[7, 33]].float()
     assert torch.equal(hh.cpu(), e)
+    assert torch.allclose(ssp[:, 0].cpu(), e.pow(2).sum(-1), rtol=1e-5) and float(ssp[:, 1:].abs().max()) == 0
     assert _rel(xx.cpu(), e * torch.rsqrt(e.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()) < 2e-3
 
 
@@ -215,7 +229,7 @@ def test_decode_attn(K, hd, nq, nkv, splits):
 
 
 @pytest.mark.parametrize("dk,nk,nv,rows_per_seq,inkernel_ab", [(128, 2, 6, [1], True), (64, 2, 4, [3, 1], False),
-                                                              (128, 1, 3, [5], False)])
+                                                              (128, 1, 3, [5], False), (64, 1, 2, [2], "lazy")])
 def test_deltanet_step(K, dk, nk, nv, rows_per_seq, inkernel_ab):
     from mi50grad_b200.models import oracle as O
     gen = torch.Generator().manual_seed(13)
@@ -233,7 +247,10 @@ def test_deltanet_step(K, dk, nk, nv, rows_per_seq, inkernel_ab):
     norm_w = (torch.rand(dv, generator=gen) + 0.5).half()
     S0 = torch.randn(nseq, nv, dk, dv, generator=gen) * 0.1
     hist0 = torch.randn(nseq, conv_dim, 3, generator=gen).half()
-    xn = torch.randn(R, H, generator=gen).half()
+    hres = torch.randn(R, H, generator=gen) * 3
+    wnorm = (torch.rand(H, generator=gen) + 0.5).half()
+    xn = (hres * torch.rsqrt(hres.pow(2).mean(-1, keepdim=True) + 1e-6) * wnorm.float()).half() \
+        if inkernel_ab == "lazy" else torch.randn(R, H, generator=gen).half()
     wa, wb = (torch.randn(nv, H, generator=gen) * 0.05).half(), (torch.randn(nv, H, generator=gen) * 0.05).half()
     if inkernel_ab:
         a_all = (xn.float() @ wa.float().t()).half().float()
@@ -259,8 +276,11 @@ def test_deltanet_step(K, dk, nk, nv, rows_per_seq, inkernel_ab):
     state_d, conv_d = S0.to(d).clone(), conv_state.to(d).clone()
     out = K.deltanet_step(proj.to(d), offs, conv_w.to(d), conv_d, state_d, A_log.to(d), dt_bias.to(d),
                           norm_w.to(d), K.make_rows(entries, d), torch.tensor(seq_rows, dtype=torch.int32, device=d),
-                          nk, nv, dk, dv, xn=xn.to(d) if inkernel_ab else None,
-                          wa=wa.to(d) if inkernel_ab else None, wb=wb.to(d) if inkernel_ab else None)
+                          nk, nv, dk, dv, xn=xn.to(d) if inkernel_ab is True else None,
+                          wa=wa.to(d) if inkernel_ab else None, wb=wb.to(d) if inkernel_ab else None,
+                          ln=K.lazy_norm(hres.to(d), torch.cat([hres.pow(2).sum(-1, keepdim=True),
+                                                                torch.zeros(R, 3)], 1).to(d), wnorm.to(d))
+                          if inkernel_ab == "lazy" else None)
     for s in range(nseq):
         r0, r1 = seq_rows[s], seq_rows[s + 1]
         hist = hist0[s].clone()

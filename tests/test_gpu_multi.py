@@ -1,0 +1,45 @@
+"""Multi-GPU tests: each case launches tests/mp_worker.py with one rank per GPU."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from helpers import free_port
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(nproc, *args, env_extra=None, timeout=600):
+    env = dict(os.environ)
+    env.update(env_extra or {})
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
+           os.path.join(HERE, "mp_worker.py"), *args]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    assert r.returncode == 0 and "WORKER-OK" in r.stdout, f"{r.stdout[-3000:]}\n{r.stderr[-3000:]}"
+    return r.stdout
+
+
+def _n():
+    return min(torch.cuda.device_count(), 8)
+
+
+@pytest.mark.parametrize("mode", ["peer", "multimem"])
+def test_allreduce_oneshot_twoshot(mode):
+    _run(_n(), "allreduce", mode)
+
+
+@pytest.mark.parametrize("ar_mode", ["exact", "deferred_ref", "deferred_consistent"])
+def test_tp_engine_tiny(ar_mode):
+    _run(2, "tp_engine", ar_mode, "multimem")
+
+
+def test_tp_engine_tiny_peer_loads():
+    _run(2, "tp_engine", "exact", "peer")
+
+
+def test_bounded_wait_times_out_cleanly():
+    _run(2, "wait_timeout", env_extra={"NCCL_NVLS_ENABLE": "0"})
