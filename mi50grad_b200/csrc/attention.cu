@@ -18,6 +18,7 @@
 #define ATT_WARPS 4
 #define ATT_THREADS (ATT_WARPS * 32)
 #define ATT_MAX_G 8
+#define ATT_MIN_SPLIT_LEN 32
 
 
 template <int HD>
@@ -30,12 +31,16 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attn_kernel(const AttnPara
     const RowMeta rm = p.rows[r];
     const int extra = rm.mask ? 64 - __clzll((long long)rm.mask) : 0;
     const int total = rm.ctx + extra;
-    const int per = (total + p.splits - 1) / p.splits;
+    // short contexts do not pay for a cross-CTA merge: one split per ATT_MIN_SPLIT_LEN slots
+    const int nsplit = max(1, min(p.splits, (total + ATT_MIN_SPLIT_LEN - 1) / ATT_MIN_SPLIT_LEN));
+    if (sp >= nsplit) return;
+    const int per = (total + nsplit - 1) / nsplit;
     const int s0 = sp * per, s1 = min(total, s0 + per);
 
     __shared__ float sm_m[ATT_WARPS][ATT_MAX_G], sm_l[ATT_WARPS][ATT_MAX_G];
     __shared__ float sm_acc[ATT_WARPS][ATT_MAX_G][HD];
     __shared__ int s_last;
+    __shared__ float sm_f[32][ATT_MAX_G], sm_linv[ATT_MAX_G];
 
     float q[ATT_MAX_G][EPL], acc[ATT_MAX_G][EPL], m[ATT_MAX_G], l[ATT_MAX_G];
 #pragma unroll
@@ -49,23 +54,29 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attn_kernel(const AttnPara
     }
     const size_t base = ((size_t)rm.seq * p.max_seq) * p.nkv * HD + (size_t)kvh * HD + lane * EPL;
     const size_t stride = (size_t)p.nkv * HD;
+    // K/V rows of the next slot are fetched while the current one is processed
+    auto fetch = [&](int s, uint4& kv, uint4& vv) {
+        const __half* kp = p.kcache + base + (size_t)s * stride;
+        const __half* vp = p.vcache + base + (size_t)s * stride;
+        if constexpr (EPL == 8) { kv = *(const uint4*)kp; vv = *(const uint4*)vp; }
+        else if constexpr (EPL == 4) { kv.x = ((const uint2*)kp)->x; kv.y = ((const uint2*)kp)->y; vv.x = ((const uint2*)vp)->x; vv.y = ((const uint2*)vp)->y; }
+        else { kv.x = *(const uint32_t*)kp; vv.x = *(const uint32_t*)vp; }
+    };
+    uint4 kv_n = make_uint4(0u, 0u, 0u, 0u), vv_n = kv_n;
+    if (s0 + warp < s1) fetch(s0 + warp, kv_n, vv_n);
     for (int s = s0 + warp; s < s1; s += ATT_WARPS) {
+        uint4 kv = kv_n, vv = vv_n;
+        if (s + ATT_WARPS < s1) fetch(s + ATT_WARPS, kv_n, vv_n);
         bool vis = s < rm.ctx || ((rm.mask >> (s - rm.ctx)) & 1ull);
         if (!vis) continue;
         float kf[EPL], vf[EPL];
-        const __half* kp = p.kcache + base + (size_t)s * stride;
-        const __half* vp = p.vcache + base + (size_t)s * stride;
-        if constexpr (EPL == 8) {
-            uint4 kv = *(const uint4*)kp, vv = *(const uint4*)vp;
+        {
             const __half2* k2 = (const __half2*)&kv; const __half2* v2 = (const __half2*)&vv;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
+            for (int e = 0; e < EPL / 2; ++e) {
                 float2 a = __half22float2(k2[e]), b = __half22float2(v2[e]);
                 kf[2 * e] = a.x; kf[2 * e + 1] = a.y; vf[2 * e] = b.x; vf[2 * e + 1] = b.y;
             }
-        } else {
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) { kf[e] = __half2float(kp[e]); vf[e] = __half2float(vp[e]); }
         }
 #pragma unroll
         for (int h = 0; h < ATT_MAX_G; ++h) {
@@ -95,6 +106,7 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attn_kernel(const AttnPara
     __syncthreads();
     // thread tid handles (h, d) pairs
     float* my = p.scratch + (((size_t)r * p.nkv + kvh) * p.splits + sp) * G * (HD + 2);
+    const int splits_orig = p.splits;
     for (int i = tid; i < G * HD; i += ATT_THREADS) {
         int h = i / HD, d = i % HD;
         float mm = -INFINITY;
@@ -107,7 +119,7 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attn_kernel(const AttnPara
             ll += sm_l[w][h] * f;
             a += sm_acc[w][h][d] * f;
         }
-        if (p.splits == 1) {
+        if (nsplit == 1) {
             float o = ll > 0.f ? a / ll : 0.f;
             size_t col = (size_t)(kvh * G + h) * HD + d;
             if (p.gate_off >= 0) o *= sigmoid_f(__half2float(p.q[(size_t)r * p.ldq + p.gate_off + col]));
@@ -117,32 +129,46 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attn_kernel(const AttnPara
             if (d == 0) { my[h * (HD + 2) + HD] = mm; my[h * (HD + 2) + HD + 1] = ll; }
         }
     }
-    if (p.splits == 1) return;
+    if (nsplit == 1) return;
     // ---- merge the splits: last CTA of this (row, kv head)
     __threadfence();
     __syncthreads();
     if (tid == 0) {
         int old = atomicAdd(&p.counters[r * p.nkv + kvh], 1);
-        s_last = (old == p.splits - 1);
+        s_last = (old == nsplit - 1);
         if (s_last) p.counters[r * p.nkv + kvh] = 0;
         __threadfence();
     }
     __syncthreads();
     if (!s_last) return;
-    const float* all = p.scratch + (((size_t)r * p.nkv + kvh) * p.splits) * G * (HD + 2);
+    const float* all = p.scratch + (((size_t)r * p.nkv + kvh) * splits_orig) * G * (HD + 2);
+    // phase 1: per (split, head) rescale factors, one round trip
+    if (tid < nsplit * G) {
+        int s = tid / G, h = tid % G;
+        const float* e = &all[(size_t)(s * G + h) * (HD + 2)];
+        sm_f[s][h] = ld_cg_f32(e + HD);                 // max of split s
+        sm_acc[0][h][s] = ld_cg_f32(e + HD + 1);        // its sum (sm_acc is free by now)
+    }
+    __syncthreads();
+    if (tid < G) {
+        float mm = -INFINITY;
+        for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, sm_f[s][tid]);
+        float ll = 0.f;
+        for (int s = 0; s < nsplit; ++s) {
+            float f = (sm_f[s][tid] == -INFINITY) ? 0.f : __expf(sm_f[s][tid] - mm);
+            ll += sm_acc[0][tid][s] * f;
+            sm_f[s][tid] = f;
+        }
+        sm_linv[tid] = ll > 0.f ? 1.f / ll : 0.f;
+    }
+    __syncthreads();
+    // phase 2: weighted sum of the partial outputs; loads of several outputs are in flight together
+#pragma unroll 4
     for (int i = tid; i < G * HD; i += ATT_THREADS) {
         int h = i / HD, d = i % HD;
-        float mm = -INFINITY;
-        for (int s = 0; s < p.splits; ++s) mm = fmaxf(mm, ld_cg_f32(&all[(size_t)(s * G + h) * (HD + 2) + HD]));
-        float ll = 0.f, a = 0.f;
-        for (int s = 0; s < p.splits; ++s) {
-            const float* e = &all[(size_t)(s * G + h) * (HD + 2)];
-            float ms = ld_cg_f32(e + HD);
-            float f = (ms == -INFINITY) ? 0.f : __expf(ms - mm);
-            ll += ld_cg_f32(e + HD + 1) * f;
-            a += ld_cg_f32(e + d) * f;
-        }
-        float o = ll > 0.f ? a / ll : 0.f;
+        float a = 0.f;
+        for (int s = 0; s < nsplit; ++s) a += ld_cg_f32(&all[(size_t)(s * G + h) * (HD + 2) + d]) * sm_f[s][h];
+        float o = a * sm_linv[h];
         size_t col = (size_t)(kvh * G + h) * HD + d;
         if (p.gate_off >= 0) o *= sigmoid_f(__half2float(p.q[(size_t)r * p.ldq + p.gate_off + col]));
         p.out[(size_t)r * p.ldo + col] = __float2half(o);
@@ -150,7 +176,7 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attn_kernel(const AttnPara
 }
 
 B2_API int b2_decode_attn(const AttnParams* p, int hd, cudaStream_t s) {
-    if (p->nq % p->nkv || p->nq / p->nkv > ATT_MAX_G || p->splits < 1) return cudaErrorInvalidValue;
+    if (p->nq % p->nkv || p->nq / p->nkv > ATT_MAX_G || p->splits < 1 || p->splits > 32) return cudaErrorInvalidValue;
     dim3 grid(p->nkv, p->n_rows, p->splits);
     if (hd == 256) decode_attn_kernel<256><<<grid, ATT_THREADS, 0, s>>>(*p);
     else if (hd == 128) decode_attn_kernel<128><<<grid, ATT_THREADS, 0, s>>>(*p);

@@ -77,43 +77,39 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_step_kernel(const DeltaPa
 
     for (int r = r0; r < r1; ++r) {
         const __half* pr = p.proj + (size_t)r * p.ld;
-        // ---- a, b
-        float a_in, b_in;
-        if (p.off_a >= 0) {
-            a_in = __half2float(pr[p.off_a + j]);
-            b_in = __half2float(pr[p.off_b + j]);
-        } else {
-            const __half* x = p.xn + (size_t)r * p.ldx;
+        // ---- phase A (no barrier inside): conv + SiLU of this CTA's channels, partial sums of the
+        // a/b projections.  With a lazily normalised input the 1/rms factor is applied to the
+        // finished dot products, so nothing here waits on it.
+        float sa = 0.f, sb = 0.f;
+        const bool inkernel_ab = p.off_a < 0;
+        if (inkernel_ab) {
             const __half* wa = p.wa + (size_t)j * p.H;
             const __half* wb = p.wb + (size_t)j * p.H;
-            float sa = 0.f, sb = 0.f;
-            float inv = 0.f;
             if (p.ln.h) {
-                if (kr == 0) { float v = lazy_inv_rms(p.ln, r, lane); if (lane == 0) red32[31] = v; }
-                __syncthreads();
-                inv = red32[31];
-            }
-            for (int i = tid * 2; i < p.H; i += DN_THREADS * 2) {
-                float2 xv;
-                if (p.ln.h) {
-                    float2 hv = *(const float2*)(p.ln.h + (size_t)r * p.ln.H + i);
+                const float* hr = p.ln.h + (size_t)r * p.ln.H;
+                for (int i = tid * 2; i < p.H; i += DN_THREADS * 2) {
+                    float2 hv = *(const float2*)(hr + i);
                     float2 ww = __half22float2(*(const __half2*)(p.ln.w + i));
-                    xv = __half22float2(__floats2half2_rn(hv.x * inv * ww.x, hv.y * inv * ww.y));
-                } else {
-                    xv = __half22float2(*(const __half2*)(x + i));
+                    float2 av = __half22float2(*(const __half2*)(wa + i));
+                    float2 bv = __half22float2(*(const __half2*)(wb + i));
+                    float x0 = hv.x * ww.x, x1 = hv.y * ww.y;
+                    sa += x0 * av.x + x1 * av.y;
+                    sb += x0 * bv.x + x1 * bv.y;
                 }
-                float2 av = __half22float2(*(const __half2*)(wa + i));
-                float2 bv = __half22float2(*(const __half2*)(wb + i));
-                sa += xv.x * av.x + xv.y * av.y;
-                sb += xv.x * bv.x + xv.y * bv.y;
+            } else {
+                const __half* x = p.xn + (size_t)r * p.ldx;
+                for (int i = tid * 2; i < p.H; i += DN_THREADS * 2) {
+                    float2 xv = __half22float2(*(const __half2*)(x + i));
+                    float2 av = __half22float2(*(const __half2*)(wa + i));
+                    float2 bv = __half22float2(*(const __half2*)(wb + i));
+                    sa += xv.x * av.x + xv.y * av.y;
+                    sb += xv.x * bv.x + xv.y * bv.y;
+                }
             }
-            sa = block_sum(sa, red32);
-            sb = block_sum(sb, red32);
-            // the projection output is an fp16 activation in the unfused path: keep that rounding
-            a_in = __half2float(__float2half(sa));
-            b_in = __half2float(__float2half(sb));
+            sa = warp_sum(sa);
+            sb = warp_sum(sb);
+            if (lane == 0) { red_m[kr][0] = sa; red_m[kr][1] = sb; }
         }
-        // ---- causal conv + SiLU on this CTA's channels
         for (int c = tid; c < NCH; c += DN_THREADS) {
             float x = __half2float(pr[proj_col(c)]);
             float o = hist[c][0] * cw[c][0] + hist[c][1] * cw[c][1] + hist[c][2] * cw[c][2] + x * cw[c][3];
@@ -122,6 +118,7 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_step_kernel(const DeltaPa
             if (c < DK) cq[c] = o; else if (c < 2 * DK) ck[c - DK] = o; else cv[c - 2 * DK] = o;
         }
         __syncthreads();
+        // ---- phase B: warps 0..2 the q/k norms and q.k, warp 3 the a/b inputs
         if (kr < 3) {
             float s = 0.f;
             for (int i = lane; i < DK; i += 32) {
@@ -130,16 +127,32 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_step_kernel(const DeltaPa
             }
             s = warp_sum(s);
             if (lane == 0) red32[kr] = s;
+        } else if (kr == 3) {
+            float a_in, b_in;
+            if (inkernel_ab) {
+                float inv = p.ln.h ? lazy_inv_rms(p.ln, r, lane) : 1.f;
+                float ta = 0.f, tb = 0.f;
+#pragma unroll
+                for (int w = 0; w < 8; ++w) { ta += red_m[w][0]; tb += red_m[w][1]; }
+                // the unfused path rounds the projection output to fp16: keep that rounding
+                a_in = __half2float(__float2half(ta * inv));
+                b_in = __half2float(__float2half(tb * inv));
+            } else {
+                a_in = __half2float(pr[p.off_a + j]);
+                b_in = __half2float(pr[p.off_b + j]);
+            }
+            if (lane == 0) { red32[3] = a_in; red32[4] = b_in; }
         }
         __syncthreads();
         const float invq = rsqrtf(red32[0] + 1e-6f) * rsqrtf((float)DK);
         const float invk = rsqrtf(red32[1] + 1e-6f);
         const float kq = red32[2] * invq * invk;
+        const float a_in = red32[3], b_in = red32[4];
         float gl = neg_expA * (a_in + dtb > 20.f ? a_in + dtb : log1pf(__expf(a_in + dtb)));
         gl = fmaxf(gl, -20.f);
         const float decay = __expf(gl);
         const float beta = sigmoid_f(b_in);
-        // ---- single pass over the state slice: m = S^T k, sq = S^T q
+        // ---- phase C: single pass over the state slice: m = S^T k, sq = S^T q
         float mp = 0.f, qp = 0.f;
 #pragma unroll
         for (int i = 0; i < RPT; ++i) {
@@ -169,7 +182,7 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_step_kernel(const DeltaPa
             float o = y * rsqrtf(tot / (float)DV + p.eps) * nw * silu_f(z);
             p.out[(size_t)r * p.ldo + j * DV + cb * DN_COLS + vcol] = __float2half(o);
         }
-        __syncthreads();
+        // the cluster barrier above also orders this row's shared-memory reads before the next row's writes
     }
     cluster.sync();                              // no CTA leaves while a peer may still read its shared memory
     if (!p.commit) return;

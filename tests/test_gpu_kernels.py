@@ -210,11 +210,11 @@ def test_decode_attn(K, hd, nq, nkv, splits):
     from mi50grad_b200.models import oracle as O
     gen = torch.Generator().manual_seed(12)
     d = _dev()
-    max_seq, nseq = 300, 2
+    max_seq, nseq = 1200, 2
     kc = torch.randn(nseq, max_seq, nkv, hd, generator=gen).half()
     vc = torch.randn(nseq, max_seq, nkv, hd, generator=gen).half()
     # rows: plain decode at ctx 200 (seq 1), ctx 3 (seq 0), a draft node with a sparse ancestor mask, ctx 0
-    entries = [(1, 200, 200, 200, 1), (0, 3, 3, 3, 1), (1, 0, 0, 100, 0b1011), (0, 0, 0, 0, 1)]
+    entries = [(1, 1100, 1100, 1100, 1), (0, 3, 3, 3, 1), (1, 0, 0, 100, 0b1011), (0, 0, 0, 0, 1), (0, 300, 300, 300, 1)]
     rows = len(entries)
     q = torch.randn(rows, 2 * nq * hd, generator=gen).half()
     out = K.decode_attn(q.to(d), K.make_rows(entries, d), kc.to(d), vc.to(d), nq, nkv, hd, gate_off=nq * hd,
