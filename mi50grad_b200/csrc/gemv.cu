@@ -602,3 +602,108 @@ B2_API int b2_gemv_f16(const GemvF16Params* p, cudaStream_t stream) {
 B2_API int b2_sizeof_gemv_int4_params() { return (int)sizeof(GemvInt4Params); }
 B2_API int b2_sizeof_gemv_f16_params() { return (int)sizeof(GemvF16Params); }
 B2_API int b2_sizeof_comm_ctx() { return (int)sizeof(CommCtx); }
+
+// ---------------------------------------------------------------------------
+// Allocation-free entry point (see gemv_noalloc.h).  The scratch block is a file-scope
+// device array; in host code its name is only a handle, so the device address is looked
+// up once per device with cudaGetSymbolAddress and that pointer is what the kernel gets.
+// ---------------------------------------------------------------------------
+#include <mutex>
+#include "gemv_noalloc.h"
+
+#define B2_NOALLOC_COUNTER_BYTES 4096u
+#define B2_NOALLOC_MAX_DEVICES 64
+
+static __device__ __align__(256) unsigned char b2_noalloc_scratch[B2_NOALLOC_SCRATCH_BYTES];
+
+static void noalloc_launch_shape(int KB, int NTL, int rows, int* k_splits, int* L) {
+    // same choice as ops/packing.py:launch_shape: fill 2 x 148 CTA slots in one wave, even L
+    const int ctas_n = NTL * 16 / GEMV_TILE_N;
+    int ks = (2 * 148) / (ctas_n > 0 ? ctas_n : 1);
+    const int ks_max = (KB + GEMV_WK - 1) / GEMV_WK;
+    if (ks > ks_max) ks = ks_max;
+    if (ks < 1) ks = 1;
+    auto even = [&](int v) { return (KB >= 2 * GEMV_WK) ? v + (v & 1) : v; };
+    int l = even((KB + GEMV_WK * ks - 1) / (GEMV_WK * ks));
+    while ((size_t)2 * GEMV_WK * l * (rows + 1) * 64 > 40000u) {
+        ++ks;
+        l = even((KB + GEMV_WK * ks - 1) / (GEMV_WK * ks));
+    }
+    *L = l;
+    *k_splits = (KB + GEMV_WK * l - 1) / (GEMV_WK * l);
+}
+
+B2_API size_t b2_gemv_int4_noalloc_required(int rows, int K, int N) {
+    if (rows < 1 || K < 8 || N < 1) return 0;
+    const int KB = (K + 63) / 64, NTL = (N + GEMV_TILE_N - 1) / GEMV_TILE_N * (GEMV_TILE_N / 16);
+    int ks, L;
+    noalloc_launch_shape(KB, NTL, rows, &ks, &L);
+    const size_t partial = ks > 1 ? (size_t)ks * rows * NTL * 16 * sizeof(float) : 0;
+    return B2_NOALLOC_COUNTER_BYTES + partial;
+}
+
+B2_API const char* b2_gemv_int4_noalloc_strerror(int code) {
+    switch (code) {
+        case B2_NOALLOC_OK: return "ok";
+        case B2_NOALLOC_ERR_BAD_ARGUMENT:
+            return "bad argument: null pointer, rows outside 1..8, K not a multiple of 8, or unsupported group size/offset";
+        case B2_NOALLOC_ERR_TOO_LARGE:
+            return "problem needs more scratch than the built-in block (B2_NOALLOC_SCRATCH_BYTES); use b2_gemv_int4 with a caller-provided buffer";
+        case B2_NOALLOC_ERR_SYMBOL: return "could not obtain the device address of the built-in scratch block";
+        default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown error";
+    }
+}
+
+B2_API int b2_gemv_int4_noalloc(const void* qfrag, const void* szfrag, const void* x, int ldx, void* out, int ldo,
+                                int rows, int K, int N, int group_size, int group_offset, cudaStream_t stream) {
+    if (!qfrag || !szfrag || !x || !out || rows < 1 || rows > B2_MAX_ROWS || K < 8 || (K & 7) || N < 1 ||
+        ldx < K || ldo < N)
+        return B2_NOALLOC_ERR_BAD_ARGUMENT;
+    int gshift;
+    switch (group_size) {
+        case 32: gshift = 0; break;
+        case 64: gshift = 1; break;
+        case 128: gshift = 2; break;
+        case 256: gshift = 3; break;
+        default: return B2_NOALLOC_ERR_BAD_ARGUMENT;
+    }
+    if (group_offset < 0 || group_offset >= group_size || (group_offset & 31)) return B2_NOALLOC_ERR_BAD_ARGUMENT;
+    const int KB = (K + 63) / 64, NTL = (N + GEMV_TILE_N - 1) / GEMV_TILE_N * (GEMV_TILE_N / 16);
+    if ((size_t)(NTL * 16 / GEMV_TILE_N + 1) * sizeof(int) > B2_NOALLOC_COUNTER_BYTES) return B2_NOALLOC_ERR_TOO_LARGE;
+    if (b2_gemv_int4_noalloc_required(rows, K, N) > B2_NOALLOC_SCRATCH_BYTES) return B2_NOALLOC_ERR_TOO_LARGE;
+
+    // ---- once per device: device address of the scratch block (the current device's copy)
+    static std::mutex mu;
+    static unsigned char* dev_ptr[B2_NOALLOC_MAX_DEVICES] = {nullptr};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= B2_NOALLOC_MAX_DEVICES) return B2_NOALLOC_ERR_SYMBOL;
+    unsigned char* base;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!dev_ptr[dev]) {
+            void* ptr = nullptr;
+            e = cudaGetSymbolAddress(&ptr, b2_noalloc_scratch);
+            if (e != cudaSuccess || !ptr) return B2_NOALLOC_ERR_SYMBOL;
+            dev_ptr[dev] = (unsigned char*)ptr;
+        }
+        base = dev_ptr[dev];
+    }
+    // ---- counters must start at zero; partial sums are overwritten before they are read
+    e = cudaMemsetAsync(base, 0, B2_NOALLOC_COUNTER_BYTES, stream);
+    if (e != cudaSuccess) return (int)e;
+
+    GemvInt4Params p;
+    memset(&p, 0, sizeof(p));
+    p.qfrag = (const uint4*)qfrag; p.szfrag = (const uint2*)szfrag; p.x = (const __half*)x;
+    p.ldx = ldx; p.rows = rows; p.K = K; p.KB = KB; p.NTL = NTL;
+    p.G = (KB * 64 + group_offset + group_size - 1) / group_size;
+    p.off32 = group_offset / 32; p.gshift = gshift;
+    noalloc_launch_shape(KB, NTL, rows, &p.k_splits, &p.L);
+    p.counters = (int*)base;
+    p.scratch = (float*)(base + B2_NOALLOC_COUNTER_BYTES);
+    p.epi.mode = EPI_STORE_F16; p.epi.out = out; p.epi.ldo = ldo; p.epi.n_valid = N;
+    p.comm.tp = 1;
+    return b2_gemv_int4(&p, stream);
+}
