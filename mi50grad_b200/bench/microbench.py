@@ -96,9 +96,102 @@ def bench_gemv(tp: int, rows: int, iters: int, only=None):
     return out
 
 
+def bench_fused(iters: int):
+    """BASELINE config 2: row-parallel INT4 GEMV + all-reduce + residual add (+ lazy RMSNorm sums) as ONE
+    kernel at TP = world size, and stand-alone all-reduces of 10 KB / 5 MB, each against NCCL
+    all-reduce plus separate kernels.  Run under torch.distributed.run; times are max over ranks."""
+    import torch.distributed as dist
+    from ..config import qwen35_27b
+    from ..ops import kernels as K
+    from ..ops import lib as L
+    from ..ops.packing import random_packed_int4
+    from ..parallel.symm import SymmComm
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    tp, rank = dist.get_world_size(), dist.get_rank()
+    dev = torch.device("cuda", local)
+    cfg = qwen35_27b()
+    H = cfg.hidden_size
+    hbm, _, src = measured_peaks()
+    results = []
+
+    def mx(us):
+        t = torch.tensor([us], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for multimem in (True, False):
+        comm = SymmComm(part_floats=512 * H, use_multimem=multimem)
+        ctx = comm.ctx()
+        for name, Kfull in (("o_proj", cfg.full_attn_q_dim), ("down_proj", cfg.intermediate_size)):
+            Kd = Kfull // tp
+            nvar = 8
+            pks = [random_packed_int4(Kd, H, 128, dev) for _ in range(nvar)]
+            x = torch.randn(1, Kd, device=dev).half()
+            h = torch.zeros(1, H, device=dev)
+            ss = torch.zeros(1, H // 128, device=dev)
+            scratch = torch.empty(max(1, pks[0].k_splits * pks[0].n_pad), device=dev)
+            counters = torch.zeros(pks[0].n_pad // 128 + 2, dtype=torch.int32, device=dev)
+            part = torch.zeros(1, H, device=dev)
+
+            def fused(i):
+                K.gemv(pks[i], x, mode=L.EPI_FINISH, h=h, ss_part=ss, comm=ctx, scratch=scratch, counters=counters)
+
+            def unfused(i):
+                K.gemv(pks[i], x, out=part, mode=L.EPI_STORE_F32, scratch=scratch, counters=counters)
+                dist.all_reduce(part)
+                K.add_rmsnorm(h, torch.ones(H, dtype=torch.float16, device=dev), part)
+            dist.barrier()
+            us_f = mx(time_launches(fused, nvar, iters))
+            dist.barrier()
+            us_u = mx(time_launches(unfused, nvar, iters))
+            comm.check_status()
+            # roofline: the slower of streaming this rank's weight shard from HBM and moving the
+            # partial vectors over NVLink (20 KB per peer, latency bound: reported for context)
+            t_hbm = pks[0].nbytes() / (hbm * 1e3)
+            results.append({"kernel": "int4_gemv_ar_residual", "shape": name, "K_local": Kd, "N": H, "tp": tp,
+                            "multimem": comm.has_multimem, "fused_us": round(us_f, 2),
+                            "gemv+nccl+add_us": round(us_u, 2), "speedup": round(us_u / us_f, 2),
+                            "hbm_floor_us": round(t_hbm, 2), "frac_of_roofline": round(t_hbm / us_f, 3),
+                            "peak_source": src})
+            if rank == 0:
+                print(json.dumps(results[-1]), flush=True)
+        for n, label in ((H, "10KB fp16 payload (5120 elems)"), (512 * H, "5MB fp16 payload (512x5120)")):
+            src_t = torch.randn(n, device=dev).half()
+            out = torch.zeros(n, device=dev)
+            for twoshot in (False, True):
+                def ours(i):
+                    comm.all_reduce_into(src_t, out, residual=True, twoshot=twoshot)
+                dist.barrier()
+                us = mx(time_launches(ours, 1, iters))
+                comm.check_status()
+                results.append({"kernel": "allreduce_residual", "payload": label, "tp": tp,
+                                "algo": "two-shot" if twoshot else "one-shot", "multimem": comm.has_multimem,
+                                "us": round(us, 2)})
+                if rank == 0:
+                    print(json.dumps(results[-1]), flush=True)
+            if multimem:
+                buf = torch.randn(n, device=dev).half()
+                acc = torch.zeros(n, device=dev)
+
+                def nccl(i):
+                    dist.all_reduce(buf)
+                    K.residual_add_(acc, buf)
+                dist.barrier()
+                us = mx(time_launches(nccl, 1, iters))
+                results.append({"kernel": "nccl_allreduce+residual_add", "payload": label, "tp": tp, "us": round(us, 2)})
+                if rank == 0:
+                    print(json.dumps(results[-1]), flush=True)
+        comm.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    return results
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv"])
+    ap.add_argument("what", choices=["gemv", "fused"])
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--iters", type=int, default=20)
@@ -106,6 +199,8 @@ def main(argv=None):
     a = ap.parse_args(argv)
     if a.what == "gemv":
         bench_gemv(a.tp, a.rows, a.iters, a.only)
+    else:
+        bench_fused(a.iters)
 
 
 if __name__ == "__main__":

@@ -56,7 +56,7 @@ __device__ __forceinline__ void signal_all(const CommCtx& c, int base, uint32_t 
 }
 
 // grid must be fully resident (host clamps it): CTAs wait for work done by other CTAs.
-__global__ void __launch_bounds__(512) allreduce_kernel(const CollParams p) {
+__global__ void __launch_bounds__(512, 2) allreduce_kernel(const CollParams p) {
     const CommCtx& c = p.comm;
     const int tp = c.tp, rank = c.rank;
     const uint32_t epoch = *c.epoch + 1u;
@@ -88,6 +88,9 @@ __global__ void __launch_bounds__(512) allreduce_kernel(const CollParams p) {
     if (s_last && !p.test_withhold) signal_all(c, 0, epoch);
     const bool ok = wait_all(c, 0, epoch, B2_KID_ALLREDUCE);
 
+    const float* peer[B2_MAX_TP];
+#pragma unroll
+    for (int r = 0; r < B2_MAX_TP; ++r) peer[r] = c.part[r < tp ? r : 0] + poff;
     auto emit = [&](size_t i, float4 s) {
         float4* o = (float4*)p.out + i;
         if (p.residual) { float4 h = *o; s.x += h.x; s.y += h.y; s.z += h.z; s.w += h.w; }
@@ -102,22 +105,40 @@ __global__ void __launch_bounds__(512) allreduce_kernel(const CollParams p) {
         if (!ok) return mine[i];
         if (c.mc_part) return multimem_ld_reduce_v4(c.mc_part + poff + 4 * i);
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < tp; ++r) {
-            float4 v = ld_relaxed_sys_v4(c.part[r] + poff + 4 * i);
-            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+#pragma unroll
+        for (int r = 0; r < B2_MAX_TP; ++r) {
+            if (r < tp) {
+                float4 v = ld_relaxed_sys_v4(peer[r] + 4 * i);
+                s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+            }
         }
         return s;
     };
 
     if (!p.twoshot) {
-        for (size_t i = gtid; i < n4; i += gsz) emit(i, reduce_at(i));
+        // four elements per step: their loads are issued together, then the results are stored
+        for (size_t i0 = gtid; i0 < n4; i0 += 4 * gsz) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) if (i0 + u * gsz < n4) v[u] = reduce_at(i0 + u * gsz);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) if (i0 + u * gsz < n4) emit(i0 + u * gsz, v[u]);
+        }
     } else {
         // ---- 2. reduce this rank's slice and store it into every rank's gather buffer
         const size_t per = (n4 + tp - 1) / tp, lo = per * rank, hi = min(n4, lo + per);
-        for (size_t i = lo + gtid; i < hi; i += gsz) {
-            float4 s = reduce_at(i);
-            if (p.mc_gather) multimem_st_v4(p.mc_gather + 4 * i, s);
-            else for (int r = 0; r < tp; ++r) ((float4*)p.gather[r])[i] = s;
+        for (size_t i0 = lo + gtid; i0 < hi; i0 += 4 * gsz) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) if (i0 + u * gsz < hi) v[u] = reduce_at(i0 + u * gsz);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                size_t i = i0 + u * gsz;
+                if (i < hi) {
+                    if (p.mc_gather) multimem_st_v4(p.mc_gather + 4 * i, v[u]);
+                    else for (int r = 0; r < tp; ++r) ((float4*)p.gather[r])[i] = v[u];
+                }
+            }
         }
         __threadfence_system();
         __syncthreads();
@@ -130,9 +151,15 @@ __global__ void __launch_bounds__(512) allreduce_kernel(const CollParams p) {
         if (s_last && !p.test_withhold) signal_all(c, B2_MAX_TP, epoch);
         const bool ok2 = wait_all(c, B2_MAX_TP, epoch, B2_KID_ALLREDUCE);
         const float* mygather = p.gather[rank];
-        for (size_t i = gtid; i < n4; i += gsz) {
-            float4 s = ok2 ? ld_relaxed_sys_v4(mygather + 4 * i) : mine[i];
-            emit(i, s);
+        for (size_t i0 = gtid; i0 < n4; i0 += 4 * gsz) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                size_t i = i0 + u * gsz;
+                if (i < n4) v[u] = ok2 ? ld_relaxed_sys_v4(mygather + 4 * i) : mine[i];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) if (i0 + u * gsz < n4) emit(i0 + u * gsz, v[u]);
         }
     }
     // ---- the last CTA to finish advances the epoch
@@ -149,6 +176,17 @@ B2_API int b2_allreduce(const CollParams* p, int max_ctas, cudaStream_t s) {
     if (p->n % 4 || p->n > (size_t)p->comm.part_stride) return cudaErrorInvalidValue;
     size_t n4 = p->n / 4;
     int ctas = (int)((n4 + 511) / 512);
+    // CTAs wait on one another, so the whole grid must be resident: ask the runtime how many fit
+    static int resident = 0;
+    if (!resident) {
+        int dev = 0, sms = 0, per_sm = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, allreduce_kernel, 512, 0) != cudaSuccess || per_sm < 1)
+            return cudaErrorLaunchOutOfResources;
+        resident = sms * per_sm;
+    }
+    if (max_ctas > resident) max_ctas = resident;
     if (ctas > max_ctas) ctas = max_ctas;
     if (ctas < 1) ctas = 1;
     allreduce_kernel<<<ctas, 512, 0, s>>>(*p);

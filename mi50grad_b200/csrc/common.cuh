@@ -30,6 +30,7 @@ struct CommCtx {
     uint32_t* epoch;              // local: number of collective calls completed
     int* status;                  // local: [0]=code [1]=kernel id [2]=peer [3]=epoch
     long long wait_ns;            // bound of every spin-wait
+    long long* trace;             // optional [8] globaltimer stamps of the last exchange (null: off)
 };
 
 // Device-resident description of one token row of a decode/verify step.  A
@@ -83,12 +84,9 @@ __device__ __forceinline__ uint2 ldg_nc_v2(const void* p) {
     return r;
 }
 // Loads that must observe another GPU's (or another CTA's) fresh writes.
-__device__ __forceinline__ float4 ld_relaxed_sys_v4(const float* p) {
-    float4 r;
-    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
-                 : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(p));
-    return r;
-}
+// Data loads that follow an acquire of the producer's flag: weak loads that bypass L1 (peer and
+// local memory alike are then read at the home L2), not volatile, so that many are in flight.
+__device__ __forceinline__ float4 ld_relaxed_sys_v4(const float* p) { return __ldcg((const float4*)p); }
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
     uint32_t s = (uint32_t)__cvta_generic_to_shared(smem_dst);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(s), "l"(gmem_src) : "memory");
@@ -110,12 +108,12 @@ __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
 }
 __device__ __forceinline__ float4 multimem_ld_reduce_v4(const float* mc) {
     float4 r;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
-                 : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(mc) : "memory");
+    asm("multimem.ld_reduce.weak.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+        : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(mc));
     return r;
 }
 __device__ __forceinline__ void multimem_st_v4(float* mc, float4 v) {
-    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1,%2,%3,%4};"
                  :: "l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 __device__ __forceinline__ long long globaltimer_ns() {
@@ -126,15 +124,24 @@ __device__ __forceinline__ long long globaltimer_ns() {
 
 // Spin until *p has reached `target` (wrap-safe) or `budget_ns` has passed.
 // Never unbounded: on expiry the caller records a status and carries on.
+__device__ __forceinline__ uint32_t ld_relaxed_sys_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ bool wait_reached(const uint32_t* p, uint32_t target, long long budget_ns) {
-    if ((int)(ld_acquire_sys_u32(p) - target) >= 0) return true;
-    long long t0 = globaltimer_ns();
-    for (;;) {
+    // spin on relaxed loads, then one acquire fence orders the data reads that follow
+    bool ok = (int)(ld_relaxed_sys_u32(p) - target) >= 0;
+    if (!ok) {
+        long long t0 = globaltimer_ns();
+        for (;;) {
 #pragma unroll 1
-        for (int i = 0; i < 64; ++i)
-            if ((int)(ld_acquire_sys_u32(p) - target) >= 0) return true;
-        if (globaltimer_ns() - t0 > budget_ns) return false;
+            for (int i = 0; i < 256 && !ok; ++i) ok = (int)(ld_relaxed_sys_u32(p) - target) >= 0;
+            if (ok || globaltimer_ns() - t0 > budget_ns) break;
+        }
     }
+    asm volatile("fence.acquire.sys;" ::: "memory");
+    return ok;
 }
 
 __device__ __forceinline__ void report_timeout(const CommCtx& c, int kernel_id, int peer, uint32_t epoch) {

@@ -1,0 +1,386 @@
+// Prefill / batched-decode GEMM on the 5th-generation tensor cores:
+//   C[t][n] = sum_k X[t][k] * W[k][n],  X fp16 activations, W INT4 (group-wise scale/zero),
+//   fp32 accumulation in tensor memory.
+//
+// Replaces the reference's prefill GEMM family (reference:
+// src/kernels/gemm_int4_prefill_hip.hip:27, gemm_int4_prefill_v2.hip:41,
+// gemm_fp16_prefill.hip:47, gemm_fp16_prefill_silu_dual.hip:62, src/asm/gemm_*.s), which
+// runs 64x64x16 tiles on vector ALUs.
+//
+// One CTA computes a [128 outputs x T tokens] tile (T <= 512, all of tensor memory):
+//   * the WEIGHT tile is the MMA's A operand (M = 128 outputs), the activations are the B
+//     operand (N = tokens, any multiple of 16 up to 256 per instruction), so a weight tile is
+//     dequantised once and used for every token, and a batch of 16..80 rows costs no padding;
+//   * warps 0-3 stream the packed nibbles (same fragment order the decode GEMV uses), expand
+//     them to fp16 with the 0x6400 trick, apply (q - zero) * scale and store the tile into
+//     shared memory in the K-major 128-byte-swizzled layout tcgen05 reads;
+//   * warp 4 (one lane) brings the activation tile with TMA (cp.async.bulk.tensor, 128-byte
+//     swizzle, no cluster broadcast) and signals an mbarrier;
+//   * warp 5 (one lane) issues tcgen05.mma (cta_group::1, kind::f16) on shared-memory
+//     descriptors and releases stages with tcgen05.commit;
+//   * warps 0-3 then read the accumulators back with tcgen05.ld and run the epilogue
+//     (store, SiLU(gate)*up for the interleaved gate/up matrix, or residual add).
+// Every mbarrier wait is bounded; on expiry the kernel records a status, skips the rest of
+// its work, releases its tensor memory and returns.
+#include <cuda.h>
+#include "kernels.cuh"
+
+#define TC_THREADS 192
+#define TC_BK 64                 // k per stage (128 bytes of fp16: one swizzle row)
+#define TC_BM 128                // outputs per CTA (MMA M)
+#define TC_A_BYTES (TC_BM * TC_BK * 2)
+#define TC_WAIT_NS 1000000000LL  // bound of every barrier wait
+
+#define TC_EPI_STORE_F16 0
+#define TC_EPI_SILU_PAIR 1
+#define TC_EPI_STORE_F32 2
+#define TC_EPI_RESID_F32 3       // out32[t][n] += y
+
+struct GemmTcParams {
+    const uint4* qfrag;      // [NTL/4][KB][4][32] packed nibbles
+    const uint2* szfrag;     // [NTL][G][8]
+    int K, KB, NTL, G, off32, gshift;
+    int T;                   // token rows in this launch's activation matrix
+    int t_tile;              // tokens per CTA (multiple of 16, <= 512)
+    int n_valid, ldo, epi, stages;
+    void* out;
+    int* status;             // [0] set to 1 when a bounded wait expired
+};
+
+// ---------------------------------------------------------------------------
+// PTX helpers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (and raises *abort_flag) when the time budget is exhausted or
+// another role has already given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    long long t0 = globaltimer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (globaltimer_ns() - t0 > TC_WAIT_NS) { *abort_flag = 1; return false; }
+    }
+}
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        :: "r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 :: "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                                // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                      // stride byte offset: next 8-row group
+    d |= (uint64_t)1 << 46;                                // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                                // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: fp16 x fp16 -> fp32, both operands K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t make_idesc_f16(int n) {
+    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------
+// Kernel
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t tc_nib_lo(uint32_t w) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(r) : "r"(w));
+    return r;
+}
+__device__ __forceinline__ uint32_t tc_nib_hi(uint32_t w) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(r) : "r"(w));
+    return r;
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xmap) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // the dynamic window is only guaranteed 16-byte aligned: align to the 1024-byte swizzle atom by hand
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int S = p.stages;
+    const int t0 = blockIdx.y * p.t_tile;
+    const int Tp = (min(p.t_tile, p.T - t0) + 15) & ~15;          // token columns of this CTA
+    const int boxes = (Tp + 63) / 64;
+    const int b_stage_bytes = ((p.t_tile + 63) / 64) * 64 * 128;
+    unsigned char* sA = smem;
+    unsigned char* sB = smem + (size_t)S * TC_A_BYTES;
+    uint64_t* bars = (uint64_t*)(sB + (size_t)S * b_stage_bytes);
+    uint64_t* full_a = bars;            // [S] 4 arrivals (one per producer warp)
+    uint64_t* full_b = bars + S;        // [S] 1 arrival + transaction bytes
+    uint64_t* empty = bars + 2 * S;     // [S] 1 arrival (tcgen05.commit)
+    uint64_t* acc_full = bars + 3 * S;  // 1 arrival
+    uint32_t* tmem_slot = (uint32_t*)(bars + 3 * S + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    int tmem_cols = 32;
+    while (tmem_cols < Tp) tmem_cols <<= 1;
+
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) { mbar_init(&full_a[s], 4); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int KB = p.KB;
+
+    if (warp < 4) {
+        // ================= weight producers =================
+        const int g = lane >> 2, t = lane & 3;
+        const int wt = blockIdx.x * 2 + (warp >> 1);
+        const int i0 = 2 * (warp & 1);
+        const uint4* gp = p.qfrag + ((size_t)wt * KB * 4 + i0) * 32 + lane;     // + kb*128 per block, + 32 per tile
+        const __half2 sixteenth = __float2half2_rn(0.0625f);
+        uint4 wv[2], wn[2];
+        if (KB > 0) { wv[0] = ldg_nc_v4(gp); wv[1] = ldg_nc_v4(gp + 32); }
+        bool ok = true;
+        for (int kb = 0; kb < KB && ok; ++kb) {
+            const int s = kb % S;
+            const uint32_t ph = (kb / S) & 1;
+            if (kb + 1 < KB) { wn[0] = ldg_nc_v4(gp + (size_t)(kb + 1) * 128); wn[1] = ldg_nc_v4(gp + (size_t)(kb + 1) * 128 + 32); }
+            ok = mbar_wait(&empty[s], ph ^ 1, abort_flag);
+            if (!ok) break;
+            unsigned char* a = sA + (size_t)s * TC_A_BYTES;
+#pragma unroll
+            for (int ii = 0; ii < 2; ++ii) {
+                const int tile = wt * 4 + i0 + ii;
+                const int row_lo = ((warp >> 1) * 4 + i0 + ii) * 16 + g, row_hi = row_lo + 8;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int grp = (2 * kb + j + p.off32) >> p.gshift;
+                    uint2 sz = ldg_nc_v2(p.szfrag + ((size_t)tile * p.G + grp) * 8 + g);
+                    __half2 s2 = *(__half2*)&sz.x, z2 = *(__half2*)&sz.y;
+                    const __half2 s_lo = __half2half2(__low2half(s2)), s_hi = __half2half2(__high2half(s2));
+                    const __half2 z_lo = __half2half2(__low2half(z2)), z_hi = __half2half2(__high2half(z2));
+                    const __half2 k1024 = __float2half2_rn(1024.f), k64 = __float2half2_rn(64.f);
+                    const __half2 cl_lo = __hadd2(k1024, z_lo), cl_hi = __hadd2(k1024, z_hi);      // 1024 + zero
+                    const __half2 ch_lo = __hneg2(__hadd2(k64, z_lo)), ch_hi = __hneg2(__hadd2(k64, z_hi));  // -(64 + zero)
+                    const uint32_t w0 = j ? wv[ii].z : wv[ii].x, w1 = j ? wv[ii].w : wv[ii].y;
+                    auto put = [&](int row, int k, __half2 v) {
+                        uint32_t off = row * 128 + ((((k >> 3) ^ (row & 7)) & 7) << 4) + (k & 7) * 2;
+                        *(__half2*)(a + off) = v;
+                    };
+                    auto deq_lo = [&](uint32_t x, __half2 c, __half2 sc) {
+                        uint32_t r = tc_nib_lo(x);
+                        return __hmul2(__hsub2(*(__half2*)&r, c), sc);
+                    };
+                    auto deq_hi = [&](uint32_t x, __half2 c, __half2 sc) {
+                        uint32_t r = tc_nib_hi(x);
+                        return __hmul2(__hfma2(*(__half2*)&r, sixteenth, c), sc);
+                    };
+                    const int kk = 32 * j + 2 * t;
+                    put(row_lo, kk, deq_lo(w0, cl_lo, s_lo));
+                    put(row_hi, kk, deq_lo(w0 >> 8, cl_hi, s_hi));
+                    put(row_lo, kk + 16, deq_hi(w0, ch_lo, s_lo));
+                    put(row_hi, kk + 16, deq_hi(w0 >> 8, ch_hi, s_hi));
+                    put(row_lo, kk + 8, deq_lo(w1, cl_lo, s_lo));
+                    put(row_hi, kk + 8, deq_lo(w1 >> 8, cl_hi, s_hi));
+                    put(row_lo, kk + 24, deq_hi(w1, ch_lo, s_lo));
+                    put(row_hi, kk + 24, deq_hi(w1 >> 8, ch_hi, s_hi));
+                }
+            }
+            fence_proxy_async_smem();           // generic-proxy stores -> visible to the tensor core
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full_a[s]);
+            wv[0] = wn[0]; wv[1] = wn[1];
+        }
+        // ================= epilogue =================
+        if (ok) ok = mbar_wait(acc_full, 0, abort_flag);
+        tc_fence_after();
+        if (ok) {
+            const int n = blockIdx.x * TC_BM + warp * 32 + lane;
+            for (int c0 = 0; c0 < Tp; c0 += 32) {
+                uint32_t r[32];
+                tc_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+                tc_wait_ld();
+                if (p.epi == TC_EPI_SILU_PAIR) {
+                    const bool is_gate = (lane & 8) == 0;
+                    const int o = blockIdx.x * (TC_BM / 2) + warp * 16 + (lane >> 4) * 8 + (lane & 7);
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        float v = __uint_as_float(r[c]);
+                        float up = __shfl_down_sync(0xffffffffu, v, 8);
+                        int tt = t0 + c0 + c;
+                        if (is_gate && c0 + c < Tp && tt < p.T && o < p.n_valid)
+                            ((__half*)p.out)[(size_t)tt * p.ldo + o] = __float2half(silu_f(v) * up);
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        int tt = t0 + c0 + c;
+                        if (c0 + c < Tp && tt < p.T && n < p.n_valid) {
+                            float v = __uint_as_float(r[c]);
+                            size_t o = (size_t)tt * p.ldo + n;
+                            if (p.epi == TC_EPI_STORE_F16) ((__half*)p.out)[o] = __float2half(v);
+                            else if (p.epi == TC_EPI_STORE_F32) ((float*)p.out)[o] = v;
+                            else ((float*)p.out)[o] += v;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 4) {
+        // ================= activation producer (TMA) =================
+        if (lane == 0) {
+            bool ok = true;
+            for (int kb = 0; kb < KB && ok; ++kb) {
+                const int s = kb % S;
+                const uint32_t ph = (kb / S) & 1;
+                ok = mbar_wait(&empty[s], ph ^ 1, abort_flag);
+                if (!ok) break;
+                mbar_arrive_expect_tx(&full_b[s], (uint32_t)boxes * 64 * 128);
+                unsigned char* b = sB + (size_t)s * b_stage_bytes;
+                for (int bx = 0; bx < boxes; ++bx)
+                    tma_load_2d(b + (size_t)bx * 64 * 128, &xmap, kb * TC_BK, t0 + bx * 64, &full_b[s]);
+            }
+        }
+    } else {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            const int n1 = min(Tp, 256), n2 = Tp - n1;
+            const uint32_t idesc1 = make_idesc_f16(n1), idesc2 = make_idesc_f16(n2 > 0 ? n2 : 16);
+            bool ok = true;
+            for (int kb = 0; kb < KB && ok; ++kb) {
+                const int s = kb % S;
+                const uint32_t ph = (kb / S) & 1;
+                ok = mbar_wait(&full_a[s], ph, abort_flag) && mbar_wait(&full_b[s], ph, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(sA + (size_t)s * TC_A_BYTES);
+                const uint32_t b_addr = smem_u32(sB + (size_t)s * b_stage_bytes);
+#pragma unroll
+                for (int k16 = 0; k16 < TC_BK / 16; ++k16) {
+                    const uint64_t ad = make_desc_sw128(a_addr + k16 * 32);
+                    const uint32_t acc = (kb > 0 || k16 > 0) ? 1u : 0u;
+                    tc_mma_f16(tmem_base, ad, make_desc_sw128(b_addr + k16 * 32), idesc1, acc);
+                    if (n2 > 0) tc_mma_f16(tmem_base + 256, ad, make_desc_sw128(b_addr + 256 * 128 + k16 * 32), idesc2, acc);
+                }
+                tc_commit(&empty[s]);           // stage reusable once these MMAs have read it
+            }
+            if (ok) tc_commit(acc_full);
+        }
+    }
+    if (*abort_flag && tid == 0 && p.status) atomicExch(p.status, 1);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 4)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(tmem_cols) : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    }
+    return fn;
+}
+
+B2_API size_t b2_gemm_tc_smem(int t_tile, int stages) {
+    size_t b = (size_t)((t_tile + 63) / 64) * 64 * 128;
+    return 1024 + (size_t)stages * (TC_A_BYTES + b) + (3 * stages + 1) * 8 + 16;
+}
+
+// x: [T][ldx] fp16 activations (ldx multiple of 8, base 16-byte aligned).
+B2_API int b2_gemm_int4_tc(const GemmTcParams* p, const void* x, int ldx, cudaStream_t stream) {
+    if (p->T < 1 || p->t_tile < 16 || p->t_tile > 512 || (p->t_tile & 15) || (ldx & 7) || ((uintptr_t)x & 15))
+        return cudaErrorInvalidValue;
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return cudaErrorNotSupported;
+    CUtensorMap map;
+    cuuint64_t dims[2] = {(cuuint64_t)p->K, (cuuint64_t)p->T};
+    cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
+    cuuint32_t box[2] = {TC_BK, 64};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)x, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    GemmTcParams q = *p;
+    size_t per_stage = TC_A_BYTES + (size_t)((q.t_tile + 63) / 64) * 64 * 128;
+    int stages = (int)((200 * 1024) / per_stage);
+    q.stages = stages > 4 ? 4 : (stages < 2 ? 2 : stages);
+    size_t smem = b2_gemm_tc_smem(q.t_tile, q.stages);
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_int4_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = smem;
+    }
+    dim3 grid(q.NTL * 16 / TC_BM, (q.T + q.t_tile - 1) / q.t_tile);
+    gemm_int4_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(q, map);
+    return cudaGetLastError();
+}
+B2_API int b2_sizeof_gemm_tc_params() { return (int)sizeof(GemmTcParams); }

@@ -180,6 +180,7 @@ __device__ void finish_rows(const GemvEpi& e, const CommCtx& c, int rows, uint32
     const int np = (H + GEMV_TILE_N - 1) / GEMV_TILE_N;
     __shared__ int s_fail;
     if (tid == 0) s_fail = 0;
+    if (tid == 0 && c.trace) c.trace[0] = globaltimer_ns();
     __syncthreads();
     if (tid == 0) *c.epoch = epoch_next;
     if (tid < c.tp && tid != c.rank && !(e.fin_flags & FIN_TEST_WITHHOLD_SIGNAL))
@@ -191,37 +192,54 @@ __device__ void finish_rows(const GemvEpi& e, const CommCtx& c, int rows, uint32
         }
     }
     __syncthreads();
+    if (tid == 0 && c.trace) c.trace[1] = globaltimer_ns();
     const bool exchange = !s_fail;
     const size_t poff = (size_t)(epoch_next & 1) * c.part_stride;
     const float* mine = c.part[c.rank] + poff;
+    const float* peer[B2_MAX_TP];
+#pragma unroll
+    for (int pr = 0; pr < B2_MAX_TP; ++pr) peer[pr] = c.part[pr < c.tp ? pr : 0] + poff;
     for (int r = 0; r < rows; ++r) {
-        float4 hv[8];
+        // all loads of a row are issued before anything is stored, so the NVLink round trips overlap
+        float4 hv[8], yv[8];
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            int n = (it * GEMV_THREADS + tid) * 4;
+            if (n < H) {
+                size_t off = (size_t)r * H + n;
+                if (exchange && c.mc_part) {
+                    yv[it] = multimem_ld_reduce_v4(c.mc_part + poff + off);
+                } else if (exchange) {
+                    float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int pr = 0; pr < B2_MAX_TP; ++pr) {
+                        if (pr < c.tp) {
+                            float4 v = ld_relaxed_sys_v4(peer[pr] + off);
+                            y.x += v.x; y.y += v.y; y.z += v.z; y.w += v.w;
+                        }
+                    }
+                    yv[it] = y;
+                } else {
+                    yv[it] = ld_cg_v4(mine + off);
+                }
+                hv[it] = *(const float4*)(e.h + off);
+            }
+        }
         float ss = 0.f;
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
             int n = (it * GEMV_THREADS + tid) * 4;
             if (n < H) {
                 size_t off = (size_t)r * H + n;
-                float4 y;
-                if (exchange && c.mc_part) {
-                    y = multimem_ld_reduce_v4(c.mc_part + poff + off);
-                } else if (exchange) {
-                    y = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int pr = 0; pr < c.tp; ++pr) {
-                        float4 v = ld_relaxed_sys_v4(c.part[pr] + poff + off);
-                        y.x += v.x; y.y += v.y; y.z += v.z; y.w += v.w;
-                    }
-                } else {
-                    y = ld_cg_v4(mine + off);
-                }
-                float4 h = *(const float4*)(e.h + off);
-                h.x += y.x; h.y += y.y; h.z += y.z; h.w += y.w;
+                float4 h = hv[it];
+                h.x += yv[it].x; h.y += yv[it].y; h.z += yv[it].z; h.w += yv[it].w;
                 *(float4*)(e.hout + off) = h;
                 hv[it] = h;
                 ss += h.x * h.x + h.y * h.y + h.z * h.z + h.w * h.w;
             }
         }
         float tot = block_sum(ss, red);
+        if (tid == 0 && c.trace) c.trace[2] = globaltimer_ns();
         for (int i = tid; i < np; i += GEMV_THREADS) e.ss_part[(size_t)r * np + i] = (i == 0) ? tot : 0.f;
         if (e.xn == nullptr || (e.fin_flags & FIN_NO_NORM)) continue;
         float inv = rsqrtf(tot / (float)H + e.eps);
@@ -286,6 +304,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_int4_kernel(const GemvIn
     // Weights do not depend on earlier kernels; everything below does.
     pdl_wait();
     const uint32_t epoch_next = (p.epi.mode == EPI_FINISH && p.comm.tp > 1) ? (*p.comm.epoch + 1u) : 0u;
+    if (p.comm.trace && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) p.comm.trace[3] = globaltimer_ns();
 
     // ---- stage activations in MMA B-fragment order, with per-chunk bias sums
     for (int i = tid; i < nCh * 8; i += GEMV_THREADS)

@@ -204,3 +204,37 @@ def residual_add_(h, delta):
     d16 = delta if delta.dtype == torch.float16 else None
     L.check(L.lib().b2_residual_add(_vp(h), _vp(d32), _vp(d16), C.c_size_t(h.numel()), L.stream()), "residual_add")
     return h
+
+
+_tc_status = {}
+
+
+def gemm_int4_tc(pk, x: torch.Tensor, out: torch.Tensor, epi: int = L.TC_EPI_STORE_F16,
+                 t_tile: Optional[int] = None, n_valid: Optional[int] = None):
+    """out[t][n] (epi) = x[t, :K] @ W for a PackedInt4 matrix on the tcgen05 tensor cores.
+    x: fp16 [T, K] (row stride multiple of 8).  SILU_PAIR: out[t][j] = silu(gate_j) * up_j for
+    the gate/up-interleaved matrix; RESID_F32: out (fp32) += product."""
+    T = x.shape[0]
+    dev = x.device
+    if t_tile is None:
+        t_tile = min(512, -(-T // 16) * 16)
+    st = _tc_status.get(dev)
+    if st is None:
+        st = _tc_status[dev] = torch.zeros(4, dtype=torch.int32, device=dev)
+    p = L.GemmTcParams()
+    p.qfrag, p.szfrag = pk.qfrag.data_ptr(), pk.szfrag.data_ptr()
+    p.K, p.KB, p.NTL, p.G, p.off32, p.gshift = pk.K, pk.KB, pk.NTL, pk.G, pk.off32, pk.gshift
+    p.T, p.t_tile, p.epi = T, t_tile, epi
+    if n_valid is None:
+        n_valid = pk.n_pad // 2 if epi == L.TC_EPI_SILU_PAIR else pk.N
+    p.n_valid, p.ldo, p.out, p.status = n_valid, out.stride(0), out.data_ptr(), st.data_ptr()
+    L.check(L.lib().b2_gemm_int4_tc(C.byref(p), C.c_void_p(x.data_ptr()), x.stride(0), L.stream()), "gemm_int4_tc")
+    return out
+
+
+def gemm_tc_check_status(device=None):
+    """Raise if a tcgen05 GEMM gave up on a bounded barrier wait since the last check."""
+    for dev, st in _tc_status.items():
+        if int(st[0].item()) != 0:
+            st.zero_()
+            raise RuntimeError("gemm_int4_tc: a bounded mbarrier wait expired")

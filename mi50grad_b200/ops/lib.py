@@ -35,7 +35,7 @@ vp, i32, f32, i64 = C.c_void_p, C.c_int, C.c_float, C.c_longlong
 class CommCtx(C.Structure):
     _fields_ = [("tp", i32), ("rank", i32), ("part_stride", i32), ("pad0", i32),
                 ("part", vp * MAX_TP), ("sig", vp * MAX_TP), ("mc_part", vp),
-                ("epoch", vp), ("status", vp), ("wait_ns", i64)]
+                ("epoch", vp), ("status", vp), ("wait_ns", i64), ("trace", vp)]
 
 
 class RowMeta(C.Structure):
@@ -89,6 +89,15 @@ class ArgmaxParams(C.Structure):
                 ("rows", vp), ("comm", CommCtx)]
 
 
+class GemmTcParams(C.Structure):
+    _fields_ = [("qfrag", vp), ("szfrag", vp), ("K", i32), ("KB", i32), ("NTL", i32), ("G", i32), ("off32", i32),
+                ("gshift", i32), ("T", i32), ("t_tile", i32), ("n_valid", i32), ("ldo", i32), ("epi", i32),
+                ("stages", i32), ("out", vp), ("status", vp)]
+
+
+TC_EPI_STORE_F16, TC_EPI_SILU_PAIR, TC_EPI_STORE_F32, TC_EPI_RESID_F32 = 0, 1, 2, 3
+
+
 class LinearDesc(C.Structure):
     _fields_ = [("kind", i32), ("K", i32), ("N", i32), ("KB", i32), ("NTL", i32), ("G", i32), ("off32", i32),
                 ("gshift", i32), ("k_splits", i32), ("L", i32), ("ldw", i32), ("kslice", i32), ("pad", i32),
@@ -128,7 +137,7 @@ _SIZE_CHECKS = {
     "b2_sizeof_gemv_f16_params": GemvF16Params, "b2_sizeof_attn_params": AttnParams,
     "b2_sizeof_delta_params": DeltaParams, "b2_sizeof_argmax_params": ArgmaxParams,
     "b2_sizeof_linear_desc": LinearDesc, "b2_sizeof_layer_desc": LayerDesc,
-    "b2_sizeof_model_desc": ModelDesc, "b2_sizeof_row_meta": RowMeta, "b2_sizeof_seq_state": SeqState,
+    "b2_sizeof_model_desc": ModelDesc, "b2_sizeof_gemm_tc_params": GemmTcParams, "b2_sizeof_row_meta": RowMeta, "b2_sizeof_seq_state": SeqState,
 }
 
 _lib: Optional[C.CDLL] = None

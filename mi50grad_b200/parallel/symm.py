@@ -68,6 +68,8 @@ class SymmComm(Communicator):
         self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.counters = torch.zeros(8, dtype=torch.int32, device=self.device)
+        self.trace = torch.zeros(8, dtype=torch.int64, device=self.device)
+        self.trace_enabled = False
         self.wait_ns = int(wait_us) * 1000
         torch.cuda.synchronize()
         dist.barrier(self.group)
@@ -81,7 +83,14 @@ class SymmComm(Communicator):
             c.sig[r] = self.peer_ptrs[r] + self.off_sig
         c.mc_part = self.multicast_ptr or None
         c.epoch, c.status, c.wait_ns = self.epoch.data_ptr(), self.status.data_ptr(), self.wait_ns
+        c.trace = self.trace.data_ptr() if self.trace_enabled else None
         return c
+
+    def last_exchange_trace(self) -> dict:
+        """globaltimer stamps (ns) of the last fused GEMV exchange on this rank, relative to the
+        kernel's start: entry of the finishing CTA, flags of all peers seen, residual+sums done."""
+        t = self.trace.tolist()
+        return {"finisher_entry_ns": t[0] - t[3], "peers_arrived_ns": t[1] - t[3], "reduced_ns": t[2] - t[3]}
 
     @property
     def has_multimem(self) -> bool:

@@ -1,0 +1,55 @@
+"""tcgen05 INT4 GEMM against a PyTorch fp32 reference."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-12))
+
+
+@pytest.mark.parametrize("K,N,T,g", [(256, 128, 16, 128), (704, 200, 48, 128), (1024, 384, 512, 128),
+                                    (2176, 640, 80, 128), (512, 256, 300, 32), (5120, 1024, 700, 128)])
+def test_gemm_int4_tc_store(K, N, T, g):
+    from mi50grad_b200.ops import kernels as Kn
+    from mi50grad_b200.ops import lib as L
+    from mi50grad_b200.ops.packing import pack_int4
+    from mi50grad_b200.utils.quant import random_int4_linear
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator().manual_seed(K + N + T)
+    lin = random_int4_linear(K, N, g, gen)
+    lin.zeros = torch.randint(0, 16, lin.zeros.shape, generator=gen).half()
+    x = torch.randn(T, K, generator=gen).half()
+    ref = x.float() @ lin.dense().t()
+    pk = pack_int4(lin, dev)
+    out = torch.full((T, N), float("nan"), dtype=torch.float16, device=dev)
+    Kn.gemm_int4_tc(pk, x.to(dev), out)
+    torch.cuda.synchronize()
+    Kn.gemm_tc_check_status()
+    assert _rel(out.cpu(), ref) < 3e-3
+    out32 = torch.zeros(T, N, dtype=torch.float32, device=dev)
+    Kn.gemm_int4_tc(pk, x.to(dev), out32, epi=L.TC_EPI_STORE_F32)
+    Kn.gemm_int4_tc(pk, x.to(dev), out32, epi=L.TC_EPI_RESID_F32)
+    torch.cuda.synchronize()
+    Kn.gemm_tc_check_status()
+    assert _rel(out32.cpu(), 2 * ref) < 2e-3
+
+
+def test_gemm_int4_tc_silu_pair():
+    from mi50grad_b200.ops import kernels as Kn
+    from mi50grad_b200.ops import lib as L
+    from mi50grad_b200.ops.packing import interleave_gate_up, pack_int4
+    from mi50grad_b200.utils.quant import random_int4_linear
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator().manual_seed(5)
+    K, F, T = 512, 704, 100
+    gate, up = random_int4_linear(K, F, 128, gen), random_int4_linear(K, F, 128, gen)
+    x = torch.randn(T, K, generator=gen).half()
+    ref = torch.nn.functional.silu(x.float() @ gate.dense().t()) * (x.float() @ up.dense().t())
+    pk = pack_int4(interleave_gate_up(gate, up), dev)
+    out = torch.zeros(T, pk.n_pad // 2, dtype=torch.float16, device=dev)
+    Kn.gemm_int4_tc(pk, x.to(dev), out, epi=L.TC_EPI_SILU_PAIR)
+    torch.cuda.synchronize()
+    Kn.gemm_tc_check_status()
+    assert _rel(out[:, :F].cpu(), ref) < 4e-3
