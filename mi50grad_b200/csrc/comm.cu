@@ -21,21 +21,6 @@
 //            epilogue -- 2(tp-1)/tp x traffic; used for prefill-sized payloads.
 #include "kernels.cuh"
 
-struct CollParams {
-    CommCtx comm;
-    const float* in;         // local input [n] fp32 (may be null when in16 is given)
-    const __half* in16;      // local input [n] fp16
-    float* out;              // local output [n]: out = sum (+ out if residual)
-    __half* out16;           // optional fp16 copy of the result
-    float* gather[B2_MAX_TP];// two-shot: per-rank symmetric result buffers [n]
-    float* mc_gather;        // multicast mapping of gather (or null)
-    size_t n;                // elements, multiple of 4
-    int residual;            // 1: out += sum
-    int twoshot;
-    int* counters;           // [4] local, zero between launches
-    int test_withhold;       // test hook: never signal, so that the bounded wait expires
-};
-
 __device__ __forceinline__ bool wait_all(const CommCtx& c, int base, uint32_t epoch, int kid) {
     // every thread < tp polls one peer's flag (its own rank's flag included)
     __shared__ int s_ok;

@@ -18,6 +18,7 @@
 #include <cstring>
 #include <vector>
 #include "kernels.cuh"
+#include "gemm_tc.cuh"
 
 #define LIN_INT4 0
 #define LIN_F16 1
@@ -74,6 +75,11 @@ struct ModelDesc {
     float* extra; float* h_tmp;            // saved attention partial; uncommitted h + partial (deferred_consistent)
     float* ss; int np; int pad3;           // [rows][np] sums of squares for the lazy RMSNorm
     void* rows; void* rows_tmpl; void* seqs; int* row_tokens; int* seq_rows; int* out_tokens;
+    // prefill (many-row) work buffers, sized for max_prefill rows
+    int max_prefill; int pad4;
+    float* p_h; void* p_xn; void* p_proj; void* p_attn; void* p_act; float* p_partial;
+    void* p_rows; void* p_rows_tmpl; int* p_row_tokens; int* tc_status;
+    float* coll_gather[B2_MAX_TP]; float* coll_mc_gather; int* coll_counters;
     CommCtx comm;
 };
 
@@ -219,6 +225,95 @@ static int step_impl(Driver* d, int rows, int n_seqs, int flags, cudaStream_t s)
     }
     return 0;
 }
+
+
+// ---------------------------------------------------------------------------
+// Prefill: T rows of ONE sequence through every layer with tensor-core GEMMs
+// (tcgen05), causal attention over the cache, the DeltaNet scan, and -- under
+// tensor parallelism -- a two-shot all-reduce fused with the residual add after
+// each row-parallel projection.  The reference prefills token-serially through
+// its DeltaNet layers and re-launches per-token norm/rope kernels (reference:
+// src/inference/tp_engine.py:1900-2224).
+// ---------------------------------------------------------------------------
+static int run_gemm(Driver* d, const LinearDesc& L, const void* x, int ldx, int T, void* out, int ldo, int n_valid,
+                    int epi, cudaStream_t s) {
+    if (L.kind != LIN_INT4) return cudaErrorNotSupported;
+    GemmTcParams p;
+    memset(&p, 0, sizeof(p));
+    p.qfrag = (const uint4*)L.w; p.szfrag = (const uint2*)L.sz;
+    p.K = L.K; p.KB = L.KB; p.NTL = L.NTL; p.G = L.G; p.off32 = L.off32; p.gshift = L.gshift;
+    p.T = T; p.t_tile = T >= 512 ? 512 : ((T + 15) & ~15);
+    p.n_valid = n_valid; p.ldo = ldo; p.epi = epi; p.out = out; p.status = d->m.tc_status;
+    d->launches++;
+    return b2_gemm_int4_tc(&p, x, ldx, s);
+}
+
+static int row_parallel(Driver* d, const LinearDesc& L, const void* x, int ldx, int T, cudaStream_t s) {
+    const ModelDesc& m = d->m;
+    if (m.comm.tp <= 1) return run_gemm(d, L, x, ldx, T, m.p_h, m.H, m.H, TC_EPI_RESID_F32, s);
+    CK(run_gemm(d, L, x, ldx, T, m.p_partial, m.H, m.H, TC_EPI_STORE_F32, s));
+    CollParams c;
+    memset(&c, 0, sizeof(c));
+    c.comm = m.comm; c.in = m.p_partial; c.out = m.p_h; c.n = (size_t)T * m.H; c.residual = 1;
+    c.twoshot = (c.n * 4 > 512 * 1024) ? 1 : 0;
+    for (int r = 0; r < m.comm.tp; ++r) c.gather[r] = m.coll_gather[r];
+    c.mc_gather = m.coll_mc_gather; c.counters = m.coll_counters;
+    d->launches++;
+    return b2_allreduce(&c, 2 * 148, s);
+}
+
+static int prefill_impl(Driver* d, int T, int flags, cudaStream_t s) {
+    const ModelDesc& m = d->m;
+    if (T < 1 || T > m.max_prefill) return cudaErrorInvalidValue;
+    d->launches = 0;
+    CK(b2_prepare_rows(m.p_rows_tmpl, m.seqs, m.p_rows, T, s)); d->launches++;
+    if (flags & STEP_EMBED_TOKENS) {
+        CK(b2_embed_rmsnorm(m.embed, m.p_row_tokens, m.p_rows, m.seqs, m.first_norm, m.p_h, m.p_xn, nullptr, 0, T,
+                            m.H, m.eps, m.vocab, s));
+        d->launches++;
+    }
+    for (int li = 0; li < m.n_layers; ++li) {
+        const LayerDesc& L = d->layers[li];
+        if (li > 0) { CK(b2_add_rmsnorm(m.p_h, nullptr, nullptr, L.attn_norm, m.p_xn, nullptr, T, m.H, m.eps, s)); d->launches++; }
+        CK(run_gemm(d, L.in_proj, m.p_xn, m.H, T, m.p_proj, m.ld_proj, L.in_proj.N, TC_EPI_STORE_F16, s));
+        if (L.type == 0) {
+            CK(b2_qknorm_rope_cachew(m.p_proj, m.ld_proj, m.p_rows, L.q_norm, L.k_norm, m.cos_tab, m.sin_tab, L.kcache,
+                                     L.vcache, T, m.nq, m.nkv, m.hd, m.rot, m.max_seq, m.rope_interleaved, m.eps, s));
+            AttnParams a;
+            memset(&a, 0, sizeof(a));
+            a.q = (const __half*)m.p_proj; a.ldq = m.ld_proj; a.gate_off = m.nq * m.hd;
+            a.kcache = (const __half*)L.kcache; a.vcache = (const __half*)L.vcache; a.rows = (const RowMeta*)m.p_rows;
+            a.out = (__half*)m.p_attn; a.ldo = m.ld_attn; a.n_rows = T; a.nq = m.nq; a.nkv = m.nkv;
+            a.max_seq = m.max_seq; a.splits = 1; a.scale = 1.0f / sqrtf((float)m.hd);
+            a.scratch = m.attn_scratch; a.counters = m.attn_counters;
+            CK(b2_decode_attn(&a, m.hd, s));
+            d->launches += 2;
+        } else {
+            DeltaParams q;
+            memset(&q, 0, sizeof(q));
+            q.proj = (const __half*)m.p_proj; q.ld = m.ld_proj;
+            q.off_q = L.off_q; q.off_k = L.off_k; q.off_v = L.off_v; q.off_z = L.off_z; q.off_a = L.off_a; q.off_b = L.off_b;
+            q.xn = (const __half*)m.p_xn; q.ldx = m.H; q.H = m.H; q.wa = (const __half*)L.wa; q.wb = (const __half*)L.wb;
+            q.conv_w = (const __half*)L.conv_w; q.conv_state = (__half*)L.conv_state; q.state = L.state;
+            q.A_log = L.A_log; q.dt_bias = (const __half*)L.dt_bias; q.norm_w = (const __half*)L.la_norm;
+            q.seq_rows = m.seq_rows; q.rows = (const RowMeta*)m.p_rows; q.out = (__half*)m.p_attn; q.ldo = m.ld_attn;
+            q.nk = m.la_nk; q.nv = m.la_nv; q.n_seqs = 1; q.eps = 1e-6f; q.commit = 1;
+            CK(b2_deltanet_step(&q, m.la_dk, m.la_dv, s));
+            d->launches++;
+        }
+        // prefill always uses the exact all-reduce placement
+        CK(row_parallel(d, L.out_proj, m.p_attn, m.ld_attn, T, s));
+        CK(b2_add_rmsnorm(m.p_h, nullptr, nullptr, L.ffn_norm, m.p_xn, nullptr, T, m.H, m.eps, s)); d->launches++;
+        CK(run_gemm(d, L.gate_up, m.p_xn, m.H, T, m.p_act, m.F_pad, m.F_pad, TC_EPI_SILU_PAIR, s));
+        CK(row_parallel(d, L.down, m.p_act, m.F_pad, T, s));
+    }
+    // final norm of every row (hidden-out interface and the lm_head input of the last row)
+    CK(b2_add_rmsnorm(m.p_h, nullptr, nullptr, d->layers[m.n_layers - 1].next_norm, m.p_xn, nullptr, T, m.H, m.eps, s));
+    d->launches++;
+    return 0;
+}
+
+B2_API int b2_driver_prefill(void* h, int T, int flags, cudaStream_t s) { return prefill_impl((Driver*)h, T, flags, s); }
 
 B2_API void* b2_driver_create(const ModelDesc* m, const LayerDesc* layers) {
     Driver* d = new Driver();

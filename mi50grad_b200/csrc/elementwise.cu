@@ -26,7 +26,7 @@ __global__ void prepare_rows_kernel(const RowMeta* __restrict__ tmpl, const SeqS
     o.seq = t.seq;
     o.pos = len + t.pos;
     o.slot = len + t.slot;
-    o.ctx = len;
+    o.ctx = len + t.ctx;          // template ctx: extra visible slots (prefill row i sees i+1 new ones)
     o.mask = t.mask;
     rows[r] = o;
 }

@@ -24,28 +24,13 @@
 // its work, releases its tensor memory and returns.
 #include <cuda.h>
 #include "kernels.cuh"
+#include "gemm_tc.cuh"
 
 #define TC_THREADS 192
 #define TC_BK 64                 // k per stage (128 bytes of fp16: one swizzle row)
 #define TC_BM 128                // outputs per CTA (MMA M)
 #define TC_A_BYTES (TC_BM * TC_BK * 2)
 #define TC_WAIT_NS 1000000000LL  // bound of every barrier wait
-
-#define TC_EPI_STORE_F16 0
-#define TC_EPI_SILU_PAIR 1
-#define TC_EPI_STORE_F32 2
-#define TC_EPI_RESID_F32 3       // out32[t][n] += y
-
-struct GemmTcParams {
-    const uint4* qfrag;      // [NTL/4][KB][4][32] packed nibbles
-    const uint2* szfrag;     // [NTL][G][8]
-    int K, KB, NTL, G, off32, gshift;
-    int T;                   // token rows in this launch's activation matrix
-    int t_tile;              // tokens per CTA (multiple of 16, <= 512)
-    int n_valid, ldo, epi, stages;
-    void* out;
-    int* status;             // [0] set to 1 when a bounded wait expired
-};
 
 // ---------------------------------------------------------------------------
 // PTX helpers

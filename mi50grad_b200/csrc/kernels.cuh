@@ -49,6 +49,22 @@ struct ArgmaxParams {
     CommCtx comm;
 };
 
+struct CollParams {
+    CommCtx comm;
+    const float* in;         // local input [n] fp32 (may be null when in16 is given)
+    const __half* in16;      // local input [n] fp16
+    float* out;              // local output [n]: out = sum (+ out if residual)
+    __half* out16;           // optional fp16 copy of the result
+    float* gather[B2_MAX_TP];// two-shot: per-rank symmetric result buffers [n]
+    float* mc_gather;        // multicast mapping of gather (or null)
+    size_t n;                // elements, multiple of 4
+    int residual;            // 1: out += sum
+    int twoshot;
+    int* counters;           // [4] local, zero between launches
+    int test_withhold;       // test hook: never signal, so that the bounded wait expires
+};
+
+B2_API int b2_allreduce(const CollParams* p, int max_ctas, cudaStream_t s);
 B2_API int b2_gemv_int4(const GemvInt4Params* p, cudaStream_t stream);
 B2_API int b2_gemv_f16(const GemvF16Params* p, cudaStream_t stream);
 B2_API int b2_decode_attn(const AttnParams* p, int hd, cudaStream_t s);

@@ -314,6 +314,16 @@ class InferenceEngine:
         b["seq_rows"] = i32(self.max_batch + 1 + R)
         b["out_tokens"] = i32(R)
         b["emb_in"] = f32(R, H)
+        # prefill buffers (tensor-core path, up to max_prefill rows per launch)
+        P = self.max_prefill = min(512, self.max_seq_len)
+        self.use_tc_prefill = all(l.packed is not None for l in lins[:-1])
+        b["p_h"], b["p_xn"] = f32(P, H), f16(P, H)
+        b["p_proj"], b["p_attn"], b["p_act"] = f16(P, b["ld_proj"]), f16(P, b["ld_attn"]), f16(P, self.F_pad)
+        b["p_partial"] = f32(P, H) if self.tp_size > 1 else f32(1)
+        b["p_rows"], b["p_rows_tmpl"] = i32(P, 6), i32(P, 6)
+        b["p_row_tokens"] = torch.full((P,), -1, dtype=torch.int32, device=dev)
+        b["tc_status"] = i32(4)
+        b["coll_counters"] = i32(8)
 
         m = L.ModelDesc()
         m.n_layers, m.H, m.vocab = cfg.num_hidden_layers, H, cfg.vocab_size
@@ -337,6 +347,16 @@ class InferenceEngine:
         m.np = self.np
         m.seqs = self.states.seqs.data_ptr()
         m.comm = self._comm_ctx()
+        m.max_prefill = self.max_prefill
+        for k in ("p_h", "p_xn", "p_proj", "p_attn", "p_act", "p_partial", "p_rows", "p_rows_tmpl", "p_row_tokens",
+                  "tc_status", "coll_counters"):
+            setattr(m, k, b[k].data_ptr())
+        if self.comm is not None and self.tp_size > 1:
+            if self.comm.part_floats < self.max_prefill * H:
+                raise ValueError("communicator staging buffer is smaller than max_prefill x hidden")
+            for r in range(self.tp_size):
+                m.coll_gather[r] = self.comm.peer_ptrs[r] + self.comm.off_gather
+            m.coll_mc_gather = (self.comm.multicast_ptr + self.comm.off_gather) if self.comm.multicast_ptr else None
         descs = (L.LayerDesc * cfg.num_hidden_layers)()
         for i, dl in enumerate(self.layers):
             d = descs[i]
@@ -421,10 +441,49 @@ class InferenceEngine:
         self.buf["row_tokens"].fill_(-1)
         return self.buf["out_tokens"][:n]
 
+    def _prefill_rows(self, n: int, seq: int, flags: int):
+        """Run n rows (already staged: tokens in p_row_tokens or embeddings in p_h/p_xn) of one
+        sequence through the tensor-core prefill path and commit them."""
+        t = torch.zeros(n, 6, dtype=torch.int32)
+        idx = torch.arange(n, dtype=torch.int32)
+        t[:, 0], t[:, 1], t[:, 2], t[:, 3] = seq, idx, idx, idx + 1      # pos, slot, visible new slots
+        self.buf["p_rows_tmpl"][:n].copy_(t.to(self.device))
+        sr = torch.zeros(self.buf["seq_rows"].shape[0], dtype=torch.int32)
+        sr[1] = n
+        self.buf["seq_rows"].copy_(sr.to(self.device))
+        self._tmpl_key = None
+        L.check(self.lib.b2_driver_prefill(C.c_void_p(self._driver), n, flags, L.stream()), "driver prefill")
+        self.states.seqs[seq, 0] += n
+        self._steps += 1
+
+    def prefill_tokens_tc(self, tokens: Sequence[int], seq: int = 0) -> int:
+        """Prompt processing on the tcgen05 GEMM path, max_prefill rows per launch; returns the
+        first generated token."""
+        self._ensure_driver()
+        from ..ops import kernels as K
+        tokens = list(tokens)
+        n = 0
+        for i in range(0, len(tokens), self.max_prefill):
+            chunk = tokens[i:i + self.max_prefill]
+            n = len(chunk)
+            self.buf["p_row_tokens"][:n].copy_(torch.tensor(chunk, dtype=torch.int32).to(self.device))
+            self._prefill_rows(n, seq, L.STEP_EMBED_TOKENS)
+        # logits of the last row: final-normed hidden state is in p_xn[n-1]
+        K.gemv(self.lm_head, self.buf["p_xn"][n - 1:n], out=self.buf["logits"][:1], mode=L.EPI_STORE_F32,
+               scratch=self.buf["gemv_scratch"], counters=self.buf["gemv_counters"])
+        tok = K.argmax(self.buf["logits"][:1, :self.spec.vocab_local], self.spec.vocab[0], self.argmax_blocks,
+                       self._comm_ctx() if self.tp_size > 1 else None)
+        self.buf["h"][:1].copy_(self.buf["p_h"][n - 1:n])
+        self.states.seqs[seq, 1] = tok[0]
+        return int(tok[0].item())
+
     def prefill_tokens(self, tokens: Sequence[int], seq: int = 0) -> int:
         """Consume a prompt; returns the first generated token and stores it as
         the sequence's next input."""
         tokens = list(tokens)
+        self._ensure_driver()
+        if self.use_tc_prefill and len(tokens) >= 16:
+            return self.prefill_tokens_tc(tokens, seq)
         out = None
         for i in range(0, len(tokens), self.max_rows):
             chunk = tokens[i:i + self.max_rows]

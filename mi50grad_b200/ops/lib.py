@@ -129,7 +129,11 @@ class ModelDesc(C.Structure):
                 ("argmax_scratch", vp), ("argmax_counters", vp), ("extra", vp), ("h_tmp", vp),
                 ("ss", vp), ("np", i32), ("pad3", i32),
                 ("rows", vp), ("rows_tmpl", vp), ("seqs", vp), ("row_tokens", vp), ("seq_rows", vp),
-                ("out_tokens", vp), ("comm", CommCtx)]
+                ("out_tokens", vp),
+                ("max_prefill", i32), ("pad4", i32), ("p_h", vp), ("p_xn", vp), ("p_proj", vp), ("p_attn", vp),
+                ("p_act", vp), ("p_partial", vp), ("p_rows", vp), ("p_rows_tmpl", vp), ("p_row_tokens", vp),
+                ("tc_status", vp), ("coll_gather", vp * MAX_TP), ("coll_mc_gather", vp), ("coll_counters", vp),
+                ("comm", CommCtx)]
 
 
 _SIZE_CHECKS = {
