@@ -242,7 +242,12 @@ static int run_gemm(Driver* d, const LinearDesc& L, const void* x, int ldx, int 
     memset(&p, 0, sizeof(p));
     p.qfrag = (const uint4*)L.w; p.szfrag = (const uint2*)L.sz;
     p.K = L.K; p.KB = L.KB; p.NTL = L.NTL; p.G = L.G; p.off32 = L.off32; p.gshift = L.gshift;
-    p.T = T; p.t_tile = T >= 512 ? 512 : ((T + 15) & ~15);
+    // tokens per CTA: as many as tensor memory holds, unless that leaves most SMs without a CTA
+    // (N = 5120 gives only 40 output tiles): then split the tokens over more CTAs
+    const int ctas_n = L.NTL * 16 / 128;
+    int tt = T >= 512 ? 512 : ((T + 15) & ~15);
+    while (tt > 128 && ctas_n * ((T + tt - 1) / tt) < 120) tt = ((tt / 2) + 15) & ~15;
+    p.T = T; p.t_tile = tt;
     p.n_valid = n_valid; p.ldo = ldo; p.epi = epi; p.out = out; p.status = d->m.tc_status;
     d->launches++;
     return b2_gemm_int4_tc(&p, x, ldx, s);

@@ -43,15 +43,18 @@ def scenario_allreduce(multimem: bool):
     return comm.has_multimem
 
 
-def scenario_tp_engine(ar_mode: str, multimem: bool):
-    """Tiny hybrid model at TP=world on GPUs vs the CPU oracle running the same
-    placement of all-reduces (single process emulation of every rank)."""
+def scenario_tp_engine(ar_mode: str, multimem: bool, model: str = "tiny"):
+    """Small hybrid model at TP=world on GPUs vs the fp32 CPU oracle.  'medium' has 8 query /
+    4 KV heads and 8 / 16 DeltaNet heads, so it shards over 8 ranks with every KV head
+    replicated on two of them."""
     from mi50grad_b200.config import EngineConfig, tiny_config
     from mi50grad_b200.engine.tp_engine import TPInferenceEngine
     from mi50grad_b200.models.oracle import OracleEngine
     from mi50grad_b200.models.weights import random_model
     rank, world = dist.get_rank(), dist.get_world_size()
-    cfg = tiny_config()
+    cfg = tiny_config() if model == "tiny" else tiny_config(
+        hidden_size=512, intermediate_size=2048, num_attention_heads=8, num_key_value_heads=4,
+        linear_num_key_heads=8, linear_num_value_heads=16, vocab_size=2048)
     mw = random_model(cfg, 0)
     eng = TPInferenceEngine(cfg, list(range(world)), max_seq_len=128,
                             engine_config=EngineConfig(ar_mode=ar_mode, use_multimem=multimem))
@@ -115,7 +118,7 @@ def main():
             mm = scenario_allreduce(sys.argv[2] == "multimem")
             extra = f"multimem={mm}"
         elif scenario == "tp_engine":
-            scenario_tp_engine(sys.argv[2], sys.argv[3] == "multimem")
+            scenario_tp_engine(sys.argv[2], sys.argv[3] == "multimem", sys.argv[4] if len(sys.argv) > 4 else "tiny")
             extra = sys.argv[2]
         elif scenario == "wait_timeout":
             scenario_wait_timeout()

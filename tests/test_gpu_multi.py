@@ -43,3 +43,11 @@ def test_tp_engine_tiny_peer_loads():
 
 def test_bounded_wait_times_out_cleanly():
     _run(2, "wait_timeout", env_extra={"NCCL_NVLS_ENABLE": "0"})
+
+
+def test_tp_engine_medium_all_gpus():
+    """TP over every GPU of the box (8: KV heads replicated on rank pairs) against the oracle."""
+    n = _n()
+    if n < 4:
+        pytest.skip("needs >= 4 GPUs")
+    _run(8 if n >= 8 else 4, "tp_engine", "exact", "multimem", "medium")
