@@ -79,6 +79,7 @@ struct ModelDesc {
     int max_prefill; int pad4;
     float* p_h; void* p_xn; void* p_proj; void* p_attn; void* p_act; float* p_partial;
     void* p_rows; void* p_rows_tmpl; int* p_row_tokens; int* tc_status;
+    void* p_ab;                            // [max_prefill][2*la_nv] fp16 a/b projections of the DeltaNet layers
     float* coll_gather[B2_MAX_TP]; float* coll_mc_gather; int* coll_counters;
     CommCtx comm;
 };
@@ -303,7 +304,19 @@ static int prefill_impl(Driver* d, int T, int flags, cudaStream_t s) {
             q.A_log = L.A_log; q.dt_bias = (const __half*)L.dt_bias; q.norm_w = (const __half*)L.la_norm;
             q.seq_rows = m.seq_rows; q.rows = (const RowMeta*)m.p_rows; q.out = (__half*)m.p_attn; q.ldo = m.ld_attn;
             q.nk = m.la_nk; q.nv = m.la_nv; q.n_seqs = 1; q.eps = 1e-6f; q.commit = 1;
-            CK(b2_deltanet_step(&q, m.la_dk, m.la_dv, s));
+            if (T >= 16) {
+                // chunked scan; a/b come from the projection buffer or from a small dense kernel
+                const void* ab = (const __half*)m.p_proj + (L.off_a >= 0 ? L.off_a : 0);
+                int ld_ab = m.ld_proj;
+                if (L.off_a < 0) {
+                    CK(b2_ab_proj(m.p_xn, m.H, L.wa, L.wb, m.la_nv, m.H, m.p_ab, 2 * m.la_nv, T, s));
+                    d->launches++;
+                    ab = m.p_ab; ld_ab = 2 * m.la_nv;
+                }
+                CK(b2_deltanet_chunk(&q, ab, ld_ab, m.la_dk, m.la_dv, s));
+            } else {
+                CK(b2_deltanet_step(&q, m.la_dk, m.la_dv, s));
+            }
             d->launches++;
         }
         // prefill always uses the exact all-reduce placement

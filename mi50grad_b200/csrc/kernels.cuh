@@ -69,6 +69,9 @@ B2_API int b2_gemv_int4(const GemvInt4Params* p, cudaStream_t stream);
 B2_API int b2_gemv_f16(const GemvF16Params* p, cudaStream_t stream);
 B2_API int b2_decode_attn(const AttnParams* p, int hd, cudaStream_t s);
 B2_API int b2_deltanet_step(const DeltaParams* p, int dk, int dv, cudaStream_t s);
+B2_API int b2_deltanet_chunk(const DeltaParams* p, const void* ab, int ld_ab, int dk, int dv, cudaStream_t s);
+B2_API int b2_ab_proj(const void* x, int ldx, const void* wa, const void* wb, int nv, int H, void* ab, int ld_ab,
+                      int rows, cudaStream_t s);
 B2_API int b2_argmax(const ArgmaxParams* p, cudaStream_t s);
 B2_API int b2_prepare_rows(const void* tmpl, const void* seqs, void* rows, int n, cudaStream_t s);
 B2_API int b2_advance(void* seqs, const int* add, int n, int add_const, cudaStream_t s);

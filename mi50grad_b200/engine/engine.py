@@ -323,6 +323,7 @@ class InferenceEngine:
         b["p_rows"], b["p_rows_tmpl"] = i32(P, 6), i32(P, 6)
         b["p_row_tokens"] = torch.full((P,), -1, dtype=torch.int32, device=dev)
         b["tc_status"] = i32(4)
+        b["p_ab"] = f16(P, max(2, 2 * sp.n_la_v))
         b["coll_counters"] = i32(8)
 
         m = L.ModelDesc()
@@ -349,7 +350,7 @@ class InferenceEngine:
         m.comm = self._comm_ctx()
         m.max_prefill = self.max_prefill
         for k in ("p_h", "p_xn", "p_proj", "p_attn", "p_act", "p_partial", "p_rows", "p_rows_tmpl", "p_row_tokens",
-                  "tc_status", "coll_counters"):
+                  "tc_status", "coll_counters", "p_ab"):
             setattr(m, k, b[k].data_ptr())
         if self.comm is not None and self.tp_size > 1:
             if self.comm.part_floats < self.max_prefill * H:

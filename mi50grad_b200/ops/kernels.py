@@ -174,6 +174,33 @@ def deltanet_step(proj, offs, conv_w, conv_state, state, A_log, dt_bias, norm_w,
     return out
 
 
+def ab_proj(x, wa, wb):
+    """[rows, 2*nv] fp16: a = x @ wa^T, b = x @ wb^T (the DeltaNet gate projections)."""
+    rows, H = x.shape
+    nv = wa.shape[0]
+    ab = torch.empty(rows, 2 * nv, dtype=torch.float16, device=x.device)
+    L.check(L.lib().b2_ab_proj(_vp(x), x.stride(0), _vp(wa), _vp(wb), nv, H, _vp(ab), ab.stride(0), rows, L.stream()),
+            "ab_proj")
+    return ab
+
+
+def deltanet_chunk(proj, offs, ab, conv_w, conv_state, state, A_log, dt_bias, norm_w, rows_meta, seq_rows, nk, nv,
+                   dk, dv, out=None, commit=True, eps=1e-6):
+    """Chunked scan over each sequence's rows; ab: fp16 [rows, >= 2*nv] with a | b."""
+    n = proj.shape[0]
+    if out is None:
+        out = torch.empty(n, nv * dv, dtype=torch.float16, device=proj.device)
+    p = L.DeltaParams()
+    p.proj, p.ld = proj.data_ptr(), proj.stride(0)
+    p.off_q, p.off_k, p.off_v, p.off_z, p.off_a, p.off_b = offs
+    p.conv_w, p.conv_state, p.state = conv_w.data_ptr(), conv_state.data_ptr(), state.data_ptr()
+    p.A_log, p.dt_bias, p.norm_w = A_log.data_ptr(), dt_bias.data_ptr(), norm_w.data_ptr()
+    p.seq_rows, p.rows, p.out, p.ldo = seq_rows.data_ptr(), rows_meta.data_ptr(), out.data_ptr(), out.stride(0)
+    p.nk, p.nv, p.n_seqs, p.eps, p.commit = nk, nv, seq_rows.shape[0] - 1, eps, 1 if commit else 0
+    L.check(L.lib().b2_deltanet_chunk(C.byref(p), _vp(ab), ab.stride(0), dk, dv, L.stream()), "deltanet_chunk")
+    return out
+
+
 def argmax(logits: torch.Tensor, vocab_offset: int = 0, blocks: int = 16, comm: Optional[L.CommCtx] = None):
     n, V = logits.shape
     dev = logits.device

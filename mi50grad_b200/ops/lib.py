@@ -132,7 +132,7 @@ class ModelDesc(C.Structure):
                 ("out_tokens", vp),
                 ("max_prefill", i32), ("pad4", i32), ("p_h", vp), ("p_xn", vp), ("p_proj", vp), ("p_attn", vp),
                 ("p_act", vp), ("p_partial", vp), ("p_rows", vp), ("p_rows_tmpl", vp), ("p_row_tokens", vp),
-                ("tc_status", vp), ("coll_gather", vp * MAX_TP), ("coll_mc_gather", vp), ("coll_counters", vp),
+                ("tc_status", vp), ("p_ab", vp), ("coll_gather", vp * MAX_TP), ("coll_mc_gather", vp), ("coll_counters", vp),
                 ("comm", CommCtx)]
 
 

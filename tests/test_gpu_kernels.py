@@ -302,6 +302,64 @@ def test_deltanet_step(K, dk, nk, nv, rows_per_seq, inkernel_ab):
         assert torch.equal(conv_d[s, 0, 0, :dk].cpu(), hist[ch].half())
 
 
+@pytest.mark.parametrize("dk,nk,nv,rows_per_seq", [(128, 1, 3, [150]), (64, 2, 4, [70, 5, 64]), (128, 2, 2, [512])])
+def test_deltanet_chunked_scan(K, dk, nk, nv, rows_per_seq):
+    """Chunked scan == token-serial oracle (outputs, final state, conv history)."""
+    from mi50grad_b200.models import oracle as O
+    gen = torch.Generator().manual_seed(21)
+    d = _dev()
+    dv, H = dk, 256
+    nseq, R = len(rows_per_seq), sum(rows_per_seq)
+    kd, vd = nk * dk, nv * dv
+    conv_dim = 2 * kd + vd
+    proj = torch.randn(R, conv_dim + vd, generator=gen).half()
+    conv_w = (torch.randn(conv_dim, 4, generator=gen) * 0.3).half()
+    A_log = torch.rand(nv, generator=gen) * 1.5 - 1.0
+    dt_bias = (torch.randn(nv, generator=gen) * 0.5).half()
+    norm_w = (torch.rand(dv, generator=gen) + 0.5).half()
+    S0 = torch.randn(nseq, nv, dk, dv, generator=gen) * 0.1
+    hist0 = torch.randn(nseq, conv_dim, 3, generator=gen).half()
+    xn = torch.randn(R, H, generator=gen).half()
+    wa, wb = (torch.randn(nv, H, generator=gen) * 0.1).half(), (torch.randn(nv, H, generator=gen) * 0.1).half()
+    ab = K.ab_proj(xn.to(d), wa.to(d), wb.to(d))
+    ab_ref = torch.cat([xn.float() @ wa.float().t(), xn.float() @ wb.float().t()], 1)
+    assert _rel(ab.cpu(), ab_ref) < 2e-3
+    CB, nch = dv // 32, 2 * dk + 32
+    conv_state = torch.zeros(nseq, nv, CB, nch, 3, dtype=torch.float16)
+    for j in range(nv):
+        kh = j // (nv // nk)
+        for cb in range(CB):
+            ch = list(range(kh * dk, (kh + 1) * dk)) + list(range(kd + kh * dk, kd + (kh + 1) * dk)) + \
+                list(range(2 * kd + j * dv + cb * 32, 2 * kd + j * dv + cb * 32 + 32))
+            conv_state[:, j, cb] = hist0[:, ch]
+    seq_rows, entries = [0], []
+    for s_, n in enumerate(rows_per_seq):
+        entries += [(s_, 0, 0, 0, 1)] * n
+        seq_rows.append(seq_rows[-1] + n)
+    state_d, conv_d = S0.to(d).clone(), conv_state.to(d).clone()
+    out = K.deltanet_chunk(proj.to(d), (0, kd, 2 * kd, conv_dim, -1, -1), ab, conv_w.to(d), conv_d, state_d,
+                           A_log.to(d), dt_bias.to(d), norm_w.to(d), K.make_rows(entries, d),
+                           torch.tensor(seq_rows, dtype=torch.int32, device=d), nk, nv, dk, dv)
+    abh = ab.cpu().float()
+    for s_ in range(nseq):
+        r0, r1 = seq_rows[s_], seq_rows[s_ + 1]
+        n = r1 - r0
+        hist = hist0[s_].clone()
+        c = O.causal_conv1d(proj[r0:r1, :conv_dim].float(), hist, conv_w)
+        qq = O.l2norm(c[:, :kd].reshape(n, nk, dk)) / math.sqrt(dk)
+        kk = O.l2norm(c[:, kd:2 * kd].reshape(n, nk, dk))
+        vv = c[:, 2 * kd:].reshape(n, nv, dv)
+        rep = nv // nk
+        g, beta = O.deltanet_gates(abh[r0:r1, :nv], abh[r0:r1, nv:], A_log, dt_bias)
+        st = S0[s_].clone()
+        y = O.deltanet_recurrent(qq.repeat_interleave(rep, 1), kk.repeat_interleave(rep, 1), vv, g, beta, st)
+        z = proj[r0:r1, conv_dim:].float().view(n, nv, dv)
+        ref = O.gated_rmsnorm(y, z, norm_w).reshape(n, vd)
+        assert _rel(out[r0:r1].cpu(), ref) < 4e-3, f"seq {s_}"
+        assert _rel(state_d[s_].cpu(), st) < 2e-3
+        assert torch.equal(conv_d[s_, 0, 0, :dk].cpu(), hist[:dk].half())
+
+
 def test_deltanet_dry_run_keeps_state(K):
     gen = torch.Generator().manual_seed(14)
     d = _dev()
