@@ -270,6 +270,7 @@ __global__ void __launch_bounds__(DN_THREADS, 1) deltanet_chunk_kernel(const Del
     float* bs = Gs + DC_C;                    // [C] beta
     float* gs = bs + DC_C;                    // [C] log-decay per row
     float* cl_ss = gs + DC_C;                 // [2][C]
+    __half* Xr = (__half*)(cl_ss + 2 * DC_C);  // [C+3][NCH] raw conv inputs of the chunk (3 history rows first)
 
     auto chan = [&](int c) -> int {
         if (c < DK) return kh * DK + c;
@@ -299,27 +300,49 @@ __global__ void __launch_bounds__(DN_THREADS, 1) deltanet_chunk_kernel(const Del
     const float qscale = rsqrtf((float)DK);
     __syncthreads();
 
+    // raw-tile staging: 16-byte cp.async pieces; rows before the sequence start come from the saved history,
+    // rows past its end are zero
+    auto stage_raw = [&](int rb_) {
+        constexpr int PPR = NCH / 8;                       // 16-byte pieces per row
+        for (int idx = tid; idx < (DC_C + 3) * PPR; idx += DN_THREADS) {
+            const int row = idx / PPR, pc = idx % PPR;
+            const int c = pc * 8;
+            const int ri = rb_ - 3 + row;
+            __half* dst = Xr + row * NCH + c;
+            if (ri >= r0 && ri < r1) {
+                cp_async16(dst, p.proj + (size_t)ri * p.ld + proj_col(c));
+            } else if (ri < r0) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) dst[e] = __float2half(hist[(c + e) * 3 + (ri - r0 + 3)]);
+            } else {
+                *(uint4*)dst = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        cp_async_commit();
+    };
+    stage_raw(r0);
+
     int chunk_idx = 0;
     for (int rb = r0; rb < r1; rb += DC_C, ++chunk_idx) {
         const int Ce = min(DC_C, r1 - rb);
-        // ---- P1: causal conv + SiLU straight from the projection rows (history for the first three)
-        for (int idx = tid; idx < DC_C * NCH; idx += DN_THREADS) {
-            const int i = idx / NCH, c = idx % NCH;
-            float o = 0.f;
-            if (i < Ce) {
-                const int col = proj_col(c);
-                float acc = 0.f;
+        // ---- P1: causal conv + SiLU from the raw tile staged in shared memory by cp.async (the
+        // copy for this chunk was issued while the previous chunk was being processed)
+        cp_async_wait<0>();
+        __syncthreads();
+        for (int item = tid; item < NCH * (DC_C / 8); item += DN_THREADS) {
+            const int c = item % NCH, i0 = (item / NCH) * 8;
+            const float w0 = cw[c * 4 + 0], w1 = cw[c * 4 + 1], w2 = cw[c * 4 + 2], w3 = cw[c * 4 + 3];
+            float x0 = __half2float(Xr[(i0 + 0) * NCH + c]), x1 = __half2float(Xr[(i0 + 1) * NCH + c]);
+            float x2 = __half2float(Xr[(i0 + 2) * NCH + c]);
+            float* dst = (c < DK) ? Qs + c : (c < 2 * DK) ? Ks + (c - DK) : Us + (c - 2 * DK);
+            const int ldd = (c < 2 * DK) ? LDK : DN_COLS;
 #pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    const int ri = rb + i - 3 + t;
-                    float x = (ri >= r0) ? __half2float(p.proj[(size_t)ri * p.ld + col]) : hist[c * 3 + (ri - r0 + 3)];
-                    acc = fmaf(x, cw[c * 4 + t], acc);
-                }
-                o = silu_f(acc);
+            for (int i = i0; i < i0 + 8; ++i) {
+                const float x3 = __half2float(Xr[(i + 3) * NCH + c]);
+                const float acc = x0 * w0 + x1 * w1 + x2 * w2 + x3 * w3;
+                dst[i * ldd] = (i < Ce) ? silu_f(acc) : 0.f;
+                x0 = x1; x1 = x2; x2 = x3;
             }
-            if (c < DK) Qs[i * LDK + c] = o;
-            else if (c < 2 * DK) Ks[i * LDK + (c - DK)] = o;
-            else Us[i * DN_COLS + (c - 2 * DK)] = o;
         }
         if (tid < DC_C) {
             float gl = 0.f, beta = 0.f;
@@ -334,6 +357,7 @@ __global__ void __launch_bounds__(DN_THREADS, 1) deltanet_chunk_kernel(const Del
             bs[tid] = beta;
         }
         __syncthreads();
+        if (rb + DC_C < r1) stage_raw(rb + DC_C);          // flies while this chunk is processed
         // ---- P2: L2-normalise q and k rows, running log-decay
         for (int i = kr; i < DC_C; i += 8) {
             float qq = 0.f, kk = 0.f;
@@ -495,7 +519,7 @@ static int launch_delta_chunk(const DeltaParams* p, const void* ab, int ld_ab, c
     constexpr int CB = DV / DN_COLS;
     constexpr int NCH = 2 * DK + DN_COLS;
     size_t smem = (size_t)(2 * DC_C * DC_LDK(DK) + 3 * DC_C * DN_COLS + 2 * DC_C * DC_LDA + DK * DN_COLS + NCH * 7 +
-                           3 * DC_C + 2 * DC_C) * sizeof(float);
+                           3 * DC_C + 2 * DC_C) * sizeof(float) + (size_t)(DC_C + 3) * NCH * sizeof(__half);
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(deltanet_chunk_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -244,10 +244,17 @@ static int run_gemm(Driver* d, const LinearDesc& L, const void* x, int ldx, int 
     p.qfrag = (const uint4*)L.w; p.szfrag = (const uint2*)L.sz;
     p.K = L.K; p.KB = L.KB; p.NTL = L.NTL; p.G = L.G; p.off32 = L.off32; p.gshift = L.gshift;
     // tokens per CTA: as many as tensor memory holds, unless that leaves most SMs without a CTA
-    // (N = 5120 gives only 40 output tiles): then split the tokens over more CTAs
+    // (N = 5120 gives only 40 output tiles): then split the tokens so that the grid fills, but does
+    // not exceed, one wave of 148 CTAs (one CTA per SM: a second partial wave would double the time)
     const int ctas_n = L.NTL * 16 / 128;
     int tt = T >= 512 ? 512 : ((T + 15) & ~15);
-    while (tt > 128 && ctas_n * ((T + tt - 1) / tt) < 120) tt = ((tt / 2) + 15) & ~15;
+    if (ctas_n < 148) {
+        int parts = 148 / ctas_n;                          // token tiles that still fit one wave
+        int need = (T + parts - 1) / parts;
+        need = (need + 15) & ~15;
+        if (need < 64) need = 64;
+        if (need < tt) tt = need;
+    }
     p.T = T; p.t_tile = tt;
     p.n_valid = n_valid; p.ldo = ldo; p.epi = epi; p.out = out; p.status = d->m.tc_status;
     d->launches++;

@@ -26,11 +26,13 @@
 #include "kernels.cuh"
 #include "gemm_tc.cuh"
 
-#define TC_THREADS 192
+#define TC_PRODUCERS 8            // dequantising warps (also the epilogue warps)
+#define TC_THREADS ((TC_PRODUCERS + 2) * 32)
 #define TC_BK 64                 // k per stage (128 bytes of fp16: one swizzle row)
 #define TC_BM 128                // outputs per CTA (MMA M)
 #define TC_A_BYTES (TC_BM * TC_BK * 2)
 #define TC_WAIT_NS 1000000000LL  // bound of every barrier wait
+#define TC_RING 6                // k-blocks of packed weights + scales in flight per producer thread (cp.async)
 
 // ---------------------------------------------------------------------------
 // PTX helpers
@@ -56,7 +58,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false (and raises *abort_flag) when the time budget is exhausted or
-// another role has already given up.
+// another role has already given up.  The timer read between polls also acts as a back-off:
+// polling the barrier harder was measured to slow the pipeline down.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     long long t0 = globaltimer_ns();
@@ -143,23 +146,24 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
     unsigned char* sA = smem;
     unsigned char* sB = smem + (size_t)S * TC_A_BYTES;
     uint64_t* bars = (uint64_t*)(sB + (size_t)S * b_stage_bytes);
-    uint64_t* full_a = bars;            // [S] 4 arrivals (one per producer warp)
+    uint64_t* full_a = bars;            // [S] one arrival per producer warp
     uint64_t* full_b = bars + S;        // [S] 1 arrival + transaction bytes
     uint64_t* empty = bars + 2 * S;     // [S] 1 arrival (tcgen05.commit)
     uint64_t* acc_full = bars + 3 * S;  // 1 arrival
     uint32_t* tmem_slot = (uint32_t*)(bars + 3 * S + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    uint4* wring = (uint4*)(((uintptr_t)(tmem_slot + 2) + 15) & ~(uintptr_t)15);   // [TC_RING][2][256 producer threads]: 16 B of nibbles, 2 x 8 B scale/zero
 
     int tmem_cols = 32;
     while (tmem_cols < Tp) tmem_cols <<= 1;
 
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { mbar_init(&full_a[s], 4); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < S; ++s) { mbar_init(&full_a[s], TC_PRODUCERS); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
         mbar_init(acc_full, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) {
+    if (warp == TC_PRODUCERS) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      :: "r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -170,78 +174,101 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
     const uint32_t tmem_base = *tmem_slot;
     const int KB = p.KB;
 
-    if (warp < 4) {
+    if (warp < TC_PRODUCERS) {
         // ================= weight producers =================
+        // warp w owns the 16-row tile w of the CTA's 128 outputs: one 16-byte load per k-block and lane
         const int g = lane >> 2, t = lane & 3;
-        const int wt = blockIdx.x * 2 + (warp >> 1);
-        const int i0 = 2 * (warp & 1);
-        const uint4* gp = p.qfrag + ((size_t)wt * KB * 4 + i0) * 32 + lane;     // + kb*128 per block, + 32 per tile
+        const int wt = blockIdx.x * 2 + (warp >> 2);
+        const int ti = warp & 3;
+        const int tile = wt * 4 + ti;
+        const uint4* gp = p.qfrag + ((size_t)wt * KB * 4 + ti) * 32 + lane;     // + kb*128 per k-block
         const __half2 sixteenth = __float2half2_rn(0.0625f);
-        uint4 wv[2], wn[2];
-        if (KB > 0) { wv[0] = ldg_nc_v4(gp); wv[1] = ldg_nc_v4(gp + 32); }
+        const __half2 k1024 = __float2half2_rn(1024.f), k64 = __float2half2_rn(64.f);
+        // swizzled byte offsets of this lane's stores: row & 7 == g for both of its rows
+        const uint32_t row_lo_off = (uint32_t)(warp * 16 + g) * 128 + t * 4, row_hi_off = row_lo_off + 8 * 128;
+        uint32_t sw[8];
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8) sw[c8] = (uint32_t)((c8 ^ g) << 4);
+        // packed weights and their scale/zero pairs stream through a cp.async ring: TC_RING-1
+        // k-blocks are always in flight, each thread later reads back only what it copied itself
+        uint4* my_ring = wring + tid;
+        auto issue = [&](int kb) {
+            const int slot = kb % TC_RING;
+            cp_async16(my_ring + (slot * 2 + 0) * 256, gp + (size_t)kb * 128);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int grp = (2 * kb + j + p.off32) >> p.gshift;
+                cp_async8((uint2*)(my_ring + (slot * 2 + 1) * 256) + j, p.szfrag + ((size_t)tile * p.G + grp) * 8 + g);
+            }
+        };
+#pragma unroll
+        for (int s = 0; s < TC_RING - 1; ++s) {
+            if (s < KB) issue(s);
+            cp_async_commit();
+        }
         bool ok = true;
         for (int kb = 0; kb < KB && ok; ++kb) {
             const int s = kb % S;
             const uint32_t ph = (kb / S) & 1;
-            if (kb + 1 < KB) { wn[0] = ldg_nc_v4(gp + (size_t)(kb + 1) * 128); wn[1] = ldg_nc_v4(gp + (size_t)(kb + 1) * 128 + 32); }
-            ok = mbar_wait(&empty[s], ph ^ 1, abort_flag);
+            if (kb + TC_RING - 1 < KB) issue(kb + TC_RING - 1);
+            cp_async_commit();
+            cp_async_wait<TC_RING - 1>();
+            const uint4 wv = my_ring[((kb % TC_RING) * 2 + 0) * 256];
+            const uint4 szq = my_ring[((kb % TC_RING) * 2 + 1) * 256];
+            {   // one lane polls: many pollers on one barrier slow the arrivals down
+                int o = 1;
+                if (lane == 0) o = mbar_wait(&empty[s], ph ^ 1, abort_flag) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, o, 0) != 0;
+            }
             if (!ok) break;
-            unsigned char* a = sA + (size_t)s * TC_A_BYTES;
+            unsigned char* a_lo = sA + (size_t)s * TC_A_BYTES + row_lo_off;
+            unsigned char* a_hi = sA + (size_t)s * TC_A_BYTES + row_hi_off;
+            if (!(p.dbg & 1))
 #pragma unroll
-            for (int ii = 0; ii < 2; ++ii) {
-                const int tile = wt * 4 + i0 + ii;
-                const int row_lo = ((warp >> 1) * 4 + i0 + ii) * 16 + g, row_hi = row_lo + 8;
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    const int grp = (2 * kb + j + p.off32) >> p.gshift;
-                    uint2 sz = ldg_nc_v2(p.szfrag + ((size_t)tile * p.G + grp) * 8 + g);
-                    __half2 s2 = *(__half2*)&sz.x, z2 = *(__half2*)&sz.y;
-                    const __half2 s_lo = __half2half2(__low2half(s2)), s_hi = __half2half2(__high2half(s2));
-                    const __half2 z_lo = __half2half2(__low2half(z2)), z_hi = __half2half2(__high2half(z2));
-                    const __half2 k1024 = __float2half2_rn(1024.f), k64 = __float2half2_rn(64.f);
-                    const __half2 cl_lo = __hadd2(k1024, z_lo), cl_hi = __hadd2(k1024, z_hi);      // 1024 + zero
-                    const __half2 ch_lo = __hneg2(__hadd2(k64, z_lo)), ch_hi = __hneg2(__hadd2(k64, z_hi));  // -(64 + zero)
-                    const uint32_t w0 = j ? wv[ii].z : wv[ii].x, w1 = j ? wv[ii].w : wv[ii].y;
-                    auto put = [&](int row, int k, __half2 v) {
-                        uint32_t off = row * 128 + ((((k >> 3) ^ (row & 7)) & 7) << 4) + (k & 7) * 2;
-                        *(__half2*)(a + off) = v;
-                    };
-                    auto deq_lo = [&](uint32_t x, __half2 c, __half2 sc) {
-                        uint32_t r = tc_nib_lo(x);
-                        return __hmul2(__hsub2(*(__half2*)&r, c), sc);
-                    };
-                    auto deq_hi = [&](uint32_t x, __half2 c, __half2 sc) {
-                        uint32_t r = tc_nib_hi(x);
-                        return __hmul2(__hfma2(*(__half2*)&r, sixteenth, c), sc);
-                    };
-                    const int kk = 32 * j + 2 * t;
-                    put(row_lo, kk, deq_lo(w0, cl_lo, s_lo));
-                    put(row_hi, kk, deq_lo(w0 >> 8, cl_hi, s_hi));
-                    put(row_lo, kk + 16, deq_hi(w0, ch_lo, s_lo));
-                    put(row_hi, kk + 16, deq_hi(w0 >> 8, ch_hi, s_hi));
-                    put(row_lo, kk + 8, deq_lo(w1, cl_lo, s_lo));
-                    put(row_hi, kk + 8, deq_lo(w1 >> 8, cl_hi, s_hi));
-                    put(row_lo, kk + 24, deq_hi(w1, ch_lo, s_lo));
-                    put(row_hi, kk + 24, deq_hi(w1 >> 8, ch_hi, s_hi));
-                }
+            for (int j = 0; j < 2; ++j) {
+                const uint2 sz = j ? make_uint2(szq.z, szq.w) : make_uint2(szq.x, szq.y);
+                const __half2 s2 = *(const __half2*)&sz.x, z2 = *(const __half2*)&sz.y;
+                const __half2 s_lo = __half2half2(__low2half(s2)), s_hi = __half2half2(__high2half(s2));
+                const __half2 z_lo = __half2half2(__low2half(z2)), z_hi = __half2half2(__high2half(z2));
+                const __half2 cl_lo = __hadd2(k1024, z_lo), cl_hi = __hadd2(k1024, z_hi);                  // 1024 + zero
+                const __half2 ch_lo = __hneg2(__hadd2(k64, z_lo)), ch_hi = __hneg2(__hadd2(k64, z_hi));   // -(64 + zero)
+                const uint32_t w0 = j ? wv.z : wv.x, w1 = j ? wv.w : wv.y;
+                auto deq_lo = [&](uint32_t x, __half2 c, __half2 sc) {
+                    uint32_t r = tc_nib_lo(x);
+                    return __hmul2(__hsub2(*(__half2*)&r, c), sc);
+                };
+                auto deq_hi = [&](uint32_t x, __half2 c, __half2 sc) {
+                    uint32_t r = tc_nib_hi(x);
+                    return __hmul2(__hfma2(*(__half2*)&r, sixteenth, c), sc);
+                };
+                // k = 32 j + 8 m + 2 t: the 16-byte column group is 4 j + m
+                *(__half2*)(a_lo + sw[4 * j + 0]) = deq_lo(w0, cl_lo, s_lo);
+                *(__half2*)(a_hi + sw[4 * j + 0]) = deq_lo(w0 >> 8, cl_hi, s_hi);
+                *(__half2*)(a_lo + sw[4 * j + 2]) = deq_hi(w0, ch_lo, s_lo);
+                *(__half2*)(a_hi + sw[4 * j + 2]) = deq_hi(w0 >> 8, ch_hi, s_hi);
+                *(__half2*)(a_lo + sw[4 * j + 1]) = deq_lo(w1, cl_lo, s_lo);
+                *(__half2*)(a_hi + sw[4 * j + 1]) = deq_lo(w1 >> 8, cl_hi, s_hi);
+                *(__half2*)(a_lo + sw[4 * j + 3]) = deq_hi(w1, ch_lo, s_lo);
+                *(__half2*)(a_hi + sw[4 * j + 3]) = deq_hi(w1 >> 8, ch_hi, s_hi);
             }
             fence_proxy_async_smem();           // generic-proxy stores -> visible to the tensor core
             __syncwarp();
             if (lane == 0) mbar_arrive(&full_a[s]);
-            wv[0] = wn[0]; wv[1] = wn[1];
         }
+        cp_async_wait<0>();
         // ================= epilogue =================
         if (ok) ok = mbar_wait(acc_full, 0, abort_flag);
         tc_fence_after();
         if (ok) {
-            const int n = blockIdx.x * TC_BM + warp * 32 + lane;
-            for (int c0 = 0; c0 < Tp; c0 += 32) {
+            const int lg = warp & 3;               // tensor-memory lane group this warp may read
+            const int n = blockIdx.x * TC_BM + lg * 32 + lane;
+            for (int c0 = (warp >> 2) * 32; c0 < Tp; c0 += 64) {
                 uint32_t r[32];
-                tc_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+                tc_ld32(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)c0, r);
                 tc_wait_ld();
                 if (p.epi == TC_EPI_SILU_PAIR) {
                     const bool is_gate = (lane & 8) == 0;
-                    const int o = blockIdx.x * (TC_BM / 2) + warp * 16 + (lane >> 4) * 8 + (lane & 7);
+                    const int o = blockIdx.x * (TC_BM / 2) + lg * 16 + (lane >> 4) * 8 + (lane & 7);
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
                         float v = __uint_as_float(r[c]);
@@ -265,7 +292,7 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
                 }
             }
         }
-    } else if (warp == 4) {
+    } else if (warp == TC_PRODUCERS) {
         // ================= activation producer (TMA) =================
         if (lane == 0) {
             bool ok = true;
@@ -274,6 +301,7 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
                 const uint32_t ph = (kb / S) & 1;
                 ok = mbar_wait(&empty[s], ph ^ 1, abort_flag);
                 if (!ok) break;
+                if (p.dbg & 2) { mbar_arrive(&full_b[s]); continue; }
                 mbar_arrive_expect_tx(&full_b[s], (uint32_t)boxes * 64 * 128);
                 unsigned char* b = sB + (size_t)s * b_stage_bytes;
                 for (int bx = 0; bx < boxes; ++bx)
@@ -294,6 +322,7 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
                 tc_fence_after();
                 const uint32_t a_addr = smem_u32(sA + (size_t)s * TC_A_BYTES);
                 const uint32_t b_addr = smem_u32(sB + (size_t)s * b_stage_bytes);
+                if (!(p.dbg & 4))
 #pragma unroll
                 for (int k16 = 0; k16 < TC_BK / 16; ++k16) {
                     const uint64_t ad = make_desc_sw128(a_addr + k16 * 32);
@@ -310,7 +339,7 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp == 4)
+    if (warp == TC_PRODUCERS)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(tmem_cols) : "memory");
 }
 
@@ -335,7 +364,7 @@ static EncodeTiledFn get_encode() {
 
 B2_API size_t b2_gemm_tc_smem(int t_tile, int stages) {
     size_t b = (size_t)((t_tile + 63) / 64) * 64 * 128;
-    return 1024 + (size_t)stages * (TC_A_BYTES + b) + (3 * stages + 1) * 8 + 16;
+    return 1024 + (size_t)stages * (TC_A_BYTES + b) + (3 * stages + 1) * 8 + 16 + 16 + (size_t)TC_RING * 2 * 256 * 16;
 }
 
 // x: [T][ldx] fp16 activations (ldx multiple of 8, base 16-byte aligned).
@@ -355,7 +384,7 @@ B2_API int b2_gemm_int4_tc(const GemmTcParams* p, const void* x, int ldx, cudaSt
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     GemmTcParams q = *p;
     size_t per_stage = TC_A_BYTES + (size_t)((q.t_tile + 63) / 64) * 64 * 128;
-    int stages = (int)((200 * 1024) / per_stage);
+    int stages = (int)((160 * 1024) / per_stage);
     q.stages = stages > 4 ? 4 : (stages < 2 ? 2 : stages);
     size_t smem = b2_gemm_tc_smem(q.t_tile, q.stages);
     static size_t configured = 0;
