@@ -296,6 +296,7 @@ class EngineConfig:
     fused_gemv_ar: bool = True
     spec_ngram: int = 3
     spec_max_draft: int = 4
+    max_step_rows: int = 0           # rows of a batched-decode / verify step (0: 8 per sequence slot)
     wait_budget_us: int = 2_000_000
     debug_guards: bool = False
 

@@ -37,7 +37,7 @@ struct LinearDesc {
 
 struct LayerDesc {
     int type;                     // 0 gated full attention, 1 gated DeltaNet
-    int pad;
+    int type_index;               // index among the layers of the same type (state / cache / staging slot)
     LinearDesc in_proj;           // [Q|gate|K|V] or [q|k|v|z(|a|b)]
     LinearDesc out_proj;          // row-parallel
     LinearDesc gate_up;           // gate/up interleaved by 8
@@ -81,6 +81,14 @@ struct ModelDesc {
     void* p_rows; void* p_rows_tmpl; int* p_row_tokens; int* tc_status;
     void* p_ab;                            // [max_prefill][2*la_nv] fp16 a/b projections of the DeltaNet layers
     float* coll_gather[B2_MAX_TP]; float* coll_mc_gather; int* coll_counters;
+    // many-row steps (batched decode, speculative verification): logits and arg-max scratch for p_logit_rows rows
+    float* p_logits; float* p_argmax_scratch; int* p_argmax_counters; int* p_out_tokens;
+    float* p_attn_scratch; int* p_attn_counters;     // split-KV scratch for p_logit_rows rows
+    int p_logit_rows; int n_lin_layers; int n_full_layers; int pad5;
+    // speculative verification
+    SpecStage spec; int* spec_acc; int* spec_result;
+    float* state0; void* conv0; long long state_layer_stride, conv_layer_stride;
+    void* k0; void* v0; long long kv_layer_stride;
     CommCtx comm;
 };
 
@@ -99,6 +107,8 @@ struct Driver {
 #define STEP_ADVANCE 8          // len += 1 for every row's sequence (plain decode)
 #define STEP_NO_COMMIT_DELTA 16 // DeltaNet state dry run
 #define STEP_MATERIALIZE_XN 32  // write the final-normed hidden states to xn (hidden-out interface)
+#define STEP_SPEC 64            // rows are draft trees: verify without touching the state, accept, commit
+#define STEP_GEMM_PATH 128      // many rows: tensor-core GEMMs and the p_* buffers (else the GEMV path, <= 8 rows)
 
 #define CK(x) do { int e_ = (x); if (e_ != 0) return e_; } while (0)
 
@@ -145,6 +155,46 @@ static GemvEpi epi_finish(Driver* d, int flags, float* hout) {
     return e;
 }
 
+static void fill_delta(const Driver* d, const LayerDesc& L, DeltaParams& q) {
+    const ModelDesc& m = d->m;
+    memset(&q, 0, sizeof(q));
+    q.off_q = L.off_q; q.off_k = L.off_k; q.off_v = L.off_v; q.off_z = L.off_z; q.off_a = L.off_a; q.off_b = L.off_b;
+    q.ldx = m.H; q.H = m.H; q.wa = (const __half*)L.wa; q.wb = (const __half*)L.wb;
+    q.conv_w = (const __half*)L.conv_w; q.conv_state = (__half*)L.conv_state; q.state = L.state;
+    q.A_log = L.A_log; q.dt_bias = (const __half*)L.dt_bias; q.norm_w = (const __half*)L.la_norm;
+    q.seq_rows = m.seq_rows; q.ldo = m.ld_attn; q.nk = m.la_nk; q.nv = m.la_nv; q.eps = 1e-6f; q.commit = 1;
+}
+
+// After the arg-max of a verify step: accept on the device, then bring DeltaNet states and the
+// KV cache to what feeding only the accepted tokens would have left.
+static int spec_tail(Driver* d, const void* rows, const int* row_tokens, const int* out_tokens, int n_seqs,
+                     cudaStream_t s) {
+    const ModelDesc& m = d->m;
+    if (!m.spec.base || !m.spec_acc) return cudaErrorInvalidValue;
+    SpecAcceptParams a;
+    memset(&a, 0, sizeof(a));
+    a.out_tokens = out_tokens; a.row_tokens = row_tokens; a.rows = (const RowMeta*)rows; a.seq_rows = m.seq_rows;
+    a.seqs = (SeqState*)m.seqs; a.acc = m.spec_acc; a.result = m.spec_result; a.n_seqs = n_seqs;
+    CK(b2_spec_accept(&a, s)); d->launches++;
+    if (m.n_lin_layers > 0) {
+        DeltaCommitParams c;
+        memset(&c, 0, sizeof(c));
+        c.state0 = m.state0; c.conv0 = (__half*)m.conv0; c.state_layer_stride = m.state_layer_stride;
+        c.conv_layer_stride = m.conv_layer_stride; c.st = m.spec; c.acc = m.spec_acc; c.rows = (const RowMeta*)rows;
+        c.seq_rows = m.seq_rows; c.nk = m.la_nk; c.nv = m.la_nv; c.n_seqs = n_seqs; c.n_layers = m.n_lin_layers;
+        CK(b2_deltanet_commit(&c, m.la_dk, m.la_dv, s)); d->launches++;
+    }
+    if (m.n_full_layers > 0) {
+        KvCompactParams k;
+        memset(&k, 0, sizeof(k));
+        k.k0 = (__half*)m.k0; k.v0 = (__half*)m.v0; k.layer_stride = m.kv_layer_stride; k.acc = m.spec_acc;
+        k.rows = (const RowMeta*)rows; k.seq_rows = m.seq_rows; k.n_layers = m.n_full_layers; k.n_seqs = n_seqs;
+        k.nkv = m.nkv; k.hd = m.hd; k.max_seq = m.max_seq;
+        CK(b2_kv_compact(&k, s)); d->launches++;
+    }
+    return 0;
+}
+
 static int step_impl(Driver* d, int rows, int n_seqs, int flags, cudaStream_t s) {
     const ModelDesc& m = d->m;
     if (rows < 1 || rows > m.max_rows || rows > B2_MAX_ROWS) return cudaErrorInvalidValue;
@@ -187,7 +237,8 @@ static int step_impl(Driver* d, int rows, int n_seqs, int flags, cudaStream_t s)
             q.seq_rows = m.seq_rows; q.rows = (const RowMeta*)m.rows; q.out = (__half*)m.attn_out; q.ldo = m.ld_attn;
             q.nk = m.la_nk; q.nv = m.la_nv; q.n_seqs = n_seqs; q.eps = 1e-6f;
             q.commit = (flags & STEP_NO_COMMIT_DELTA) ? 0 : 1;
-            CK(b2_deltanet_step(&q, m.la_dk, m.la_dv, s));
+            if (flags & STEP_SPEC) CK(b2_deltanet_verify(&q, &m.spec, L.type_index, m.la_dk, m.la_dv, s));
+            else CK(b2_deltanet_step(&q, m.la_dk, m.la_dv, s));
             d->launches++;
         }
         int f_attn = 0, f_ffn = 0;
@@ -223,6 +274,10 @@ static int step_impl(Driver* d, int rows, int n_seqs, int flags, cudaStream_t s)
     if (flags & STEP_ADVANCE) {
         CK(b2_advance(m.seqs, nullptr, n_seqs, 1, s));
         d->launches++;
+    }
+    if (flags & STEP_SPEC) {
+        if (!(flags & STEP_ARGMAX) || (flags & STEP_ADVANCE)) return cudaErrorInvalidValue;
+        CK(spec_tail(d, m.rows, m.row_tokens, m.out_tokens, n_seqs, s));
     }
     return 0;
 }
@@ -275,7 +330,7 @@ static int row_parallel(Driver* d, const LinearDesc& L, const void* x, int ldx, 
     return b2_allreduce(&c, 2 * 148, s);
 }
 
-static int prefill_impl(Driver* d, int T, int flags, cudaStream_t s) {
+static int rows_impl(Driver* d, int T, int n_seqs, int flags, cudaStream_t s) {
     const ModelDesc& m = d->m;
     if (T < 1 || T > m.max_prefill) return cudaErrorInvalidValue;
     d->launches = 0;
@@ -297,21 +352,21 @@ static int prefill_impl(Driver* d, int T, int flags, cudaStream_t s) {
             a.q = (const __half*)m.p_proj; a.ldq = m.ld_proj; a.gate_off = m.nq * m.hd;
             a.kcache = (const __half*)L.kcache; a.vcache = (const __half*)L.vcache; a.rows = (const RowMeta*)m.p_rows;
             a.out = (__half*)m.p_attn; a.ldo = m.ld_attn; a.n_rows = T; a.nq = m.nq; a.nkv = m.nkv;
-            a.max_seq = m.max_seq; a.splits = 1; a.scale = 1.0f / sqrtf((float)m.hd);
-            a.scratch = m.attn_scratch; a.counters = m.attn_counters;
+            a.max_seq = m.max_seq; a.scale = 1.0f / sqrtf((float)m.hd);
+            // few rows with long contexts (batched decode, verification): split the KV range; a prompt's
+            // many rows already fill the GPU
+            if (T <= m.p_logit_rows && m.p_attn_scratch) { a.splits = m.attn_splits; a.scratch = m.p_attn_scratch; a.counters = m.p_attn_counters; }
+            else { a.splits = 1; a.scratch = m.attn_scratch; a.counters = m.attn_counters; }
             CK(b2_decode_attn(&a, m.hd, s));
             d->launches += 2;
         } else {
             DeltaParams q;
-            memset(&q, 0, sizeof(q));
-            q.proj = (const __half*)m.p_proj; q.ld = m.ld_proj;
-            q.off_q = L.off_q; q.off_k = L.off_k; q.off_v = L.off_v; q.off_z = L.off_z; q.off_a = L.off_a; q.off_b = L.off_b;
-            q.xn = (const __half*)m.p_xn; q.ldx = m.H; q.H = m.H; q.wa = (const __half*)L.wa; q.wb = (const __half*)L.wb;
-            q.conv_w = (const __half*)L.conv_w; q.conv_state = (__half*)L.conv_state; q.state = L.state;
-            q.A_log = L.A_log; q.dt_bias = (const __half*)L.dt_bias; q.norm_w = (const __half*)L.la_norm;
-            q.seq_rows = m.seq_rows; q.rows = (const RowMeta*)m.p_rows; q.out = (__half*)m.p_attn; q.ldo = m.ld_attn;
-            q.nk = m.la_nk; q.nv = m.la_nv; q.n_seqs = 1; q.eps = 1e-6f; q.commit = 1;
-            if (T >= 16) {
+            fill_delta(d, L, q);
+            q.proj = (const __half*)m.p_proj; q.ld = m.ld_proj; q.xn = (const __half*)m.p_xn;
+            q.rows = (const RowMeta*)m.p_rows; q.out = (__half*)m.p_attn; q.n_seqs = n_seqs;
+            if (flags & STEP_SPEC) {
+                CK(b2_deltanet_verify(&q, &m.spec, L.type_index, m.la_dk, m.la_dv, s));
+            } else if (n_seqs == 1 && T >= 16) {
                 // chunked scan; a/b come from the projection buffer or from a small dense kernel
                 const void* ab = (const __half*)m.p_proj + (L.off_a >= 0 ? L.off_a : 0);
                 int ld_ab = m.ld_proj;
@@ -332,13 +387,49 @@ static int prefill_impl(Driver* d, int T, int flags, cudaStream_t s) {
         CK(run_gemm(d, L.gate_up, m.p_xn, m.H, T, m.p_act, m.F_pad, m.F_pad, TC_EPI_SILU_PAIR, s));
         CK(row_parallel(d, L.down, m.p_act, m.F_pad, T, s));
     }
-    // final norm of every row (hidden-out interface and the lm_head input of the last row)
+    // final norm of every row (hidden-out interface and the lm_head input)
     CK(b2_add_rmsnorm(m.p_h, nullptr, nullptr, d->layers[m.n_layers - 1].next_norm, m.p_xn, nullptr, T, m.H, m.eps, s));
     d->launches++;
+    if (flags & STEP_LM_HEAD) {
+        // logits of every row: the fp16 lm_head goes through the same tcgen05 pipeline, weights by TMA
+        if (T > m.p_logit_rows || m.lm_head.kind != LIN_F16) return cudaErrorInvalidValue;
+        GemmTcParams g;
+        memset(&g, 0, sizeof(g));
+        g.K = m.lm_head.K; g.T = T; g.t_tile = T >= 512 ? 512 : ((T + 15) & ~15);
+        g.n_valid = m.vocab_local; g.ldo = m.ld_logits; g.epi = TC_EPI_STORE_F32; g.out = m.p_logits; g.status = m.tc_status;
+        CK(b2_gemm_f16_tc(&g, m.lm_head.w, m.lm_head.ldw, m.p_xn, m.H, s));
+        d->launches++;
+    }
+    if (flags & STEP_ARGMAX) {
+        if (!(flags & STEP_LM_HEAD)) return cudaErrorInvalidValue;
+        ArgmaxParams a;
+        memset(&a, 0, sizeof(a));
+        a.logits = m.p_logits; a.ld = m.ld_logits; a.n_rows = T; a.vocab_local = m.vocab_local;
+        a.vocab_offset = m.vocab_offset; a.blocks = m.argmax_blocks; a.scratch = m.p_argmax_scratch;
+        a.counters = m.p_argmax_counters; a.out_tokens = m.p_out_tokens;
+        a.seqs = (flags & STEP_ADVANCE) ? (SeqState*)m.seqs : nullptr; a.rows = (const RowMeta*)m.p_rows; a.comm = m.comm;
+        CK(b2_argmax(&a, s));
+        d->launches++;
+    }
+    if (flags & STEP_ADVANCE) {
+        CK(b2_advance(m.seqs, nullptr, n_seqs, 1, s));
+        d->launches++;
+    }
+    if (flags & STEP_SPEC) {
+        if (!(flags & STEP_ARGMAX) || (flags & STEP_ADVANCE)) return cudaErrorInvalidValue;
+        CK(spec_tail(d, m.p_rows, m.p_row_tokens, m.p_out_tokens, n_seqs, s));
+    }
     return 0;
 }
 
-B2_API int b2_driver_prefill(void* h, int T, int flags, cudaStream_t s) { return prefill_impl((Driver*)h, T, flags, s); }
+static int run_impl(Driver* d, int rows, int n_seqs, int flags, cudaStream_t s) {
+    return (flags & STEP_GEMM_PATH) ? rows_impl(d, rows, n_seqs, flags, s) : step_impl(d, rows, n_seqs, flags, s);
+}
+
+B2_API int b2_driver_prefill(void* h, int T, int flags, cudaStream_t s) { return rows_impl((Driver*)h, T, 1, flags, s); }
+B2_API int b2_driver_rows(void* h, int T, int n_seqs, int flags, cudaStream_t s) {
+    return rows_impl((Driver*)h, T, n_seqs, flags, s);
+}
 
 B2_API void* b2_driver_create(const ModelDesc* m, const LayerDesc* layers) {
     Driver* d = new Driver();
@@ -354,7 +445,7 @@ B2_API void b2_driver_destroy(void* h) {
     delete d;
 }
 B2_API int b2_driver_step(void* h, int rows, int n_seqs, int flags, cudaStream_t s) {
-    return step_impl((Driver*)h, rows, n_seqs, flags, s);
+    return run_impl((Driver*)h, rows, n_seqs, flags, s);
 }
 B2_API long long b2_driver_launches(void* h) { return ((Driver*)h)->launches; }
 
@@ -365,7 +456,7 @@ B2_API int b2_driver_capture(void* h, int rows, int n_seqs, int flags, cudaStrea
     if (d->graph) { cudaGraphDestroy(d->graph); d->graph = nullptr; }
     cudaError_t e = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal);
     if (e != cudaSuccess) return e;
-    int r = step_impl(d, rows, n_seqs, flags, s);
+    int r = run_impl(d, rows, n_seqs, flags, s);
     cudaGraph_t g = nullptr;
     e = cudaStreamEndCapture(s, &g);
     if (r != 0) { if (g) cudaGraphDestroy(g); return r; }

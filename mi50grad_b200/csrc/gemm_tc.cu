@@ -133,7 +133,8 @@ __device__ __forceinline__ uint32_t tc_nib_hi(uint32_t w) {
 }
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xmap) {
+gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xmap,
+                    const __grid_constant__ CUtensorMap wmap) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the dynamic window is only guaranteed 16-byte aligned: align to the 1024-byte swizzle atom by hand
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -192,6 +193,7 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
         // packed weights and their scale/zero pairs stream through a cp.async ring: TC_RING-1
         // k-blocks are always in flight, each thread later reads back only what it copied itself
         uint4* my_ring = wring + tid;
+        const bool dense = p.dense != 0;          // fp16 weights arrive by TMA: nothing to dequantise
         auto issue = [&](int kb) {
             const int slot = kb % TC_RING;
             cp_async16(my_ring + (slot * 2 + 0) * 256, gp + (size_t)kb * 128);
@@ -203,11 +205,11 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
         };
 #pragma unroll
         for (int s = 0; s < TC_RING - 1; ++s) {
-            if (s < KB) issue(s);
+            if (s < KB && !dense) issue(s);
             cp_async_commit();
         }
         bool ok = true;
-        for (int kb = 0; kb < KB && ok; ++kb) {
+        for (int kb = 0; kb < KB && ok && !dense; ++kb) {
             const int s = kb % S;
             const uint32_t ph = (kb / S) & 1;
             if (kb + TC_RING - 1 < KB) issue(kb + TC_RING - 1);
@@ -302,7 +304,9 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
                 ok = mbar_wait(&empty[s], ph ^ 1, abort_flag);
                 if (!ok) break;
                 if (p.dbg & 2) { mbar_arrive(&full_b[s]); continue; }
-                mbar_arrive_expect_tx(&full_b[s], (uint32_t)boxes * 64 * 128);
+                mbar_arrive_expect_tx(&full_b[s], (uint32_t)boxes * 64 * 128 + (p.dense ? TC_A_BYTES : 0));
+                if (p.dense)
+                    tma_load_2d(sA + (size_t)s * TC_A_BYTES, &wmap, kb * TC_BK, blockIdx.x * TC_BM, &full_b[s]);
                 unsigned char* b = sB + (size_t)s * b_stage_bytes;
                 for (int bx = 0; bx < boxes; ++bx)
                     tma_load_2d(b + (size_t)bx * 64 * 128, &xmap, kb * TC_BK, t0 + bx * 64, &full_b[s]);
@@ -317,7 +321,7 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
             for (int kb = 0; kb < KB && ok; ++kb) {
                 const int s = kb % S;
                 const uint32_t ph = (kb / S) & 1;
-                ok = mbar_wait(&full_a[s], ph, abort_flag) && mbar_wait(&full_b[s], ph, abort_flag);
+                ok = (p.dense || mbar_wait(&full_a[s], ph, abort_flag)) && mbar_wait(&full_b[s], ph, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t a_addr = smem_u32(sA + (size_t)s * TC_A_BYTES);
@@ -368,7 +372,8 @@ B2_API size_t b2_gemm_tc_smem(int t_tile, int stages) {
 }
 
 // x: [T][ldx] fp16 activations (ldx multiple of 8, base 16-byte aligned).
-B2_API int b2_gemm_int4_tc(const GemmTcParams* p, const void* x, int ldx, cudaStream_t stream) {
+static int launch_tc(const GemmTcParams* p, const void* w, int ldw, int n_rows_w, const void* x, int ldx,
+                     cudaStream_t stream) {
     if (p->T < 1 || p->t_tile < 16 || p->t_tile > 512 || (p->t_tile & 15) || (ldx & 7) || ((uintptr_t)x & 15))
         return cudaErrorInvalidValue;
     EncodeTiledFn enc = get_encode();
@@ -382,7 +387,18 @@ B2_API int b2_gemm_int4_tc(const GemmTcParams* p, const void* x, int ldx, cudaSt
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    CUtensorMap wmap = map;
+    if (w) {
+        if ((ldw & 7) || ((uintptr_t)w & 15) || (p->K % TC_BK)) return cudaErrorInvalidValue;
+        cuuint64_t wd[2] = {(cuuint64_t)p->K, (cuuint64_t)n_rows_w};
+        cuuint64_t ws[1] = {(cuuint64_t)ldw * 2};
+        cuuint32_t wb[2] = {TC_BK, TC_BM};
+        r = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)w, wd, ws, wb, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    }
     GemmTcParams q = *p;
+    q.dense = w ? 1 : 0;
     size_t per_stage = TC_A_BYTES + (size_t)((q.t_tile + 63) / 64) * 64 * 128;
     int stages = (int)((160 * 1024) / per_stage);
     q.stages = stages > 4 ? 4 : (stages < 2 ? 2 : stages);
@@ -394,7 +410,21 @@ B2_API int b2_gemm_int4_tc(const GemmTcParams* p, const void* x, int ldx, cudaSt
         configured = smem;
     }
     dim3 grid(q.NTL * 16 / TC_BM, (q.T + q.t_tile - 1) / q.t_tile);
-    gemm_int4_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(q, map);
+    gemm_int4_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(q, map, wmap);
     return cudaGetLastError();
+}
+B2_API int b2_gemm_int4_tc(const GemmTcParams* p, const void* x, int ldx, cudaStream_t stream) {
+    return launch_tc(p, nullptr, 0, 0, x, ldx, stream);
+}
+// Dense fp16 weights w[N][ldw] (row = output feature) take the same pipeline: the weight tile is a
+// second TMA load into the stage the dequantising warps would have filled.  p->K, T, t_tile, n_valid (= N),
+// ldo, epi, out, status are used; the INT4 fields are ignored.
+B2_API int b2_gemm_f16_tc(const GemmTcParams* p, const void* w, int ldw, const void* x, int ldx, cudaStream_t stream) {
+    if (!w || p->n_valid < 1) return cudaErrorInvalidValue;
+    GemmTcParams q = *p;
+    q.KB = q.K / TC_BK;
+    q.NTL = (q.n_valid + TC_BM - 1) / TC_BM * (TC_BM / 16);
+    q.qfrag = nullptr; q.szfrag = nullptr;
+    return launch_tc(&q, w, ldw, q.n_valid, x, ldx, stream);
 }
 B2_API int b2_sizeof_gemm_tc_params() { return (int)sizeof(GemmTcParams); }

@@ -17,8 +17,9 @@ struct GemmTcParams {
     void* out;
     int* status;             // [0] set to 1 when a bounded wait expired
     int dbg;                 // timing experiments only: 1 skip dequant+stores, 2 skip TMA loads, 4 skip MMA issue
-    int pad;
+    int dense;               // set by the launcher: weights are fp16 and come through a tensor map
 };
 
 
 B2_API int b2_gemm_int4_tc(const GemmTcParams* p, const void* x, int ldx, cudaStream_t stream);
+B2_API int b2_gemm_f16_tc(const GemmTcParams* p, const void* w, int ldw, const void* x, int ldx, cudaStream_t stream);

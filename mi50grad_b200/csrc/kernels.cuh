@@ -64,6 +64,56 @@ struct CollParams {
     int test_withhold;       // test hook: never signal, so that the bounded wait expires
 };
 
+// ---- speculative verification (csrc/speculative.cu)
+#define SPEC_MAX_NODES 16          // rows per sequence in one verify step: the pending token + up to 15 drafts
+
+// What the DeltaNet verify kernel leaves behind for the commit kernel, one block per
+// (linear-attention layer, launched sequence): normalised keys, the rank-1 update vectors
+// u, the cumulative log-decay G along each node's path, and the raw conv inputs.
+struct SpecStage {
+    unsigned char* base;
+    long long layer_stride, seq_stride;      // bytes
+    int off_k;                               // f32 [SPEC_MAX_NODES][nk][dk]
+    int off_u;                               // f32 [SPEC_MAX_NODES][nv][dv]
+    int off_g;                               // f32 [SPEC_MAX_NODES][nv]
+    int off_x;                               // f16 [SPEC_MAX_NODES][2*nk*dk + nv*dv]
+};
+
+struct SpecAcceptParams {
+    const int* out_tokens;       // [rows] the model's greedy prediction after each row
+    const int* row_tokens;       // [rows] tokens that were fed (-1: the sequence's pending token)
+    const RowMeta* rows;
+    const int* seq_rows;         // [n_seqs+1]
+    SeqState* seqs;              // len += accepted path length, token = next pending token
+    int* acc;                    // [n_seqs][SPEC_MAX_NODES+2]: path length, slot of the root, path node indices
+    int* result;                 // [n_seqs][SPEC_MAX_NODES+2]: accepted drafts, next token, accepted draft tokens
+    int n_seqs, pad;
+};
+
+struct DeltaCommitParams {
+    float* state0;               // state of the first linear-attention layer [seq][nv][dk][dv]
+    __half* conv0;               // conv history of the first linear-attention layer
+    long long state_layer_stride, conv_layer_stride;   // elements
+    SpecStage st;
+    const int* acc;
+    const RowMeta* rows;
+    const int* seq_rows;
+    int nk, nv, n_seqs, n_layers;
+};
+
+struct KvCompactParams {
+    __half* k0; __half* v0;      // caches of the first full-attention layer [seq][max_seq][nkv][hd]
+    long long layer_stride;      // elements
+    const int* acc;
+    const RowMeta* rows;
+    const int* seq_rows;
+    int n_layers, n_seqs, nkv, hd, max_seq, pad;
+};
+
+B2_API int b2_deltanet_verify(const DeltaParams* p, const SpecStage* st, int layer, int dk, int dv, cudaStream_t s);
+B2_API int b2_deltanet_commit(const DeltaCommitParams* p, int dk, int dv, cudaStream_t s);
+B2_API int b2_spec_accept(const SpecAcceptParams* p, cudaStream_t s);
+B2_API int b2_kv_compact(const KvCompactParams* p, cudaStream_t s);
 B2_API int b2_allreduce(const CollParams* p, int max_ctas, cudaStream_t s);
 B2_API int b2_gemv_int4(const GemvInt4Params* p, cudaStream_t stream);
 B2_API int b2_gemv_f16(const GemvF16Params* p, cudaStream_t stream);

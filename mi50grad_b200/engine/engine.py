@@ -128,6 +128,7 @@ class InferenceEngine:
         self._driver = None
         self._graph_key = None
         self._tmpl_key = None
+        self._ptmpl_key = None
         self._launch_counts: Dict[int, int] = {}
         self._steps = 0
         self._init_rope_tables()
@@ -325,6 +326,22 @@ class InferenceEngine:
         b["tc_status"] = i32(4)
         b["p_ab"] = f16(P, max(2, 2 * sp.n_la_v))
         b["coll_counters"] = i32(8)
+        # many-row steps (batched decode, speculative verification): logits / arg-max / split-KV scratch
+        SR = self.step_rows = min(P, max(8, self.ecfg.max_step_rows or 8 * self.max_batch))
+        b["p_logits"] = f32(SR, b["ld_logits"])
+        b["p_argmax_scratch"], b["p_argmax_counters"] = f32(SR * self.argmax_blocks * 2), i32(SR + 8)
+        b["p_out_tokens"] = i32(P)
+        b["p_attn_scratch"] = f32(SR * sp.n_kv * self.attn_splits * G * (cfg.head_dim + 2))
+        b["p_attn_counters"] = i32(SR * sp.n_kv + 8)
+        # speculative verification: staging of the DeltaNet verify kernel, acceptance results
+        offs = [C.c_int() for _ in range(4)]
+        self.lib.b2_spec_stage_layout.restype = C.c_longlong
+        blk = int(self.lib.b2_spec_stage_layout(sp.n_la_k, sp.n_la_v, cfg.linear_key_head_dim,
+                                                cfg.linear_value_head_dim, *[C.byref(o) for o in offs]))
+        n_lin = len(self.states.dn.layers)
+        b["spec_stage"] = torch.zeros(max(1, n_lin) * self.max_batch * blk, dtype=torch.uint8, device=dev)
+        b["spec_acc"] = i32(self.max_batch, L.SPEC_MAX_NODES + 2)
+        b["spec_result"] = i32(self.max_batch, L.SPEC_MAX_NODES + 2)
 
         m = L.ModelDesc()
         m.n_layers, m.H, m.vocab = cfg.num_hidden_layers, H, cfg.vocab_size
@@ -352,6 +369,18 @@ class InferenceEngine:
         for k in ("p_h", "p_xn", "p_proj", "p_attn", "p_act", "p_partial", "p_rows", "p_rows_tmpl", "p_row_tokens",
                   "tc_status", "coll_counters", "p_ab"):
             setattr(m, k, b[k].data_ptr())
+        for k in ("p_logits", "p_argmax_scratch", "p_argmax_counters", "p_out_tokens", "p_attn_scratch",
+                  "p_attn_counters", "spec_acc", "spec_result"):
+            setattr(m, k, b[k].data_ptr())
+        m.p_logit_rows, m.n_lin_layers, m.n_full_layers = SR, n_lin, len(self.states.kv.layers)
+        m.spec.base, m.spec.layer_stride, m.spec.seq_stride = b["spec_stage"].data_ptr(), self.max_batch * blk, blk
+        m.spec.off_k, m.spec.off_u, m.spec.off_g, m.spec.off_x = [o.value for o in offs]
+        dn, kv = self.states.dn, self.states.kv
+        if n_lin:
+            m.state0, m.conv0 = dn.S.data_ptr(), dn.conv.data_ptr()
+            m.state_layer_stride, m.conv_layer_stride = dn.S.stride(0), dn.conv.stride(0)
+        if len(kv.layers):
+            m.k0, m.v0, m.kv_layer_stride = kv.k.data_ptr(), kv.v.data_ptr(), kv.k.stride(0)
         if self.comm is not None and self.tp_size > 1:
             if self.comm.part_floats < self.max_prefill * H:
                 raise ValueError("communicator staging buffer is smaller than max_prefill x hidden")
@@ -362,6 +391,7 @@ class InferenceEngine:
         for i, dl in enumerate(self.layers):
             d = descs[i]
             d.type = dl.type
+            d.type_index = self.states.kv.index[i] if dl.type == 0 else self.states.dn.index[i]
             d.in_proj, d.out_proj = dl.in_proj.desc(), dl.out_proj.desc()
             d.gate_up, d.down = dl.gate_up.desc(), dl.down.desc()
             d.attn_norm = dl.attn_norm.data_ptr()
@@ -452,7 +482,7 @@ class InferenceEngine:
         sr = torch.zeros(self.buf["seq_rows"].shape[0], dtype=torch.int32)
         sr[1] = n
         self.buf["seq_rows"].copy_(sr.to(self.device))
-        self._tmpl_key = None
+        self._tmpl_key = self._ptmpl_key = None
         L.check(self.lib.b2_driver_prefill(C.c_void_p(self._driver), n, flags, L.stream()), "driver prefill")
         self.states.seqs[seq, 0] += n
         self._steps += 1
@@ -501,9 +531,28 @@ class InferenceEngine:
         [n_steps, len(seqs)] when `collect`."""
         seqs = list(seqs) if seqs is not None else [0]
         self._ensure_driver()
-        self._template_decode(seqs)
         rows = len(seqs)
         flags = L.STEP_EMBED_TOKENS | L.STEP_LM_HEAD | L.STEP_ARGMAX | L.STEP_ADVANCE
+        out_buf = self.buf["out_tokens"]
+        if rows > self.max_rows:
+            # more sequences than the GEMV kernels take rows: tensor-core path
+            if not self.use_tc_prefill or rows > self.step_rows:
+                raise ValueError(f"{rows} sequences exceed what this engine was sized for ({self.step_rows})")
+            key = ("decode", tuple(seqs))
+            if self._ptmpl_key != key:
+                t = torch.zeros(rows, 6, dtype=torch.int32)
+                t[:, 0] = torch.tensor(seqs, dtype=torch.int32)
+                t[:, 4] = 1
+                self.buf["p_rows_tmpl"][:rows].copy_(t.to(self.device))
+                sr = torch.zeros(self.buf["seq_rows"].shape[0], dtype=torch.int32)
+                sr[:rows + 1] = torch.arange(rows + 1, dtype=torch.int32)
+                self.buf["seq_rows"].copy_(sr.to(self.device))
+                self.buf["p_row_tokens"][:rows].fill_(-1)
+                self._ptmpl_key, self._tmpl_key = key, None
+            flags |= L.STEP_GEMM_PATH
+            out_buf = self.buf["p_out_tokens"]
+        else:
+            self._template_decode(seqs)
         use_graph = self.ecfg.use_graph if graph is None else graph
         outs = []
         if use_graph:
@@ -518,14 +567,14 @@ class InferenceEngine:
             if collect:
                 for _ in range(n_steps):
                     L.check(self.lib.b2_driver_replay(C.c_void_p(self._driver), 1, L.stream()), "graph replay")
-                    outs.append(self.buf["out_tokens"][:rows].clone())
+                    outs.append(out_buf[:rows].clone())
             else:
                 L.check(self.lib.b2_driver_replay(C.c_void_p(self._driver), n_steps, L.stream()), "graph replay")
         else:
             for _ in range(n_steps):
                 self._run(rows, rows, flags)
                 if collect:
-                    outs.append(self.buf["out_tokens"][:rows].clone())
+                    outs.append(out_buf[:rows].clone())
         self._steps += n_steps
         return torch.stack(outs) if collect else None
 
@@ -552,6 +601,70 @@ class InferenceEngine:
         self._pin_out.copy_(self.buf["out_tokens"][:1], non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return int(self._pin_out[0])
+
+    # ------------------------------------------------------------------ speculative verification
+    def spec_step(self, drafts: Sequence[Sequence[int]], parents: Sequence[Sequence[int]],
+                  seqs: Optional[Sequence[int]] = None, roots: Optional[Sequence[int]] = None):
+        """One verify-and-commit step for several sequences.  For sequence i the
+        pending token (roots[i], default: the token the last step stored) and the
+        draft tree drafts[i] / parents[i] (parent -1 = child of the pending token,
+        parents precede children) go through the model in ONE pass; the longest
+        path the model would have produced greedily is accepted on the device and
+        KV cache, DeltaNet state and sequence length end up as if only the accepted
+        tokens had been fed.  Returns [(accepted draft tokens, next pending token)]."""
+        seqs = list(seqs) if seqs is not None else list(range(len(drafts)))
+        self._ensure_driver()
+        n_seqs = len(seqs)
+        if n_seqs > self.max_batch or len(drafts) != n_seqs or len(parents) != n_seqs:
+            raise ValueError("one draft list per sequence, at most max_batch sequences")
+        rows, seq_rows, toks = [], [0], []
+        for i, sq in enumerate(seqs):
+            d, par = list(drafts[i]), list(parents[i])
+            if len(d) != len(par) or len(d) + 1 > L.SPEC_MAX_NODES:
+                raise ValueError(f"a draft tree has at most {L.SPEC_MAX_NODES - 1} nodes")
+            masks, depth = [1], [0]
+            for t, pp in enumerate(par):
+                if not -1 <= pp < t:
+                    raise ValueError("parents must precede their children")
+                masks.append(masks[pp + 1] | (1 << (t + 1)))
+                depth.append(depth[pp + 1] + 1)
+            for t in range(len(d) + 1):
+                rows.append((sq, depth[t], t, masks[t]))
+            toks += [-1 if roots is None else int(roots[i])] + [int(x) for x in d]
+            seq_rows.append(len(rows))
+        R = len(rows)
+        gemm_path = R > self.max_rows
+        if gemm_path and (not self.use_tc_prefill or R > self.step_rows):
+            raise ValueError(f"{R} rows exceed what this engine was sized for ({self.step_rows})")
+        key = ("spec", tuple(rows))
+        flags = L.STEP_EMBED_TOKENS | L.STEP_LM_HEAD | L.STEP_ARGMAX | L.STEP_SPEC
+        if gemm_path:
+            flags |= L.STEP_GEMM_PATH
+            if self._ptmpl_key != key:
+                t = torch.zeros(R, 6, dtype=torch.int32)
+                for r, (sq, dep, slot, mask) in enumerate(rows):
+                    t[r, 0], t[r, 1], t[r, 2], t[r, 4] = sq, dep, slot, mask
+                self.buf["p_rows_tmpl"][:R].copy_(t.to(self.device))
+                sr = torch.zeros(self.buf["seq_rows"].shape[0], dtype=torch.int32)
+                sr[:len(seq_rows)] = torch.tensor(seq_rows, dtype=torch.int32)
+                self.buf["seq_rows"].copy_(sr.to(self.device))
+                self._ptmpl_key, self._tmpl_key = key, None
+            self.buf["p_row_tokens"][:R].copy_(torch.tensor(toks, dtype=torch.int32).to(self.device))
+        else:
+            self._set_template(key, rows, seq_rows)
+            self._ptmpl_key = None
+            rt = torch.full((self.max_rows,), -1, dtype=torch.int32)
+            rt[:R] = torch.tensor(toks, dtype=torch.int32)
+            self.buf["row_tokens"].copy_(rt.to(self.device))
+        self._run(R, n_seqs, flags)
+        if not gemm_path:
+            self.buf["row_tokens"].fill_(-1)
+        res = self.buf["spec_result"][:n_seqs].tolist()
+        return [(r[2:2 + r[0]], r[1]) for r in res]
+
+    def spec_step_tokens(self, root: int, drafts: Sequence[int], parents: Sequence[int], seq: int = 0):
+        """Single-sequence form used by generate.speculative.EngineBackend."""
+        return self.spec_step([list(drafts)], [list(parents)], [seq], [root])[0]
 
     def logits(self, rows: int = 1) -> torch.Tensor:
         """fp32 logits of the last step, this rank's vocabulary slice."""

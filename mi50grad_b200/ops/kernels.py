@@ -259,6 +259,24 @@ def gemm_int4_tc(pk, x: torch.Tensor, out: torch.Tensor, epi: int = L.TC_EPI_STO
     return out
 
 
+def gemm_f16_tc(w: torch.Tensor, x: torch.Tensor, out: torch.Tensor, epi: int = L.TC_EPI_STORE_F32,
+                t_tile: Optional[int] = None):
+    """out[t][n] (epi) = x[t, :K] @ w[n, :K] for dense fp16 weights on the tcgen05 tensor cores
+    (the lm_head of many rows).  K must be a multiple of 64."""
+    T, dev = x.shape[0], x.device
+    if t_tile is None:
+        t_tile = min(512, -(-T // 16) * 16)
+    st = _tc_status.get(dev)
+    if st is None:
+        st = _tc_status[dev] = torch.zeros(4, dtype=torch.int32, device=dev)
+    p = L.GemmTcParams()
+    p.K, p.T, p.t_tile, p.epi = w.shape[1], T, t_tile, epi
+    p.n_valid, p.ldo, p.out, p.status = w.shape[0], out.stride(0), out.data_ptr(), st.data_ptr()
+    L.check(L.lib().b2_gemm_f16_tc(C.byref(p), C.c_void_p(w.data_ptr()), w.stride(0), C.c_void_p(x.data_ptr()),
+                                   x.stride(0), L.stream()), "gemm_f16_tc")
+    return out
+
+
 def gemm_tc_check_status(device=None):
     """Raise if a tcgen05 GEMM gave up on a bounded barrier wait since the last check."""
     for dev, st in _tc_status.items():

@@ -28,6 +28,7 @@ FIN_TEST_WITHHOLD_SIGNAL = 32
 LIN_INT4, LIN_F16, LIN_NONE = 0, 1, 2
 STEP_EMBED_TOKENS, STEP_LM_HEAD, STEP_ARGMAX, STEP_ADVANCE, STEP_NO_COMMIT_DELTA = 1, 2, 4, 8, 16
 STEP_MATERIALIZE_XN = 32
+STEP_SPEC, STEP_GEMM_PATH = 64, 128
 
 vp, i32, f32, i64 = C.c_void_p, C.c_int, C.c_float, C.c_longlong
 
@@ -92,7 +93,7 @@ class ArgmaxParams(C.Structure):
 class GemmTcParams(C.Structure):
     _fields_ = [("qfrag", vp), ("szfrag", vp), ("K", i32), ("KB", i32), ("NTL", i32), ("G", i32), ("off32", i32),
                 ("gshift", i32), ("T", i32), ("t_tile", i32), ("n_valid", i32), ("ldo", i32), ("epi", i32),
-                ("stages", i32), ("out", vp), ("status", vp), ("dbg", i32), ("pad", i32)]
+                ("stages", i32), ("out", vp), ("status", vp), ("dbg", i32), ("dense", i32)]
 
 
 TC_EPI_STORE_F16, TC_EPI_SILU_PAIR, TC_EPI_STORE_F32, TC_EPI_RESID_F32 = 0, 1, 2, 3
@@ -105,12 +106,20 @@ class LinearDesc(C.Structure):
 
 
 class LayerDesc(C.Structure):
-    _fields_ = [("type", i32), ("pad", i32), ("in_proj", LinearDesc), ("out_proj", LinearDesc),
+    _fields_ = [("type", i32), ("type_index", i32), ("in_proj", LinearDesc), ("out_proj", LinearDesc),
                 ("gate_up", LinearDesc), ("down", LinearDesc), ("attn_norm", vp), ("ffn_norm", vp), ("next_norm", vp),
                 ("q_norm", vp), ("k_norm", vp), ("kcache", vp), ("vcache", vp),
                 ("wa", vp), ("wb", vp), ("conv_w", vp), ("conv_state", vp), ("state", vp),
                 ("A_log", vp), ("dt_bias", vp), ("la_norm", vp),
                 ("off_q", i32), ("off_k", i32), ("off_v", i32), ("off_z", i32), ("off_a", i32), ("off_b", i32)]
+
+
+class SpecStage(C.Structure):
+    _fields_ = [("base", vp), ("layer_stride", i64), ("seq_stride", i64), ("off_k", i32), ("off_u", i32),
+                ("off_g", i32), ("off_x", i32)]
+
+
+SPEC_MAX_NODES = 16
 
 
 class ModelDesc(C.Structure):
@@ -133,6 +142,12 @@ class ModelDesc(C.Structure):
                 ("max_prefill", i32), ("pad4", i32), ("p_h", vp), ("p_xn", vp), ("p_proj", vp), ("p_attn", vp),
                 ("p_act", vp), ("p_partial", vp), ("p_rows", vp), ("p_rows_tmpl", vp), ("p_row_tokens", vp),
                 ("tc_status", vp), ("p_ab", vp), ("coll_gather", vp * MAX_TP), ("coll_mc_gather", vp), ("coll_counters", vp),
+                ("p_logits", vp), ("p_argmax_scratch", vp), ("p_argmax_counters", vp), ("p_out_tokens", vp),
+                ("p_attn_scratch", vp), ("p_attn_counters", vp),
+                ("p_logit_rows", i32), ("n_lin_layers", i32), ("n_full_layers", i32), ("pad5", i32),
+                ("spec", SpecStage), ("spec_acc", vp), ("spec_result", vp),
+                ("state0", vp), ("conv0", vp), ("state_layer_stride", i64), ("conv_layer_stride", i64),
+                ("k0", vp), ("v0", vp), ("kv_layer_stride", i64),
                 ("comm", CommCtx)]
 
 
@@ -141,7 +156,7 @@ _SIZE_CHECKS = {
     "b2_sizeof_gemv_f16_params": GemvF16Params, "b2_sizeof_attn_params": AttnParams,
     "b2_sizeof_delta_params": DeltaParams, "b2_sizeof_argmax_params": ArgmaxParams,
     "b2_sizeof_linear_desc": LinearDesc, "b2_sizeof_layer_desc": LayerDesc,
-    "b2_sizeof_model_desc": ModelDesc, "b2_sizeof_gemm_tc_params": GemmTcParams, "b2_sizeof_row_meta": RowMeta, "b2_sizeof_seq_state": SeqState,
+    "b2_sizeof_model_desc": ModelDesc, "b2_sizeof_spec_stage": SpecStage, "b2_sizeof_gemm_tc_params": GemmTcParams, "b2_sizeof_row_meta": RowMeta, "b2_sizeof_seq_state": SeqState,
 }
 
 _lib: Optional[C.CDLL] = None

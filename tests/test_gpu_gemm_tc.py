@@ -53,3 +53,17 @@ def test_gemm_int4_tc_silu_pair():
     torch.cuda.synchronize()
     Kn.gemm_tc_check_status()
     assert _rel(out[:, :F].cpu(), ref) < 4e-3
+
+
+@pytest.mark.parametrize("T,N,K", [(80, 1000, 256), (16, 128, 5120), (300, 777, 1024)])
+def test_gemm_f16_tc_dense_weights(T, N, K):
+    g = torch.Generator(device="cuda").manual_seed(T + N)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).half()
+    x = torch.randn(T, K, device="cuda", generator=g).half()
+    out = torch.zeros(T, -(-N // 4) * 4, dtype=torch.float32, device="cuda")
+    from mi50grad_b200.ops import kernels as K_
+    K_.gemm_f16_tc(w, x, out)
+    K_.gemm_tc_check_status()
+    ref = x.float() @ w.float().t()
+    err = (out[:, :N] - ref).abs().max().item()
+    assert err < 2e-3 * max(1.0, ref.abs().max().item()), err
