@@ -276,8 +276,9 @@ static int step_impl(Driver* d, int rows, int n_seqs, int flags, cudaStream_t s)
         d->launches++;
     }
     if (flags & STEP_SPEC) {
-        if (!(flags & STEP_ARGMAX) || (flags & STEP_ADVANCE)) return cudaErrorInvalidValue;
-        CK(spec_tail(d, m.rows, m.row_tokens, m.out_tokens, n_seqs, s));
+        // without an arg-max this is a verify-only pass (hidden states out, nothing committed)
+        if (flags & STEP_ADVANCE) return cudaErrorInvalidValue;
+        if (flags & STEP_ARGMAX) CK(spec_tail(d, m.rows, m.row_tokens, m.out_tokens, n_seqs, s));
     }
     return 0;
 }
@@ -416,8 +417,8 @@ static int rows_impl(Driver* d, int T, int n_seqs, int flags, cudaStream_t s) {
         d->launches++;
     }
     if (flags & STEP_SPEC) {
-        if (!(flags & STEP_ARGMAX) || (flags & STEP_ADVANCE)) return cudaErrorInvalidValue;
-        CK(spec_tail(d, m.p_rows, m.p_row_tokens, m.p_out_tokens, n_seqs, s));
+        if (flags & STEP_ADVANCE) return cudaErrorInvalidValue;
+        if (flags & STEP_ARGMAX) CK(spec_tail(d, m.p_rows, m.p_row_tokens, m.p_out_tokens, n_seqs, s));
     }
     return 0;
 }

@@ -26,13 +26,15 @@
 #include "kernels.cuh"
 #include "gemm_tc.cuh"
 
-#define TC_PRODUCERS 8            // dequantising warps (also the epilogue warps)
+#define TC_PRODUCERS 16           // dequantising warps (also the epilogue warps): two groups of 8, group g takes
+                                  // the k-blocks of parity g, so two k-blocks are being dequantised at any time
+#define TC_GROUP_WARPS 8
 #define TC_THREADS ((TC_PRODUCERS + 2) * 32)
 #define TC_BK 64                 // k per stage (128 bytes of fp16: one swizzle row)
 #define TC_BM 128                // outputs per CTA (MMA M)
 #define TC_A_BYTES (TC_BM * TC_BK * 2)
 #define TC_WAIT_NS 1000000000LL  // bound of every barrier wait
-#define TC_RING 6                // k-blocks of packed weights + scales in flight per producer thread (cp.async)
+#define TC_RING 3                // own k-blocks of packed weights + scales in flight per producer thread (cp.async)
 
 // ---------------------------------------------------------------------------
 // PTX helpers
@@ -70,6 +72,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         if (*abort_flag) return false;
         if (globaltimer_ns() - t0 > TC_WAIT_NS) { *abort_flag = 1; return false; }
     }
+}
+// One lane of a converged warp.  The single-thread roles run their loops with the whole warp
+// converged and elect a lane only around the tcgen05 / TMA instructions: their descriptor and
+// coordinate operands are warp-uniform, and inside a divergent `if (lane == 0)` region the
+// compiler cannot keep them in uniform registers, which made every such instruction cost
+// well over a hundred cycles to issue.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+    return pred != 0;
 }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -147,19 +159,19 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
     unsigned char* sA = smem;
     unsigned char* sB = smem + (size_t)S * TC_A_BYTES;
     uint64_t* bars = (uint64_t*)(sB + (size_t)S * b_stage_bytes);
-    uint64_t* full_a = bars;            // [S] one arrival per producer warp
-    uint64_t* full_b = bars + S;        // [S] 1 arrival + transaction bytes
-    uint64_t* empty = bars + 2 * S;     // [S] 1 arrival (tcgen05.commit)
-    uint64_t* acc_full = bars + 3 * S;  // 1 arrival
-    uint32_t* tmem_slot = (uint32_t*)(bars + 3 * S + 1);
+    uint64_t* full = bars;              // [S] operands of the stage are in place: one arrival per producer warp of
+                                        // the stage's group (INT4 weights) + 1 arrival with the TMA transaction bytes
+    uint64_t* empty = bars + S;         // [S] 1 arrival (tcgen05.commit)
+    uint64_t* acc_full = bars + 2 * S;  // 1 arrival
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * S + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    uint4* wring = (uint4*)(((uintptr_t)(tmem_slot + 2) + 15) & ~(uintptr_t)15);   // [TC_RING][2][256 producer threads]: 16 B of nibbles, 2 x 8 B scale/zero
+    uint4* wring = (uint4*)(((uintptr_t)(tmem_slot + 2) + 15) & ~(uintptr_t)15);   // [TC_RING][2][512 producer threads]: 16 B of nibbles, 2 x 8 B scale/zero
 
     int tmem_cols = 32;
     while (tmem_cols < Tp) tmem_cols <<= 1;
 
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { mbar_init(&full_a[s], TC_PRODUCERS); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < S; ++s) { mbar_init(&full[s], p.dense ? 1 : TC_GROUP_WARPS + 1); mbar_init(&empty[s], 1); }
         mbar_init(acc_full, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -175,57 +187,64 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
     const uint32_t tmem_base = *tmem_slot;
     const int KB = p.KB;
 
+    // Every role walks the stages with running counters (stage index, phase bit, addresses).  The
+    // loops of the single-thread roles are chains of dependent instructions, so each instruction
+    // taken out of them shortens the time per k-block directly.
     if (warp < TC_PRODUCERS) {
         // ================= weight producers =================
         // warp w owns the 16-row tile w of the CTA's 128 outputs: one 16-byte load per k-block and lane
         const int g = lane >> 2, t = lane & 3;
-        const int wt = blockIdx.x * 2 + (warp >> 2);
-        const int ti = warp & 3;
+        const int grp = warp >> 3, w8 = warp & 7;
+        const int wt = blockIdx.x * 2 + (w8 >> 2);
+        const int ti = w8 & 3;
         const int tile = wt * 4 + ti;
-        const uint4* gp = p.qfrag + ((size_t)wt * KB * 4 + ti) * 32 + lane;     // + kb*128 per k-block
+        const bool dense = p.dense != 0;          // fp16 weights arrive by TMA: nothing to dequantise
         const __half2 sixteenth = __float2half2_rn(0.0625f);
         const __half2 k1024 = __float2half2_rn(1024.f), k64 = __float2half2_rn(64.f);
         // swizzled byte offsets of this lane's stores: row & 7 == g for both of its rows
-        const uint32_t row_lo_off = (uint32_t)(warp * 16 + g) * 128 + t * 4, row_hi_off = row_lo_off + 8 * 128;
+        const uint32_t row_lo_off = (uint32_t)(w8 * 16 + g) * 128 + t * 4;
         uint32_t sw[8];
 #pragma unroll
         for (int c8 = 0; c8 < 8; ++c8) sw[c8] = (uint32_t)((c8 ^ g) << 4);
-        // packed weights and their scale/zero pairs stream through a cp.async ring: TC_RING-1
-        // k-blocks are always in flight, each thread later reads back only what it copied itself
+        // packed weights and their scale/zero pairs stream through a cp.async ring: TC_RING-1 of
+        // the group's k-blocks are always in flight, each thread later reads back only what it copied
         uint4* my_ring = wring + tid;
-        const bool dense = p.dense != 0;          // fp16 weights arrive by TMA: nothing to dequantise
-        auto issue = [&](int kb) {
-            const int slot = kb % TC_RING;
-            cp_async16(my_ring + (slot * 2 + 0) * 256, gp + (size_t)kb * 128);
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const int grp = (2 * kb + j + p.off32) >> p.gshift;
-                cp_async8((uint2*)(my_ring + (slot * 2 + 1) * 256) + j, p.szfrag + ((size_t)tile * p.G + grp) * 8 + g);
-            }
+        const uint4* gq = dense ? nullptr : p.qfrag + ((size_t)wt * KB * 4 + ti) * 32 + lane + (size_t)grp * 128;
+        const uint2* gs = dense ? nullptr : p.szfrag + (size_t)tile * p.G * 8 + g;
+        int c_issue = p.off32 + 2 * grp;          // 32-k chunk counter of the next k-block to issue
+        int slot_issue = 0;
+        auto issue = [&]() {
+            uint4* dst = my_ring + slot_issue * 1024;
+            cp_async16(dst, gq);
+            cp_async8((uint2*)(dst + 512), gs + (size_t)(c_issue >> p.gshift) * 8);
+            cp_async8((uint2*)(dst + 512) + 1, gs + (size_t)((c_issue + 1) >> p.gshift) * 8);
+            gq += 256; c_issue += 4;
+            slot_issue = slot_issue == TC_RING - 1 ? 0 : slot_issue + 1;
         };
 #pragma unroll
-        for (int s = 0; s < TC_RING - 1; ++s) {
-            if (s < KB && !dense) issue(s);
+        for (int i = 0; i < TC_RING - 1; ++i) {
+            if (grp + 2 * i < KB && !dense) issue();
             cp_async_commit();
         }
         bool ok = true;
-        for (int kb = 0; kb < KB && ok && !dense; ++kb) {
-            const int s = kb % S;
-            const uint32_t ph = (kb / S) & 1;
-            if (kb + TC_RING - 1 < KB) issue(kb + TC_RING - 1);
+        int st = grp, slot = 0;
+        uint32_t ph = 0;
+        unsigned char* a_stage = sA + (size_t)grp * TC_A_BYTES + row_lo_off;
+        for (int kb = grp; kb < KB && !dense; kb += 2) {
+            if (kb + 2 * (TC_RING - 1) < KB) issue();
             cp_async_commit();
             cp_async_wait<TC_RING - 1>();
-            const uint4 wv = my_ring[((kb % TC_RING) * 2 + 0) * 256];
-            const uint4 szq = my_ring[((kb % TC_RING) * 2 + 1) * 256];
+            const uint4 wv = my_ring[slot * 1024];
+            const uint4 szq = my_ring[slot * 1024 + 512];
+            slot = slot == TC_RING - 1 ? 0 : slot + 1;
             {   // one lane polls: many pollers on one barrier slow the arrivals down
                 int o = 1;
-                if (lane == 0) o = mbar_wait(&empty[s], ph ^ 1, abort_flag) ? 1 : 0;
+                if (lane == 0) o = mbar_wait(&empty[st], ph ^ 1, abort_flag) ? 1 : 0;
                 ok = __shfl_sync(0xffffffffu, o, 0) != 0;
             }
             if (!ok) break;
-            unsigned char* a_lo = sA + (size_t)s * TC_A_BYTES + row_lo_off;
-            unsigned char* a_hi = sA + (size_t)s * TC_A_BYTES + row_hi_off;
-            if (!(p.dbg & 1))
+            unsigned char* a_lo = a_stage;
+            unsigned char* a_hi = a_stage + 8 * 128;
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 const uint2 sz = j ? make_uint2(szq.z, szq.w) : make_uint2(szq.x, szq.y);
@@ -255,7 +274,9 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
             }
             fence_proxy_async_smem();           // generic-proxy stores -> visible to the tensor core
             __syncwarp();
-            if (lane == 0) mbar_arrive(&full_a[s]);
+            if (lane == 0) mbar_arrive(&full[st]);
+            st += 2; a_stage += 2 * TC_A_BYTES;       // S is even: a group keeps to the stages of its parity
+            if (st >= S) { st -= S; ph ^= 1; a_stage = sA + (size_t)st * TC_A_BYTES + row_lo_off; }
         }
         cp_async_wait<0>();
         // ================= epilogue =================
@@ -264,7 +285,7 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
         if (ok) {
             const int lg = warp & 3;               // tensor-memory lane group this warp may read
             const int n = blockIdx.x * TC_BM + lg * 32 + lane;
-            for (int c0 = (warp >> 2) * 32; c0 < Tp; c0 += 64) {
+            for (int c0 = (warp >> 2) * 32; c0 < Tp; c0 += (TC_PRODUCERS / 4) * 32) {
                 uint32_t r[32];
                 tc_ld32(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)c0, r);
                 tc_wait_ld();
@@ -296,47 +317,58 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
         }
     } else if (warp == TC_PRODUCERS) {
         // ================= activation producer (TMA) =================
-        if (lane == 0) {
-            bool ok = true;
-            for (int kb = 0; kb < KB && ok; ++kb) {
-                const int s = kb % S;
-                const uint32_t ph = (kb / S) & 1;
-                ok = mbar_wait(&empty[s], ph ^ 1, abort_flag);
-                if (!ok) break;
-                if (p.dbg & 2) { mbar_arrive(&full_b[s]); continue; }
-                mbar_arrive_expect_tx(&full_b[s], (uint32_t)boxes * 64 * 128 + (p.dense ? TC_A_BYTES : 0));
-                if (p.dense)
-                    tma_load_2d(sA + (size_t)s * TC_A_BYTES, &wmap, kb * TC_BK, blockIdx.x * TC_BM, &full_b[s]);
-                unsigned char* b = sB + (size_t)s * b_stage_bytes;
-                for (int bx = 0; bx < boxes; ++bx)
-                    tma_load_2d(b + (size_t)bx * 64 * 128, &xmap, kb * TC_BK, t0 + bx * 64, &full_b[s]);
+        {
+            const bool dense = p.dense != 0;
+            const uint32_t tx = (uint32_t)boxes * 64 * 128 + (dense ? TC_A_BYTES : 0);
+            const int row_w = blockIdx.x * TC_BM;
+            int st = 0;
+            uint32_t ph = 0;
+            unsigned char* a = sA;
+            unsigned char* b = sB;
+            for (int kb = 0, kx = 0; kb < KB; ++kb, kx += TC_BK) {
+                if (!mbar_wait(&empty[st], ph ^ 1, abort_flag)) break;
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(&full[st], tx);
+                    if (dense) tma_load_2d(a, &wmap, kx, row_w, &full[st]);
+                    for (int bx = 0; bx < boxes; ++bx)
+                        tma_load_2d(b + bx * (64 * 128), &xmap, kx, t0 + bx * 64, &full[st]);
+                }
+                __syncwarp();
+                a += TC_A_BYTES; b += b_stage_bytes;
+                if (++st == S) { st = 0; ph ^= 1; a = sA; b = sB; }
             }
         }
     } else {
         // ================= MMA issuer =================
-        if (lane == 0) {
+        {
+            const bool dense = p.dense != 0;
             const int n1 = min(Tp, 256), n2 = Tp - n1;
             const uint32_t idesc1 = make_idesc_f16(n1), idesc2 = make_idesc_f16(n2 > 0 ? n2 : 16);
+            // descriptors differ between stages and k16 steps only in the start-address field (16-byte units)
+            const uint64_t ad0 = make_desc_sw128(smem_u32(sA)), bd0 = make_desc_sw128(smem_u32(sB));
+            const uint64_t a_step = TC_A_BYTES >> 4, b_step = (uint64_t)(b_stage_bytes >> 4), b_half = (256 * 128) >> 4;
+            uint64_t ad = ad0, bd = bd0;
+            int st = 0;
+            uint32_t ph = 0;
             bool ok = true;
-            for (int kb = 0; kb < KB && ok; ++kb) {
-                const int s = kb % S;
-                const uint32_t ph = (kb / S) & 1;
-                ok = (p.dense || mbar_wait(&full_a[s], ph, abort_flag)) && mbar_wait(&full_b[s], ph, abort_flag);
+            for (int kb = 0; kb < KB; ++kb) {
+                ok = mbar_wait(&full[st], ph, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(sA + (size_t)s * TC_A_BYTES);
-                const uint32_t b_addr = smem_u32(sB + (size_t)s * b_stage_bytes);
-                if (!(p.dbg & 4))
+                if (elect_one()) {
 #pragma unroll
-                for (int k16 = 0; k16 < TC_BK / 16; ++k16) {
-                    const uint64_t ad = make_desc_sw128(a_addr + k16 * 32);
-                    const uint32_t acc = (kb > 0 || k16 > 0) ? 1u : 0u;
-                    tc_mma_f16(tmem_base, ad, make_desc_sw128(b_addr + k16 * 32), idesc1, acc);
-                    if (n2 > 0) tc_mma_f16(tmem_base + 256, ad, make_desc_sw128(b_addr + 256 * 128 + k16 * 32), idesc2, acc);
+                    for (int k16 = 0; k16 < TC_BK / 16; ++k16) {
+                        tc_mma_f16(tmem_base, ad + 2 * k16, bd + 2 * k16, idesc1, (kb | k16) ? 1u : 0u);
+                        if (n2 > 0) tc_mma_f16(tmem_base + 256, ad + 2 * k16, bd + b_half + 2 * k16, idesc2, (kb | k16) ? 1u : 0u);
+                    }
+                    tc_commit(&empty[st]);      // stage reusable once these MMAs have read it
                 }
-                tc_commit(&empty[s]);           // stage reusable once these MMAs have read it
+                __syncwarp();
+                ad += a_step; bd += b_step;
+                if (++st == S) { st = 0; ph ^= 1; ad = ad0; bd = bd0; }
             }
-            if (ok) tc_commit(acc_full);
+            if (ok && elect_one()) tc_commit(acc_full);
+            __syncwarp();
         }
     }
     if (*abort_flag && tid == 0 && p.status) atomicExch(p.status, 1);
@@ -368,7 +400,7 @@ static EncodeTiledFn get_encode() {
 
 B2_API size_t b2_gemm_tc_smem(int t_tile, int stages) {
     size_t b = (size_t)((t_tile + 63) / 64) * 64 * 128;
-    return 1024 + (size_t)stages * (TC_A_BYTES + b) + (3 * stages + 1) * 8 + 16 + 16 + (size_t)TC_RING * 2 * 256 * 16;
+    return 1024 + (size_t)stages * (TC_A_BYTES + b) + (2 * stages + 1) * 8 + 16 + 16 + (size_t)TC_RING * 2 * (TC_PRODUCERS * 32) * 16;
 }
 
 // x: [T][ldx] fp16 activations (ldx multiple of 8, base 16-byte aligned).
@@ -400,8 +432,12 @@ static int launch_tc(const GemmTcParams* p, const void* w, int ldw, int n_rows_w
     GemmTcParams q = *p;
     q.dense = w ? 1 : 0;
     size_t per_stage = TC_A_BYTES + (size_t)((q.t_tile + 63) / 64) * 64 * 128;
-    int stages = (int)((160 * 1024) / per_stage);
-    q.stages = stages > 4 ? 4 : (stages < 2 ? 2 : stages);
+    // as many stages as shared memory holds next to the weight ring, an even number (the two producer
+    // groups alternate stages); deep pipelines matter most for few tokens, where a stage is consumed quickly
+    const size_t fixed = 1024 + 256 + (size_t)TC_RING * 2 * (TC_PRODUCERS * 32) * 16;
+    int stages = (int)((227 * 1024 - fixed) / per_stage);
+    stages = stages > 8 ? 8 : stages;
+    q.stages = stages < 2 ? 2 : (stages & ~1);
     size_t smem = b2_gemm_tc_smem(q.t_tile, q.stages);
     static size_t configured = 0;
     if (smem > configured) {

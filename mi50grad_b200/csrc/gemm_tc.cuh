@@ -16,7 +16,7 @@ struct GemmTcParams {
     int n_valid, ldo, epi, stages;
     void* out;
     int* status;             // [0] set to 1 when a bounded wait expired
-    int dbg;                 // timing experiments only: 1 skip dequant+stores, 2 skip TMA loads, 4 skip MMA issue
+    int pad;
     int dense;               // set by the launcher: weights are fp16 and come through a tensor map
 };
 

@@ -604,14 +604,21 @@ class InferenceEngine:
 
     # ------------------------------------------------------------------ speculative verification
     def spec_step(self, drafts: Sequence[Sequence[int]], parents: Sequence[Sequence[int]],
-                  seqs: Optional[Sequence[int]] = None, roots: Optional[Sequence[int]] = None):
+                  seqs: Optional[Sequence[int]] = None, roots: Optional[Sequence[int]] = None,
+                  graph: bool = False, tokens_dev: Optional[torch.Tensor] = None, sync: bool = True):
         """One verify-and-commit step for several sequences.  For sequence i the
         pending token (roots[i], default: the token the last step stored) and the
         draft tree drafts[i] / parents[i] (parent -1 = child of the pending token,
         parents precede children) go through the model in ONE pass; the longest
         path the model would have produced greedily is accepted on the device and
         KV cache, DeltaNet state and sequence length end up as if only the accepted
-        tokens had been fed.  Returns [(accepted draft tokens, next pending token)]."""
+        tokens had been fed.  Returns [(accepted draft tokens, next pending token)].
+
+        `graph`: replay the step from a CUDA graph captured for this tree shape.
+        `tokens_dev`: int32 device tensor with the row tokens (pending token or -1,
+        then the drafts, per sequence) instead of the host lists in `drafts`, whose
+        values are then ignored.  `sync=False` skips the result download (read
+        `buf["spec_result"]` later)."""
         seqs = list(seqs) if seqs is not None else list(range(len(drafts)))
         self._ensure_driver()
         n_seqs = len(seqs)
@@ -649,16 +656,32 @@ class InferenceEngine:
                 sr[:len(seq_rows)] = torch.tensor(seq_rows, dtype=torch.int32)
                 self.buf["seq_rows"].copy_(sr.to(self.device))
                 self._ptmpl_key, self._tmpl_key = key, None
-            self.buf["p_row_tokens"][:R].copy_(torch.tensor(toks, dtype=torch.int32).to(self.device))
+            tok_buf = self.buf["p_row_tokens"]
         else:
             self._set_template(key, rows, seq_rows)
             self._ptmpl_key = None
-            rt = torch.full((self.max_rows,), -1, dtype=torch.int32)
-            rt[:R] = torch.tensor(toks, dtype=torch.int32)
-            self.buf["row_tokens"].copy_(rt.to(self.device))
-        self._run(R, n_seqs, flags)
+            tok_buf = self.buf["row_tokens"]
+        if tokens_dev is not None:
+            tok_buf[:R].copy_(tokens_dev[:R], non_blocking=True)
+        else:
+            tok_buf[:R].copy_(torch.tensor(toks, dtype=torch.int32).to(self.device))
+        if graph:
+            gkey = ("spec", key, flags)
+            if self._graph_key != gkey:
+                torch.cuda.synchronize()
+                with torch.cuda.stream(self._stream):
+                    L.check(self.lib.b2_driver_capture(C.c_void_p(self._driver), R, n_seqs, flags,
+                                                       C.c_void_p(self._stream.cuda_stream)), "graph capture")
+                torch.cuda.synchronize()
+                self._graph_key = gkey
+            L.check(self.lib.b2_driver_replay(C.c_void_p(self._driver), 1, L.stream()), "graph replay")
+            self._steps += 1
+        else:
+            self._run(R, n_seqs, flags)
         if not gemm_path:
             self.buf["row_tokens"].fill_(-1)
+        if not sync:
+            return None
         res = self.buf["spec_result"][:n_seqs].tolist()
         return [(r[2:2 + r[0]], r[1]) for r in res]
 
@@ -693,6 +716,33 @@ class InferenceEngine:
         self._run(n, 1, L.STEP_MATERIALIZE_XN | (0 if commit else L.STEP_NO_COMMIT_DELTA))
         if commit:
             self.states.seqs[seq, 0] += n
+        return self.buf["xn"][:n]
+
+    def forward_embeddings_tree(self, embs, parents: Sequence[int], seq: int = 0) -> torch.Tensor:
+        """Verify-only pass over a draft tree given as embeddings (<= 8 nodes; node 0
+        is the root with parent -1, parents precede children): returns the
+        final-normed hidden state of every node; KV slots beyond the committed
+        length are scratch and the DeltaNet state is untouched."""
+        self._ensure_driver()
+        e = self._as_dev(embs).reshape(-1, self.config.hidden_size)
+        n = e.shape[0]
+        if n > self.max_rows or len(parents) != n or parents[0] != -1:
+            raise ValueError(f"1..{self.max_rows} nodes, parents[0] == -1")
+        masks, depth = [], []
+        for t, pp in enumerate(parents):
+            if t and not 0 <= pp < t:
+                raise ValueError("parents must precede their children")
+            masks.append((masks[pp] if t else 0) | (1 << t))
+            depth.append(depth[pp] + 1 if t else 0)
+        self._set_template(("tree", seq, tuple(parents)), [(seq, depth[t], t, masks[t]) for t in range(n)], [0, n])
+        self.buf["emb_in"][:n].copy_(e)
+        L.check(self.lib.b2_load_rmsnorm(None, C.c_void_p(self.buf["emb_in"].data_ptr()),
+                                         C.c_void_p(self.layers[0].attn_norm.data_ptr()),
+                                         C.c_void_p(self.buf["h"].data_ptr()), None,
+                                         C.c_void_p(self.buf["ss"].data_ptr()), self.np, n,
+                                         self.config.hidden_size, C.c_float(self.config.rms_norm_eps),
+                                         L.stream()), "load_rmsnorm")
+        self._run(n, 1, L.STEP_MATERIALIZE_XN | L.STEP_SPEC)
         return self.buf["xn"][:n]
 
     def decode_step(self, token_embedding, position: Optional[int] = None, seq: int = 0):

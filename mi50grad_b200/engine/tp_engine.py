@@ -125,6 +125,79 @@ class TPInferenceEngine:
             return [o.cpu().numpy() for o in out]
         return [o.clone() for o in out]
 
+    # ------------------------------------------------------------------ speculation
+    def spec_step(self, drafts, parents, seqs=None, roots=None):
+        """One-pass verify-and-commit for several sequences (engine.InferenceEngine.spec_step)."""
+        return self.engine.spec_step(drafts, parents, seqs, roots)
+
+    def spec_step_tokens(self, root: int, drafts, parents, seq: int = 0):
+        return self.engine.spec_step_tokens(root, drafts, parents, seq)
+
+    def decode_step_tree(self, token_embeddings: List, tree_mask, kv_embeddings=None, seq: int = 0) -> List:
+        """Hidden states of every node of a draft tree from ONE forward pass, nothing
+        committed (reference: src/inference/tp_engine.py:3070-3341).  `tree_mask` is a
+        generate.tree_attention.TreeAttentionMask (its topology gives the parents) or a
+        list of parent indices.  Unlike the reference, nodes get RoPE position
+        length + depth, draft K/V go to scratch slots beyond the committed length, and
+        the DeltaNet layers follow the tree.  `kv_embeddings` is not needed: the
+        committed KV cache is used."""
+        topo = getattr(tree_mask, "tree", None) or getattr(tree_mask, "topology", None)
+        parents = list(topo.parents()) if topo is not None else [int(p) for p in tree_mask]
+        embs = torch.stack([torch.as_tensor(e).float() for e in token_embeddings])
+        out = self.engine.forward_embeddings_tree(embs, parents, seq)
+        if isinstance(token_embeddings[0], np.ndarray):
+            return [o.cpu().numpy() for o in out]
+        return [o.clone() for o in out]
+
+    def set_speculative_mode(self, enabled: bool, ngram_size: int = 3, max_draft_len: int = 5):
+        """(reference: src/inference/tp_engine.py:6597-6631)  Buffers for verification are
+        always allocated; this records the draft parameters used by generate.speculative."""
+        self._spec_mode = {"ngram_size": ngram_size, "max_draft_len": max_draft_len} if enabled else None
+        self.ecfg = self.ecfg.replace(spec_ngram=ngram_size, spec_max_draft=max_draft_len)
+
+    def decode_step_speculative(self, token_embeddings: List, position: int, draft_tokens: List[int], seq: int = 0):
+        """Hidden state after each of the given embeddings (pending token first, then
+        the drafts) from one pass, nothing committed; returns (hidden states, number of
+        drafts) like the reference (src/inference/tp_engine.py:6633-6678).  The caller
+        compares lm_head(hidden[i]) with draft i+1; `spec_step` does all of it on the
+        device and is what the generators use."""
+        if position != self.engine.states.length(seq):
+            self.engine.states.set_length(seq, position)
+        n = len(token_embeddings)
+        hs = self.decode_step_tree(token_embeddings, list(range(-1, n - 1)), seq=seq)
+        return hs, len(draft_tokens)
+
+    def set_eagle_mode(self, enabled: bool, k_draft: int = 5, temperature: float = 0.0):
+        """(reference: src/inference/tp_engine.py:6680-6708)"""
+        self._eagle = {"k_draft": k_draft, "temperature": temperature} if enabled else None
+
+    def generate_eagle_drafts(self, hidden_state, k: Optional[int] = None) -> List[int]:
+        """k draft tokens from a final-normed hidden state with the model's own head:
+        token = argmax(lm_head(h)), h <- normalised embedding of the token (reference:
+        src/inference/tp_engine.py:6710-6794, which zeroes the hidden state after the
+        first token).  Logits come from the device lm_head, all ranks get the same ids."""
+        k = k if k is not None else (getattr(self, "_eagle", None) or {}).get("k_draft", 5)
+        eng = self.engine
+        h = torch.as_tensor(hidden_state).float().flatten().to(eng.device)
+        out: List[int] = []
+        for _ in range(k):
+            logits = torch.as_tensor(self.compute_logits(h))
+            t = int(torch.argmax(logits))
+            out.append(t)
+            e = eng.embed[t].float()
+            h = e * torch.rsqrt(e.pow(2).mean() + self.config.rms_norm_eps)
+        return out
+
+    def decode_step_eagle(self, hidden_state, position: int, seq: int = 0):
+        """Draft with `generate_eagle_drafts`, verify and commit in one pass; returns
+        (accepted draft tokens, next pending token).  The pending token is the one the
+        last step stored for the sequence."""
+        if position != self.engine.states.length(seq):
+            self.engine.states.set_length(seq, position)
+        k = (getattr(self, "_eagle", None) or {}).get("k_draft", 5)
+        drafts = self.generate_eagle_drafts(hidden_state, k + 1)[1:]
+        return self.engine.spec_step([drafts], [list(range(-1, len(drafts) - 1))], [seq])[0]
+
     def compute_logits(self, hidden=None):
         """fp32 logits over the full vocabulary on every rank (the slices are
         all-gathered; the reference computes logits on GPU 0 only:

@@ -237,7 +237,7 @@ _tc_status = {}
 
 
 def gemm_int4_tc(pk, x: torch.Tensor, out: torch.Tensor, epi: int = L.TC_EPI_STORE_F16,
-                 t_tile: Optional[int] = None, n_valid: Optional[int] = None, dbg: int = 0):
+                 t_tile: Optional[int] = None, n_valid: Optional[int] = None):
     """out[t][n] (epi) = x[t, :K] @ W for a PackedInt4 matrix on the tcgen05 tensor cores.
     x: fp16 [T, K] (row stride multiple of 8).  SILU_PAIR: out[t][j] = silu(gate_j) * up_j for
     the gate/up-interleaved matrix; RESID_F32: out (fp32) += product."""
@@ -247,11 +247,11 @@ def gemm_int4_tc(pk, x: torch.Tensor, out: torch.Tensor, epi: int = L.TC_EPI_STO
         t_tile = min(512, -(-T // 16) * 16)
     st = _tc_status.get(dev)
     if st is None:
-        st = _tc_status[dev] = torch.zeros(4, dtype=torch.int32, device=dev)
+        st = _tc_status[dev] = torch.zeros(64, dtype=torch.int32, device=dev)
     p = L.GemmTcParams()
     p.qfrag, p.szfrag = pk.qfrag.data_ptr(), pk.szfrag.data_ptr()
     p.K, p.KB, p.NTL, p.G, p.off32, p.gshift = pk.K, pk.KB, pk.NTL, pk.G, pk.off32, pk.gshift
-    p.T, p.t_tile, p.epi, p.dbg = T, t_tile, epi, dbg
+    p.T, p.t_tile, p.epi = T, t_tile, epi
     if n_valid is None:
         n_valid = pk.n_pad // 2 if epi == L.TC_EPI_SILU_PAIR else pk.N
     p.n_valid, p.ldo, p.out, p.status = n_valid, out.stride(0), out.data_ptr(), st.data_ptr()
@@ -268,7 +268,7 @@ def gemm_f16_tc(w: torch.Tensor, x: torch.Tensor, out: torch.Tensor, epi: int = 
         t_tile = min(512, -(-T // 16) * 16)
     st = _tc_status.get(dev)
     if st is None:
-        st = _tc_status[dev] = torch.zeros(4, dtype=torch.int32, device=dev)
+        st = _tc_status[dev] = torch.zeros(64, dtype=torch.int32, device=dev)
     p = L.GemmTcParams()
     p.K, p.T, p.t_tile, p.epi = w.shape[1], T, t_tile, epi
     p.n_valid, p.ldo, p.out, p.status = w.shape[0], out.stride(0), out.data_ptr(), st.data_ptr()

@@ -108,3 +108,35 @@ def test_batched_decode_more_sequences_than_gemv_rows():
     # the same step replayed from a captured graph
     out_g = eng.decode_tokens(2, seqs=list(range(10)), graph=True).cpu()
     assert out_g.shape == (2, 10)
+
+
+def test_tp_engine_tree_hooks_match_oracle():
+    from helpers import cosine
+    from mi50grad_b200.config import tiny_config
+    from mi50grad_b200.engine.tp_engine import TPInferenceEngine
+    from mi50grad_b200.generate.tree_attention import TreeAttentionMask, TreeTopology
+    from mi50grad_b200.models.oracle import OracleEngine
+    from mi50grad_b200.models.weights import random_model
+    cfg = tiny_config()
+    mw = random_model(cfg, 4)
+    eng = TPInferenceEngine(cfg, max_seq_len=128)
+    eng.load_model(mw)
+    orc = OracleEngine(mw, max_seq_len=128)
+    ids = _prompt(cfg, 10, 31)
+    eng.prefill_tokens(ids)
+    orc.forward(orc.embed(ids))
+    toks, parents = [5, 6, 7, 8, 9, 10], [-1, 0, 0, 1, 1, 2]
+    topo = TreeTopology.from_parents(toks, parents)
+    embs = orc.embed(toks)
+    ref = orc.final_norm(orc.forward(embs, parents=parents))
+    S_before = eng.engine.states.dn.S.clone()
+    hs = eng.decode_step_tree([e.numpy() for e in embs], TreeAttentionMask(topo, kv_len=10))
+    assert torch.equal(S_before, eng.engine.states.dn.S) and eng.engine.states.length(0) == 10
+    for i in range(len(toks)):
+        assert cosine(torch.from_numpy(hs[i]).float(), ref[i]) > 0.999, i
+    hs2, n = eng.decode_step_speculative([e for e in embs[:3]], 10, [6, 7])
+    ref2 = orc.final_norm(orc.forward(embs[:3], parents=[-1, 0, 1]))
+    assert n == 2 and all(cosine(hs2[i].float().cpu(), ref2[i]) > 0.999 for i in range(3))
+    eng.set_eagle_mode(True, k_draft=3)
+    d = eng.generate_eagle_drafts(hs[0], 3)
+    assert len(d) == 3 and d[0] == int(torch.argmax(orc.compute_logits(ref[0])))
