@@ -102,8 +102,11 @@ def torch_baseline(args, cfg, world, rank, local):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # the decode step is graph-captured on one GPU; with NCCL all-reduces in the step the capture
+    # stalled on this software stack, so multi-GPU runs of the baseline are eager
+    use_graph = world == 1
     eng.prefill(prompt)
-    eng.decode(warm, graph=True)
+    eng.decode(warm, graph=use_graph)
     barrier_sync()
     sampler = ClockSampler(local)
     if rank == 0:
@@ -111,7 +114,7 @@ def torch_baseline(args, cfg, world, rank, local):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier_sync()
     ev0.record()
-    eng.decode(steps, graph=True)
+    eng.decode(steps, graph=use_graph)
     ev1.record()
     barrier_sync()
     t = torch.tensor([ev0.elapsed_time(ev1)], device="cuda")
@@ -143,7 +146,7 @@ def torch_baseline(args, cfg, world, rank, local):
             "config": {"model": "Qwen3.5-27B (random init, fp16 dense)" if args.model == "27b" else "tiny hybrid",
                        "global_batch": 1, "seq_len": args.prompt_len + steps, "parallelism": f"tp{world}",
                        "l2": "inputs larger than L2: every step streams %.1f GB of weights per GPU" % (eng.weight_bytes() / 1e9),
-                       "graph": "decode step captured with torch.cuda.graphs"},
+                       "graph": "decode step captured with torch.cuda.graphs" if use_graph else "eager launches"},
             "clocks": clocks, "gpu_launches": 0, "pp512": pp,
             "hbm_gbs_achieved": round(eng.weight_bytes() / (ms / steps / 1e3) / 1e9, 1)}))
     if world > 1:

@@ -79,6 +79,50 @@ def scenario_tp_engine(ar_mode: str, multimem: bool, model: str = "tiny"):
     eng.cleanup()
 
 
+def scenario_spec():
+    """Speculative verification and many-row steps at TP=world against the oracle: a draft tree
+    (GEMV path), three sequences with chains (tensor-core path), batched decode of 10 sequences."""
+    from mi50grad_b200.config import EngineConfig, tiny_config
+    from mi50grad_b200.engine.tp_engine import TPInferenceEngine
+    from mi50grad_b200.models.oracle import OracleEngine
+    from mi50grad_b200.models.weights import random_model
+    world = dist.get_world_size()
+    cfg = tiny_config()
+    mw = random_model(cfg, 5)
+    eng = TPInferenceEngine(cfg, list(range(world)), max_seq_len=128, max_batch=10, engine_config=EngineConfig())
+    eng.load_model(mw)
+    orc = OracleEngine(mw, max_seq_len=128, max_batch=10)
+    prm = lambda n, s: torch.randint(0, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(s)).tolist()
+    wrong = lambda t: (t + 3) % cfg.vocab_size
+    prompts = [prm(6 + i, 40 + i) for i in range(10)]
+    refs = [orc.greedy_generate(p, 9, seq=i)[0] for i, p in enumerate(prompts)]
+    for i, p in enumerate(prompts):
+        assert eng.prefill_tokens(p, seq=i) == refs[i][0], i
+    # tree on sequence 0 (5 drafts + pending token = 6 rows)
+    r = refs[0]
+    drafts, parents = [wrong(r[1]), r[1], r[2], wrong(r[2]), wrong(r[3])], [-1, -1, 1, 1, 2]
+    (acc, nxt), = eng.spec_step([drafts], [parents], [0])
+    assert acc == [r[1], r[2]] and nxt == r[3], (acc, nxt, r[:5])
+    # chains on sequences 1..3 (12 rows: tensor-core path)
+    dr, pa, exp = [], [], []
+    for i in (1, 2, 3):
+        r = refs[i]
+        n_ok = i - 1
+        d = [r[1 + k] if k < n_ok else wrong(r[1 + k]) for k in range(3)]
+        dr.append(d); pa.append([-1, 0, 1]); exp.append((d[:n_ok], r[1 + n_ok]))
+    res = eng.spec_step(dr, pa, [1, 2, 3])
+    assert [(a, n) for a, n in res] == exp, (res, exp)
+    # batched decode of the untouched sequences 4..9 plus the advanced ones: all ten
+    out = eng.decode_tokens(2, seqs=list(range(10)), graph=False).cpu()
+    adv = {0: 3, 1: 1, 2: 2, 3: 3}
+    for i in range(10):
+        a = adv.get(i, 0)
+        assert out[:, i].tolist() == refs[i][a + 1:a + 3], (i, out[:, i].tolist(), refs[i])
+    torch.cuda.synchronize()
+    eng.check_status()
+    eng.cleanup()
+
+
 def scenario_wait_timeout():
     """A flag that nobody raises: the bounded wait must return with a status and
     leave the context usable.  Plain peer loads, no multicast."""
@@ -120,6 +164,9 @@ def main():
         elif scenario == "tp_engine":
             scenario_tp_engine(sys.argv[2], sys.argv[3] == "multimem", sys.argv[4] if len(sys.argv) > 4 else "tiny")
             extra = sys.argv[2]
+        elif scenario == "spec":
+            scenario_spec()
+            extra = ""
         elif scenario == "wait_timeout":
             scenario_wait_timeout()
             extra = ""

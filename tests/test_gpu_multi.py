@@ -41,6 +41,10 @@ def test_tp_engine_tiny_peer_loads():
     _run(2, "tp_engine", "exact", "peer")
 
 
+def test_speculative_and_many_row_steps_under_tp():
+    _run(2, "spec")
+
+
 def test_bounded_wait_times_out_cleanly():
     _run(2, "wait_timeout", env_extra={"NCCL_NVLS_ENABLE": "0"})
 
