@@ -1,0 +1,167 @@
+"""Small, self-contained workloads for profiler captures and kernel timing.
+
+    python -m mi50grad_b200.bench.profile_cases <case> [--time]
+
+Each case launches one kernel family a few times on inputs larger than L2 but
+only a few hundred MB in total, brackets the launches of interest with
+cudaProfilerStart/Stop (use `ncu --profile-from-start off`), and with --time
+prints CUDA-event timings taken from a graph replay instead.
+
+cases: gemv_gateup, gemv_down, gemm_int4, gemm_dense, attn_decode, attn_rows,
+       deltanet_step, deltanet_chunk, spec_step
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from ..ops import kernels as K
+from ..ops import lib as L
+from ..ops.packing import random_packed_int4
+from .microbench import time_launches
+
+
+def _profiled(fn, reps: int = 2):
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStart()
+    for _ in range(reps):
+        fn()
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStop()
+
+
+def _report(name, us, bytes_=0.0, flops=0.0):
+    msg = f"{name}: {us:.1f} us"
+    if bytes_:
+        msg += f"  {bytes_ / us / 1e3:.0f} GB/s"
+    if flops:
+        msg += f"  {flops / us / 1e6:.0f} TFLOP/s"
+    print(msg, flush=True)
+
+
+def case_gemv(which: str, timed: bool):
+    dev = torch.device("cuda")
+    Kd, N, mode = (5120, 34816, L.EPI_SILU_PAIR) if which == "gemv_gateup" else (17408, 5120, L.EPI_STORE_F32)
+    pks = [random_packed_int4(Kd, N, 128, dev) for _ in range(3)]          # rotate: 3 x 89 MB > L2
+    x = torch.randn(1, Kd, device=dev).half()
+    out = torch.zeros(1, N, dtype=torch.float16 if mode == L.EPI_SILU_PAIR else torch.float32, device=dev)
+    scratch = torch.zeros(8 * 1024 * 1024, dtype=torch.float32, device=dev)
+    counters = torch.zeros(8192, dtype=torch.int32, device=dev)
+    from ..engine.engine import DeviceLinear
+    lins = [DeviceLinear(packed=p) for p in pks]
+    run = lambda i=0: K.gemv(lins[i % 3], x, out=out, mode=mode, scratch=scratch, counters=counters)
+    if timed:
+        _report(which, time_launches(run, 3, 12), bytes_=pks[0].nbytes())
+    else:
+        state = {"i": 0}
+        def step():
+            run(state["i"]); state["i"] += 1
+        _profiled(step, 3)
+
+
+def case_gemm(which: str, timed: bool):
+    dev = torch.device("cuda")
+    if which == "gemm_int4":
+        shapes = [(17408, 5120, 512, 176), (5120, 34816, 512, 512), (5120, 34816, 80, 80)]
+        for Kd, N, T, tt in shapes:
+            pk = random_packed_int4(Kd, N, 128, dev)
+            x = torch.randn(T, Kd, device=dev).half()
+            out = torch.zeros(T, pk.n_pad, dtype=torch.float32, device=dev)
+            run = lambda i=0: K.gemm_int4_tc(pk, x, out, epi=L.TC_EPI_STORE_F32, t_tile=tt)
+            if timed:
+                _report(f"gemm_int4 K={Kd} N={N} T={T} t_tile={tt}", time_launches(run, 1, 6),
+                        bytes_=pk.nbytes(), flops=2.0 * T * Kd * N)
+            else:
+                _profiled(run, 1)
+    else:
+        w = (torch.randn(34816, 5120, device=dev) * 0.02).half()
+        for T, tt in ((512, 512), (80, 80)):
+            x = torch.randn(T, 5120, device=dev).half()
+            out = torch.zeros(T, 34816, dtype=torch.float32, device=dev)
+            run = lambda i=0: K.gemm_f16_tc(w, x, out, t_tile=tt)
+            if timed:
+                _report(f"gemm_dense K=5120 N=34816 T={T}", time_launches(run, 1, 6), bytes_=w.numel() * 2,
+                        flops=2.0 * T * 5120 * 34816)
+            else:
+                _profiled(run, 1)
+    K.gemm_tc_check_status()
+
+
+def case_attn(which: str, timed: bool):
+    """attn_decode: 1 row, ctx 4096.  attn_rows: 80 rows (16 sequences x 5 draft rows), ctx 4096."""
+    dev = torch.device("cuda")
+    nq, nkv, hd, ctx = 24, 4, 256, 4096
+    n_seq, per = (1, 1) if which == "attn_decode" else (16, 5)
+    kc = torch.randn(n_seq, ctx + 64, nkv, hd, device=dev).half()
+    vc = torch.randn(n_seq, ctx + 64, nkv, hd, device=dev).half()
+    rows = [(s, ctx + i, ctx + i, ctx, (1 << (i + 1)) - 1) for s in range(n_seq) for i in range(per)]
+    rm = K.make_rows(rows, dev)
+    q = torch.randn(len(rows), 2 * nq * hd, device=dev).half()
+    run = lambda i=0: K.decode_attn(q, rm, kc, vc, nq, nkv, hd, gate_off=nq * hd, splits=16)
+    if timed:
+        _report(which, time_launches(run, 1, 6), bytes_=2.0 * n_seq * ctx * nkv * hd * 2)
+    else:
+        _profiled(run, 1)
+
+
+def case_spec_step(timed: bool):
+    """One 80-row verify-and-commit step of the 27B model (16 sequences x ctx 4096 x 4 drafts) on
+    synthetic state; prints the step time.  Holds the whole model (about 22 GB): for launch lists
+    (one pass per kernel) only, not for multi-pass captures."""
+    from ..config import EngineConfig, qwen35_27b
+    from ..engine.engine import InferenceEngine
+    B, ctx, D = 16, 4096, 4
+    eng = InferenceEngine(qwen35_27b(), max_seq_len=ctx + 64, max_batch=B,
+                          engine_config=EngineConfig(max_step_rows=B * (D + 1)))
+    eng.init_random(0)
+    eng._ensure_driver()
+    eng.states.kv.k.normal_(0, 0.5)
+    eng.states.kv.v.normal_(0, 0.5)
+    eng.states.dn.S.normal_(0, 0.05)
+    drafts = [[1, 2, 3, 4] for _ in range(B)]
+    parents = [list(range(-1, D - 1)) for _ in range(B)]
+
+    def step():
+        eng.states.seqs[:, 0] = ctx
+        eng.states.seqs[:, 1] = 5
+        eng.spec_step(drafts, parents, list(range(B)), sync=False)
+    step(); step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.cudart().cudaProfilerStart()
+    e0.record(); step(); e1.record()
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStop()
+    print(f"spec_step 80 rows: {e0.elapsed_time(e1):.2f} ms", flush=True)
+
+
+def case_deltanet(which: str, timed: bool):
+    from .microbench_deltanet import run_case
+    run_case(which, timed, _profiled, _report)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case")
+    ap.add_argument("--time", action="store_true")
+    a = ap.parse_args()
+    if a.case.startswith("gemv"):
+        case_gemv(a.case, a.time)
+    elif a.case.startswith("gemm"):
+        case_gemm(a.case, a.time)
+    elif a.case.startswith("attn"):
+        case_attn(a.case, a.time)
+    elif a.case == "spec_step":
+        case_spec_step(a.time)
+    elif a.case.startswith("deltanet"):
+        case_deltanet(a.case, a.time)
+    else:
+        raise SystemExit(f"unknown case {a.case}")
+    print("ok")
+
+
+if __name__ == "__main__":
+    main()

@@ -237,19 +237,49 @@ B2_API int b2_delta_conv_channels(int dk) { return 2 * dk + DN_COLS; }
 // chunk live in shared memory in fp32; the state slice stays in registers across chunks.
 // ===========================================================================
 #define DC_C 64                  // rows per chunk
-#define DC_LDK(DK) ((DK) + 4)    // padded row stride of the q/k tiles
+#define DC_LDK(DK) ((DK) + 4)    // padded row stride of the q/k tiles (conflict-free fragment loads)
 #define DC_LDA (DC_C + 4)
+#define DC_LDU (DN_COLS + 8)     // row stride of U and of the state copy (they are B operands)
+
+// The matrix products of a chunk run on the tensor cores as TF32 (fp32 storage, 10-bit
+// mantissa: the precision of the fp16 activations the inputs come from), accumulating in fp32.
+__device__ __forceinline__ float tf32r(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], float a0, float a1, float a2, float a3, float b0, float b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(__float_as_uint(a0)), "r"(__float_as_uint(a1)), "r"(__float_as_uint(a2)), "r"(__float_as_uint(a3)),
+                   "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)));
+}
+
+// Four 8x4 fp32 tiles in one instruction: lane l supplies the address of row (l & 7) of tile l >> 3
+// (16 bytes = 4 floats per row); afterwards every lane holds element (lane >> 2, lane & 3) of each
+// tile, which is exactly the TF32 fragment layout of mma.m16n8k8.
+__device__ __forceinline__ void ldsm4(float (&r)[4], const float* row_ptr) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(row_ptr);
+    uint32_t x0, x1, x2, x3;
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(a));
+    r[0] = __uint_as_float(x0); r[1] = __uint_as_float(x1); r[2] = __uint_as_float(x2); r[3] = __uint_as_float(x3);
+}
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.f + __expf(-x)); }
 
 template <int DK, int DV>
 __global__ void __launch_bounds__(DN_THREADS, 1) deltanet_chunk_kernel(const DeltaParams p, const __half* __restrict__ ab, int ld_ab) {
     constexpr int CB = DV / DN_COLS;
-    constexpr int RPT = DK / 8;
+    constexpr int MT = DK / 16;               // 16-row tiles of the state slice, one or two per warp
+    constexpr int SPW = (MT + 7) / 8;         // state m-tiles per warp
     constexpr int NCH = 2 * DK + DN_COLS;
     constexpr int LDK = DC_LDK(DK);
+    static_assert(DK % 16 == 0 && MT <= 16, "state tiling");
     cg::cluster_group cluster = cg::this_cluster();
     pdl_launch_dependents();
     const int cb = blockIdx.x, j = blockIdx.y, si = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, kr = tid >> 5, vcol = lane;
+    const int g = lane >> 2, t = lane & 3;    // fragment coordinates
     const int kh = j / (p.nv / p.nk);
     const int r0 = p.seq_rows[si], r1 = p.seq_rows[si + 1];
     if (r0 >= r1) return;
@@ -258,13 +288,13 @@ __global__ void __launch_bounds__(DN_THREADS, 1) deltanet_chunk_kernel(const Del
     extern __shared__ __align__(16) float dsm[];
     float* Qs = dsm;                          // [C][LDK]
     float* Ks = Qs + DC_C * LDK;              // [C][LDK]
-    float* Us = Ks + DC_C * LDK;              // [C][32]  v -> b -> u (in place)
-    float* QSs = Us + DC_C * DN_COLS;         // [C][32]  exp(G) Q S0
+    float* Us = Ks + DC_C * LDK;              // [C][LDU]  v -> b -> u (in place)
+    float* QSs = Us + DC_C * DC_LDU;          // [C][32]   exp(G) Q S0
     float* Ys = QSs + DC_C * DN_COLS;         // [C][32]
     float* As = Ys + DC_C * DN_COLS;          // [C][LDA]
     float* Ws = As + DC_C * DC_LDA;           // [C][LDA]
-    float* S0s = Ws + DC_C * DC_LDA;          // [DK][32]
-    float* hist = S0s + DK * DN_COLS;         // [NCH][3]
+    float* S0t = Ws + DC_C * DC_LDA;          // [32][LDK]  transposed copy of the state slice (a B operand)
+    float* hist = S0t + DN_COLS * LDK;        // [NCH][3]
     float* cw = hist + NCH * 3;               // [NCH][4]
     float* Gs = cw + NCH * 4;                 // [C] running log-decay
     float* bs = Gs + DC_C;                    // [C] beta
@@ -285,15 +315,29 @@ __global__ void __launch_bounds__(DN_THREADS, 1) deltanet_chunk_kernel(const Del
     __half* my_hist = p.conv_state + ((((size_t)seq * p.nv + j) * CB + cb) * NCH) * 3;
     for (int c = tid; c < NCH; c += DN_THREADS) {
 #pragma unroll
-        for (int t = 0; t < 3; ++t) hist[c * 3 + t] = __half2float(my_hist[c * 3 + t]);
+        for (int q = 0; q < 3; ++q) hist[c * 3 + q] = __half2float(my_hist[c * 3 + q]);
         const __half* w = p.conv_w + (size_t)chan(c) * 4;
 #pragma unroll
-        for (int t = 0; t < 4; ++t) cw[c * 4 + t] = __half2float(w[t]);
+        for (int q = 0; q < 4; ++q) cw[c * 4 + q] = __half2float(w[q]);
     }
-    float S[RPT];
-    float* sp = p.state + (((size_t)seq * p.nv + j) * DK) * DV + cb * DN_COLS + vcol;
+    // The state slice [DK x 32] lives in registers as accumulator fragments: warp w owns the
+    // 16-row tiles w (and w + 8), each as four 16x8 tiles: S[m][n][0..3] = rows g / g+8, cols 2t / 2t+1.
+    float S[SPW][4][4];
+    float* sp = p.state + (((size_t)seq * p.nv + j) * DK) * DV + cb * DN_COLS;
 #pragma unroll
-    for (int i = 0; i < RPT; ++i) S[i] = sp[(size_t)(kr + 8 * i) * DV];
+    for (int m = 0; m < SPW; ++m) {
+        const int mt = kr + 8 * m;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            if (mt < MT) {
+                const float2 lo = *(const float2*)(sp + (size_t)(16 * mt + g) * DV + 8 * n + 2 * t);
+                const float2 hi = *(const float2*)(sp + (size_t)(16 * mt + g + 8) * DV + 8 * n + 2 * t);
+                S[m][n][0] = lo.x; S[m][n][1] = lo.y; S[m][n][2] = hi.x; S[m][n][3] = hi.y;
+            } else {
+                S[m][n][0] = S[m][n][1] = S[m][n][2] = S[m][n][3] = 0.f;
+            }
+        }
+    }
     const float neg_expA = -__expf(p.A_log[j]);
     const float dtb = __half2float(p.dt_bias[j]);
     const float nw = __half2float(p.norm_w[cb * DN_COLS + vcol]);
@@ -321,10 +365,21 @@ __global__ void __launch_bounds__(DN_THREADS, 1) deltanet_chunk_kernel(const Del
         cp_async_commit();
     };
     stage_raw(r0);
+    // the gate inputs of a chunk are fetched one chunk ahead (a global round trip off the critical path)
+    float a_pre = 0.f, b_pre = 0.f;
+    auto fetch_gates = [&](int rb_) {
+        a_pre = b_pre = 0.f;
+        if (tid < DC_C && rb_ + tid < r1) {
+            const __half* abr = ab + (size_t)(rb_ + tid) * ld_ab;
+            a_pre = __half2float(abr[j]); b_pre = __half2float(abr[p.nv + j]);
+        }
+    };
+    fetch_gates(r0);
 
     int chunk_idx = 0;
     for (int rb = r0; rb < r1; rb += DC_C, ++chunk_idx) {
         const int Ce = min(DC_C, r1 - rb);
+        const int slot = chunk_idx & 1;
         // ---- P1: causal conv + SiLU from the raw tile staged in shared memory by cp.async (the
         // copy for this chunk was issued while the previous chunk was being processed)
         cp_async_wait<0>();
@@ -335,163 +390,270 @@ __global__ void __launch_bounds__(DN_THREADS, 1) deltanet_chunk_kernel(const Del
             float x0 = __half2float(Xr[(i0 + 0) * NCH + c]), x1 = __half2float(Xr[(i0 + 1) * NCH + c]);
             float x2 = __half2float(Xr[(i0 + 2) * NCH + c]);
             float* dst = (c < DK) ? Qs + c : (c < 2 * DK) ? Ks + (c - DK) : Us + (c - 2 * DK);
-            const int ldd = (c < 2 * DK) ? LDK : DN_COLS;
+            const int ldd = (c < 2 * DK) ? LDK : DC_LDU;
 #pragma unroll
             for (int i = i0; i < i0 + 8; ++i) {
                 const float x3 = __half2float(Xr[(i + 3) * NCH + c]);
                 const float acc = x0 * w0 + x1 * w1 + x2 * w2 + x3 * w3;
-                dst[i * ldd] = (i < Ce) ? silu_f(acc) : 0.f;
+                dst[i * ldd] = (i < Ce) ? silu_fast(acc) : 0.f;
                 x0 = x1; x1 = x2; x2 = x3;
             }
         }
         if (tid < DC_C) {
             float gl = 0.f, beta = 0.f;
             if (tid < Ce) {
-                const __half* abr = ab + (size_t)(rb + tid) * ld_ab;
-                float a_in = __half2float(abr[j]), b_in = __half2float(abr[p.nv + j]);
+                const float a_in = a_pre, b_in = b_pre;
                 float sp_ = a_in + dtb;
                 gl = fmaxf(neg_expA * (sp_ > 20.f ? sp_ : log1pf(__expf(sp_))), -20.f);
                 beta = sigmoid_f(b_in);
             }
             gs[tid] = gl;
             bs[tid] = beta;
+            cl_ss[slot * DC_C + tid] = 0.f;
         }
         __syncthreads();
         if (rb + DC_C < r1) stage_raw(rb + DC_C);          // flies while this chunk is processed
-        // ---- P2: L2-normalise q and k rows, running log-decay
-        for (int i = kr; i < DC_C; i += 8) {
-            float qq = 0.f, kk = 0.f;
-            for (int k = lane; k < DK; k += 32) { float a = Qs[i * LDK + k], b = Ks[i * LDK + k]; qq += a * a; kk += b * b; }
-            qq = warp_sum(qq); kk = warp_sum(kk);
-            const float iq = rsqrtf(qq + 1e-6f) * qscale, ik = rsqrtf(kk + 1e-6f);
-            for (int k = lane; k < DK; k += 32) { Qs[i * LDK + k] *= iq; Ks[i * LDK + k] *= ik; }
-        }
-        if (tid == 0) {
-            float run = 0.f;
-            for (int i = 0; i < DC_C; ++i) { run += gs[i]; Gs[i] = run; }
-        }
-        // state slice to shared memory for the S0 products
+        fetch_gates(rb + DC_C);
+        // output gates of this chunk, needed only at its end
+        float zf[8];
 #pragma unroll
-        for (int i = 0; i < RPT; ++i) S0s[(kr + 8 * i) * DN_COLS + vcol] = S[i];
+        for (int u = 0; u < 8; ++u) {
+            const int i = kr + 8 * u;
+            zf[u] = (i < Ce) ? __half2float(p.proj[(size_t)(rb + i) * p.ld + p.off_z + j * DV + cb * DN_COLS + vcol]) : 0.f;
+        }
+        // ---- P2: L2-normalise q and k rows (stored rounded to TF32), running log-decay, state copy
+        if (kr == 0) {
+            // inclusive scan of the 64 log-decays: two per lane
+            float a = gs[lane], b = gs[lane + 32];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float ua = __shfl_up_sync(0xffffffffu, a, o), ub = __shfl_up_sync(0xffffffffu, b, o);
+                if (lane >= o) { a += ua; b += ub; }
+            }
+            const float tot = __shfl_sync(0xffffffffu, a, 31);
+            Gs[lane] = a; Gs[lane + 32] = b + tot;
+        }
+#pragma unroll 1
+        for (int ub = 0; ub < 8; ub += 4) {
+            // four rows at a time: their loads and the eight reductions overlap
+            constexpr int PL = DK / 32;
+            float qv[4][PL], kv[4][PL], qq[4], kk[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int i = kr + 8 * (ub + r);
+                qq[r] = kk[r] = 0.f;
+#pragma unroll
+                for (int m = 0; m < PL; ++m) {
+                    qv[r][m] = Qs[i * LDK + lane + 32 * m]; kv[r][m] = Ks[i * LDK + lane + 32 * m];
+                    qq[r] += qv[r][m] * qv[r][m]; kk[r] += kv[r][m] * kv[r][m];
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    qq[r] += __shfl_xor_sync(0xffffffffu, qq[r], o);
+                    kk[r] += __shfl_xor_sync(0xffffffffu, kk[r], o);
+                }
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int i = kr + 8 * (ub + r);
+                const float iq = rsqrtf(qq[r] + 1e-6f) * qscale, ik = rsqrtf(kk[r] + 1e-6f);
+#pragma unroll
+                for (int m = 0; m < PL; ++m) {
+                    Qs[i * LDK + lane + 32 * m] = tf32r(qv[r][m] * iq);
+                    Ks[i * LDK + lane + 32 * m] = tf32r(kv[r][m] * ik);
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < SPW; ++m) {
+            const int mt = kr + 8 * m;
+            if (mt < MT) {
+#pragma unroll
+                for (int n = 0; n < 4; ++n)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        S0t[(8 * n + 2 * t + (e & 1)) * LDK + 16 * mt + g + (e >> 1) * 8] = tf32r(S[m][n][e]);
+            }
+        }
         __syncthreads();
-        // ---- P3: A and W (lower triangle), 4x4 register tiles
+        // ---- P3: A = beta decay (K K^T) below the diagonal, W = decay (Q K^T) on and below it, in
+        // 16x16 blocks of the lower triangle dealt round-robin to the warps.  Fragments come from
+        // ldmatrix: one instruction per operand and k-step.
         {
-            const int ti = tid >> 4, tj = tid & 15;
-            if (tj <= ti) {
-                float kk[4][4], qk[4][4];
+            const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 4;       // A operand addressing
+            const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 4;       // B operand, two 8-column tiles
+            for (int blk = kr; blk < 10; blk += 8) {
+                const int mi = blk >= 6 ? 3 : (blk >= 3 ? 2 : (blk >= 1 ? 1 : 0));
+                const int nj = blk - mi * (mi + 1) / 2;
+                float kk[2][4], qk[2][4];
 #pragma unroll
-                for (int a = 0; a < 4; ++a)
+                for (int n = 0; n < 2; ++n)
 #pragma unroll
-                    for (int b = 0; b < 4; ++b) kk[a][b] = qk[a][b] = 0.f;
-                for (int k = 0; k < DK; k += 4) {
-                    float4 kr4[4], qr4[4], kc4[4];
-#pragma unroll
-                    for (int a = 0; a < 4; ++a) {
-                        kr4[a] = *(const float4*)&Ks[(4 * ti + a) * LDK + k];
-                        qr4[a] = *(const float4*)&Qs[(4 * ti + a) * LDK + k];
-                        kc4[a] = *(const float4*)&Ks[(4 * tj + a) * LDK + k];
-                    }
-#pragma unroll
-                    for (int a = 0; a < 4; ++a)
-#pragma unroll
-                        for (int b = 0; b < 4; ++b) {
-                            kk[a][b] += kr4[a].x * kc4[b].x + kr4[a].y * kc4[b].y + kr4[a].z * kc4[b].z + kr4[a].w * kc4[b].w;
-                            qk[a][b] += qr4[a].x * kc4[b].x + qr4[a].y * kc4[b].y + qr4[a].z * kc4[b].z + qr4[a].w * kc4[b].w;
-                        }
+                    for (int e = 0; e < 4; ++e) kk[n][e] = qk[n][e] = 0.f;
+                const float* ka = Ks + (16 * mi + a_row) * LDK + a_col;
+                const float* qa = Qs + (16 * mi + a_row) * LDK + a_col;
+                const float* kb = Ks + (16 * nj + b_row) * LDK + b_col;
+#pragma unroll 4
+                for (int k0 = 0; k0 < DK; k0 += 8) {
+                    float fa[4], fq[4], fb[4];
+                    ldsm4(fa, ka + k0); ldsm4(fq, qa + k0); ldsm4(fb, kb + k0);
+                    mma_tf32(kk[0], fa[0], fa[1], fa[2], fa[3], fb[0], fb[1]);
+                    mma_tf32(kk[1], fa[0], fa[1], fa[2], fa[3], fb[2], fb[3]);
+                    mma_tf32(qk[0], fq[0], fq[1], fq[2], fq[3], fb[0], fb[1]);
+                    mma_tf32(qk[1], fq[0], fq[1], fq[2], fq[3], fb[2], fb[3]);
                 }
 #pragma unroll
-                for (int a = 0; a < 4; ++a)
+                for (int n = 0; n < 2; ++n)
 #pragma unroll
-                    for (int b = 0; b < 4; ++b) {
-                        const int i = 4 * ti + a, jj = 4 * tj + b;
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = 16 * mi + g + (e >> 1) * 8, jj = 16 * nj + 8 * n + 2 * t + (e & 1);
                         const float dec = (jj <= i) ? __expf(Gs[i] - Gs[jj]) : 0.f;
-                        As[i * DC_LDA + jj] = (jj < i) ? bs[i] * dec * kk[a][b] : 0.f;
-                        Ws[i * DC_LDA + jj] = dec * qk[a][b];
+                        As[i * DC_LDA + jj] = (jj < i) ? bs[i] * dec * kk[n][e] : 0.f;
+                        Ws[i * DC_LDA + jj] = tf32r(dec * qk[n][e]);
                     }
             }
-        }
-        // ---- P4: K S0 and Q S0; b = beta (v - exp(G) K S0) in place of v
-        {
-            float ak[8], aq[8];
+            // ---- P4: K S0 and Q S0; b = beta (v - exp(G) K S0) in place of v.  Warp w: row tile w & 3,
+            // column tiles 2 (w >> 2) and 2 (w >> 2) + 1.
+            const int mi = kr & 3, nb = (kr >> 2) * 2;
+            float ak[2][4], aq[2][4];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) ak[u] = aq[u] = 0.f;
-            for (int k = 0; k < DK; k += 4) {
-                const float s0 = S0s[(k + 0) * DN_COLS + vcol], s1 = S0s[(k + 1) * DN_COLS + vcol];
-                const float s2 = S0s[(k + 2) * DN_COLS + vcol], s3 = S0s[(k + 3) * DN_COLS + vcol];
+            for (int n = 0; n < 2; ++n)
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int i = kr + 8 * u;
-                    const float4 k4 = *(const float4*)&Ks[i * LDK + k], q4 = *(const float4*)&Qs[i * LDK + k];
-                    ak[u] += k4.x * s0 + k4.y * s1 + k4.z * s2 + k4.w * s3;
-                    aq[u] += q4.x * s0 + q4.y * s1 + q4.z * s2 + q4.w * s3;
+                for (int e = 0; e < 4; ++e) ak[n][e] = aq[n][e] = 0.f;
+            const float* ka = Ks + (16 * mi + a_row) * LDK + a_col;
+            const float* qa = Qs + (16 * mi + a_row) * LDK + a_col;
+            const float* sb = S0t + (8 * nb + b_row) * LDK + b_col;
+#pragma unroll 4
+            for (int k0 = 0; k0 < DK; k0 += 8) {
+                float fa[4], fq[4], fb[4];
+                ldsm4(fa, ka + k0); ldsm4(fq, qa + k0); ldsm4(fb, sb + k0);
+                mma_tf32(ak[0], fa[0], fa[1], fa[2], fa[3], fb[0], fb[1]);
+                mma_tf32(ak[1], fa[0], fa[1], fa[2], fa[3], fb[2], fb[3]);
+                mma_tf32(aq[0], fq[0], fq[1], fq[2], fq[3], fb[0], fb[1]);
+                mma_tf32(aq[1], fq[0], fq[1], fq[2], fq[3], fb[2], fb[3]);
+            }
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = 16 * mi + g + (e >> 1) * 8, col = 8 * (nb + n) + 2 * t + (e & 1);
+                    const float eg = __expf(Gs[i]);
+                    Us[i * DC_LDU + col] = bs[i] * (Us[i * DC_LDU + col] - eg * ak[n][e]);
+                    QSs[i * DN_COLS + col] = eg * aq[n][e];
                 }
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int i = kr + 8 * u;
-                const float eg = __expf(Gs[i]);
-                Us[i * DN_COLS + vcol] = bs[i] * (Us[i * DN_COLS + vcol] - eg * ak[u]);
-                QSs[i * DN_COLS + vcol] = eg * aq[u];
-            }
         }
         __syncthreads();
         // ---- P5: (I + A) U = B by forward substitution, 8 rows per block: every warp first removes
-        // the contribution of all earlier blocks from its row, then warp 0 finishes the 8x8 triangle
+        // the contribution of all earlier blocks from its row, then warp 0 solves the 8x8 triangle
+        // with one column per lane in registers
         for (int blk = 0; blk < DC_C / 8; ++blk) {
             const int i = 8 * blk + kr;
-            float acc = Us[i * DN_COLS + vcol];
-            for (int jj = 0; jj < 8 * blk; ++jj) acc = fmaf(-As[i * DC_LDA + jj], Us[jj * DN_COLS + vcol], acc);
-            Us[i * DN_COLS + vcol] = acc;
+            float acc = Us[i * DC_LDU + vcol];
+            for (int j0 = 0; j0 < 8 * blk; j0 += 8) {
+                float av[8], uv[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) { av[q] = As[i * DC_LDA + j0 + q]; uv[q] = Us[(j0 + q) * DC_LDU + vcol]; }
+#pragma unroll
+                for (int q = 0; q < 8; ++q) acc = fmaf(-av[q], uv[q], acc);
+            }
+            Us[i * DC_LDU + vcol] = acc;
             __syncthreads();
             if (kr == 0) {
+                float u[8];
 #pragma unroll
-                for (int a = 1; a < 8; ++a) {
-                    const int ia = 8 * blk + a;
-                    float t = Us[ia * DN_COLS + vcol];
+                for (int a = 0; a < 8; ++a) u[a] = Us[(8 * blk + a) * DC_LDU + vcol];
+#pragma unroll
+                for (int a = 1; a < 8; ++a)
 #pragma unroll
                     for (int b = 0; b < 8; ++b)
-                        if (b < a) t = fmaf(-As[ia * DC_LDA + 8 * blk + b], Us[(8 * blk + b) * DN_COLS + vcol], t);
-                    Us[ia * DN_COLS + vcol] = t;
-                }
+                        if (b < a) u[a] = fmaf(-As[(8 * blk + a) * DC_LDA + 8 * blk + b], u[b], u[a]);
+#pragma unroll
+                for (int a = 1; a < 8; ++a) Us[(8 * blk + a) * DC_LDU + vcol] = u[a];
             }
             __syncthreads();
         }
-        // ---- P6: Y = exp(G) Q S0 + W U, partial sum of squares per row
-        const int slot = chunk_idx & 1;
-#pragma unroll 1
-        for (int u = 0; u < 8; ++u) {
-            const int i = kr + 8 * u;
-            float y = QSs[i * DN_COLS + vcol];
-            for (int jj = 0; jj <= i; ++jj) y = fmaf(Ws[i * DC_LDA + jj], Us[jj * DN_COLS + vcol], y);
-            Ys[i * DN_COLS + vcol] = y;
-            float ss = warp_sum(y * y);
-            if (lane == 0) cl_ss[slot * DC_C + i] = ss;
+        // ---- P6: Y = exp(G) Q S0 + W U (W is zero above the diagonal), sum of squares per row
+        {
+            const int mi = kr & 3, nb = (kr >> 2) * 2;
+            float y[2][4];
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    y[n][e] = QSs[(16 * mi + g + (e >> 1) * 8) * DN_COLS + 8 * (nb + n) + 2 * t + (e & 1)];
+            const float* wa = Ws + (16 * mi + g) * DC_LDA + t;
+            for (int k0 = 0; k0 < 16 * (mi + 1); k0 += 8) {
+                const float a0 = wa[k0], a1 = wa[8 * DC_LDA + k0], a2 = wa[k0 + 4], a3 = wa[8 * DC_LDA + k0 + 4];
+#pragma unroll
+                for (int n = 0; n < 2; ++n)
+                    mma_tf32(y[n], a0, a1, a2, a3, tf32r(Us[(k0 + t) * DC_LDU + 8 * (nb + n) + g]),
+                             tf32r(Us[(k0 + t + 4) * DC_LDU + 8 * (nb + n) + g]));
+            }
+            float s_lo = 0.f, s_hi = 0.f;
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    Ys[(16 * mi + g + (e >> 1) * 8) * DN_COLS + 8 * (nb + n) + 2 * t + (e & 1)] = y[n][e];
+                    if (e < 2) s_lo += y[n][e] * y[n][e]; else s_hi += y[n][e] * y[n][e];
+                }
+            s_lo += __shfl_xor_sync(0xffffffffu, s_lo, 1); s_lo += __shfl_xor_sync(0xffffffffu, s_lo, 2);
+            s_hi += __shfl_xor_sync(0xffffffffu, s_hi, 1); s_hi += __shfl_xor_sync(0xffffffffu, s_hi, 2);
+            if (t == 0) {
+                atomicAdd(&cl_ss[slot * DC_C + 16 * mi + g], s_lo);
+                atomicAdd(&cl_ss[slot * DC_C + 16 * mi + g + 8], s_hi);
+            }
         }
-        // ---- P7: S' = exp(G_C) S0 + (exp(G_C - G) K)^T U   (state slice in registers)
+        // ---- P7: S' = exp(G_C) S0 + K^T (exp(G_C - G) U), accumulated into the register fragments
         {
             const float gC = Gs[DC_C - 1];
             const float egC = __expf(gC);
 #pragma unroll
-            for (int i2 = 0; i2 < RPT; ++i2) S[i2] *= egC;
-            for (int i = 0; i < Ce; ++i) {
-                const float u = Us[i * DN_COLS + vcol] * __expf(gC - Gs[i]);
+            for (int m = 0; m < SPW; ++m)
 #pragma unroll
-                for (int i2 = 0; i2 < RPT; ++i2) S[i2] = fmaf(Ks[i * LDK + kr + 8 * i2], u, S[i2]);
+                for (int n = 0; n < 4; ++n)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) S[m][n][e] *= egC;
+            for (int k0 = 0; k0 < DC_C; k0 += 8) {
+                const float tl0 = __expf(gC - Gs[k0 + t]), tl1 = __expf(gC - Gs[k0 + t + 4]);
+                float b0[4], b1[4];
+#pragma unroll
+                for (int n = 0; n < 4; ++n) {
+                    b0[n] = tf32r(Us[(k0 + t) * DC_LDU + 8 * n + g] * tl0);
+                    b1[n] = tf32r(Us[(k0 + t + 4) * DC_LDU + 8 * n + g] * tl1);
+                }
+#pragma unroll
+                for (int m = 0; m < SPW; ++m) {
+                    const int mt = kr + 8 * m;
+                    if (mt < MT) {
+                        // A = K^T: element (dk row, chunk row) = Ks[chunk row][dk row]
+                        const float* kt = Ks + (k0 + t) * LDK + 16 * mt + g;
+                        const float a0 = kt[0], a1 = kt[8], a2 = kt[4 * LDK], a3 = kt[4 * LDK + 8];
+#pragma unroll
+                        for (int n = 0; n < 4; ++n) mma_tf32(S[m][n], a0, a1, a2, a3, b0[n], b1[n]);
+                    }
+                }
             }
         }
         cluster.sync();
-        // ---- gated RMSNorm across the head's column blocks, output
-#pragma unroll 1
-        for (int u = 0; u < 8; ++u) {
-            const int i = kr + 8 * u;
-            if (i < Ce) {
-                float tot = 0.f;
+        // ---- gated RMSNorm across the head's column blocks, output.  The warp's 8 rows x CB peers
+        // are read from distributed shared memory by 8 CB lanes at once, and the gate values are
+        // loaded before anything is stored.
+        {
+            float v = 0.f;
+            if (lane < 8 * CB) v = cluster.map_shared_rank(cl_ss, lane % CB)[slot * DC_C + kr + 8 * (lane / CB)];
 #pragma unroll
-                for (int c = 0; c < CB; ++c) tot += cluster.map_shared_rank(cl_ss, c)[slot * DC_C + i];
-                const int r = rb + i;
-                const float z = __half2float(p.proj[(size_t)r * p.ld + p.off_z + j * DV + cb * DN_COLS + vcol]);
-                const float o = Ys[i * DN_COLS + vcol] * rsqrtf(tot / (float)DV + p.eps) * nw * silu_f(z);
-                p.out[(size_t)r * p.ldo + j * DV + cb * DN_COLS + vcol] = __float2half(o);
+            for (int o = CB / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = kr + 8 * u;
+                const float tot = __shfl_sync(0xffffffffu, v, u * CB);
+                if (i < Ce) {
+                    const float o = Ys[i * DN_COLS + vcol] * rsqrtf(tot / (float)DV + p.eps) * nw * silu_fast(zf[u]);
+                    p.out[(size_t)(rb + i) * p.ldo + j * DV + cb * DN_COLS + vcol] = __float2half(o);
+                }
             }
         }
         __syncthreads();
@@ -499,26 +661,33 @@ __global__ void __launch_bounds__(DN_THREADS, 1) deltanet_chunk_kernel(const Del
     cluster.sync();
     if (!p.commit) return;
 #pragma unroll
-    for (int i = 0; i < RPT; ++i) sp[(size_t)(kr + 8 * i) * DV] = S[i];
+    for (int m = 0; m < SPW; ++m) {
+        const int mt = kr + 8 * m;
+        if (mt < MT) {
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                *(float2*)(sp + (size_t)(16 * mt + g) * DV + 8 * n + 2 * t) = make_float2(S[m][n][0], S[m][n][1]);
+                *(float2*)(sp + (size_t)(16 * mt + g + 8) * DV + 8 * n + 2 * t) = make_float2(S[m][n][2], S[m][n][3]);
+            }
+        }
+    }
     // last three raw conv inputs (older history shifts in when the sequence was shorter than 3 rows)
-    const int n = r1 - r0;
     for (int c = tid; c < NCH; c += DN_THREADS) {
         const int col = proj_col(c);
 #pragma unroll
-        for (int t = 0; t < 3; ++t) {
-            const int ri = r1 - 3 + t;
+        for (int q = 0; q < 3; ++q) {
+            const int ri = r1 - 3 + q;
             float x = (ri >= r0) ? __half2float(p.proj[(size_t)ri * p.ld + col]) : hist[c * 3 + (ri - r0 + 3)];
-            my_hist[c * 3 + t] = __float2half(x);
+            my_hist[c * 3 + q] = __float2half(x);
         }
     }
-    (void)n;
 }
 
 template <int DK, int DV>
 static int launch_delta_chunk(const DeltaParams* p, const void* ab, int ld_ab, cudaStream_t s) {
     constexpr int CB = DV / DN_COLS;
     constexpr int NCH = 2 * DK + DN_COLS;
-    size_t smem = (size_t)(2 * DC_C * DC_LDK(DK) + 3 * DC_C * DN_COLS + 2 * DC_C * DC_LDA + DK * DN_COLS + NCH * 7 +
+    size_t smem = (size_t)(2 * DC_C * DC_LDK(DK) + DC_C * DC_LDU + 2 * DC_C * DN_COLS + 2 * DC_C * DC_LDA + DN_COLS * DC_LDK(DK) + NCH * 7 +
                            3 * DC_C + 2 * DC_C) * sizeof(float) + (size_t)(DC_C + 3) * NCH * sizeof(__half);
     static bool configured = false;
     if (!configured) {

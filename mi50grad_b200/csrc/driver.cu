@@ -354,12 +354,17 @@ static int rows_impl(Driver* d, int T, int n_seqs, int flags, cudaStream_t s) {
             a.kcache = (const __half*)L.kcache; a.vcache = (const __half*)L.vcache; a.rows = (const RowMeta*)m.p_rows;
             a.out = (__half*)m.p_attn; a.ldo = m.ld_attn; a.n_rows = T; a.nq = m.nq; a.nkv = m.nkv;
             a.max_seq = m.max_seq; a.scale = 1.0f / sqrtf((float)m.hd);
-            // few rows with long contexts (batched decode, verification): split the KV range; a prompt's
-            // many rows already fill the GPU
-            if (T <= m.p_logit_rows && m.p_attn_scratch) { a.splits = m.attn_splits; a.scratch = m.p_attn_scratch; a.counters = m.p_attn_counters; }
-            else { a.splits = 1; a.scratch = m.attn_scratch; a.counters = m.attn_counters; }
-            CK(b2_decode_attn(&a, m.hd, s));
-            d->launches += 2;
+            // tensor-core attention over 16-row tiles; few tiles with long contexts (batched decode,
+            // verification) are cut into cache slices so that the GPU fills, a prompt's many tiles are not
+            a.splits = 1; a.scratch = m.attn_scratch; a.counters = m.attn_counters;
+            if (T <= m.p_logit_rows && m.p_attn_scratch) {
+                const int tiles = (T + 15) / 16 > n_seqs ? (T + 15) / 16 : n_seqs;
+                int sp = 148 / (tiles * m.nkv);
+                sp = sp < 1 ? 1 : (sp > m.attn_splits ? m.attn_splits : sp);
+                a.splits = sp; a.scratch = m.p_attn_scratch;
+            }
+            CK(b2_attn_rows(&a, m.seq_rows, n_seqs, m.hd, s));
+            d->launches += a.splits > 1 ? 3 : 2;
         } else {
             DeltaParams q;
             fill_delta(d, L, q);

@@ -151,6 +151,24 @@ def decode_attn(q, rows_meta, kcache, vcache, nq, nkv, hd, gate_off=-1, splits=4
     return out
 
 
+def attn_rows(q, rows_meta, seq_rows, kcache, vcache, nq, nkv, hd, gate_off=-1, splits=1, out=None):
+    """Tensor-core attention for many rows (16-row tiles per sequence); seq_rows: int32 [n_seqs+1]."""
+    n = q.shape[0]
+    dev = q.device
+    if out is None:
+        out = torch.empty(n, nq * hd, dtype=torch.float16, device=dev)
+    p = L.AttnParams()
+    p.q, p.ldq, p.gate_off = q.data_ptr(), q.stride(0), gate_off
+    p.kcache, p.vcache, p.rows = kcache.data_ptr(), vcache.data_ptr(), rows_meta.data_ptr()
+    p.out, p.ldo, p.n_rows, p.nq, p.nkv = out.data_ptr(), out.stride(0), n, nq, nkv
+    p.max_seq, p.splits, p.scale = kcache.shape[1], splits, 1.0 / hd ** 0.5
+    scratch = torch.empty(max(1, n * nq * splits * (hd + 2)), dtype=torch.float32, device=dev)
+    p.scratch = scratch.data_ptr()
+    L.check(L.lib().b2_attn_rows(C.byref(p), C.c_void_p(seq_rows.data_ptr()), seq_rows.shape[0] - 1, hd, L.stream()),
+            "attn_rows")
+    return out
+
+
 def deltanet_step(proj, offs, conv_w, conv_state, state, A_log, dt_bias, norm_w, rows_meta, seq_rows, nk, nv,
                   dk, dv, xn=None, wa=None, wb=None, out=None, commit=True, eps=1e-6, ln=None):
     """offs = (off_q, off_k, off_v, off_z, off_a, off_b)."""

@@ -228,6 +228,33 @@ def test_decode_attn(K, hd, nq, nkv, splits):
         assert _rel(out[r].cpu().view(nq, hd), o[0]) < 3e-3, f"row {r}"
 
 
+@pytest.mark.parametrize("hd,nq,nkv,splits", [(256, 6, 1, 1), (256, 24, 4, 3), (64, 4, 2, 1), (64, 6, 2, 4)])
+def test_attn_rows_tensor_core(K, hd, nq, nkv, splits):
+    """Many-row attention: a 40-row causal prompt chunk behind 5 cached tokens (three tiles, the last
+    partial), a 6-node draft tree behind 137 cached tokens, and a single decode row."""
+    from mi50grad_b200.models import oracle as O
+    gen = torch.Generator().manual_seed(15)
+    d = _dev()
+    max_seq, nseq = 256, 3
+    kc = torch.randn(nseq, max_seq, nkv, hd, generator=gen).half()
+    vc = torch.randn(nseq, max_seq, nkv, hd, generator=gen).half()
+    entries = [(0, 5 + i, 5 + i, 5 + i + 1, 0) for i in range(40)]
+    anc = [0b1, 0b11, 0b101, 0b1011, 0b10011, 0b100101]
+    entries += [(1, 137, 137 + i, 137, anc[i]) for i in range(6)]
+    entries += [(2, 200, 200, 200, 1)]
+    seq_rows = torch.tensor([0, 40, 46, 47], dtype=torch.int32)
+    rows = len(entries)
+    q = torch.randn(rows, 2 * nq * hd, generator=gen).half()
+    out = K.attn_rows(q.to(d), K.make_rows(entries, d), seq_rows.to(d), kc.to(d), vc.to(d), nq, nkv, hd,
+                      gate_off=nq * hd, splits=splits)
+    for r, (s_, _, _, ctx, mask) in enumerate(entries):
+        vis = list(range(ctx)) + [ctx + j for j in range(64) if (mask >> j) & 1]
+        o = O.attention(q[r:r + 1, :nq * hd].float().view(1, nq, hd), kc[s_, vis].float(), vc[s_, vis].float(),
+                        torch.ones(1, len(vis), dtype=torch.bool))
+        o = o * torch.sigmoid(q[r, nq * hd:].float().view(1, nq, hd))
+        assert _rel(out[r].cpu().view(nq, hd), o[0]) < 4e-3, f"row {r}"
+
+
 @pytest.mark.parametrize("dk,nk,nv,rows_per_seq,inkernel_ab", [(128, 2, 6, [1], True), (64, 2, 4, [3, 1], False),
                                                               (128, 1, 3, [5], False), (64, 1, 2, [2], "lazy")])
 def test_deltanet_step(K, dk, nk, nv, rows_per_seq, inkernel_ab):
