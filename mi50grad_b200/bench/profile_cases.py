@@ -8,7 +8,7 @@ cudaProfilerStart/Stop (use `ncu --profile-from-start off`), and with --time
 prints CUDA-event timings taken from a graph replay instead.
 
 cases: gemv_gateup, gemv_down, gemm_int4, gemm_dense, attn_decode, attn_rows,
-       deltanet_step, deltanet_chunk, spec_step
+       deltanet_step, deltanet_chunk, spec_step, prefill
 """
 from __future__ import annotations
 
@@ -100,7 +100,11 @@ def case_attn(which: str, timed: bool):
     rows = [(s, ctx + i, ctx + i, ctx, (1 << (i + 1)) - 1) for s in range(n_seq) for i in range(per)]
     rm = K.make_rows(rows, dev)
     q = torch.randn(len(rows), 2 * nq * hd, device=dev).half()
-    run = lambda i=0: K.decode_attn(q, rm, kc, vc, nq, nkv, hd, gate_off=nq * hd, splits=16)
+    if which == "attn_rows":
+        seq_rows = torch.arange(0, n_seq * per + 1, per, dtype=torch.int32, device=dev)
+        run = lambda i=0: K.attn_rows(q, rm, seq_rows, kc, vc, nq, nkv, hd, gate_off=nq * hd, splits=2)
+    else:
+        run = lambda i=0: K.decode_attn(q, rm, kc, vc, nq, nkv, hd, gate_off=nq * hd, splits=16)
     if timed:
         _report(which, time_launches(run, 1, 6), bytes_=2.0 * n_seq * ctx * nkv * hd * 2)
     else:
@@ -138,6 +142,27 @@ def case_spec_step(timed: bool):
     print(f"spec_step 80 rows: {e0.elapsed_time(e1):.2f} ms", flush=True)
 
 
+def case_prefill(timed: bool):
+    """pp512 of the 27B model at TP=1 (whole model resident: launch lists only)."""
+    from ..config import qwen35_27b
+    from ..engine.engine import InferenceEngine
+    cfg = qwen35_27b()
+    eng = InferenceEngine(cfg, max_seq_len=1024)
+    eng.init_random(0)
+    toks = torch.randint(0, cfg.vocab_size, (512,), generator=torch.Generator().manual_seed(1)).tolist()
+    eng.prefill_tokens(toks[:64])
+    eng.reset()
+    eng.prefill_tokens(toks)
+    eng.reset()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.cudart().cudaProfilerStart()
+    e0.record(); eng.prefill_tokens(toks); e1.record()
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStop()
+    print(f"pp512: {e0.elapsed_time(e1):.2f} ms", flush=True)
+
+
 def case_deltanet(which: str, timed: bool):
     from .microbench_deltanet import run_case
     run_case(which, timed, _profiled, _report)
@@ -156,6 +181,8 @@ def main():
         case_attn(a.case, a.time)
     elif a.case == "spec_step":
         case_spec_step(a.time)
+    elif a.case == "prefill":
+        case_prefill(a.time)
     elif a.case.startswith("deltanet"):
         case_deltanet(a.case, a.time)
     else:

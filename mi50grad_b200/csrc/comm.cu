@@ -52,6 +52,8 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const CollParams p) {
 
     // ---- 1. publish the local input in this rank's symmetric staging buffer
     float4* mine = (float4*)(c.part[rank] + poff);
+    const size_t per_push = (n4 + tp - 1) / tp;
+    if (!p.pushed)
     for (size_t i = gtid; i < n4; i += gsz) {
         float4 v;
         if (p.in) v = ((const float4*)p.in)[i];
@@ -62,7 +64,8 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const CollParams p) {
         }
         mine[i] = v;
     }
-    __threadfence();
+    if (p.pushed) __threadfence_system();       // the producers' stores to peer memory precede the flag
+    else __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
         s_last = (atomicAdd(&p.counters[0], 1) == (int)gridDim.x - 1);
@@ -87,6 +90,19 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const CollParams p) {
         }
     };
     auto reduce_at = [&](size_t i) -> float4 {
+        if (p.pushed) {
+            // slice element i - lo from every source rank, all in this rank's own memory
+            const size_t il = i - per_push * rank;
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int r = 0; r < B2_MAX_TP; ++r) {
+                if (r < tp) {
+                    float4 v = ld_relaxed_sys_v4((const float*)(mine + (size_t)r * per_push + il));
+                    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+                }
+            }
+            return s;
+        }
         if (!ok) return mine[i];
         if (c.mc_part) return multimem_ld_reduce_v4(c.mc_part + poff + 4 * i);
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -141,7 +157,7 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const CollParams p) {
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 size_t i = i0 + u * gsz;
-                if (i < n4) v[u] = ok2 ? ld_relaxed_sys_v4(mygather + 4 * i) : mine[i];
+                if (i < n4) v[u] = (ok2 || p.pushed) ? ld_relaxed_sys_v4(mygather + 4 * i) : mine[i];
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) if (i0 + u * gsz < n4) emit(i0 + u * gsz, v[u]);
@@ -159,6 +175,8 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const CollParams p) {
 
 B2_API int b2_allreduce(const CollParams* p, int max_ctas, cudaStream_t s) {
     if (p->n % 4 || p->n > (size_t)p->comm.part_stride) return cudaErrorInvalidValue;
+    if (p->pushed && (!p->twoshot || (((p->n / 4 + p->comm.tp - 1) / p->comm.tp) * p->comm.tp * 4 > (size_t)p->comm.part_stride)))
+        return cudaErrorInvalidValue;
     size_t n4 = p->n / 4;
     int ctas = (int)((n4 + 511) / 512);
     // CTAs wait on one another, so the whole grid must be resident: ask the runtime how many fit

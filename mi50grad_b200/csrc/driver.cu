@@ -313,6 +313,13 @@ static int run_gemm(Driver* d, const LinearDesc& L, const void* x, int ldx, int 
     }
     p.T = T; p.t_tile = tt;
     p.n_valid = n_valid; p.ldo = ldo; p.epi = epi; p.out = out; p.status = d->m.tc_status;
+    if (epi == TC_EPI_PUSH_F32) {
+        const CommCtx& c = d->m.comm;
+        const size_t n4 = (size_t)T * ldo / 4;
+        for (int r = 0; r < c.tp; ++r) p.push[r] = c.part[r];
+        p.epoch = c.epoch; p.part_stride = (long long)c.part_stride;
+        p.push_tp = c.tp; p.push_rank = c.rank; p.push_per = (unsigned)((n4 + c.tp - 1) / c.tp);
+    }
     d->launches++;
     return b2_gemm_int4_tc(&p, x, ldx, s);
 }
@@ -320,11 +327,14 @@ static int run_gemm(Driver* d, const LinearDesc& L, const void* x, int ldx, int 
 static int row_parallel(Driver* d, const LinearDesc& L, const void* x, int ldx, int T, cudaStream_t s) {
     const ModelDesc& m = d->m;
     if (m.comm.tp <= 1) return run_gemm(d, L, x, ldx, T, m.p_h, m.H, m.H, TC_EPI_RESID_F32, s);
-    CK(run_gemm(d, L, x, ldx, T, m.p_partial, m.H, m.H, TC_EPI_STORE_F32, s));
+    // Tensor parallel: the GEMM epilogue pushes every output tile into the staging buffer of the rank
+    // that reduces that slice (reduce-scatter traffic overlaps the GEMM); the collective kernel then
+    // sums its slice from local memory, multicasts it, and adds the residual.
+    CK(run_gemm(d, L, x, ldx, T, nullptr, m.H, m.H, TC_EPI_PUSH_F32, s));
     CollParams c;
     memset(&c, 0, sizeof(c));
-    c.comm = m.comm; c.in = m.p_partial; c.out = m.p_h; c.n = (size_t)T * m.H; c.residual = 1;
-    c.twoshot = (c.n * 4 > 512 * 1024) ? 1 : 0;
+    c.comm = m.comm; c.in = nullptr; c.out = m.p_h; c.n = (size_t)T * m.H; c.residual = 1;
+    c.twoshot = 1; c.pushed = 1;
     for (int r = 0; r < m.comm.tp; ++r) c.gather[r] = m.coll_gather[r];
     c.mc_gather = m.coll_mc_gather; c.counters = m.coll_counters;
     d->launches++;

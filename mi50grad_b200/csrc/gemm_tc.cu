@@ -300,6 +300,19 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
                         if (is_gate && c0 + c < Tp && tt < p.T && o < p.n_valid)
                             ((__half*)p.out)[(size_t)tt * p.ldo + o] = __float2half(silu_f(v) * up);
                     }
+                } else if (p.epi == TC_EPI_PUSH_F32) {
+                    // plain stores into the owner's memory over NVLink (posted writes, 128 bytes per warp)
+                    const size_t poff = (size_t)((*p.epoch + 1u) & 1u) * (size_t)p.part_stride;
+#pragma unroll 4
+                    for (int c = 0; c < 32; ++c) {
+                        int tt = t0 + c0 + c;
+                        if (c0 + c < Tp && tt < p.T && n < p.n_valid) {
+                            const unsigned e = (unsigned)tt * (unsigned)p.ldo + (unsigned)n;
+                            const unsigned i4 = e >> 2, owner = i4 / p.push_per;
+                            float* dst = p.push[owner] + poff + ((size_t)p.push_rank * p.push_per + (i4 - owner * p.push_per)) * 4 + (e & 3u);
+                            *dst = __uint_as_float(r[c]);
+                        }
+                    }
                 } else {
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {

@@ -6,6 +6,9 @@
 #define TC_EPI_SILU_PAIR 1
 #define TC_EPI_STORE_F32 2
 #define TC_EPI_RESID_F32 3       // out32[t][n] += y
+#define TC_EPI_PUSH_F32 4        // tensor parallel: y goes straight into the symmetric staging buffer of the
+                                 // rank that will reduce that slice of the [T x n_valid] output (reduce-scatter
+                                 // fused into the GEMM epilogue; the collective kernel then reads local memory only)
 
 struct GemmTcParams {
     const uint4* qfrag;      // [NTL/4][KB][4][32] packed nibbles
@@ -18,6 +21,14 @@ struct GemmTcParams {
     int* status;             // [0] set to 1 when a bounded wait expired
     int pad;
     int dense;               // set by the launcher: weights are fp16 and come through a tensor map
+    // TC_EPI_PUSH_F32: the flattened output (float4 units) is cut into push_tp slices of push_per; slice o
+    // lives on rank o at push[o] + parity offset + (push_rank * push_per + index in slice) * 4 floats
+    float* push[B2_MAX_TP];
+    const unsigned int* epoch;   // collective epoch counter of this rank (parity of the next collective)
+    long long part_stride;       // floats between the two parity halves of a staging buffer
+    int push_tp, push_rank;
+    unsigned int push_per;       // float4 elements per slice
+    int pad2;
 };
 
 

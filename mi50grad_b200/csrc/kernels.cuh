@@ -62,6 +62,8 @@ struct CollParams {
     int twoshot;
     int* counters;           // [4] local, zero between launches
     int test_withhold;       // test hook: never signal, so that the bounded wait expires
+    int pushed;              // 1: the producers already stored every rank's slice contributions into the owners'
+                             //    staging buffers ([source rank][slice]); nothing to publish, reduce from local memory
 };
 
 // ---- speculative verification (csrc/speculative.cu)

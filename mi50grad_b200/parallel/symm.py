@@ -35,7 +35,7 @@ class CollParams(C.Structure):
     _fields_ = [("comm", L.CommCtx), ("in_", C.c_void_p), ("in16", C.c_void_p), ("out", C.c_void_p),
                 ("out16", C.c_void_p), ("gather", C.c_void_p * L.MAX_TP), ("mc_gather", C.c_void_p),
                 ("n", C.c_size_t), ("residual", C.c_int), ("twoshot", C.c_int), ("counters", C.c_void_p),
-                ("test_withhold", C.c_int)]
+                ("test_withhold", C.c_int), ("pushed", C.c_int)]
 
 
 class SymmComm(Communicator):
