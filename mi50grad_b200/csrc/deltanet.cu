@@ -718,32 +718,59 @@ B2_API int b2_deltanet_chunk(const DeltaParams* p, const void* ab, int ld_ab, in
     return cudaErrorInvalidValue;
 }
 
-// a/b projections for many rows: ab[r][o] = x[r] . w[o], o < n_out (tiny dense weights).
+// a/b projections for many rows: ab[r][o] = x[r] . w[o], o < 2 nv (tiny dense weights).  A CTA stages
+// AB_ROWS activation rows in shared memory and computes 8 outputs (one per warp) for all of them:
+// grid = (row groups, output groups).
+#define AB_ROWS 8
 __global__ void __launch_bounds__(256) ab_proj_kernel(const __half* __restrict__ x, int ldx, const __half* __restrict__ wa,
                                                       const __half* __restrict__ wb, int nv, int H,
-                                                      __half* __restrict__ ab, int ld_ab) {
-    extern __shared__ __align__(16) __half xs[];
+                                                      __half* __restrict__ ab, int ld_ab, int rows) {
+    extern __shared__ __align__(16) __half xs[];           // [AB_ROWS][H]
     pdl_launch_dependents();
-    const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    for (int i = tid * 8; i < H; i += 256 * 8) *(uint4*)(xs + i) = *(const uint4*)(x + (size_t)r * ldx + i);
+    const int r0 = blockIdx.x * AB_ROWS, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nr = min(AB_ROWS, rows - r0);
+    for (int i = tid * 8; i < AB_ROWS * H; i += 256 * 8) {
+        const int r = i / H, c = i - r * H;
+        *(uint4*)(xs + i) = r < nr ? *(const uint4*)(x + (size_t)(r0 + r) * ldx + c) : make_uint4(0u, 0u, 0u, 0u);
+    }
     __syncthreads();
-    for (int o = warp; o < 2 * nv; o += 8) {
+    for (int o = blockIdx.y * 8 + warp; o < min(2 * nv, (int)blockIdx.y * 8 + 8); o += 8) {
         const __half* w = (o < nv) ? wa + (size_t)o * H : wb + (size_t)(o - nv) * H;
-        float acc = 0.f;
-        for (int i = lane * 8; i < H; i += 256) {
-            uint4 wv = *(const uint4*)(w + i), xv = *(const uint4*)(xs + i);
-            const __half2* w2 = (const __half2*)&wv; const __half2* x2 = (const __half2*)&xv;
+        float acc[AB_ROWS];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) { float2 a = __half22float2(w2[q]), b = __half22float2(x2[q]); acc += a.x * b.x + a.y * b.y; }
+        for (int r = 0; r < AB_ROWS; ++r) acc[r] = 0.f;
+        for (int i = lane * 8; i < H; i += 256) {
+            const uint4 wv = *(const uint4*)(w + i);
+            const __half2* w2 = (const __half2*)&wv;
+            float2 wf[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) wf[q] = __half22float2(w2[q]);
+#pragma unroll
+            for (int r = 0; r < AB_ROWS; ++r) {
+                const uint4 xv = *(const uint4*)(xs + r * H + i);
+                const __half2* x2 = (const __half2*)&xv;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) { const float2 b = __half22float2(x2[q]); acc[r] += wf[q].x * b.x + wf[q].y * b.y; }
+            }
         }
-        acc = warp_sum(acc);
-        if (lane == 0) ab[(size_t)r * ld_ab + o] = __float2half(acc);
+#pragma unroll
+        for (int r = 0; r < AB_ROWS; ++r) {
+            const float v = warp_sum(acc[r]);
+            if (lane == 0 && r < nr) ab[(size_t)(r0 + r) * ld_ab + o] = __float2half(v);
+        }
     }
 }
 B2_API int b2_ab_proj(const void* x, int ldx, const void* wa, const void* wb, int nv, int H, void* ab, int ld_ab,
                       int rows, cudaStream_t s) {
-    if (H % 8) return cudaErrorInvalidValue;
-    ab_proj_kernel<<<rows, 256, (size_t)H * 2, s>>>((const __half*)x, ldx, (const __half*)wa, (const __half*)wb, nv, H,
-                                                    (__half*)ab, ld_ab);
+    if (H % 8 || (ldx % 8)) return cudaErrorInvalidValue;
+    const size_t smem = (size_t)AB_ROWS * H * 2;
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(ab_proj_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = smem;
+    }
+    ab_proj_kernel<<<dim3((rows + AB_ROWS - 1) / AB_ROWS, (2 * nv + 7) / 8), 256, smem, s>>>((const __half*)x, ldx, (const __half*)wa,
+                                                                     (const __half*)wb, nv, H, (__half*)ab, ld_ab, rows);
     return cudaGetLastError();
 }

@@ -84,7 +84,8 @@ struct ModelDesc {
     // many-row steps (batched decode, speculative verification): logits and arg-max scratch for p_logit_rows rows
     float* p_logits; float* p_argmax_scratch; int* p_argmax_counters; int* p_out_tokens;
     float* p_attn_scratch; int* p_attn_counters;     // split-KV scratch for p_logit_rows rows
-    int p_logit_rows; int n_lin_layers; int n_full_layers; int pad5;
+    int p_logit_rows; int n_lin_layers; int n_full_layers;
+    int ab_off;                            // column of p_proj where the a | b gate projections of many-row steps go (-1: none)
     // speculative verification
     SpecStage spec; int* spec_acc; int* spec_result;
     float* state0; void* conv0; long long state_layer_stride, conv_layer_stride;
@@ -380,18 +381,19 @@ static int rows_impl(Driver* d, int T, int n_seqs, int flags, cudaStream_t s) {
             fill_delta(d, L, q);
             q.proj = (const __half*)m.p_proj; q.ld = m.ld_proj; q.xn = (const __half*)m.p_xn;
             q.rows = (const RowMeta*)m.p_rows; q.out = (__half*)m.p_attn; q.n_seqs = n_seqs;
+            // the tiny a/b gate projections: from the in-projection if the checkpoint quantised them with it,
+            // else one small dense kernel for all rows into spare columns of the projection buffer
+            const void* ab = (const __half*)m.p_proj + (L.off_a >= 0 ? L.off_a : 0);
+            if (L.off_a < 0 && m.ab_off >= 0) {
+                CK(b2_ab_proj(m.p_xn, m.H, L.wa, L.wb, m.la_nv, m.H, (__half*)m.p_proj + m.ab_off, m.ld_proj, T, s));
+                d->launches++;
+                ab = (const __half*)m.p_proj + m.ab_off;
+                q.off_a = m.ab_off; q.off_b = m.ab_off + m.la_nv;
+            }
             if (flags & STEP_SPEC) {
                 CK(b2_deltanet_verify(&q, &m.spec, L.type_index, m.la_dk, m.la_dv, s));
             } else if (n_seqs == 1 && T >= 16) {
-                // chunked scan; a/b come from the projection buffer or from a small dense kernel
-                const void* ab = (const __half*)m.p_proj + (L.off_a >= 0 ? L.off_a : 0);
-                int ld_ab = m.ld_proj;
-                if (L.off_a < 0) {
-                    CK(b2_ab_proj(m.p_xn, m.H, L.wa, L.wb, m.la_nv, m.H, m.p_ab, 2 * m.la_nv, T, s));
-                    d->launches++;
-                    ab = m.p_ab; ld_ab = 2 * m.la_nv;
-                }
-                CK(b2_deltanet_chunk(&q, ab, ld_ab, m.la_dk, m.la_dv, s));
+                CK(b2_deltanet_chunk(&q, ab, m.ld_proj, m.la_dk, m.la_dv, s));
             } else {
                 CK(b2_deltanet_step(&q, m.la_dk, m.la_dv, s));
             }

@@ -139,8 +139,57 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const float* __restric
         if (xn32) xn32[(size_t)r * H + i] = v;
     }
 }
+// Same, for H % 4 == 0 and H <= 8192: the row is read once with 16-byte loads and kept in registers.
+__global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ delta32,
+                                                              const __half* __restrict__ delta16,
+                                                              const __half* __restrict__ w, __half* __restrict__ xn,
+                                                              float* __restrict__ xn32, int H, float eps) {
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    const int r = blockIdx.x, n4 = H >> 2;
+    float4* hr = (float4*)(h + (size_t)r * H);
+    float4 v[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int i = threadIdx.x + 256 * u;
+        if (i < n4) {
+            float4 a = hr[i];
+            if (delta32) { const float4 d = ((const float4*)(delta32 + (size_t)r * H))[i]; a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w; }
+            if (delta16) {
+                const uint2 d = ((const uint2*)(delta16 + (size_t)r * H))[i];
+                const float2 d0 = __half22float2(*(const __half2*)&d.x), d1 = __half22float2(*(const __half2*)&d.y);
+                a.x += d0.x; a.y += d0.y; a.z += d1.x; a.w += d1.y;
+            }
+            v[u] = a;
+            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+        }
+    }
+    const float inv = rsqrtf(block_sum(ss, red) / (float)H + eps);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int i = threadIdx.x + 256 * u;
+        if (i < n4) {
+            if (delta32 || delta16) hr[i] = v[u];
+            const uint2 wv = ((const uint2*)w)[i];
+            const float2 w0 = __half22float2(*(const __half2*)&wv.x), w1 = __half22float2(*(const __half2*)&wv.y);
+            const float4 o = make_float4(v[u].x * inv * w0.x, v[u].y * inv * w0.y, v[u].z * inv * w1.x, v[u].w * inv * w1.y);
+            if (xn) {
+                const __half2 a = __floats2half2_rn(o.x, o.y), b = __floats2half2_rn(o.z, o.w);
+                uint2 pk; pk.x = *(const uint32_t*)&a; pk.y = *(const uint32_t*)&b;
+                ((uint2*)(xn + (size_t)r * H))[i] = pk;
+            }
+            if (xn32) ((float4*)(xn32 + (size_t)r * H))[i] = o;
+        }
+    }
+}
 B2_API int b2_add_rmsnorm(float* h, const float* delta32, const void* delta16, const void* w, void* xn,
                           float* xn32, int n_rows, int H, float eps, cudaStream_t s) {
+    if (H % 4 == 0 && H <= 8192) {
+        add_rmsnorm_vec_kernel<<<n_rows, 256, 0, s>>>(h, delta32, (const __half*)delta16, (const __half*)w,
+                                                      (__half*)xn, xn32, H, eps);
+        return cudaGetLastError();
+    }
     add_rmsnorm_kernel<<<n_rows, 256, 0, s>>>(h, delta32, (const __half*)delta16, (const __half*)w,
                                               (__half*)xn, xn32, H, eps);
     return cudaGetLastError();

@@ -291,7 +291,11 @@ class InferenceEngine:
         self.F_pad = self.layers[0].gate_up.n_pad // 2
         b = self.buf = {}
         b["h"], b["xn"] = f32(R, H), f16(R, H)
-        b["ld_proj"] = max(dl.in_proj.N for dl in self.layers)
+        # row stride of the projection buffers: widest in-projection + spare columns for the a | b gate
+        # projections of many-row steps
+        n_in = -(-max(dl.in_proj.N for dl in self.layers) // 8) * 8
+        self.ab_off = n_in
+        b["ld_proj"] = n_in + -(-max(2, 2 * sp.n_la_v) // 8) * 8
         b["proj"] = f16(R, b["ld_proj"])
         b["ld_attn"] = max(dl.out_proj.K for dl in self.layers)
         b["attn_out"] = f16(R, b["ld_attn"])
@@ -373,6 +377,7 @@ class InferenceEngine:
                   "p_attn_counters", "spec_acc", "spec_result"):
             setattr(m, k, b[k].data_ptr())
         m.p_logit_rows, m.n_lin_layers, m.n_full_layers = SR, n_lin, len(self.states.kv.layers)
+        m.ab_off = self.ab_off
         m.spec.base, m.spec.layer_stride, m.spec.seq_stride = b["spec_stage"].data_ptr(), self.max_batch * blk, blk
         m.spec.off_k, m.spec.off_u, m.spec.off_g, m.spec.off_x = [o.value for o in offs]
         dn, kv = self.states.dn, self.states.kv

@@ -146,7 +146,7 @@ class ModelDesc(C.Structure):
                 ("tc_status", vp), ("p_ab", vp), ("coll_gather", vp * MAX_TP), ("coll_mc_gather", vp), ("coll_counters", vp),
                 ("p_logits", vp), ("p_argmax_scratch", vp), ("p_argmax_counters", vp), ("p_out_tokens", vp),
                 ("p_attn_scratch", vp), ("p_attn_counters", vp),
-                ("p_logit_rows", i32), ("n_lin_layers", i32), ("n_full_layers", i32), ("pad5", i32),
+                ("p_logit_rows", i32), ("n_lin_layers", i32), ("n_full_layers", i32), ("ab_off", i32),
                 ("spec", SpecStage), ("spec_acc", vp), ("spec_result", vp),
                 ("state0", vp), ("conv0", vp), ("state_layer_stride", i64), ("conv_layer_stride", i64),
                 ("k0", vp), ("v0", vp), ("kv_layer_stride", i64),
