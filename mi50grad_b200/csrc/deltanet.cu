@@ -236,7 +236,7 @@ B2_API int b2_delta_conv_channels(int dk) { return 2 * dk + DN_COLS; }
 // which is exchanged through distributed shared memory once per chunk).  All matrices of a
 // chunk live in shared memory in fp32; the state slice stays in registers across chunks.
 // ===========================================================================
-#define DC_C 64                  // rows per chunk
+#define DC_C 32                  // rows per chunk: small enough that two CTAs share an SM and overlap their phases
 #define DC_LDK(DK) ((DK) + 4)    // padded row stride of the q/k tiles (conflict-free fragment loads)
 #define DC_LDA (DC_C + 4)
 #define DC_LDU (DN_COLS + 8)     // row stride of U and of the state copy (they are B operands)
@@ -265,10 +265,16 @@ __device__ __forceinline__ void ldsm4(float (&r)[4], const float* row_ptr) {
                  : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(a));
     r[0] = __uint_as_float(x0); r[1] = __uint_as_float(x1); r[2] = __uint_as_float(x2); r[3] = __uint_as_float(x3);
 }
+__device__ __forceinline__ void ldsm2(float (&r)[2], const float* row_ptr) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(row_ptr);
+    uint32_t x0, x1;
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(x0), "=r"(x1) : "r"(a));
+    r[0] = __uint_as_float(x0); r[1] = __uint_as_float(x1);
+}
 __device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.f + __expf(-x)); }
 
 template <int DK, int DV>
-__global__ void __launch_bounds__(DN_THREADS, 1) deltanet_chunk_kernel(const DeltaParams p, const __half* __restrict__ ab, int ld_ab) {
+__global__ void __launch_bounds__(DN_THREADS, 2) deltanet_chunk_kernel(const DeltaParams p, const __half* __restrict__ ab, int ld_ab) {
     constexpr int CB = DV / DN_COLS;
     constexpr int MT = DK / 16;               // 16-row tiles of the state slice, one or two per warp
     constexpr int SPW = (MT + 7) / 8;         // state m-tiles per warp
@@ -384,18 +390,21 @@ __global__ void __launch_bounds__(DN_THREADS, 1) deltanet_chunk_kernel(const Del
         // copy for this chunk was issued while the previous chunk was being processed)
         cp_async_wait<0>();
         __syncthreads();
-        for (int item = tid; item < NCH * (DC_C / 8); item += DN_THREADS) {
-            const int c = item % NCH, i0 = (item / NCH) * 8;
-            const float w0 = cw[c * 4 + 0], w1 = cw[c * 4 + 1], w2 = cw[c * 4 + 2], w3 = cw[c * 4 + 3];
-            float x0 = __half2float(Xr[(i0 + 0) * NCH + c]), x1 = __half2float(Xr[(i0 + 1) * NCH + c]);
-            float x2 = __half2float(Xr[(i0 + 2) * NCH + c]);
+        // two adjacent channels per item (one 4-byte shared-memory load serves both), 8 rows per item
+        for (int item = tid; item < (NCH / 2) * (DC_C / 8); item += DN_THREADS) {
+            const int c = 2 * (item % (NCH / 2)), i0 = (item / (NCH / 2)) * 8;
+            const float4 wa4 = *(const float4*)&cw[c * 4], wb4 = *(const float4*)&cw[c * 4 + 4];
+            float2 x0 = __half22float2(*(const __half2*)&Xr[(i0 + 0) * NCH + c]);
+            float2 x1 = __half22float2(*(const __half2*)&Xr[(i0 + 1) * NCH + c]);
+            float2 x2 = __half22float2(*(const __half2*)&Xr[(i0 + 2) * NCH + c]);
             float* dst = (c < DK) ? Qs + c : (c < 2 * DK) ? Ks + (c - DK) : Us + (c - 2 * DK);
             const int ldd = (c < 2 * DK) ? LDK : DC_LDU;
 #pragma unroll
             for (int i = i0; i < i0 + 8; ++i) {
-                const float x3 = __half2float(Xr[(i + 3) * NCH + c]);
-                const float acc = x0 * w0 + x1 * w1 + x2 * w2 + x3 * w3;
-                dst[i * ldd] = (i < Ce) ? silu_fast(acc) : 0.f;
+                const float2 x3 = __half22float2(*(const __half2*)&Xr[(i + 3) * NCH + c]);
+                const float a0 = x0.x * wa4.x + x1.x * wa4.y + x2.x * wa4.z + x3.x * wa4.w;
+                const float a1 = x0.y * wb4.x + x1.y * wb4.y + x2.y * wb4.z + x3.y * wb4.w;
+                *(float2*)&dst[i * ldd] = (i < Ce) ? make_float2(silu_fast(a0), silu_fast(a1)) : make_float2(0.f, 0.f);
                 x0 = x1; x1 = x2; x2 = x3;
             }
         }
@@ -415,26 +424,28 @@ __global__ void __launch_bounds__(DN_THREADS, 1) deltanet_chunk_kernel(const Del
         if (rb + DC_C < r1) stage_raw(rb + DC_C);          // flies while this chunk is processed
         fetch_gates(rb + DC_C);
         // output gates of this chunk, needed only at its end
-        float zf[8];
+        float zf[DC_C / 8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int u = 0; u < DC_C / 8; ++u) {
             const int i = kr + 8 * u;
             zf[u] = (i < Ce) ? __half2float(p.proj[(size_t)(rb + i) * p.ld + p.off_z + j * DV + cb * DN_COLS + vcol]) : 0.f;
         }
         // ---- P2: L2-normalise q and k rows (stored rounded to TF32), running log-decay, state copy
         if (kr == 0) {
-            // inclusive scan of the 64 log-decays: two per lane
-            float a = gs[lane], b = gs[lane + 32];
+            // inclusive scan of the log-decays: DC_C / 32 per lane
+            static_assert(DC_C == 32 || DC_C == 64, "chunk size");
+            float a = gs[lane], b = DC_C > 32 ? gs[lane + DC_C - 32] : 0.f;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const float ua = __shfl_up_sync(0xffffffffu, a, o), ub = __shfl_up_sync(0xffffffffu, b, o);
                 if (lane >= o) { a += ua; b += ub; }
             }
             const float tot = __shfl_sync(0xffffffffu, a, 31);
-            Gs[lane] = a; Gs[lane + 32] = b + tot;
+            Gs[lane] = a;
+            if (DC_C > 32) Gs[lane + DC_C - 32] = b + tot;
         }
 #pragma unroll 1
-        for (int ub = 0; ub < 8; ub += 4) {
+        for (int ub = 0; ub < DC_C / 8; ub += 4) {
             // four rows at a time: their loads and the eight reductions overlap
             constexpr int PL = DK / 32;
             float qv[4][PL], kv[4][PL], qq[4], kk[4];
@@ -479,63 +490,66 @@ __global__ void __launch_bounds__(DN_THREADS, 1) deltanet_chunk_kernel(const Del
         }
         __syncthreads();
         // ---- P3: A = beta decay (K K^T) below the diagonal, W = decay (Q K^T) on and below it, in
-        // 16x16 blocks of the lower triangle dealt round-robin to the warps.  Fragments come from
+        // 16x8 tiles of the lower triangle dealt round-robin to the warps.  Fragments come from
         // ldmatrix: one instruction per operand and k-step.
+        constexpr int MB = DC_C / 16;                 // 16-row blocks of a chunk
+        constexpr int NTW = (MB * 4) / 8;             // 8-column tiles of U / Y per warp in P4 and P6 (1 or 2)
+        const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 4;       // A operand addressing
+        const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 4;       // B operand, two 8-column tiles
         {
-            const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 4;       // A operand addressing
-            const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 4;       // B operand, two 8-column tiles
-            for (int blk = kr; blk < 10; blk += 8) {
-                const int mi = blk >= 6 ? 3 : (blk >= 3 ? 2 : (blk >= 1 ? 1 : 0));
-                const int nj = blk - mi * (mi + 1) / 2;
-                float kk[2][4], qk[2][4];
-#pragma unroll
-                for (int n = 0; n < 2; ++n)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) kk[n][e] = qk[n][e] = 0.f;
+            for (int tile = kr; tile < MB * (MB + 1); tile += 8) {
+                int mi = 0, ni = tile;                 // row block mi holds tiles ni = 0 .. 2 mi + 1
+                while (ni >= 2 * mi + 2) { ni -= 2 * mi + 2; ++mi; }
+                float kk[4] = {0.f, 0.f, 0.f, 0.f}, qk[4] = {0.f, 0.f, 0.f, 0.f};
                 const float* ka = Ks + (16 * mi + a_row) * LDK + a_col;
                 const float* qa = Qs + (16 * mi + a_row) * LDK + a_col;
-                const float* kb = Ks + (16 * nj + b_row) * LDK + b_col;
+                const float* kb = Ks + (8 * ni + (lane & 7)) * LDK + ((lane >> 3) & 1) * 4;   // x2: lanes 0-15 give the rows
 #pragma unroll 4
                 for (int k0 = 0; k0 < DK; k0 += 8) {
-                    float fa[4], fq[4], fb[4];
-                    ldsm4(fa, ka + k0); ldsm4(fq, qa + k0); ldsm4(fb, kb + k0);
-                    mma_tf32(kk[0], fa[0], fa[1], fa[2], fa[3], fb[0], fb[1]);
-                    mma_tf32(kk[1], fa[0], fa[1], fa[2], fa[3], fb[2], fb[3]);
-                    mma_tf32(qk[0], fq[0], fq[1], fq[2], fq[3], fb[0], fb[1]);
-                    mma_tf32(qk[1], fq[0], fq[1], fq[2], fq[3], fb[2], fb[3]);
+                    float fa[4], fq[4], fb[2];
+                    ldsm4(fa, ka + k0); ldsm4(fq, qa + k0); ldsm2(fb, kb + k0);
+                    mma_tf32(kk, fa[0], fa[1], fa[2], fa[3], fb[0], fb[1]);
+                    mma_tf32(qk, fq[0], fq[1], fq[2], fq[3], fb[0], fb[1]);
                 }
 #pragma unroll
-                for (int n = 0; n < 2; ++n)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int i = 16 * mi + g + (e >> 1) * 8, jj = 16 * nj + 8 * n + 2 * t + (e & 1);
-                        const float dec = (jj <= i) ? __expf(Gs[i] - Gs[jj]) : 0.f;
-                        As[i * DC_LDA + jj] = (jj < i) ? bs[i] * dec * kk[n][e] : 0.f;
-                        Ws[i * DC_LDA + jj] = tf32r(dec * qk[n][e]);
-                    }
+                for (int e = 0; e < 4; ++e) {
+                    const int i = 16 * mi + g + (e >> 1) * 8, jj = 8 * ni + 2 * t + (e & 1);
+                    const float dec = (jj <= i) ? __expf(Gs[i] - Gs[jj]) : 0.f;
+                    As[i * DC_LDA + jj] = (jj < i) ? bs[i] * dec * kk[e] : 0.f;
+                    Ws[i * DC_LDA + jj] = tf32r(dec * qk[e]);
+                }
             }
-            // ---- P4: K S0 and Q S0; b = beta (v - exp(G) K S0) in place of v.  Warp w: row tile w & 3,
-            // column tiles 2 (w >> 2) and 2 (w >> 2) + 1.
-            const int mi = kr & 3, nb = (kr >> 2) * 2;
-            float ak[2][4], aq[2][4];
+            // ---- P4: K S0 and Q S0; b = beta (v - exp(G) K S0) in place of v.  Warp w: row block
+            // w % MB, column tiles NTW (w / MB) ...
+            const int mi = kr % MB, nb = (kr / MB) * NTW;
+            float ak[NTW][4], aq[NTW][4];
 #pragma unroll
-            for (int n = 0; n < 2; ++n)
+            for (int n = 0; n < NTW; ++n)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) ak[n][e] = aq[n][e] = 0.f;
             const float* ka = Ks + (16 * mi + a_row) * LDK + a_col;
             const float* qa = Qs + (16 * mi + a_row) * LDK + a_col;
-            const float* sb = S0t + (8 * nb + b_row) * LDK + b_col;
+            const float* sb4 = S0t + (8 * nb + b_row) * LDK + b_col;
+            const float* sb2 = S0t + (8 * nb + (lane & 7)) * LDK + ((lane >> 3) & 1) * 4;
 #pragma unroll 4
             for (int k0 = 0; k0 < DK; k0 += 8) {
                 float fa[4], fq[4], fb[4];
-                ldsm4(fa, ka + k0); ldsm4(fq, qa + k0); ldsm4(fb, sb + k0);
-                mma_tf32(ak[0], fa[0], fa[1], fa[2], fa[3], fb[0], fb[1]);
-                mma_tf32(ak[1], fa[0], fa[1], fa[2], fa[3], fb[2], fb[3]);
-                mma_tf32(aq[0], fq[0], fq[1], fq[2], fq[3], fb[0], fb[1]);
-                mma_tf32(aq[1], fq[0], fq[1], fq[2], fq[3], fb[2], fb[3]);
+                ldsm4(fa, ka + k0); ldsm4(fq, qa + k0);
+                if constexpr (NTW == 2) {
+                    ldsm4(fb, sb4 + k0);
+                } else {
+                    float f2[2];
+                    ldsm2(f2, sb2 + k0);
+                    fb[0] = f2[0]; fb[1] = f2[1]; fb[2] = fb[3] = 0.f;
+                }
+#pragma unroll
+                for (int n = 0; n < NTW; ++n) {
+                    mma_tf32(ak[n], fa[0], fa[1], fa[2], fa[3], fb[2 * n], fb[2 * n + 1]);
+                    mma_tf32(aq[n], fq[0], fq[1], fq[2], fq[3], fb[2 * n], fb[2 * n + 1]);
+                }
             }
 #pragma unroll
-            for (int n = 0; n < 2; ++n)
+            for (int n = 0; n < NTW; ++n)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int i = 16 * mi + g + (e >> 1) * 8, col = 8 * (nb + n) + 2 * t + (e & 1);
@@ -576,24 +590,25 @@ __global__ void __launch_bounds__(DN_THREADS, 1) deltanet_chunk_kernel(const Del
         }
         // ---- P6: Y = exp(G) Q S0 + W U (W is zero above the diagonal), sum of squares per row
         {
-            const int mi = kr & 3, nb = (kr >> 2) * 2;
-            float y[2][4];
+            const int mi = kr % MB, nb = (kr / MB) * NTW;
+            float y[NTW][4];
 #pragma unroll
-            for (int n = 0; n < 2; ++n)
+            for (int n = 0; n < NTW; ++n)
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
                     y[n][e] = QSs[(16 * mi + g + (e >> 1) * 8) * DN_COLS + 8 * (nb + n) + 2 * t + (e & 1)];
-            const float* wa = Ws + (16 * mi + g) * DC_LDA + t;
+            const float* wa = Ws + (16 * mi + a_row) * DC_LDA + a_col;
             for (int k0 = 0; k0 < 16 * (mi + 1); k0 += 8) {
-                const float a0 = wa[k0], a1 = wa[8 * DC_LDA + k0], a2 = wa[k0 + 4], a3 = wa[8 * DC_LDA + k0 + 4];
+                float fa[4];
+                ldsm4(fa, wa + k0);
 #pragma unroll
-                for (int n = 0; n < 2; ++n)
-                    mma_tf32(y[n], a0, a1, a2, a3, tf32r(Us[(k0 + t) * DC_LDU + 8 * (nb + n) + g]),
+                for (int n = 0; n < NTW; ++n)
+                    mma_tf32(y[n], fa[0], fa[1], fa[2], fa[3], tf32r(Us[(k0 + t) * DC_LDU + 8 * (nb + n) + g]),
                              tf32r(Us[(k0 + t + 4) * DC_LDU + 8 * (nb + n) + g]));
             }
             float s_lo = 0.f, s_hi = 0.f;
 #pragma unroll
-            for (int n = 0; n < 2; ++n)
+            for (int n = 0; n < NTW; ++n)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     Ys[(16 * mi + g + (e >> 1) * 8) * DN_COLS + 8 * (nb + n) + 2 * t + (e & 1)] = y[n][e];
@@ -638,16 +653,16 @@ __global__ void __launch_bounds__(DN_THREADS, 1) deltanet_chunk_kernel(const Del
             }
         }
         cluster.sync();
-        // ---- gated RMSNorm across the head's column blocks, output.  The warp's 8 rows x CB peers
-        // are read from distributed shared memory by 8 CB lanes at once, and the gate values are
+        // ---- gated RMSNorm across the head's column blocks, output.  The warp's DC_C/8 rows x CB
+        // peers are read from distributed shared memory by that many lanes at once, and the gate values are
         // loaded before anything is stored.
         {
             float v = 0.f;
-            if (lane < 8 * CB) v = cluster.map_shared_rank(cl_ss, lane % CB)[slot * DC_C + kr + 8 * (lane / CB)];
+            if (lane < (DC_C / 8) * CB) v = cluster.map_shared_rank(cl_ss, lane % CB)[slot * DC_C + kr + 8 * (lane / CB)];
 #pragma unroll
             for (int o = CB / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < DC_C / 8; ++u) {
                 const int i = kr + 8 * u;
                 const float tot = __shfl_sync(0xffffffffu, v, u * CB);
                 if (i < Ce) {

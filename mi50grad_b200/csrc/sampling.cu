@@ -113,3 +113,179 @@ B2_API int b2_argmax(const ArgmaxParams* p, cudaStream_t s) {
     return cudaGetLastError();
 }
 B2_API int b2_sizeof_argmax_params() { return (int)sizeof(ArgmaxParams); }
+
+// ---------------------------------------------------------------------------
+// Temperature / top-k / top-p sampling on the device, one CTA per row (the reference samples in
+// numpy on the host after downloading the logits: src/inference/sampler.py:24-80).  Same pipeline:
+// repetition penalty -> temperature -> top-k -> softmax -> top-p -> multinomial.
+//   1. penalty on the row's past tokens (values are read first, then written, so duplicates in the
+//      list count once);
+//   2. the top-k threshold by bisection over the order-preserving integer image of the logits
+//      (32 counting passes over the row, which stays in L2);
+//   3. candidates above the threshold are gathered into shared memory (at most SAMPLE_MAX_CAND; with
+//      top_k = 0 the SAMPLE_MAX_CAND most likely tokens stand in for the whole vocabulary), sorted
+//      by (value descending, id ascending) with a bitonic network;
+//   4. softmax at the given temperature, inclusive scan, top-p cut, one uniform draw from a counter
+//      hash of (seed, row).
+// Optionally the kept candidates and their probabilities are written out so that tests can compare
+// the distribution itself with the host implementation.
+// ---------------------------------------------------------------------------
+#define SAMPLE_MAX_CAND 1024
+#define SAMPLE_THREADS 1024
+
+struct SampleParams {
+    float* logits;               // [rows][ld] fp32, modified in place by the repetition penalty
+    int ld, n_rows, vocab, vocab_offset;
+    float temperature, top_p, rep_penalty;
+    int top_k;                   // 0: no top-k (capped at SAMPLE_MAX_CAND candidates)
+    const int* past;             // [rows][max_past] token ids (global), may be null
+    const int* n_past;           // [rows]
+    int max_past, pad;
+    unsigned long long seed;
+    int* out_tokens;             // [rows]
+    int* dbg_ids;                // optional [rows][SAMPLE_MAX_CAND]: kept candidates (-1 padded)
+    float* dbg_probs;            // optional [rows][SAMPLE_MAX_CAND]
+};
+
+__device__ __forceinline__ unsigned ord_key(float f) {
+    unsigned b = __float_as_uint(f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float uniform01(unsigned long long seed, unsigned long long ctr) {
+    // splitmix64
+    unsigned long long z = seed + 0x9E3779B97F4A7C15ull * (ctr + 1);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return (float)((z >> 40) + 0.5) * (1.0f / 16777216.0f);
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const SampleParams p) {
+    __shared__ float c_val[SAMPLE_MAX_CAND];
+    __shared__ int c_id[SAMPLE_MAX_CAND];
+    __shared__ float red[32];
+    __shared__ int ired[32];
+    __shared__ int s_cnt, s_keep;
+    __shared__ float s_tot;
+    const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float* row = p.logits + (size_t)r * p.ld;
+    // ---- 1. repetition penalty
+    if (p.past && p.rep_penalty != 1.f) {
+        const int np = min(p.n_past[r], min(p.max_past, SAMPLE_MAX_CAND));
+        const int tok = tid < np ? p.past[(size_t)r * p.max_past + tid] - p.vocab_offset : -1;
+        const bool in = tok >= 0 && tok < p.vocab;
+        const float v = in ? row[tok] : 0.f;
+        __syncthreads();
+        if (in) row[tok] = v > 0.f ? v / p.rep_penalty : v * p.rep_penalty;
+        __syncthreads();
+    }
+    auto block_count = [&](int c) -> int {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+        __syncthreads();
+        if (lane == 0) ired[warp] = c;
+        __syncthreads();
+        int t = 0;
+#pragma unroll
+        for (int w = 0; w < SAMPLE_THREADS / 32; ++w) t += ired[w];
+        return t;
+    };
+    // ---- 2. threshold key: the largest T with count(key >= T) >= K
+    const int K = min(p.top_k > 0 ? p.top_k : SAMPLE_MAX_CAND, min(SAMPLE_MAX_CAND, p.vocab));
+    unsigned T = 0u;
+    for (int bit = 31; bit >= 0; --bit) {
+        const unsigned cand = T | (1u << bit);
+        int c = 0;
+        for (int i = tid; i < p.vocab; i += SAMPLE_THREADS) c += ord_key(row[i]) >= cand;
+        if (block_count(c) >= K) T = cand;
+    }
+    // ---- 3. gather: everything above the threshold, then ties at it until K candidates
+    if (tid == 0) s_cnt = 0;
+    c_val[tid] = -INFINITY; c_id[tid] = 0x7fffffff;
+    __syncthreads();
+    for (int i = tid; i < p.vocab; i += SAMPLE_THREADS) {
+        const float v = row[i];
+        if (ord_key(v) > T) { const int s = atomicAdd(&s_cnt, 1); if (s < SAMPLE_MAX_CAND) { c_val[s] = v; c_id[s] = i; } }
+    }
+    __syncthreads();
+    for (int i0 = 0; i0 < p.vocab; i0 += SAMPLE_THREADS) {        // ties in index order, lowest ids first
+        const int i = i0 + tid;
+        const bool tie = i < p.vocab && ord_key(row[i]) == T;
+        const unsigned m = __ballot_sync(0xffffffffu, tie);
+        __syncthreads();
+        if (lane == 0) ired[warp] = __popc(m);
+        __syncthreads();
+        int before = 0;
+        for (int w = 0; w < warp; ++w) before += ired[w];
+        int total = before;
+        for (int w = warp; w < SAMPLE_THREADS / 32; ++w) total += ired[w];
+        const int base = s_cnt;
+        if (tie) {
+            const int s = base + before + __popc(m & ((1u << lane) - 1u));
+            if (s < K) { c_val[s] = row[i]; c_id[s] = i; }
+        }
+        __syncthreads();
+        if (tid == 0) s_cnt = min(K, base + total);
+        __syncthreads();
+        if (s_cnt >= K) break;
+    }
+    // ---- sort 1024 slots by (value desc, id asc)
+    for (int k = 2; k <= SAMPLE_MAX_CAND; k <<= 1)
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            const int partner = tid ^ j;
+            if (partner > tid) {
+                const bool up = (tid & k) == 0;
+                const float va = c_val[tid], vb = c_val[partner];
+                const int ia = c_id[tid], ib = c_id[partner];
+                const bool a_first = va > vb || (va == vb && ia < ib);      // a belongs before b
+                if (a_first != up) { c_val[tid] = vb; c_val[partner] = va; c_id[tid] = ib; c_id[partner] = ia; }
+            }
+            __syncthreads();
+        }
+    const int n = min(s_cnt, K);
+    // ---- 4. softmax, scan, top-p, draw
+    const float inv_t = 1.f / fmaxf(p.temperature, 1e-6f);
+    const float vmax = c_val[0];
+    float e = tid < n ? __expf((c_val[tid] - vmax) * inv_t) : 0.f;
+    float x = e;                                                   // inclusive scan of e over the block
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const float y = __shfl_up_sync(0xffffffffu, x, o); if (lane >= o) x += y; }
+    if (lane == 31) red[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+        float w = red[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const float y = __shfl_up_sync(0xffffffffu, w, o); if (lane >= o) w += y; }
+        red[lane] = w;
+    }
+    __syncthreads();
+    const float cum = x + (warp ? red[warp - 1] : 0.f);
+    if (tid == SAMPLE_THREADS - 1) s_tot = cum;
+    if (tid == 0) s_keep = n;
+    __syncthreads();
+    const float tot = s_tot;
+    // keep = 1 + number of candidates whose cumulative mass is still below top_p
+    if (p.top_p < 1.f && tid < n && cum / tot >= p.top_p) atomicMin(&s_keep, tid + 1);
+    __syncthreads();
+    const int keep = s_keep;
+    if (tid == keep - 1) s_tot = cum;                              // mass of the kept prefix
+    __syncthreads();
+    const float kept = s_tot;
+    const float u = uniform01(p.seed, (unsigned long long)r) * kept;
+    if (tid == 0) s_cnt = keep - 1;                                // default: last kept (guards rounding)
+    __syncthreads();
+    if (tid < keep && cum >= u) atomicMin(&s_cnt, tid);
+    __syncthreads();
+    if (tid == 0) p.out_tokens[r] = c_id[s_cnt] + p.vocab_offset;
+    if (p.dbg_ids) {
+        p.dbg_ids[(size_t)r * SAMPLE_MAX_CAND + tid] = tid < keep ? c_id[tid] + p.vocab_offset : -1;
+        p.dbg_probs[(size_t)r * SAMPLE_MAX_CAND + tid] = tid < keep ? e / kept : 0.f;
+    }
+}
+
+B2_API int b2_sample(const SampleParams* p, cudaStream_t s) {
+    if (p->n_rows < 1 || p->vocab < 1 || p->temperature <= 0.f || p->top_k < 0 || p->top_p <= 0.f) return cudaErrorInvalidValue;
+    sample_kernel<<<p->n_rows, SAMPLE_THREADS, 0, s>>>(*p);
+    return cudaGetLastError();
+}
+B2_API int b2_sizeof_sample_params() { return (int)sizeof(SampleParams); }

@@ -58,15 +58,32 @@ class TextGenerator:
         past = list(prompt_ids)
         rng = np.random.default_rng(params.seed)
         tok = self.prefill(prompt_ids, seq)
+        # on one GPU the sampler runs on the device (only the sampled id crosses PCIe); under tensor
+        # parallelism the vocabulary slices are gathered and sampled on the host
+        on_device = (not greedy and params.temperature > 0 and getattr(self.engine, "tp_size", 1) == 1
+                     and torch.cuda.is_available())
+        draw = (lambda i: self._sample_device(params, past, i)) if on_device else \
+            (lambda i: sample_token(self._full_logits(), params, past, rng))
         if not greedy:
-            tok = sample_token(self._full_logits(), params, past, rng)
+            tok = draw(0)
         for i in range(max_tokens):
             yield tok
             past.append(tok)
             if tok in stop or i == max_tokens - 1:
                 return
             nxt = self.core.step_host(tok, seq)
-            tok = nxt if greedy else sample_token(self._full_logits(), params, past, rng)
+            tok = nxt if greedy else draw(i + 1)
+
+    def _sample_device(self, params: SamplingParams, past: Sequence[int], step: int) -> int:
+        from ..ops import kernels as K
+        dev = self.core.device
+        window = list(past)[-1024:]
+        pt = torch.tensor([window], dtype=torch.int32, device=dev) if window else torch.zeros(1, 1, dtype=torch.int32, device=dev)
+        npast = torch.tensor([len(window)], dtype=torch.int32, device=dev)
+        seed = (params.seed if params.seed is not None else 0) * 1000003 + step
+        tok = K.sample_top_p(self.core.logits(1), params.temperature, params.top_k, params.top_p,
+                             params.repetition_penalty, pt, npast, seed=seed)
+        return int(tok[0].item())
 
     def _full_logits(self):
         lg = self.engine.compute_logits(None) if hasattr(self.engine, "tp_size") and self.engine.tp_size > 1 \

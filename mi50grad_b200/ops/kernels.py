@@ -254,6 +254,31 @@ def residual_add_(h, delta):
 _tc_status = {}
 
 
+def sample_top_p(logits: torch.Tensor, temperature: float = 1.0, top_k: int = 50, top_p: float = 0.9,
+                 repetition_penalty: float = 1.0, past: Optional[torch.Tensor] = None,
+                 n_past: Optional[torch.Tensor] = None, seed: int = 0, vocab_offset: int = 0, debug: bool = False):
+    """Sample one token per row of fp32 logits [rows, vocab] on the device (temperature > 0).
+    `past`: int32 [rows, max_past] token ids for the repetition penalty with counts `n_past`.
+    The logits are modified in place by the penalty.  Returns int32 [rows] (and, with `debug`,
+    the kept candidate ids and their probabilities, [rows, 1024] each)."""
+    n, V = logits.shape
+    dev = logits.device
+    out = torch.empty(n, dtype=torch.int32, device=dev)
+    p = L.SampleParams()
+    p.logits, p.ld, p.n_rows, p.vocab, p.vocab_offset = logits.data_ptr(), logits.stride(0), n, V, vocab_offset
+    p.temperature, p.top_p, p.rep_penalty, p.top_k = temperature, top_p, repetition_penalty, top_k
+    if past is not None:
+        p.past, p.n_past, p.max_past = past.data_ptr(), n_past.data_ptr(), past.shape[1]
+    p.seed, p.out_tokens = seed & 0xFFFFFFFFFFFFFFFF, out.data_ptr()
+    ids = probs = None
+    if debug:
+        ids = torch.empty(n, L.SAMPLE_MAX_CAND, dtype=torch.int32, device=dev)
+        probs = torch.empty(n, L.SAMPLE_MAX_CAND, dtype=torch.float32, device=dev)
+        p.dbg_ids, p.dbg_probs = ids.data_ptr(), probs.data_ptr()
+    L.check(L.lib().b2_sample(C.byref(p), L.stream()), "sample")
+    return (out, ids, probs) if debug else out
+
+
 def gemm_int4_tc(pk, x: torch.Tensor, out: torch.Tensor, epi: int = L.TC_EPI_STORE_F16,
                  t_tile: Optional[int] = None, n_valid: Optional[int] = None):
     """out[t][n] (epi) = x[t, :K] @ W for a PackedInt4 matrix on the tcgen05 tensor cores.

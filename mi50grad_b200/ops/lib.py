@@ -116,6 +116,16 @@ class LayerDesc(C.Structure):
                 ("off_q", i32), ("off_k", i32), ("off_v", i32), ("off_z", i32), ("off_a", i32), ("off_b", i32)]
 
 
+class SampleParams(C.Structure):
+    _fields_ = [("logits", vp), ("ld", i32), ("n_rows", i32), ("vocab", i32), ("vocab_offset", i32),
+                ("temperature", f32), ("top_p", f32), ("rep_penalty", f32), ("top_k", i32),
+                ("past", vp), ("n_past", vp), ("max_past", i32), ("pad", i32), ("seed", C.c_ulonglong),
+                ("out_tokens", vp), ("dbg_ids", vp), ("dbg_probs", vp)]
+
+
+SAMPLE_MAX_CAND = 1024
+
+
 class SpecStage(C.Structure):
     _fields_ = [("base", vp), ("layer_stride", i64), ("seq_stride", i64), ("off_k", i32), ("off_u", i32),
                 ("off_g", i32), ("off_x", i32)]
@@ -158,7 +168,7 @@ _SIZE_CHECKS = {
     "b2_sizeof_gemv_f16_params": GemvF16Params, "b2_sizeof_attn_params": AttnParams,
     "b2_sizeof_delta_params": DeltaParams, "b2_sizeof_argmax_params": ArgmaxParams,
     "b2_sizeof_linear_desc": LinearDesc, "b2_sizeof_layer_desc": LayerDesc,
-    "b2_sizeof_model_desc": ModelDesc, "b2_sizeof_spec_stage": SpecStage, "b2_sizeof_gemm_tc_params": GemmTcParams, "b2_sizeof_row_meta": RowMeta, "b2_sizeof_seq_state": SeqState,
+    "b2_sizeof_model_desc": ModelDesc, "b2_sizeof_spec_stage": SpecStage, "b2_sizeof_sample_params": SampleParams, "b2_sizeof_gemm_tc_params": GemmTcParams, "b2_sizeof_row_meta": RowMeta, "b2_sizeof_seq_state": SeqState,
 }
 
 _lib: Optional[C.CDLL] = None

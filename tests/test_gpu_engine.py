@@ -127,3 +127,16 @@ def test_fp16_attention_checkpoint_variant():
     ids = _prompt(cfg, 12, seed=8)
     ref, _ = orc.greedy_generate(ids, 6)
     assert eng.generate_tokens(ids, 6) == ref
+
+
+def test_generator_samples_on_device(setup):
+    from mi50grad_b200.generate.generate import TextGenerator
+    from mi50grad_b200.generate.sampler import SamplingParams
+    cfg, mw, eng, orc = setup
+    gen = TextGenerator(eng)
+    prm = SamplingParams(temperature=0.8, top_k=20, top_p=0.9, repetition_penalty=1.2, max_tokens=10, seed=5)
+    a = gen.generate_ids(_prompt(cfg, 9, seed=11), prm)
+    b = gen.generate_ids(_prompt(cfg, 9, seed=11), prm)
+    assert a == b and len(a) == 10 and all(0 <= t < cfg.vocab_size for t in a)
+    c = gen.generate_ids(_prompt(cfg, 9, seed=11), SamplingParams(temperature=0.8, top_k=20, top_p=0.9, max_tokens=10, seed=6))
+    assert c != a or len(set(a)) == 1

@@ -431,3 +431,40 @@ def test_small_elementwise(K):
     hd = h.to(d).clone()
     K.residual_add_(hd, g[:777].to(d))
     assert _rel(hd.cpu(), h + g[:777].float()) < 1e-6
+
+
+@pytest.mark.parametrize("temp,top_k,top_p,pen", [(0.8, 50, 0.9, 1.3), (1.0, 5, 1.0, 1.0), (0.6, 0, 0.95, 1.1)])
+def test_device_sampler_distribution_matches_host(K, temp, top_k, top_p, pen):
+    """The kept candidates and their probabilities equal generate.sampler.filtered_probs; draws fall
+    in the support and follow it."""
+    import numpy as np
+    from mi50grad_b200.generate.sampler import SamplingParams, filtered_probs
+    d = _dev()
+    gen = torch.Generator().manual_seed(33)
+    V, rows = 5003, 3
+    logits = torch.randn(rows, V, generator=gen) * 3.0
+    logits[0, 17] = logits[0, 900] = 9.5                         # a tie among the top candidates
+    past = torch.randint(0, V, (rows, 12), generator=gen).int()
+    past[:, 3] = past[:, 4]                                       # duplicate entries count once
+    n_past = torch.tensor([12, 5, 0], dtype=torch.int32)
+    prm = SamplingParams(temperature=temp, top_k=top_k, top_p=top_p, repetition_penalty=pen)
+    lg = logits.to(d).clone()
+    tok, ids, probs = K.sample_top_p(lg, temp, top_k, top_p, pen, past.to(d), n_past.to(d), seed=7, debug=True)
+    for r in range(rows):
+        ref = filtered_probs(logits[r].numpy().copy(), prm, past[r, :int(n_past[r])].tolist())
+        sup = np.nonzero(ref)[0]
+        got_ids = ids[r].cpu().numpy()
+        got_ids = got_ids[got_ids >= 0]
+        assert sorted(got_ids.tolist()) == sorted(sup.tolist()), r
+        gp = probs[r].cpu().numpy()[:len(got_ids)]
+        assert np.allclose(gp, ref[got_ids], atol=2e-5), r
+        assert int(tok[r]) in set(sup.tolist())
+    # draws follow the distribution: 400 seeds on row 1
+    ref = filtered_probs(logits[1].numpy().copy(), prm, past[1, :5].tolist())
+    counts = {}
+    for s in range(400):
+        t = int(K.sample_top_p(logits[1:2].to(d).clone(), temp, top_k, top_p, pen, past[1:2].to(d), n_past[1:2].to(d),
+                               seed=1000 + s)[0])
+        counts[t] = counts.get(t, 0) + 1
+    top = int(np.argmax(ref))
+    assert abs(counts.get(top, 0) / 400.0 - ref[top]) < 0.1
