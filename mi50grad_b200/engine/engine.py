@@ -285,9 +285,22 @@ class InferenceEngine:
         cfg, sp, dev, R = self.config, self.spec, self.device, self.max_rows
         H = cfg.hidden_size
         lins = [l for dl in self.layers for l in (dl.in_proj, dl.out_proj, dl.gate_up, dl.down)] + [self.lm_head]
-        f32 = lambda *s: torch.zeros(*s, dtype=torch.float32, device=dev)
-        f16 = lambda *s: torch.zeros(*s, dtype=torch.float16, device=dev)
-        i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
+        # work buffers; with debug_guards each one sits between poisoned bands that are checked after
+        # every eager step (utils/guards.py)
+        self._guards = None
+        if self.ecfg.debug_guards:
+            from ..utils.guards import GuardedAllocator
+            self._guards = GuardedAllocator(dev)
+        counter = [0]
+
+        def alloc(shape, dtype):
+            if self._guards is None:
+                return torch.zeros(*shape, dtype=dtype, device=dev)
+            counter[0] += 1
+            return self._guards.zeros(f"#{counter[0]}", shape, dtype)
+        f32 = lambda *s: alloc(s, torch.float32)
+        f16 = lambda *s: alloc(s, torch.float16)
+        i32 = lambda *s: alloc(s, torch.int32)
         self.F_pad = self.layers[0].gate_up.n_pad // 2
         b = self.buf = {}
         b["h"], b["xn"] = f32(R, H), f16(R, H)
@@ -454,6 +467,26 @@ class InferenceEngine:
         self._ensure_driver()
         L.check(self.lib.b2_driver_step(C.c_void_p(self._driver), rows, n_seqs, flags, L.stream()), "driver step")
         self._steps += 1
+        if self._guards is not None:
+            self.check_guards()
+
+    def check_guards(self):
+        """debug_guards: synchronise and verify that no kernel wrote outside a work buffer; the
+        report names buffers by their key in `self.buf`."""
+        if self._guards is None:
+            return
+        torch.cuda.synchronize(self.device)
+        from ..utils.guards import GuardError
+        try:
+            self._guards.check_all()
+        except GuardError as e:
+            names = {t.data_ptr(): k for k, t in self.buf.items() if torch.is_tensor(t)}
+            by_ptr = {raw[self._guards.band:].data_ptr(): n for n, (raw, _) in self._guards._bufs.items()}
+            alias = {n: names.get(p, n) for p, n in by_ptr.items()}
+            msg = str(e)
+            for n, k in alias.items():
+                msg = msg.replace(f"{n}:", f"{k}:")
+            raise GuardError(msg) from None
 
     # ------------------------------------------------------------------ token-level API
     def step_tokens(self, tokens: Sequence[int], seq: int = 0, logits: bool = True,

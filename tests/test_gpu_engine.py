@@ -140,3 +140,20 @@ def test_generator_samples_on_device(setup):
     assert a == b and len(a) == 10 and all(0 <= t < cfg.vocab_size for t in a)
     c = gen.generate_ids(_prompt(cfg, 9, seed=11), SamplingParams(temperature=0.8, top_k=20, top_p=0.9, max_tokens=10, seed=6))
     assert c != a or len(set(a)) == 1
+
+
+def test_debug_guards_see_no_out_of_bounds_write():
+    """Every work buffer between poisoned bands: decode, verify and many-row steps leave them intact."""
+    from mi50grad_b200.config import EngineConfig, tiny_config
+    from mi50grad_b200.engine.engine import InferenceEngine
+    from mi50grad_b200.models.weights import random_model
+    cfg = tiny_config()
+    eng = InferenceEngine(cfg, max_seq_len=128, max_batch=3, engine_config=EngineConfig(debug_guards=True))
+    eng.load_model(random_model(cfg, 0))
+    for i in range(3):
+        eng.prefill_tokens(_prompt(cfg, 20 + i, seed=40 + i), seq=i)     # tensor-core path
+        eng.check_guards()
+    eng.decode_tokens(3, seqs=[0, 1, 2], graph=False)
+    eng.spec_step([[1, 2, 3], [4, 5, 6], [7, 8, 9]], [[-1, 0, 1]] * 3, [0, 1, 2])   # 12 rows: many-row verify
+    eng.spec_step([[1, 2]], [[-1, -1]], [0])
+    assert eng._guards is not None and len(eng._guards.names()) > 30
