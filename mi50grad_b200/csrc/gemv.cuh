@@ -64,6 +64,9 @@ struct GemvInt4Params {
     int ldx, rows, K, KB, NTL, G;
     int off32, gshift;       // group of chunk c = (c + off32) >> gshift   (chunk = 32 k)
     int k_splits, L;         // CTAs along K, k64-blocks per warp
+    int cluster_splitk;      // set by the launcher: the k_splits CTAs of an output tile form a thread-block cluster
+                             // and reduce their partial tiles through distributed shared memory
+    int pad1;
     float* scratch;          // [k_splits][rows][NTL*16] split-K partials
     int* counters;           // [gridDim.x + 1], zero between launches
     LazyNorm ln;

@@ -60,7 +60,7 @@ class GemvEpi(C.Structure):
 class GemvInt4Params(C.Structure):
     _fields_ = [("qfrag", vp), ("szfrag", vp), ("x", vp),
                 ("ldx", i32), ("rows", i32), ("K", i32), ("KB", i32), ("NTL", i32), ("G", i32),
-                ("off32", i32), ("gshift", i32), ("k_splits", i32), ("L", i32),
+                ("off32", i32), ("gshift", i32), ("k_splits", i32), ("L", i32), ("cluster_splitk", i32), ("pad1", i32),
                 ("scratch", vp), ("counters", vp), ("ln", LazyNorm), ("epi", GemvEpi), ("comm", CommCtx)]
 
 
