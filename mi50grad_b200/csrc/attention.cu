@@ -143,8 +143,8 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attn_kernel(const AttnPara
     if (!s_last) return;
     const float* all = p.scratch + (((size_t)r * p.nkv + kvh) * splits_orig) * G * (HD + 2);
     // phase 1: per (split, head) rescale factors, one round trip
-    if (tid < nsplit * G) {
-        int s = tid / G, h = tid % G;
+    for (int idx = tid; idx < nsplit * G; idx += ATT_THREADS) {
+        int s = idx / G, h = idx % G;
         const float* e = &all[(size_t)(s * G + h) * (HD + 2)];
         sm_f[s][h] = ld_cg_f32(e + HD);                 // max of split s
         sm_acc[0][h][s] = ld_cg_f32(e + HD + 1);        // its sum (sm_acc is free by now)

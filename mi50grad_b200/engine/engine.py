@@ -317,7 +317,8 @@ class InferenceEngine:
         b["logits"] = f32(R, b["ld_logits"])
         b["gemv_scratch"] = f32(max(1, max(l.scratch_floats(R) for l in lins)))
         b["gemv_counters"] = i32(8192)
-        self.attn_splits = 16 if self.max_seq_len <= 4096 else 32
+        # cache slices per decode-attention row: long contexts need more CTAs than (rows x KV heads) gives
+        self.attn_splits = 16 if self.max_seq_len <= 1024 else 32
         G = sp.n_q // sp.n_kv
         b["attn_scratch"] = f32(R * sp.n_kv * self.attn_splits * G * (cfg.head_dim + 2))
         b["attn_counters"] = i32(R * sp.n_kv + 8)

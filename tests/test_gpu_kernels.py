@@ -205,7 +205,7 @@ def test_qknorm_rope_cachew(K, hd, rot, style):
         assert torch.equal(vc[s, slot].cpu(), v[r].half())
 
 
-@pytest.mark.parametrize("hd,nq,nkv,splits", [(256, 6, 1, 4), (256, 24, 4, 1), (64, 4, 2, 3), (128, 3, 1, 8)])
+@pytest.mark.parametrize("hd,nq,nkv,splits", [(256, 6, 1, 4), (256, 24, 4, 1), (64, 4, 2, 3), (128, 3, 1, 8), (256, 24, 4, 32)])
 def test_decode_attn(K, hd, nq, nkv, splits):
     from mi50grad_b200.models import oracle as O
     gen = torch.Generator().manual_seed(12)
