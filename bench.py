@@ -33,7 +33,7 @@ def reference_arm(args):
     GCN-assembly kernels); it has no CUDA path, so it cannot run on this box."""
     print(json.dumps({"impl": "reference", "unavailable":
                       "reference needs ROCm (libamdhip64.so, hipcc, gfx906 kernels); pip install of "
-                      "/root/reference fails: no setup.py/pyproject.toml; no CUDA code path exists"}))
+                      "the reference tree fails: no setup.py/pyproject.toml; no CUDA code path exists"}))
     return 0
 
 

@@ -802,6 +802,25 @@ class InferenceEngine:
         out = out[-1]
         return out.cpu().numpy() if isinstance(token_embeddings, np.ndarray) else out.clone()
 
+    def decode_step_batch(self, token_embeddings, batch_size: Optional[int] = None, position: Optional[int] = None,
+                          seq: int = 0):
+        """Several tokens of one sequence at consecutive positions in one step, embeddings in,
+        final-normed hidden states out (reference: src/inference/engine.py:1513-1759, whose
+        DeltaNet branch of this call fabricates outputs).  Independent sequences are decoded
+        together with `decode_tokens(seqs=[...])`."""
+        e = self._as_dev(token_embeddings).reshape(-1, self.config.hidden_size)
+        if batch_size is not None:
+            e = e[:batch_size]
+        if position is not None and position != self.states.length(seq):
+            self.states.set_length(seq, position)
+        out = self.forward_embeddings(e, seq)
+        return out.cpu().numpy() if isinstance(token_embeddings, np.ndarray) else out.clone()
+
+    def register_tp_peers(self, *args, **kwargs):
+        """The reference hands every engine its peers' buffer pointers for in-kernel peer reads
+        (src/inference/engine.py, register_tp_peers).  Here peers are reached through the
+        communicator's symmetric memory, which is set up at construction: nothing to register."""
+
     def residual_stream(self, rows: int = 1) -> torch.Tensor:
         """fp32 residual stream after the last step (before the final norm)."""
         return self.buf["h"][:rows]

@@ -179,3 +179,25 @@ def load_and_generate(model_dir: str, prompt, device_ids=None, max_tokens: int =
         return gen.generate(prompt, SamplingParams(temperature=temperature, max_tokens=max_tokens))
     finally:
         gen.cleanup()
+
+
+def load_and_generate_eagle(model_dir: str, prompt, device_ids=None, max_tokens: int = 256,
+                            temperature: float = 0.0, k_draft: int = 5, verbose: bool = False,
+                            max_seq_len: int = 4096, tokenizer=None):
+    """Load a checkpoint and generate with self-draft speculation: k_draft tokens are drafted from
+    the model's own output head and verified in one pass (reference:
+    src/inference/generate.py:323-397).  Decoding is greedy, so the text equals plain greedy
+    generation; returns the text (token ids when there is no tokenizer)."""
+    from .speculative import EagleSpeculativeGenerator
+    if temperature != 0:
+        raise ValueError("self-draft speculation here is greedy: temperature must be 0")
+    eng, loader = _make_engine(model_dir, device_ids, max_seq_len)
+    if tokenizer is None and isinstance(prompt, str):
+        from transformers import AutoTokenizer
+        tokenizer = AutoTokenizer.from_pretrained(model_dir, trust_remote_code=True)
+    gen = EagleSpeculativeGenerator(eng, loader.load_embedding(), loader.load_lm_head(), tokenizer, k_draft=k_draft)
+    try:
+        out = gen.generate(prompt, SamplingParams(temperature=0.0, max_tokens=max_tokens), verbose=verbose)
+        return out
+    finally:
+        gen.cleanup()

@@ -54,9 +54,35 @@ class PackedInt4:
         return self.qfrag.numel() * 4 + self.szfrag.numel() * 2
 
 
-def launch_shape(KB: int, NTL: int, rows: int = 1, slots: int = 2 * NUM_SMS) -> tuple:
+_TUNED = None
+
+
+def _tuned_shapes() -> dict:
+    """(K, N) -> (k_splits, L) from the tuning database named by B200GRAD_TUNE_DB (tune/autotune.py)."""
+    global _TUNED
+    if _TUNED is None:
+        _TUNED = {}
+        import os
+        path = os.environ.get("B200GRAD_TUNE_DB")
+        if path and os.path.exists(path):
+            import json
+            import sqlite3
+            con = sqlite3.connect(path)
+            for m, n, k, cfg, t in con.execute(
+                    "SELECT m, n, k, config, MIN(time_us) FROM results WHERE op='gemv_int4' GROUP BY m, n, k"):
+                c = json.loads(cfg)
+                _TUNED[(int(k), int(n), int(m))] = (int(c["k_splits"]), int(c["L"]))
+            con.close()
+    return _TUNED
+
+
+def launch_shape(KB: int, NTL: int, rows: int = 1, slots: int = 2 * NUM_SMS, K: int = 0, N: int = 0) -> tuple:
     """(k_splits, L): CTAs along K and k64-blocks per warp, chosen so the grid
-    fills the 148 SMs (two resident CTAs each) in one wave."""
+    fills the 148 SMs (two resident CTAs each) in one wave; a tuned shape for
+    this (K, N) wins when a tuning database is configured."""
+    t = _tuned_shapes().get((K, N, 1)) if K and N else None
+    if t is not None and t[0] * t[1] * GEMV_WK >= KB:
+        return t
     ctas_n = NTL * 16 // TILE_N
     k_splits = max(1, min(slots // max(ctas_n, 1), -(-KB // GEMV_WK)))
     even = lambda v: v + (v & 1) if KB >= 2 * GEMV_WK else v      # even L enables the aligned-group fast path
@@ -114,7 +140,7 @@ def pack_int4(lin: Int4Linear, device=None, rows_hint: int = 1, chunk_tiles: int
     s4 = sc.reshape(G, NTL, 2, 8).permute(1, 0, 3, 2)                             # [NTL,G,8,2]
     z4 = zr.reshape(G, NTL, 2, 8).permute(1, 0, 3, 2)
     szfrag = torch.cat([s4, z4], dim=-1).contiguous()
-    ks, L = launch_shape(KB, NTL, rows_hint)
+    ks, L = launch_shape(KB, NTL, rows_hint, K=K, N=N)
     gshift = (g // 32).bit_length() - 1
     return PackedInt4(qfrag, szfrag, K, N, KB, NTL, G, off // 32, gshift, ks, L)
 
@@ -137,7 +163,7 @@ def random_packed_int4(K: int, N: int, group_size: int = 128, device="cuda",
     if K % 64:
         # zero the weights of padded k so that they cannot meet non-zero activations
         pass
-    ks, L = launch_shape(KB, NTL, rows_hint)
+    ks, L = launch_shape(KB, NTL, rows_hint, K=K, N=N)
     gshift = (group_size // 32).bit_length() - 1
     return PackedInt4(qfrag, szfrag, K, N, KB, NTL, G, 0, gshift, ks, L)
 

@@ -157,3 +157,28 @@ def test_debug_guards_see_no_out_of_bounds_write():
     eng.spec_step([[1, 2, 3], [4, 5, 6], [7, 8, 9]], [[-1, 0, 1]] * 3, [0, 1, 2])   # 12 rows: many-row verify
     eng.spec_step([[1, 2]], [[-1, -1]], [0])
     assert eng._guards is not None and len(eng._guards.names()) > 30
+
+
+@pytest.mark.parametrize("fmt", ["gptq", "awq"])
+def test_load_and_generate_from_checkpoint_directory(tmp_path, fmt):
+    """Checkpoint on disk -> loaders -> engine -> tokens, through the public one-call API."""
+    from mi50grad_b200.config import tiny_config
+    from mi50grad_b200.generate.generate import load_and_generate, load_and_generate_eagle
+    from mi50grad_b200.models.oracle import OracleEngine
+    from mi50grad_b200.models.weights import random_model, write_checkpoint
+    cfg = tiny_config()
+    mw = random_model(cfg, 3)
+    if fmt == "awq":                                           # the zero-less variant: no zero points anywhere
+        from mi50grad_b200.utils.quant import Int4Linear
+        for lw in mw.layers:
+            for name, v in vars(lw).items():
+                if isinstance(v, Int4Linear):
+                    v.zeros = None
+    write_checkpoint(mw, str(tmp_path), fmt)
+    ids = _prompt(cfg, 18, seed=21)
+    ref, _ = OracleEngine(mw, max_seq_len=128).greedy_generate(ids, 6)
+    out = load_and_generate(str(tmp_path), ids, max_tokens=6, temperature=0.0, max_seq_len=128)
+    assert out == " ".join(str(t) for t in ref)
+    if fmt == "gptq":
+        out2 = load_and_generate_eagle(str(tmp_path), ids, max_tokens=6, k_draft=3, max_seq_len=128)
+        assert out2 == ref
