@@ -11,15 +11,20 @@
 //   * the WEIGHT tile is the MMA's A operand (M = 128 outputs), the activations are the B
 //     operand (N = tokens, any multiple of 16 up to 256 per instruction), so a weight tile is
 //     dequantised once and used for every token, and a batch of 16..80 rows costs no padding;
-//   * warps 0-3 stream the packed nibbles (same fragment order the decode GEMV uses), expand
-//     them to fp16 with the 0x6400 trick, apply (q - zero) * scale and store the tile into
-//     shared memory in the K-major 128-byte-swizzled layout tcgen05 reads;
-//   * warp 4 (one lane) brings the activation tile with TMA (cp.async.bulk.tensor, 128-byte
-//     swizzle, no cluster broadcast) and signals an mbarrier;
-//   * warp 5 (one lane) issues tcgen05.mma (cta_group::1, kind::f16) on shared-memory
-//     descriptors and releases stages with tcgen05.commit;
-//   * warps 0-3 then read the accumulators back with tcgen05.ld and run the epilogue
-//     (store, SiLU(gate)*up for the interleaved gate/up matrix, or residual add).
+//   * warps 0-15 (two groups of 8, alternating k-blocks) stream the packed nibbles through a
+//     cp.async ring (same fragment order the decode GEMV uses), expand them to fp16 with the
+//     0x6400 trick, apply (q - zero) * scale and store the tile into shared memory in the
+//     K-major 128-byte-swizzled layout tcgen05 reads;
+//   * warp 16 brings the activation tile with TMA (cp.async.bulk.tensor, 128-byte swizzle, no
+//     cluster broadcast) onto the stage's mbarrier; with dense fp16 weights (the lm_head of many
+//     rows) it loads the weight tile the same way and the dequantising warps idle;
+//   * warp 17 issues tcgen05.mma (cta_group::1, kind::f16) on shared-memory descriptors and
+//     releases stages with tcgen05.commit; both single-lane roles keep their warp converged and
+//     elect a lane only around the tcgen05 / TMA instructions;
+//   * warps 0-15 then read the accumulators back with tcgen05.ld and run the epilogue: store,
+//     SiLU(gate)*up for the interleaved gate/up matrix, residual add, or -- under tensor
+//     parallelism -- stores straight into the staging buffer of the rank that reduces that
+//     slice of the output (reduce-scatter fused into the GEMM).
 // Every mbarrier wait is bounded; on expiry the kernel records a status, skips the rest of
 // its work, releases its tensor memory and returns.
 #include <cuda.h>
