@@ -342,7 +342,9 @@ def main():
     comm = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        import datetime
+        # a short collective timeout: if one rank fails, the others stop within minutes instead of waiting
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=180))
         from mi50grad_b200.parallel.symm import SymmComm
     cfg = qwen35_27b() if args.model == "27b" else tiny_config()
     if args.impl == "torch":
