@@ -8,7 +8,7 @@ cudaProfilerStart/Stop (use `ncu --profile-from-start off`), and with --time
 prints CUDA-event timings taken from a graph replay instead.
 
 cases: gemv_gateup, gemv_down, gemm_int4, gemm_dense, attn_decode, attn_rows,
-       deltanet_step, deltanet_chunk, spec_step, prefill
+       deltanet_step, deltanet_chunk, spec_step, prefill, decode_step
 """
 from __future__ import annotations
 
@@ -163,6 +163,22 @@ def case_prefill(timed: bool):
     print(f"pp512: {e0.elapsed_time(e1):.2f} ms", flush=True)
 
 
+def case_decode_step(timed: bool):
+    """One eager decode step of the 27B model at TP=1 after a 128-token prompt (launch lists only)."""
+    from ..config import qwen35_27b
+    from ..engine.engine import InferenceEngine
+    cfg = qwen35_27b()
+    eng = InferenceEngine(cfg, max_seq_len=1024)
+    eng.init_random(0)
+    eng.prefill_tokens(torch.randint(0, cfg.vocab_size, (128,), generator=torch.Generator().manual_seed(1)).tolist())
+    eng.decode_tokens(4, graph=False)
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStart()
+    eng.decode_tokens(1, graph=False)
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStop()
+
+
 def case_deltanet(which: str, timed: bool):
     from .microbench_deltanet import run_case
     run_case(which, timed, _profiled, _report)
@@ -183,6 +199,8 @@ def main():
         case_spec_step(a.time)
     elif a.case == "prefill":
         case_prefill(a.time)
+    elif a.case == "decode_step":
+        case_decode_step(a.time)
     elif a.case.startswith("deltanet"):
         case_deltanet(a.case, a.time)
     else:
