@@ -182,3 +182,20 @@ def test_load_and_generate_from_checkpoint_directory(tmp_path, fmt):
     if fmt == "gptq":
         out2 = load_and_generate_eagle(str(tmp_path), ids, max_tokens=6, k_draft=3, max_seq_len=128)
         assert out2 == ref
+
+
+def test_prompt_longer_than_one_prefill_launch(setup):
+    """A 130-token prompt in launches of 48 rows: the chunked scan carries state and conv history
+    across launches, attention sees the rows of earlier launches through the cache."""
+    cfg, mw, eng, orc = setup
+    eng._ensure_driver()
+    saved = eng.max_prefill
+    try:
+        eng.max_prefill = 48
+        ids = _prompt(cfg, 130, seed=17)
+        orc.reset()
+        ref, _ = orc.greedy_generate(ids, 5)
+        assert eng.generate_tokens(ids, 5, graph=False) == ref
+        assert eng.states.length(0) == 130 + 4
+    finally:
+        eng.max_prefill = saved
