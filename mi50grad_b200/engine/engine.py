@@ -547,6 +547,47 @@ class InferenceEngine:
         self.states.seqs[seq, 1] = tok[0]
         return int(tok[0].item())
 
+    def score_tokens(self, tokens: Sequence[int], seq: int = 0) -> torch.Tensor:
+        """Teacher-forced log-probabilities: feeds `tokens` to an empty sequence slot and returns
+        log p(tokens[i+1] | tokens[:i+1]) for i = 0 .. n-2 (fp32, device).  Rows go through the
+        many-row path in launches of `step_rows`, with the lm_head applied to every row.  Under
+        tensor parallelism the vocabulary slices are combined with two small all-reduces."""
+        self._ensure_driver()
+        if not self.use_tc_prefill:
+            raise NotImplementedError("scoring uses the tensor-core path (all projections INT4)")
+        tokens = [int(t) for t in tokens]
+        self.states.reset(seq)
+        out = []
+        a, b = self.spec.vocab
+        for i in range(0, len(tokens), self.step_rows):
+            chunk = tokens[i:i + self.step_rows]
+            n = len(chunk)
+            self.buf["p_row_tokens"][:n].copy_(torch.tensor(chunk, dtype=torch.int32).to(self.device))
+            self._prefill_rows(n, seq, L.STEP_EMBED_TOKENS | L.STEP_LM_HEAD)
+            nxt = torch.tensor(tokens[i + 1:i + 1 + n], dtype=torch.long, device=self.device)
+            m = nxt.numel()
+            if m == 0:
+                break
+            lg = self.buf["p_logits"][:m, :self.spec.vocab_local]
+            mx = lg.max(dim=-1).values
+            local = (nxt >= a) & (nxt < b)
+            tgt = torch.where(local, lg.gather(1, (nxt - a).clamp(0, self.spec.vocab_local - 1)[:, None])[:, 0],
+                              torch.zeros_like(mx))
+            if self.tp_size > 1:
+                import torch.distributed as dist
+                dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+                dist.all_reduce(tgt)
+            se = torch.exp(lg - mx[:, None]).sum(dim=-1)
+            if self.tp_size > 1:
+                import torch.distributed as dist
+                dist.all_reduce(se)
+            out.append(tgt - mx - torch.log(se))
+        return torch.cat(out) if out else torch.zeros(0, device=self.device)
+
+    def perplexity(self, tokens: Sequence[int], seq: int = 0) -> float:
+        lp = self.score_tokens(tokens, seq)
+        return float(torch.exp(-lp.mean()).item()) if lp.numel() else float("nan")
+
     def prefill_tokens(self, tokens: Sequence[int], seq: int = 0) -> int:
         """Consume a prompt; returns the first generated token and stores it as
         the sequence's next input."""

@@ -100,6 +100,12 @@ class TPInferenceEngine:
     def step_tokens(self, tokens, seq: int = 0, logits: bool = True, commit: bool = True):
         return self.engine.step_tokens(tokens, seq, logits, commit)
 
+    def score_tokens(self, tokens, seq: int = 0):
+        return self.engine.score_tokens(tokens, seq)
+
+    def perplexity(self, tokens, seq: int = 0) -> float:
+        return self.engine.perplexity(tokens, seq)
+
     def generate_tokens(self, prompt, n_new: int, seq: int = 0, graph=None):
         return self.engine.generate_tokens(prompt, n_new, seq, graph)
 

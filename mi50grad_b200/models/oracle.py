@@ -374,6 +374,17 @@ class OracleEngine:
     def embed(self, token_ids) -> torch.Tensor:
         return self.w.embed[torch.as_tensor(token_ids, dtype=torch.long)].float()
 
+    def score_tokens(self, tokens: Sequence[int], seq: int = 0) -> torch.Tensor:
+        """log p(tokens[i+1] | tokens[:i+1]) for i = 0 .. n-2 (teacher forcing from an empty slot)."""
+        self.reset(seq)
+        x = self.forward(self.embed(list(tokens)), seq)
+        logp = torch.log_softmax(self.compute_logits(self.final_norm(x)), dim=-1)
+        nxt = torch.as_tensor(list(tokens)[1:], dtype=torch.long)
+        return logp[:-1].gather(1, nxt[:, None])[:, 0]
+
+    def perplexity(self, tokens: Sequence[int], seq: int = 0) -> float:
+        return float(torch.exp(-self.score_tokens(tokens, seq).mean()))
+
     def greedy_generate(self, prompt_ids: Sequence[int], n_new: int, seq: int = 0):
         """Returns (tokens, logits per step)."""
         h = self.prefill_step(self.embed(list(prompt_ids)), seq)

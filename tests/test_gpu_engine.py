@@ -199,3 +199,12 @@ def test_prompt_longer_than_one_prefill_launch(setup):
         assert eng.states.length(0) == 130 + 4
     finally:
         eng.max_prefill = saved
+
+
+def test_score_tokens_matches_oracle(setup):
+    cfg, mw, eng, orc = setup
+    ids = _prompt(cfg, 45, seed=23)
+    ref = orc.score_tokens(ids)
+    got = eng.score_tokens(ids).cpu()
+    assert got.shape == ref.shape
+    assert (got - ref).abs().max() < 0.05 and abs(eng.perplexity(ids) / orc.perplexity(ids) - 1) < 0.02

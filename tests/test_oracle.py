@@ -86,3 +86,17 @@ def test_snapshot_restore_roundtrip():
     e.restore(snap)
     b = e.forward(e.embed([4, 5]))
     assert torch.equal(a, b)
+
+
+def test_oracle_score_tokens_matches_stepwise_logits():
+    cfg = tiny_config()
+    mw = random_model(cfg, 0)
+    ids = torch.randint(0, cfg.vocab_size, (12,), generator=torch.Generator().manual_seed(3)).tolist()
+    eng = O.OracleEngine(mw)
+    lp = eng.score_tokens(ids)
+    assert lp.shape == (11,) and bool((lp < 0).all())
+    e2 = O.OracleEngine(mw)
+    h = e2.prefill_step(e2.embed(ids[:5]))
+    ref = torch.log_softmax(e2.compute_logits(h), -1)[ids[5]]
+    assert abs(float(lp[4]) - float(ref)) < 1e-4
+    assert 1.0 < eng.perplexity(ids) < 10 * cfg.vocab_size
