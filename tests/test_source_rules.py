@@ -25,7 +25,7 @@ def test_closed_constructs_absent():
     tail = "Batch" + "Async"                                      # the batched-copy entry points, never spelled out
     banned_calls = [pre + mid + tail for pre in ("cuda", "cu") for mid in ("Memcpy", "Memcpy3D")]
     for name, text in SOURCES.items():
-        for m in re.finditer(r'cp\.async\.bulk[^"]*', text):        # bulk / tensor copies: plain form only, no broadcast qualifier
+        for m in re.finditer(r'cp\.async\.bulk[\w.:]*', text):        # bulk / tensor copies: plain form only, no broadcast qualifier
             assert "cast" not in m.group(0), (name, m.group(0))
         assert "wgmma" not in text, name
         assert "__trap" not in text and "asm(\"trap" not in text, name
