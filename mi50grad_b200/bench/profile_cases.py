@@ -8,7 +8,7 @@ cudaProfilerStart/Stop (use `ncu --profile-from-start off`), and with --time
 prints CUDA-event timings taken from a graph replay instead.
 
 cases: gemv_gateup, gemv_down, gemm_int4, gemm_dense, attn_decode, attn_rows,
-       deltanet_step, deltanet_chunk, spec_step, prefill, decode_step
+       deltanet_step, deltanet_chunk, spec_step, prefill, decode_step, linear_q8
 """
 from __future__ import annotations
 
@@ -179,6 +179,28 @@ def case_decode_step(timed: bool):
     torch.cuda.cudart().cudaProfilerStop()
 
 
+def case_linear_q8(timed: bool):
+    """W8A8 and W4A8 products of the gate_up shape (K 5120, N 34816) at 1, 8 and 64 rows."""
+    dev = torch.device("cuda")
+    Kd, N = 5120, 34816
+    w8 = [torch.randint(-128, 128, (N, Kd), dtype=torch.int8, device=dev) for _ in range(2)]     # 2 x 178 MB > L2
+    sw = torch.rand(N, device=dev) * 0.01
+    w4 = [torch.randint(-2**31, 2**31 - 1, (N, Kd // 8), dtype=torch.int32, device=dev) for _ in range(3)]
+    gs = (torch.rand(Kd // 128, N, device=dev) * 0.01).half()
+    for T in (1, 8, 64):
+        x = torch.randn(T, Kd, device=dev).half()
+        xq, sx = K.act_quant_int8(x)
+        r8 = lambda i=0: K.linear_w8a8(w8[i % 2], sw, xq, sx, out_dtype=torch.float16)
+        r4 = lambda i=0: K.linear_w4a8(w4[i % 3], gs, xq, sx, out_dtype=torch.float16)
+        if timed:
+            _report(f"linear_w8a8 T={T}", time_launches(r8, 2, 8), bytes_=N * Kd, flops=2.0 * T * Kd * N)
+            _report(f"linear_w4a8 T={T}", time_launches(r4, 3, 9), bytes_=N * Kd / 2, flops=2.0 * T * Kd * N)
+            _report(f"act_quant T={T}", time_launches(lambda i=0: K.act_quant_int8(x), 1, 8))
+        else:
+            _profiled(r8, 1)
+            _profiled(r4, 1)
+
+
 def case_deltanet(which: str, timed: bool):
     from .microbench_deltanet import run_case
     run_case(which, timed, _profiled, _report)
@@ -201,6 +223,8 @@ def main():
         case_prefill(a.time)
     elif a.case == "decode_step":
         case_decode_step(a.time)
+    elif a.case == "linear_q8":
+        case_linear_q8(a.time)
     elif a.case.startswith("deltanet"):
         case_deltanet(a.case, a.time)
     else:

@@ -326,3 +326,48 @@ def gemm_tc_check_status(device=None):
         if int(st[0].item()) != 0:
             st.zero_()
             raise RuntimeError("gemm_int4_tc: a bounded mbarrier wait expired")
+
+
+def act_quant_int8(x: torch.Tensor):
+    """Dynamic symmetric int8 quantisation of fp16 activations, one scale per row
+    (reference: src/kernels/activation_quant.hip quantises per tensor; with one row the two agree).
+    x: fp16 [T, K] with contiguous rows.  Returns (xq int8 [T, K], scale fp32 [T])."""
+    assert x.dtype == torch.float16 and x.dim() == 2 and x.stride(1) == 1
+    T, Kd = x.shape
+    xq = torch.empty(T, Kd, dtype=torch.int8, device=x.device)
+    scale = torch.empty(T, dtype=torch.float32, device=x.device)
+    p = L.ActQuantParams()
+    p.x, p.xq, p.scale, p.T, p.K, p.ldx = x.data_ptr(), xq.data_ptr(), scale.data_ptr(), T, Kd, x.stride(0)
+    L.check(L.lib().b2_act_quant(C.byref(p), L.stream()), "act_quant")
+    return xq, scale
+
+
+def _linear_q8(w, xq, x_scale, N, out_dtype, w_scale=None, g_scale=None, group=0):
+    T, Kd = xq.shape
+    assert xq.dtype == torch.int8 and xq.is_contiguous() and x_scale.dtype == torch.float32 and w.is_contiguous()
+    out = torch.empty(T, N, dtype=out_dtype, device=xq.device)
+    p = L.Quant8Params()
+    p.w, p.xq, p.x_scale, p.out = w.data_ptr(), xq.data_ptr(), x_scale.data_ptr(), out.data_ptr()
+    p.w_scale, p.g_scale = _vp(w_scale), _vp(g_scale)
+    p.K, p.N, p.T, p.ldo, p.group = Kd, N, T, N, group
+    p.out_f16, p.w4 = int(out_dtype == torch.float16), int(g_scale is not None)
+    L.check(L.lib().b2_linear_q8(C.byref(p), L.stream()), "linear_q8")
+    return out
+
+
+def linear_w8a8(w_int8: torch.Tensor, w_scale: torch.Tensor, xq: torch.Tensor, x_scale: torch.Tensor,
+                out_dtype=torch.float32) -> torch.Tensor:
+    """out[t][n] = x_scale[t] * w_scale[n] * sum_k xq[t][k] * w_int8[n][k] on the int8 tensor-core path
+    (reference: src/kernels/gemv_w8a8.hip for one row, src/kernels/gemm_w8a8.hip for many).
+    w_int8: [N, K] with K a multiple of 64; any number of rows."""
+    assert w_int8.dtype == torch.int8 and w_scale.dtype == torch.float32
+    return _linear_q8(w_int8, xq, x_scale, w_int8.shape[0], out_dtype, w_scale=w_scale)
+
+
+def linear_w4a8(w_packed: torch.Tensor, g_scale: torch.Tensor, xq: torch.Tensor, x_scale: torch.Tensor,
+                group: int = 128, out_dtype=torch.float32) -> torch.Tensor:
+    """Same product for signed-nibble weights [N, K/8] int32 with per-group fp16 scales [K/group, N]
+    (the layout `utils.quant.int4_to_w4a8` produces; reference: src/kernels/gemv_w4a8.hip).
+    Integer accumulation inside a group, fp32 across groups."""
+    assert w_packed.dtype == torch.int32 and g_scale.dtype == torch.float16 and g_scale.is_contiguous()
+    return _linear_q8(w_packed, xq, x_scale, w_packed.shape[0], out_dtype, g_scale=g_scale, group=group)

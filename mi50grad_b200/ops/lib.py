@@ -126,6 +126,16 @@ class SampleParams(C.Structure):
 SAMPLE_MAX_CAND = 1024
 
 
+class Quant8Params(C.Structure):
+    _fields_ = [("w", vp), ("w_scale", vp), ("g_scale", vp), ("xq", vp), ("x_scale", vp), ("out", vp),
+                ("K", i32), ("N", i32), ("T", i32), ("ldo", i32), ("group", i32), ("out_f16", i32),
+                ("w4", i32), ("pad", i32)]
+
+
+class ActQuantParams(C.Structure):
+    _fields_ = [("x", vp), ("xq", vp), ("scale", vp), ("T", i32), ("K", i32), ("ldx", i32), ("pad", i32)]
+
+
 class SpecStage(C.Structure):
     _fields_ = [("base", vp), ("layer_stride", i64), ("seq_stride", i64), ("off_k", i32), ("off_u", i32),
                 ("off_g", i32), ("off_x", i32)]
@@ -168,7 +178,7 @@ _SIZE_CHECKS = {
     "b2_sizeof_gemv_f16_params": GemvF16Params, "b2_sizeof_attn_params": AttnParams,
     "b2_sizeof_delta_params": DeltaParams, "b2_sizeof_argmax_params": ArgmaxParams,
     "b2_sizeof_linear_desc": LinearDesc, "b2_sizeof_layer_desc": LayerDesc,
-    "b2_sizeof_model_desc": ModelDesc, "b2_sizeof_spec_stage": SpecStage, "b2_sizeof_sample_params": SampleParams, "b2_sizeof_gemm_tc_params": GemmTcParams, "b2_sizeof_row_meta": RowMeta, "b2_sizeof_seq_state": SeqState,
+    "b2_sizeof_model_desc": ModelDesc, "b2_sizeof_spec_stage": SpecStage, "b2_sizeof_sample_params": SampleParams, "b2_sizeof_quant8_params": Quant8Params, "b2_sizeof_act_quant_params": ActQuantParams, "b2_sizeof_gemm_tc_params": GemmTcParams, "b2_sizeof_row_meta": RowMeta, "b2_sizeof_seq_state": SeqState,
 }
 
 _lib: Optional[C.CDLL] = None

@@ -277,8 +277,11 @@ def dequantize_w4a8(w_packed: torch.Tensor, scales: torch.Tensor,
     return q * scales.to(torch.float32).t()[:, gi]
 
 
-def quantize_activation_int8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Dynamic per-tensor symmetric int8 (reference: src/kernels/activation_quant.hip)."""
-    amax = x.abs().amax().clamp_min(1e-12).to(torch.float32)
+def quantize_activation_int8(x: torch.Tensor, per_row: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Dynamic symmetric int8 (reference: src/kernels/activation_quant.hip): one scale for the
+    tensor, or with `per_row` one per row of a 2-D input (what the device kernel computes)."""
+    xf = x.to(torch.float32)
+    amax = (xf.abs().amax(dim=-1, keepdim=True) if per_row else xf.abs().amax()).clamp_min(1e-12)
     scale = amax / 127.0
-    return torch.round(x.to(torch.float32) / scale).clamp(-128, 127).to(torch.int8), scale
+    q = torch.round(xf / scale).clamp(-128, 127).to(torch.int8)
+    return q, (scale.squeeze(-1) if per_row else scale)

@@ -131,3 +131,16 @@ def test_rank_failure_is_detected_and_run_recovers():
         assert toks == ref
     assert "injected" in res[1][1]
     assert "reported failure" in res[0][1] and "injected" in res[0][1]
+
+
+def test_activation_quant_per_row_matches_per_tensor_on_one_row():
+    import torch
+    from mi50grad_b200.utils import quant as Q
+    x = torch.randn(1, 256)
+    q1, s1 = Q.quantize_activation_int8(x)
+    q2, s2 = Q.quantize_activation_int8(x, per_row=True)
+    assert torch.equal(q1, q2) and torch.allclose(s1, s2[0])
+    x = torch.randn(3, 64) * torch.tensor([[1.0], [10.0], [0.1]])
+    q, s = Q.quantize_activation_int8(x, per_row=True)
+    assert s.shape == (3,) and q.abs().amax(dim=1).tolist() == [127, 127, 127]
+    assert torch.allclose(q.float() * s[:, None], x, atol=float(s.max()) * 0.51)
