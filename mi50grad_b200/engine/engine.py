@@ -600,7 +600,12 @@ class InferenceEngine:
             chunk = tokens[i:i + self.max_rows]
             last = i + self.max_rows >= len(tokens)
             out = self.step_tokens(chunk, seq, logits=last)
-        tok = out[len(chunk) - 1]
+        n = len(chunk)
+        tok = out[n - 1]
+        if n > 1:
+            # the prompt's last row becomes row 0, where logits() and compute_logits(None) look
+            self.buf["logits"][0].copy_(self.buf["logits"][n - 1])
+            self.buf["h"][0].copy_(self.buf["h"][n - 1])
         self.states.seqs[seq, 1] = tok
         return int(tok.item())
 
@@ -876,7 +881,9 @@ class InferenceEngine:
             self.buf["xn"][:1].copy_(hdn.half())
             x, ln = self.buf["xn"][:1], None
         else:
-            x, ln = None, K.lazy_norm(self.buf["h"], self.buf["ss"], self.final_norm, self.config.rms_norm_eps)
+            # the norm is taken from the hidden state itself: the running sum of squares that the
+            # step's kernels hand to one another is not kept for rows moved by a prefill
+            x, ln = K.add_rmsnorm(self.buf["h"][:1], self.final_norm, eps=self.config.rms_norm_eps), None
         K.gemv(self.lm_head, x, out=self.buf["logits"][:1], mode=L.EPI_STORE_F32, ln=ln, rows=1,
                scratch=self.buf["gemv_scratch"], counters=self.buf["gemv_counters"])
         out = self.buf["logits"][0, :self.spec.vocab_local]

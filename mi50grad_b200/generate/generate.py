@@ -58,10 +58,11 @@ class TextGenerator:
         past = list(prompt_ids)
         rng = np.random.default_rng(params.seed)
         tok = self.prefill(prompt_ids, seq)
-        # on one GPU the sampler runs on the device (only the sampled id crosses PCIe); under tensor
-        # parallelism the vocabulary slices are gathered and sampled on the host
-        on_device = (not greedy and params.temperature > 0 and getattr(self.engine, "tp_size", 1) == 1
-                     and torch.cuda.is_available())
+        # on a GPU the sampler runs on the device (only the sampled id crosses PCIe); under tensor
+        # parallelism every rank samples the all-gathered logits with the same seed, so all ranks draw
+        # the same token without another exchange.  CPU engines sample on the host.
+        on_device = (not greedy and params.temperature > 0 and torch.cuda.is_available()
+                     and torch.device(getattr(self.core, "device", "cpu")).type == "cuda")
         draw = (lambda i: self._sample_device(params, past, i)) if on_device else \
             (lambda i: sample_token(self._full_logits(), params, past, rng))
         if not greedy:
@@ -81,7 +82,11 @@ class TextGenerator:
         pt = torch.tensor([window], dtype=torch.int32, device=dev) if window else torch.zeros(1, 1, dtype=torch.int32, device=dev)
         npast = torch.tensor([len(window)], dtype=torch.int32, device=dev)
         seed = (params.seed if params.seed is not None else 0) * 1000003 + step
-        tok = K.sample_top_p(self.core.logits(1), params.temperature, params.top_k, params.top_p,
+        if getattr(self.engine, "tp_size", 1) > 1:
+            logits = self.engine.compute_logits(None).reshape(1, -1).contiguous()
+        else:
+            logits = self.core.logits(1)
+        tok = K.sample_top_p(logits, params.temperature, params.top_k, params.top_p,
                              params.repetition_penalty, pt, npast, seed=seed)
         return int(tok[0].item())
 

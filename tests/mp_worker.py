@@ -152,6 +152,41 @@ def scenario_wait_timeout():
     assert float(out[0]) == dist.get_world_size()
 
 
+def scenario_sample():
+    """Non-greedy generation under TP: every rank samples the gathered logits on the device with the
+    same seed; the ranks agree, and the draw equals the device sampler run on the gathered logits."""
+    from mi50grad_b200.config import EngineConfig, tiny_config
+    from mi50grad_b200.engine.tp_engine import TPInferenceEngine
+    from mi50grad_b200.generate.generate import TextGenerator
+    from mi50grad_b200.generate.sampler import SamplingParams
+    from mi50grad_b200.models.weights import random_model
+    from mi50grad_b200.ops import kernels as K
+    world = dist.get_world_size()
+    cfg = tiny_config()
+    eng = TPInferenceEngine(cfg, list(range(world)), max_seq_len=128, engine_config=EngineConfig())
+    eng.load_model(random_model(cfg, 5))
+    gen = TextGenerator(eng)
+    prompt = [3, 14, 15, 92, 65]
+    sp = SamplingParams(temperature=0.8, top_k=40, top_p=0.9, repetition_penalty=1.1, max_tokens=12, seed=11)
+    ids = gen.generate_ids(prompt, sp)
+    assert len(ids) == 12 and all(0 <= t < cfg.vocab_size for t in ids)
+    again = gen.generate_ids(prompt, sp)
+    assert again == ids                                            # same seed, same stream
+    other = gen.generate_ids(prompt, SamplingParams(temperature=0.8, top_k=40, top_p=0.9, max_tokens=12, seed=12))
+    t = torch.tensor(ids + other, device="cuda")
+    all_t = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(all_t, t)
+    assert all(torch.equal(a, t) for a in all_t)                   # every rank drew the same tokens
+    # the gathered logits are the full vocabulary: a near-zero temperature draw is their arg-max
+    full = eng.compute_logits(None)
+    assert full.numel() == cfg.vocab_size
+    cold = K.sample_top_p(full.reshape(1, -1).clone(), 1e-4, 1, 1.0, seed=1)
+    assert int(cold[0]) == int(full.argmax())
+    first = gen.prefill(prompt)
+    assert first == int(eng.compute_logits(None).argmax())         # gathered logits of the last step
+    eng.cleanup()
+
+
 def main():
     scenario = sys.argv[1]
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -166,6 +201,9 @@ def main():
             extra = sys.argv[2]
         elif scenario == "spec":
             scenario_spec()
+            extra = ""
+        elif scenario == "sample":
+            scenario_sample()
             extra = ""
         elif scenario == "wait_timeout":
             scenario_wait_timeout()

@@ -140,6 +140,12 @@ def test_generator_samples_on_device(setup):
     assert a == b and len(a) == 10 and all(0 <= t < cfg.vocab_size for t in a)
     c = gen.generate_ids(_prompt(cfg, 9, seed=11), SamplingParams(temperature=0.8, top_k=20, top_p=0.9, max_tokens=10, seed=6))
     assert c != a or len(set(a)) == 1
+    # after a short prompt (several rows in one step) the logits offered to the sampler are the last row's
+    first = gen.prefill(_prompt(cfg, 5, seed=12))
+    assert int(eng.logits(1)[0].argmax()) == first
+    assert int(eng.compute_logits(None).argmax()) == first
+    first = gen.prefill(_prompt(cfg, 21, seed=13))
+    assert int(eng.compute_logits(None).argmax()) == first
 
 
 def test_debug_guards_see_no_out_of_bounds_write():

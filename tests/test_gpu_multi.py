@@ -45,6 +45,10 @@ def test_speculative_and_many_row_steps_under_tp():
     _run(2, "spec")
 
 
+def test_device_sampling_under_tp():
+    _run(2, "sample")
+
+
 def test_bounded_wait_times_out_cleanly():
     _run(2, "wait_timeout", env_extra={"NCCL_NVLS_ENABLE": "0"})
 
