@@ -107,7 +107,7 @@ class InferenceEngine:
         if not torch.cuda.is_available():
             raise RuntimeError("InferenceEngine needs a CUDA device; use models.oracle.OracleEngine on CPU")
         if quant_format != "w4a16":
-            raise NotImplementedError("the decode path runs w4a16; w8a8/w4a8 are converter-only here")
+            raise NotImplementedError("the whole-model step runs w4a16; w8a8/w4a8 run per layer through engine.ffn_q8.FfnQ8")
         self.config = config
         self.ecfg = (engine_config or EngineConfig()).replace(
             tp_size=tp_size, tp_rank=tp_rank, max_seq_len=max_seq_len, max_batch=max_batch)

@@ -96,3 +96,15 @@ def test_w8a8_and_w4a8_conversions():
     x = torch.randn(256, generator=g)
     xq, sx = Q.quantize_activation_int8(x)
     assert (xq.float() * sx - x).abs().max() <= sx * 0.51
+
+
+def test_ffn_q8_rejects_unknown_format_and_reference_shape():
+    from mi50grad_b200.engine.ffn_q8 import FfnQ8, reference_ffn
+    g = torch.Generator().manual_seed(0)
+    gate, up = Q.random_int4_linear(128, 256, 128, generator=g), Q.random_int4_linear(128, 256, 128, generator=g)
+    down = Q.random_int4_linear(256, 128, 128, generator=g)
+    with pytest.raises(ValueError):
+        FfnQ8(gate, up, down, "w2a2", device="cpu")
+    assert reference_ffn(gate, up, down, torch.randn(3, 128)).shape == (3, 128)
+    ffn = FfnQ8(gate, up, down, "w4a8", device="cpu")             # conversion and storage need no GPU
+    assert ffn.weight_bytes() == 3 * (128 * 256 // 2) + 2 * (1 * 256 * 2) + 2 * 128 * 2
