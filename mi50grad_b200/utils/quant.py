@@ -268,6 +268,32 @@ def int4_to_w4a8(lin: Int4Linear) -> Tuple[torch.Tensor, torch.Tensor]:
     return pack_int4_cols(s.t().contiguous()), lin.scales.clone()
 
 
+def int4_to_w4a8_per_channel(lin: Int4Linear) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The same nibbles with ONE scale per output channel, the mean of its group scales
+    (reference: src/kernels/repack_w4a8.py:119-138, a test aid: it gives up the per-group accuracy).
+    Returns (W_packed[N, K/8] int32, scale[N] fp32)."""
+    packed, scales = int4_to_w4a8(lin)
+    return packed, scales.to(torch.float32).mean(dim=0)
+
+
+def dense_to_w4a8(w: torch.Tensor, group_size: int = 128) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Quantise a real matrix W[N, K] straight to the W4A8 layout: symmetric, scale = max|w| / 7 per
+    (group, channel) (reference: src/kernels/repack_w4a8.py:177-208).  Returns (packed, scales[G, N] fp16)."""
+    N, K = w.shape
+    assert K % group_size == 0 and K % 8 == 0
+    wg = w.to(torch.float32).reshape(N, K // group_size, group_size)
+    scale = (wg.abs().amax(dim=2) / 7.0).clamp_min(1e-8).to(torch.float16)           # [N, G]
+    q = torch.round(wg / scale.to(torch.float32)[:, :, None]).clamp(-8, 7).to(torch.int64).reshape(N, K)
+    return pack_int4_cols(q & 0xF), scale.t().contiguous()
+
+
+def w4a8_roundtrip_error(w: torch.Tensor, group_size: int = 128) -> float:
+    """max |W - dequant(quant(W))| / max|W| (reference: src/kernels/repack_w4a8.py:211-227)."""
+    packed, scales = dense_to_w4a8(w, group_size)
+    back = dequantize_w4a8(packed, scales, group_size)
+    return float((back - w.to(torch.float32)).abs().max() / w.abs().max().clamp_min(1e-12))
+
+
 def dequantize_w4a8(w_packed: torch.Tensor, scales: torch.Tensor,
                     group_size: int = 128) -> torch.Tensor:
     q = unpack_int4_cols(w_packed).to(torch.int64)       # [N, K]

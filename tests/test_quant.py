@@ -108,3 +108,16 @@ def test_ffn_q8_rejects_unknown_format_and_reference_shape():
     assert reference_ffn(gate, up, down, torch.randn(3, 128)).shape == (3, 128)
     ffn = FfnQ8(gate, up, down, "w4a8", device="cpu")             # conversion and storage need no GPU
     assert ffn.weight_bytes() == 3 * (128 * 256 // 2) + 2 * (1 * 256 * 2) + 2 * 128 * 2
+
+
+def test_w4a8_per_channel_and_dense_roundtrip():
+    g = torch.Generator().manual_seed(2)
+    lin = Q.random_int4_linear(256, 64, 128, generator=g)
+    packed, s_ch = Q.int4_to_w4a8_per_channel(lin)
+    p2, s_grp = Q.int4_to_w4a8(lin)
+    assert torch.equal(packed, p2) and s_ch.shape == (64,)
+    assert torch.allclose(s_ch, s_grp.float().mean(dim=0))
+    w = torch.randn(48, 256, generator=g)
+    assert Q.w4a8_roundtrip_error(w, 128) < 0.5 / 7 + 1e-3          # half a step of a 4-bit symmetric grid
+    pk, sc = Q.dense_to_w4a8(w, 128)
+    assert pk.shape == (48, 32) and pk.dtype == torch.int32 and sc.shape == (2, 48) and sc.dtype == torch.float16
