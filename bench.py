@@ -354,7 +354,7 @@ def main():
         return batch_spec(args, cfg, world, rank, local)
     max_seq = max(1024, args.prompt_len + args.steps + args.warmup + 640)
     eng = TPInferenceEngine(cfg, device_ids=list(range(world)), max_seq_len=max_seq,
-                            engine_config=EngineConfig(ar_mode=args.ar_mode))
+                            engine_config=EngineConfig.from_env(ar_mode=args.ar_mode))
     eng.init_random(seed=0, int4_attention=not args.fp16_attention)
     gen = torch.Generator().manual_seed(1234)
     prompt = torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=gen).tolist()

@@ -294,6 +294,7 @@ class EngineConfig:
     use_graph: bool = True
     use_multimem: bool = True
     fused_gemv_ar: bool = True
+    use_chain: bool = False          # consecutive INT4 projections of a decode step run as one persistent launch
     spec_ngram: int = 3
     spec_max_draft: int = 4
     max_step_rows: int = 0           # rows of a batched-decode / verify step (0: 8 per sequence slot)
@@ -319,6 +320,8 @@ class EngineConfig:
             kw["use_graph"] = env["B200GRAD_GRAPH"] not in ("0", "false", "")
         if "B200GRAD_MULTIMEM" in env:
             kw["use_multimem"] = env["B200GRAD_MULTIMEM"] not in ("0", "false", "")
+        if "B200GRAD_CHAIN" in env:
+            kw["use_chain"] = env["B200GRAD_CHAIN"] not in ("0", "false", "")
         if "B200GRAD_DEBUG_GUARDS" in env:
             kw["debug_guards"] = env["B200GRAD_DEBUG_GUARDS"] not in ("0", "false", "")
         return EngineConfig(**kw)

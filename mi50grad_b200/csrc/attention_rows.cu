@@ -271,11 +271,10 @@ template <int HD>
 static int launch_rows(const AttnParams* p, const int* seq_rows, int n_seqs, int splits, cudaStream_t s) {
     const int G = p->nq / p->nkv;
     const size_t smem = ((size_t)G * AR_ROWS + 4 * AR_KV) * (HD + AR_PAD) * sizeof(__half);
-    static size_t configured = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_rows_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static SmemOptIn optin;
+    {
+        cudaError_t e = optin.ensure(attn_rows_kernel<HD>, smem);
         if (e != cudaSuccess) return e;
-        configured = smem;
     }
     const int tiles = (p->n_rows + AR_ROWS - 1) / AR_ROWS + n_seqs;       // upper bound; surplus CTAs exit at once
     dim3 grid(tiles, p->nkv, splits);

@@ -31,6 +31,12 @@ struct CommCtx {
     int* status;                  // local: [0]=code [1]=kernel id [2]=peer [3]=epoch
     long long wait_ns;            // bound of every spin-wait
     long long* trace;             // optional [8] globaltimer stamps of the last exchange (null: off)
+    // Tile-granular exchange of the persistent chain kernel: every 64-column output tile is pushed
+    // to the peers by the warp that completes it and announced with its own flag word.
+    float* tpart[B2_MAX_TP];      // [2][tp][B2_MAX_ROWS][tile_h] fp32 partial tiles by (parity, source rank), per rank
+    uint32_t* tsig[B2_MAX_TP];    // [B2_MAX_TP][tile_flags] arrival words by (source rank, tile), per rank
+    int tile_h;                   // row length the tile area was sized for (0: no tile area)
+    int tile_flags;               // flag words per source rank
 };
 
 // Device-resident description of one token row of a decode/verify step.  A
@@ -167,9 +173,36 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
 
+// The opt-in to more than 48 KB of dynamic shared memory is an attribute of (kernel, device), not of
+// the process: remember it per device, under a lock, so that a process that drives several GPUs or
+// launches from several threads opts in on each device exactly once.
+#include <mutex>
+#define B2_MAX_DEVICES 64
+struct SmemOptIn {
+    size_t have[B2_MAX_DEVICES] = {0};
+    std::mutex mu;
+    template <typename F>
+    cudaError_t ensure(F kernel, size_t bytes) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        if (dev < 0 || dev >= B2_MAX_DEVICES) return cudaErrorInvalidDevice;
+        std::lock_guard<std::mutex> lock(mu);
+        if (bytes > have[dev]) {
+            e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+            if (e != cudaSuccess) return e;
+            have[dev] = bytes;
+        }
+        return cudaSuccess;
+    }
+};
+
 #define B2_KID_GEMV_FIN 1
 #define B2_KID_ALLREDUCE 2
 #define B2_KID_ARGMAX 3
 #define B2_KID_BARRIER 4
 #define B2_KID_TEST 5
 #define B2_KID_GEMM_RS 6
+#define B2_KID_CHAIN_DEP 7      // chain kernel: an op's producers did not finish
+#define B2_KID_CHAIN_TILE 8     // chain kernel: a peer's tile did not arrive
+#define B2_KID_CHAIN_COPY 9     // chain kernel: a weight copy did not land

@@ -704,11 +704,10 @@ static int launch_delta_chunk(const DeltaParams* p, const void* ab, int ld_ab, c
     constexpr int NCH = 2 * DK + DN_COLS;
     size_t smem = (size_t)(2 * DC_C * DC_LDK(DK) + DC_C * DC_LDU + 2 * DC_C * DN_COLS + 2 * DC_C * DC_LDA + DN_COLS * DC_LDK(DK) + NCH * 7 +
                            3 * DC_C + 2 * DC_C) * sizeof(float) + (size_t)(DC_C + 3) * NCH * sizeof(__half);
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(deltanet_chunk_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static SmemOptIn optin;
+    {
+        cudaError_t e = optin.ensure(deltanet_chunk_kernel<DK, DV>, smem);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(CB, p->nv, p->n_seqs);
@@ -779,11 +778,10 @@ B2_API int b2_ab_proj(const void* x, int ldx, const void* wa, const void* wb, in
                       int rows, cudaStream_t s) {
     if (H % 8 || (ldx % 8)) return cudaErrorInvalidValue;
     const size_t smem = (size_t)AB_ROWS * H * 2;
-    static size_t configured = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(ab_proj_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static SmemOptIn optin;
+    {
+        cudaError_t e = optin.ensure(ab_proj_kernel, smem);
         if (e != cudaSuccess) return e;
-        configured = smem;
     }
     ab_proj_kernel<<<dim3((rows + AB_ROWS - 1) / AB_ROWS, (2 * nv + 7) / 8), 256, smem, s>>>((const __half*)x, ldx, (const __half*)wa,
                                                                      (const __half*)wb, nv, H, (__half*)ab, ld_ab, rows);

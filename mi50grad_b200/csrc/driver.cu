@@ -19,6 +19,7 @@
 #include <vector>
 #include "kernels.cuh"
 #include "gemm_tc.cuh"
+#include "chain.cuh"
 
 #define LIN_INT4 0
 #define LIN_F16 1
@@ -90,12 +91,25 @@ struct ModelDesc {
     SpecStage spec; int* spec_acc; int* spec_result;
     float* state0; void* conv0; long long state_layer_stride, conv_layer_stride;
     void* k0; void* v0; long long kv_layer_stride;
+    // persistent projection chain (csrc/chain.cu)
+    float* chain_scratch; int* chain_counters; int chain_cstride; int use_chain;
     CommCtx comm;
+};
+
+// Projections queued for one chain launch, with what the stand-alone GEMV path needs to run them
+// instead when the chain kernel cannot take them (fp16 weights, too many rows for shared memory).
+struct PendingChain {
+    ChainParams cp;
+    const LinearDesc* lin[CH_MAX_OPS];
+    int n = 0;
 };
 
 struct Driver {
     ModelDesc m;
     std::vector<LayerDesc> layers;
+    PendingChain pend;
+    long long chain_launches = 0;         // chain kernels issued by the last eager step
+    long long exchanges = 0;              // cross-GPU exchanges issued by the last eager step
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     int graph_rows = 0, graph_flags = 0;
@@ -153,7 +167,48 @@ static GemvEpi epi_finish(Driver* d, int flags, float* hout) {
     memset(&e, 0, sizeof(e));
     e.mode = EPI_FINISH; e.n_valid = d->m.H; e.fin_flags = flags;
     e.h = d->m.h; e.hout = hout; e.ss_part = d->m.ss; e.extra = d->m.extra; e.eps = d->m.eps;
+    e.ss_np = d->m.np;
     return e;
+}
+
+// ---- projection chains: consecutive INT4 projections of a step are queued and issued as ONE
+// persistent launch (csrc/chain.cu); anything else flushes the queue first.
+static int chain_flush(Driver* d, int rows, cudaStream_t s) {
+    PendingChain& pc = d->pend;
+    if (pc.n == 0) return 0;
+    const int n = pc.n;
+    pc.n = 0;
+    pc.cp.n_ops = n; pc.cp.rows = rows;
+    pc.cp.scratch = d->m.chain_scratch; pc.cp.counters = d->m.chain_counters; pc.cp.cstride = d->m.chain_cstride;
+    pc.cp.comm = d->m.comm; pc.cp.prof = nullptr;
+    if (d->m.use_chain && d->m.chain_scratch && b2_chain_feasible(&pc.cp)) {
+        d->launches++; d->chain_launches++;
+        return b2_chain(&pc.cp, s);
+    }
+    for (int i = 0; i < n; ++i) {
+        const ChainOp& op = pc.cp.op[i];
+        CK(run_linear(d, *pc.lin[i], op.x, op.ldx, op.ln, rows, op.epi, s));
+    }
+    return 0;
+}
+
+static int chain_add(Driver* d, const LinearDesc& L, const void* x, int ldx, const LazyNorm& ln, int rows,
+                     const GemvEpi& epi, cudaStream_t s) {
+    if (epi.mode == EPI_FINISH && d->m.comm.tp > 1 && !(epi.fin_flags & FIN_NO_COMM)) d->exchanges++;
+    if (L.kind != LIN_INT4) {
+        CK(chain_flush(d, rows, s));
+        return run_linear(d, L, x, ldx, ln, rows, epi, s);
+    }
+    PendingChain& pc = d->pend;
+    if (pc.n == CH_MAX_OPS) CK(chain_flush(d, rows, s));
+    ChainOp& op = pc.cp.op[pc.n];
+    memset(&op, 0, sizeof(op));
+    op.qfrag = (const uint4*)L.w; op.szfrag = (const uint2*)L.sz; op.x = (const __half*)x; op.ldx = ldx;
+    op.K = L.K; op.KB = L.KB; op.NWT = L.NTL / 4; op.G = L.G; op.off32 = L.off32; op.gshift = L.gshift;
+    op.ln = ln; op.epi = epi;
+    pc.lin[pc.n] = &L;
+    pc.n++;
+    return 0;
 }
 
 static void fill_delta(const Driver* d, const LayerDesc& L, DeltaParams& q) {
@@ -199,7 +254,7 @@ static int spec_tail(Driver* d, const void* rows, const int* row_tokens, const i
 static int step_impl(Driver* d, int rows, int n_seqs, int flags, cudaStream_t s) {
     const ModelDesc& m = d->m;
     if (rows < 1 || rows > m.max_rows || rows > B2_MAX_ROWS) return cudaErrorInvalidValue;
-    d->launches = 0;
+    d->launches = 0; d->chain_launches = 0; d->exchanges = 0; d->pend.n = 0;
     const bool tp = m.comm.tp > 1;
     CK(b2_prepare_rows(m.rows_tmpl, m.seqs, m.rows, rows, s)); d->launches++;
     if (flags & STEP_EMBED_TOKENS) {
@@ -212,11 +267,14 @@ static int step_impl(Driver* d, int rows, int n_seqs, int flags, cudaStream_t s)
         const LayerDesc& L = d->layers[li];
         const LazyNorm ln_in = lazy(d, m.h, L.attn_norm);
         // ---- token mixer
-        CK(run_linear(d, L.in_proj, nullptr, 0, ln_in, rows, epi_store(m.proj, m.ld_proj, L.in_proj.N, EPI_STORE_F16), s));
+        // the in-projection rides at the end of the previous layer's chain (out_proj, gate/up, down)
+        CK(chain_add(d, L.in_proj, nullptr, 0, ln_in, rows, epi_store(m.proj, m.ld_proj, L.in_proj.N, EPI_STORE_F16), s));
+        CK(chain_flush(d, rows, s));
         if (L.type == 0) {
             CK(b2_qknorm_rope_cachew(m.proj, m.ld_proj, m.rows, L.q_norm, L.k_norm, m.cos_tab, m.sin_tab, L.kcache,
                                      L.vcache, rows, m.nq, m.nkv, m.hd, m.rot, m.max_seq, m.rope_interleaved,
                                      m.eps, s));
+            d->launches++;
             AttnParams a;
             memset(&a, 0, sizeof(a));
             a.q = (const __half*)m.proj; a.ldq = m.ld_proj; a.gate_off = m.nq * m.hd;
@@ -225,7 +283,7 @@ static int step_impl(Driver* d, int rows, int n_seqs, int flags, cudaStream_t s)
             a.max_seq = m.max_seq; a.splits = m.attn_splits; a.scale = 1.0f / sqrtf((float)m.hd);
             a.scratch = m.attn_scratch; a.counters = m.attn_counters;
             CK(b2_decode_attn(&a, m.hd, s));
-            d->launches += 2;
+            d->launches++;
         } else {
             DeltaParams q;
             memset(&q, 0, sizeof(q));
@@ -247,13 +305,14 @@ static int step_impl(Driver* d, int rows, int n_seqs, int flags, cudaStream_t s)
         if (!tp) { f_attn = FIN_NO_COMM; f_ffn = FIN_NO_COMM; }
         else if (m.ar_mode == 1) { f_attn = FIN_NO_COMM; }
         else if (m.ar_mode == 2) { f_attn = FIN_NO_COMM | FIN_NO_H_WRITE | FIN_SAVE_EXTRA; f_ffn = FIN_ADD_EXTRA; h_mid = m.h_tmp; }
-        CK(run_linear(d, L.out_proj, m.attn_out, m.ld_attn, no_lazy(), rows, epi_finish(d, f_attn, h_mid), s));
+        CK(chain_add(d, L.out_proj, m.attn_out, m.ld_attn, no_lazy(), rows, epi_finish(d, f_attn, h_mid), s));
         // ---- FFN
-        CK(run_linear(d, L.gate_up, nullptr, 0, lazy(d, h_mid, L.ffn_norm), rows,
-                      epi_store(m.act, m.F_pad, m.F_pad, EPI_SILU_PAIR), s));
-        CK(run_linear(d, L.down, m.act, m.F_pad, no_lazy(), rows, epi_finish(d, f_ffn, m.h), s));
+        CK(chain_add(d, L.gate_up, nullptr, 0, lazy(d, h_mid, L.ffn_norm), rows,
+                     epi_store(m.act, m.F_pad, m.F_pad, EPI_SILU_PAIR), s));
+        CK(chain_add(d, L.down, m.act, m.F_pad, no_lazy(), rows, epi_finish(d, f_ffn, m.h), s));
         last_norm = L.next_norm;
     }
+    CK(chain_flush(d, rows, s));
     if (flags & STEP_LM_HEAD) {
         CK(run_linear(d, m.lm_head, nullptr, 0, lazy(d, m.h, last_norm), rows,
                       epi_store(m.logits, m.ld_logits, m.vocab_local, EPI_STORE_F32), s));
@@ -466,6 +525,8 @@ B2_API int b2_driver_step(void* h, int rows, int n_seqs, int flags, cudaStream_t
     return run_impl((Driver*)h, rows, n_seqs, flags, s);
 }
 B2_API long long b2_driver_launches(void* h) { return ((Driver*)h)->launches; }
+B2_API long long b2_driver_chain_launches(void* h) { return ((Driver*)h)->chain_launches; }
+B2_API long long b2_driver_exchanges(void* h) { return ((Driver*)h)->exchanges; }
 
 // Capture one step into a graph (the stream must be a non-default stream).
 B2_API int b2_driver_capture(void* h, int rows, int n_seqs, int flags, cudaStream_t s) {

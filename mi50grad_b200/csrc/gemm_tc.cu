@@ -215,14 +215,14 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
         // the group's k-blocks are always in flight, each thread later reads back only what it copied
         uint4* my_ring = wring + tid;
         const uint4* gq = dense ? nullptr : p.qfrag + ((size_t)wt * KB * 4 + ti) * 32 + lane + (size_t)grp * 128;
-        const uint2* gs = dense ? nullptr : p.szfrag + (size_t)tile * p.G * 8 + g;
+        const uint2* gs = dense ? nullptr : p.szfrag + ((size_t)wt * p.G * 4 + ti) * 8 + g;
         int c_issue = p.off32 + 2 * grp;          // 32-k chunk counter of the next k-block to issue
         int slot_issue = 0;
         auto issue = [&]() {
             uint4* dst = my_ring + slot_issue * 1024;
             cp_async16(dst, gq);
-            cp_async8((uint2*)(dst + 512), gs + (size_t)(c_issue >> p.gshift) * 8);
-            cp_async8((uint2*)(dst + 512) + 1, gs + (size_t)((c_issue + 1) >> p.gshift) * 8);
+            cp_async8((uint2*)(dst + 512), gs + (size_t)(c_issue >> p.gshift) * 32);
+            cp_async8((uint2*)(dst + 512) + 1, gs + (size_t)((c_issue + 1) >> p.gshift) * 32);
             gq += 256; c_issue += 4;
             slot_issue = slot_issue == TC_RING - 1 ? 0 : slot_issue + 1;
         };
@@ -457,11 +457,10 @@ static int launch_tc(const GemmTcParams* p, const void* w, int ldw, int n_rows_w
     stages = stages > 8 ? 8 : stages;
     q.stages = stages < 2 ? 2 : (stages & ~1);
     size_t smem = b2_gemm_tc_smem(q.t_tile, q.stages);
-    static size_t configured = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_int4_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static SmemOptIn optin;
+    {
+        cudaError_t e = optin.ensure(gemm_int4_tc_kernel, smem);
         if (e != cudaSuccess) return e;
-        configured = smem;
     }
     dim3 grid(q.NTL * 16 / TC_BM, (q.T + q.t_tile - 1) / q.t_tile);
     gemm_int4_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(q, map, wmap);

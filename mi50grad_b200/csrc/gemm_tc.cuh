@@ -12,7 +12,7 @@
 
 struct GemmTcParams {
     const uint4* qfrag;      // [NTL/4][KB][4][32] packed nibbles
-    const uint2* szfrag;     // [NTL][G][8]
+    const uint2* szfrag;     // [NTL/4][G][4][8]
     int K, KB, NTL, G, off32, gshift;
     int T;                   // token rows in this launch's activation matrix
     int t_tile;              // tokens per CTA (multiple of 16, <= 512)

@@ -167,7 +167,8 @@ __device__ void complete_tile(float* ybuf, const TileCtx& t, const GemvEpi& e, c
                     }
                 }
                 float tot = block_sum(sq, red);
-                if (tid == 0) e.ss_part[(size_t)r * np + blockIdx.x] = tot;
+                const int snp = e.ss_np > 0 ? e.ss_np : np, per = snp / np;
+                if (tid < per) e.ss_part[(size_t)r * snp + blockIdx.x * per + tid] = tid == 0 ? tot : 0.f;
             }
             return;
         }
@@ -265,7 +266,8 @@ __device__ void finish_rows(const GemvEpi& e, const CommCtx& c, int rows, uint32
         }
         float tot = block_sum(ss, red);
         if (tid == 0 && c.trace) c.trace[2] = globaltimer_ns();
-        for (int i = tid; i < np; i += GEMV_THREADS) e.ss_part[(size_t)r * np + i] = (i == 0) ? tot : 0.f;
+        const int snp = e.ss_np > 0 ? e.ss_np : np;
+        for (int i = tid; i < snp; i += GEMV_THREADS) e.ss_part[(size_t)r * snp + i] = (i == 0) ? tot : 0.f;
         if (e.xn == nullptr || (e.fin_flags & FIN_NO_NORM)) continue;
         float inv = rsqrtf(tot / (float)H + e.eps);
 #pragma unroll
@@ -396,12 +398,12 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_int4_kernel(const GemvIn
         for (int r = 0; r < 4; ++r) acc[i][r] = tot[i][r] = 0.f;
     float c1r0 = 0.f, c1r1 = 0.f, c2r0 = 0.f, c2r1 = 0.f;
     int cur = -1;
-    const uint2* szp = p.szfrag + (size_t)wt * GEMV_NT * p.G * 8 + g;
+    const uint2* szp = p.szfrag + (size_t)wt * p.G * (GEMV_NT * 8) + g;
 
     auto flush = [&](int grp) {
 #pragma unroll
         for (int i = 0; i < GEMV_NT; ++i) {
-            uint2 sz = ldg_nc_v2(szp + ((size_t)i * p.G + grp) * 8);
+            uint2 sz = ldg_nc_v2(szp + ((size_t)grp * GEMV_NT + i) * 8);
             float2 s = __half22float2(*(__half2*)&sz.x), z = __half22float2(*(__half2*)&sz.y);
             tot[i][0] += s.x * (acc[i][0] - c1r0 - z.x * c2r0);
             tot[i][1] += s.x * (acc[i][1] - c1r1 - z.x * c2r1);
@@ -599,12 +601,10 @@ B2_API int b2_gemv_int4(const GemvInt4Params* p, cudaStream_t stream) {
     size_t smem = b2_gemv_int4_smem(p->rows, p->L);
     // groups of 128 aligned to even k-blocks let the kernel drop all per-chunk group bookkeeping
     const bool fast = p->gshift == 2 && p->off32 == 0 && (p->L % 2 == 0);
-    static size_t configured[2] = {0, 0};
-    if (smem > configured[fast]) {
-        cudaError_t e = fast ? cudaFuncSetAttribute(gemv_int4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                             : cudaFuncSetAttribute(gemv_int4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static SmemOptIn optin[2];
+    {
+        cudaError_t e = fast ? optin[1].ensure(gemv_int4_kernel<true>, smem) : optin[0].ensure(gemv_int4_kernel<false>, smem);
         if (e != cudaSuccess) return e;
-        configured[fast] = smem;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p->NTL * 16 / GEMV_TILE_N, p->k_splits);
@@ -645,11 +645,10 @@ B2_API int b2_gemv_int4(const GemvInt4Params* p, cudaStream_t stream) {
 template <int MR>
 static int launch_f16(const GemvF16Params* p, cudaStream_t stream) {
     size_t smem = (size_t)MR * p->kslice * 2 + (B2_MAX_ROWS * GEMV_TILE_N + 32 + 4) * 4;
-    static size_t configured = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_f16_kernel<MR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static SmemOptIn optin;
+    {
+        cudaError_t e = optin.ensure(gemv_f16_kernel<MR>, smem);
         if (e != cudaSuccess) return e;
-        configured = smem;
     }
     dim3 grid((p->N + GEMV_TILE_N - 1) / GEMV_TILE_N, p->k_splits);
     gemv_f16_kernel<MR><<<grid, GEMV_THREADS, smem, stream>>>(*p);
@@ -712,7 +711,8 @@ B2_API const char* b2_gemv_int4_noalloc_strerror(int code) {
     switch (code) {
         case B2_NOALLOC_OK: return "ok";
         case B2_NOALLOC_ERR_BAD_ARGUMENT:
-            return "bad argument: null pointer, rows outside 1..8, K not a multiple of 8, or unsupported group size/offset";
+            return "bad argument: null pointer, rows outside 1..8, K not a multiple of 8, unsupported group size/offset, "
+                   "odd ldx, or a misaligned pointer (x: 4 bytes, out: 2, qfrag: 16, szfrag: 8)";
         case B2_NOALLOC_ERR_TOO_LARGE:
             return "problem needs more scratch than the built-in block (B2_NOALLOC_SCRATCH_BYTES); use b2_gemv_int4 with a caller-provided buffer";
         case B2_NOALLOC_ERR_SYMBOL: return "could not obtain the device address of the built-in scratch block";
@@ -724,6 +724,10 @@ B2_API int b2_gemv_int4_noalloc(const void* qfrag, const void* szfrag, const voi
                                 int rows, int K, int N, int group_size, int group_offset, cudaStream_t stream) {
     if (!qfrag || !szfrag || !x || !out || rows < 1 || rows > B2_MAX_ROWS || K < 8 || (K & 7) || N < 1 ||
         ldx < K || ldo < N)
+        return B2_NOALLOC_ERR_BAD_ARGUMENT;
+    // the kernel reads activations as fp16 pairs, weights as 16-byte words and scale/zero entries as
+    // 8-byte words: a pointer or stride that breaks those alignments would fault on the device
+    if ((ldx & 1) || ((uintptr_t)x & 3) || ((uintptr_t)out & 1) || ((uintptr_t)qfrag & 15) || ((uintptr_t)szfrag & 7))
         return B2_NOALLOC_ERR_BAD_ARGUMENT;
     int gshift;
     switch (group_size) {

@@ -54,12 +54,14 @@ struct GemvEpi {
                              // buffer when FIN_NO_H_WRITE)
     float* ss_part;          // [rows][ceil(n_valid/128)] per-tile sums of squares of hout
     float eps;
-    int pad;
+    int ss_np;               // row stride of ss_part (0: one entry per 128-column tile).  When it is a multiple
+                             // of that, a 128-column tile writes its sum into the first of its entries and
+                             // zero into the others, so that producers with 64-column tiles can share the buffer
 };
 
 struct GemvInt4Params {
     const uint4* qfrag;      // [NTL][KB][32] fragment-ordered nibbles
-    const uint2* szfrag;     // [NTL][G][8] (scale_lo, scale_hi, zero_lo, zero_hi) halves
+    const uint2* szfrag;     // [NTL/4][G][4][8] (scale_lo, scale_hi, zero_lo, zero_hi) halves
     const __half* x;         // [rows][ldx]
     int ldx, rows, K, KB, NTL, G;
     int off32, gshift;       // group of chunk c = (c + off32) >> gshift   (chunk = 32 k)

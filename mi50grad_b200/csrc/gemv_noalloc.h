@@ -22,6 +22,12 @@
 //    capture.
 //  * Problem sizes whose split-K partials or counters do not fit in the block are refused
 //    with B2_NOALLOC_ERR_TOO_LARGE; nothing is launched.
+//  * Alignment: x must be 4-byte aligned and ldx even (activations are read as fp16 pairs), out
+//    2-byte aligned, qfrag 16-byte and szfrag 8-byte aligned (tensors from any CUDA allocator
+//    are).  Anything else is refused with B2_NOALLOC_ERR_BAD_ARGUMENT before a launch: a misaligned
+//    device access would otherwise fault and leave the context unusable.
+//  * The first call on each device of a process also opts the kernel in to its shared-memory size
+//    on that device; calls from several threads are serialised for that step.
 //  * All calls share the one block.  The arrival counters are cleared in stream order at
 //    the start of every call; the partial sums are fully overwritten before they are read.
 //    Two calls that overlap on the GPU (different streams, or graphs replayed
@@ -32,7 +38,7 @@
 #define B2_NOALLOC_SCRATCH_BYTES (4u << 20)   // 4 MiB per GPU, of which the first 4 KiB are counters
 
 #define B2_NOALLOC_OK 0
-#define B2_NOALLOC_ERR_BAD_ARGUMENT (-1)      // null pointer, rows outside 1..8, K % 8, unsupported group size
+#define B2_NOALLOC_ERR_BAD_ARGUMENT (-1)      // null pointer, rows outside 1..8, K % 8, unsupported group size, misalignment
 #define B2_NOALLOC_ERR_TOO_LARGE (-2)         // needs more scratch than B2_NOALLOC_SCRATCH_BYTES
 #define B2_NOALLOC_ERR_SYMBOL (-3)            // the scratch block's device address could not be obtained
 // positive return values are cudaError_t codes from the launch

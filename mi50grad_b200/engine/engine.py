@@ -326,8 +326,18 @@ class InferenceEngine:
         b["argmax_scratch"] = f32(R * self.argmax_blocks * 2)
         b["argmax_counters"] = i32(R + 8)
         b["extra"], b["h_tmp"] = f32(R, H), f32(R, H)
-        self.np = -(-H // 128)
+        # sums of squares for the lazy RMSNorm: one entry per 64 columns (the chain kernel's tile); the
+        # 128-column tiles of the stand-alone GEMV fill two entries each
+        self.np = 2 * -(-H // 128)
         b["ss"] = f32(R, self.np)
+        # persistent projection chain: split-K pieces and tile / dependency counters
+        int4 = [l for l in lins if l.packed is not None]
+        self.use_chain = bool(self.ecfg.use_chain and int4)
+        self.lib.b2_chain_scratch_floats.restype = C.c_longlong
+        need = max([int(self.lib.b2_chain_scratch_floats(l.packed.KB, l.packed.NTL // 4, R)) for l in int4] + [1])
+        b["chain_scratch"] = f32(need)
+        self.chain_cstride = max([l.packed.NTL // 4 for l in int4] + [1])
+        b["chain_counters"] = i32(L.CH_MAX_OPS * self.chain_cstride + L.CH_MAX_OPS + 4)
         b["rows"], b["rows_tmpl"] = i32(R, 6), i32(R, 6)
         b["row_tokens"] = torch.full((R,), -1, dtype=torch.int32, device=dev)
         b["seq_rows"] = i32(self.max_batch + 1 + R)
@@ -381,6 +391,8 @@ class InferenceEngine:
             setattr(m, k, b[k].data_ptr())
         m.ld_proj, m.ld_attn, m.ld_logits = b["ld_proj"], b["ld_attn"], b["ld_logits"]
         m.np = self.np
+        m.chain_scratch, m.chain_counters = b["chain_scratch"].data_ptr(), b["chain_counters"].data_ptr()
+        m.chain_cstride, m.use_chain = self.chain_cstride, int(self.use_chain)
         m.seqs = self.states.seqs.data_ptr()
         m.comm = self._comm_ctx()
         m.max_prefill = self.max_prefill

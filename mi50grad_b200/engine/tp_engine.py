@@ -46,7 +46,7 @@ class TPInferenceEngine:
         self.comm = None
         if self.tp_size > 1:
             from ..parallel.symm import SymmComm
-            self.comm = SymmComm(part_floats=min(512, max_seq_len) * config.hidden_size,
+            self.comm = SymmComm(hidden=config.hidden_size, part_floats=min(512, max_seq_len) * config.hidden_size,
                                  use_multimem=self.ecfg.use_multimem, wait_us=self.ecfg.wait_budget_us)
         self.engine = InferenceEngine(config, device_id, max_seq_len, self.tp_size, self.tp_rank, quant_format,
                                       use_int4_attention, self.ecfg, self.comm, max_batch)

@@ -104,6 +104,57 @@ def gemv(lin, x: Optional[torch.Tensor], out: Optional[torch.Tensor] = None, mod
     return ss_part if mode == L.EPI_FINISH else out
 
 
+def chain_op(pk, x: Optional[torch.Tensor] = None, ln: Optional[L.LazyNorm] = None, mode: int = L.EPI_STORE_F16,
+             out: Optional[torch.Tensor] = None, n_valid: Optional[int] = None, fin_flags: int = 0, h=None,
+             hout=None, extra=None, ss_part=None, eps: float = 1e-6) -> L.ChainOp:
+    """One projection of a `chain` launch: `pk` is a PackedInt4, the input either fp16 rows `x` or a
+    lazily normalised stream `ln`, the epilogue as in `gemv` (FINISH tiles are 64 columns wide:
+    `ss_part` is [rows, >= N/64])."""
+    op = L.ChainOp()
+    op.qfrag, op.szfrag = pk.qfrag.data_ptr(), pk.szfrag.data_ptr()
+    op.x, op.ldx = (x.data_ptr(), x.stride(0)) if x is not None else (None, 0)
+    op.K, op.KB, op.NWT, op.G, op.off32, op.gshift = pk.K, pk.KB, pk.NTL // 4, pk.G, pk.off32, pk.gshift
+    if ln is not None:
+        op.ln = ln
+    if mode == L.EPI_SILU_PAIR:
+        nv = n_valid if n_valid is not None else pk.n_pad // 2
+    elif mode == L.EPI_FINISH:
+        nv = pk.N
+    else:
+        nv = n_valid if n_valid is not None else pk.N
+    op.epi = _epi(mode, out, out.stride(0) if out is not None else 0, nv, fin_flags, h, None, None, extra,
+                  hout, ss_part, eps)
+    if ss_part is not None:
+        op.epi.ss_np = ss_part.shape[1]
+    return op
+
+
+def chain_scratch(ops, rows: int, device):
+    """(scratch, counters, cstride) large enough for any chain over the projections in `ops`."""
+    lib = L.lib()
+    need = max(int(lib.b2_chain_scratch_floats(o.KB, o.NWT, rows)) for o in ops)
+    cstride = max(o.NWT for o in ops)
+    return (torch.empty(max(1, need), dtype=torch.float32, device=device),
+            torch.zeros(L.CH_MAX_OPS * cstride + L.CH_MAX_OPS + 4, dtype=torch.int32, device=device), cstride)
+
+
+def chain(ops, rows: int, scratch: torch.Tensor, counters: torch.Tensor, cstride: int,
+          comm: Optional[L.CommCtx] = None, prof: Optional[torch.Tensor] = None):
+    """Run up to four dependent INT4 projections (`chain_op`) as ONE persistent launch
+    (csrc/chain.cu).  Raises if the shapes do not fit the kernel's shared memory."""
+    lib = L.lib()
+    p = L.ChainParams()
+    p.n_ops, p.rows, p.cstride = len(ops), rows, cstride
+    for i, o in enumerate(ops):
+        p.op[i] = o
+    p.scratch, p.counters = scratch.data_ptr(), counters.data_ptr()
+    p.prof = None if prof is None else prof.data_ptr()     # int64 [SMs * 8 warps, 4, 8] per-warp timing record
+    p.comm = comm if comm is not None else L.null_comm()
+    if not lib.b2_chain_feasible(C.byref(p)):
+        raise ValueError("projection chain does not fit one launch (rows x K too large for shared memory, or bad shapes)")
+    L.check(lib.b2_chain(C.byref(p), L.stream()), "chain")
+
+
 def add_rmsnorm(h: torch.Tensor, w: torch.Tensor, delta: Optional[torch.Tensor] = None, eps: float = 1e-6,
                 out32: bool = False):
     """h (fp32 [rows, H]) += delta; returns rmsnorm(h)*w as fp16 (or fp32)."""

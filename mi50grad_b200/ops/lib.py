@@ -18,7 +18,7 @@ from typing import Optional
 
 import torch
 
-LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libb200grad.so"
+LIB_PATH = Path(os.environ.get("B200GRAD_LIB") or Path(__file__).resolve().parent.parent / "lib" / "libb200grad.so")
 MAX_TP = 8
 MAX_ROWS = 8
 
@@ -36,7 +36,8 @@ vp, i32, f32, i64 = C.c_void_p, C.c_int, C.c_float, C.c_longlong
 class CommCtx(C.Structure):
     _fields_ = [("tp", i32), ("rank", i32), ("part_stride", i32), ("pad0", i32),
                 ("part", vp * MAX_TP), ("sig", vp * MAX_TP), ("mc_part", vp),
-                ("epoch", vp), ("status", vp), ("wait_ns", i64), ("trace", vp)]
+                ("epoch", vp), ("status", vp), ("wait_ns", i64), ("trace", vp),
+                ("tpart", vp * MAX_TP), ("tsig", vp * MAX_TP), ("tile_h", i32), ("tile_flags", i32)]
 
 
 class RowMeta(C.Structure):
@@ -54,7 +55,7 @@ class LazyNorm(C.Structure):
 class GemvEpi(C.Structure):
     _fields_ = [("mode", i32), ("ldo", i32), ("n_valid", i32), ("fin_flags", i32), ("out", vp),
                 ("h", vp), ("norm_w", vp), ("xn", vp), ("extra", vp), ("local_part", vp),
-                ("hout", vp), ("ss_part", vp), ("eps", f32), ("pad", i32)]
+                ("hout", vp), ("ss_part", vp), ("eps", f32), ("ss_np", i32)]
 
 
 class GemvInt4Params(C.Structure):
@@ -68,6 +69,21 @@ class GemvF16Params(C.Structure):
     _fields_ = [("w", vp), ("x", vp), ("ldw", i32), ("ldx", i32), ("rows", i32), ("K", i32), ("N", i32),
                 ("k_splits", i32), ("kslice", i32), ("scratch", vp), ("counters", vp),
                 ("ln", LazyNorm), ("epi", GemvEpi), ("comm", CommCtx)]
+
+
+CH_MAX_OPS = 4
+
+
+class ChainOp(C.Structure):
+    _fields_ = [("qfrag", vp), ("szfrag", vp), ("x", vp), ("ldx", i32), ("K", i32), ("KB", i32), ("NWT", i32),
+                ("G", i32), ("off32", i32), ("gshift", i32), ("gsz", i32), ("cBase", i32), ("cRem", i32), ("pmax", i32),
+                ("pad", i32),
+                ("ln", LazyNorm), ("epi", GemvEpi)]
+
+
+class ChainParams(C.Structure):
+    _fields_ = [("n_ops", i32), ("rows", i32), ("stages", i32), ("cstride", i32), ("op", ChainOp * CH_MAX_OPS),
+                ("scratch", vp), ("counters", vp), ("prof", vp), ("comm", CommCtx)]
 
 
 class AttnParams(C.Structure):
@@ -170,6 +186,7 @@ class ModelDesc(C.Structure):
                 ("spec", SpecStage), ("spec_acc", vp), ("spec_result", vp),
                 ("state0", vp), ("conv0", vp), ("state_layer_stride", i64), ("conv_layer_stride", i64),
                 ("k0", vp), ("v0", vp), ("kv_layer_stride", i64),
+                ("chain_scratch", vp), ("chain_counters", vp), ("chain_cstride", i32), ("use_chain", i32),
                 ("comm", CommCtx)]
 
 
@@ -179,6 +196,7 @@ _SIZE_CHECKS = {
     "b2_sizeof_delta_params": DeltaParams, "b2_sizeof_argmax_params": ArgmaxParams,
     "b2_sizeof_linear_desc": LinearDesc, "b2_sizeof_layer_desc": LayerDesc,
     "b2_sizeof_model_desc": ModelDesc, "b2_sizeof_spec_stage": SpecStage, "b2_sizeof_sample_params": SampleParams, "b2_sizeof_quant8_params": Quant8Params, "b2_sizeof_act_quant_params": ActQuantParams, "b2_sizeof_gemm_tc_params": GemmTcParams, "b2_sizeof_row_meta": RowMeta, "b2_sizeof_seq_state": SeqState,
+    "b2_sizeof_chain_params": ChainParams, "b2_sizeof_chain_op": ChainOp,
 }
 
 _lib: Optional[C.CDLL] = None
@@ -206,6 +224,9 @@ def lib() -> C.CDLL:
             raise RuntimeError(f"struct layout mismatch for {st.__name__}: C {f()} vs ctypes {C.sizeof(st)}")
     _lib.b2_driver_create.restype = vp
     _lib.b2_driver_launches.restype = i64
+    _lib.b2_driver_chain_launches.restype = i64
+    _lib.b2_driver_exchanges.restype = i64
+    _lib.b2_chain_scratch_floats.restype = i64
     _lib.b2_gemv_int4_smem.restype = C.c_size_t
     return _lib
 

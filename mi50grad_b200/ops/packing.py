@@ -4,7 +4,9 @@ INT4 projections are re-packed once, at load time, from the checkpoint's
 K-packed `qweight[K/8, N]` into tensor-core fragment order (see csrc/gemv.cu):
 
     qfrag [NTL/4][KB][4 tiles][32 lanes][4 words]   int32   (a warp's 2 KB per k-block is contiguous)
-    szfrag[NTL][G ][8][4]                 fp16  (scale n, scale n+8, zero n, zero n+8)
+    szfrag[NTL/4][G][4 tiles][8][4]                  fp16    (scale n, scale n+8, zero n, zero n+8; the 256 bytes
+                                                              of a 64-column warp tile and one group are contiguous,
+                                                              so they can ride along with the weights in one bulk copy)
 
 where an n-tile is 16 output features, a k-block 64 input features (two chunks
 of 32), and lane (g = lane>>2, t = lane&3) of chunk j owns words 2j and 2j+1.
@@ -31,7 +33,7 @@ GEMV_WK = 4
 @dataclass
 class PackedInt4:
     qfrag: torch.Tensor       # int32 [NTL/4, KB, 4, 32, 4]
-    szfrag: torch.Tensor      # fp16  [NTL, G, 8, 4]
+    szfrag: torch.Tensor      # fp16  [NTL/4, G, 4, 8, 4]
     K: int                    # real input features
     N: int                    # real output features
     KB: int
@@ -105,6 +107,18 @@ def _frag_index(device):
     return (n_in * 32 + k_in).reshape(-1)                                          # [32*2*8]
 
 
+def _sz_by_warp_tile(sz: torch.Tensor) -> torch.Tensor:
+    """[NTL, G, 8, 4] (per 16-column tile) -> [NTL/4, G, 4, 8, 4] (per 64-column warp tile, group-major)."""
+    NTL, G = sz.shape[0], sz.shape[1]
+    return sz.reshape(NTL // 4, 4, G, 8, 4).permute(0, 2, 1, 3, 4).contiguous()
+
+
+def _sz_by_tile(szfrag: torch.Tensor) -> torch.Tensor:
+    """Inverse of _sz_by_warp_tile."""
+    NWT, G = szfrag.shape[0], szfrag.shape[1]
+    return szfrag.permute(0, 2, 1, 3, 4).reshape(NWT * 4, G, 8, 4)
+
+
 def pack_int4(lin: Int4Linear, device=None, rows_hint: int = 1, chunk_tiles: int = 256) -> PackedInt4:
     dev = device or lin.qweight.device
     g, off = lin.group_size, lin.group_offset
@@ -139,7 +153,7 @@ def pack_int4(lin: Int4Linear, device=None, rows_hint: int = 1, chunk_tiles: int
         zr[:lin.num_groups, :N] = lin.zeros.to(dev)
     s4 = sc.reshape(G, NTL, 2, 8).permute(1, 0, 3, 2)                             # [NTL,G,8,2]
     z4 = zr.reshape(G, NTL, 2, 8).permute(1, 0, 3, 2)
-    szfrag = torch.cat([s4, z4], dim=-1).contiguous()
+    szfrag = _sz_by_warp_tile(torch.cat([s4, z4], dim=-1))
     ks, L = launch_shape(KB, NTL, rows_hint, K=K, N=N)
     gshift = (g // 32).bit_length() - 1
     return PackedInt4(qfrag, szfrag, K, N, KB, NTL, G, off // 32, gshift, ks, L)
@@ -159,7 +173,7 @@ def random_packed_int4(K: int, N: int, group_size: int = 128, device="cuda",
     n_idx = (torch.arange(NTL, device=device)[:, None, None] * 16
              + torch.arange(8, device=device)[None, :, None] + 8 * torch.arange(2, device=device)[None, None, :])
     sc = sc * (n_idx < N)[:, None, :, :]
-    szfrag = torch.cat([sc, torch.full_like(sc, zero)], dim=-1).to(torch.float16).contiguous()
+    szfrag = _sz_by_warp_tile(torch.cat([sc, torch.full_like(sc, zero)], dim=-1).to(torch.float16))
     if K % 64:
         # zero the weights of padded k so that they cannot meet non-zero activations
         pass
@@ -183,8 +197,9 @@ def unpack_fragments(pk: PackedInt4) -> Int4Linear:
     q = q[:pk.N, :pk.K].t().contiguous()                                           # [K, N]
     from ..utils.quant import pack_int4_rows
     g = 32 << pk.gshift
-    s = pk.szfrag[..., :2].permute(1, 0, 3, 2).reshape(pk.G, pk.NTL * 16)[:, :pk.N]
-    z = pk.szfrag[..., 2:].permute(1, 0, 3, 2).reshape(pk.G, pk.NTL * 16)[:, :pk.N]
+    sz = _sz_by_tile(pk.szfrag)
+    s = sz[..., :2].permute(1, 0, 3, 2).reshape(pk.G, pk.NTL * 16)[:, :pk.N]
+    z = sz[..., 2:].permute(1, 0, 3, 2).reshape(pk.G, pk.NTL * 16)[:, :pk.N]
     Gr = -(-(pk.K + pk.off32 * 32) // g)
     return Int4Linear(pack_int4_rows(q), s[:Gr].contiguous(), z[:Gr].contiguous(), g, pk.off32 * 32)
 

@@ -16,6 +16,8 @@ Layout of the symmetric block (bytes):
     [0, 2*part_floats*4)            partial-sum staging, double-buffered by epoch parity
     [+0, +gather_floats*4)          two-shot gather area
     [.., +256)                      flag words: [0,8) phase A, [8,16) phase B (uint32, by source rank)
+    [.., +2*tp*8*tile_h*4)          tile staging of the chain kernel: [parity][source rank][row][tile_h] fp32
+    [.., +8*TILE_FLAGS*4)           tile flags: [source rank][tile] uint32
 """
 from __future__ import annotations
 
@@ -58,7 +60,12 @@ class SymmComm(Communicator):
         self.gather_floats = self.part_floats
         self.off_gather = 2 * self.part_floats * 4
         self.off_sig = self.off_gather + self.gather_floats * 4
-        nbytes = self.off_sig + 256
+        # tile-granular exchange of the persistent chain kernel (csrc/chain.cu)
+        self.tile_h = -(-int(hidden) // 64) * 64
+        self.tile_flags = max(128, self.tile_h // 64)
+        self.off_tpart = self.off_sig + 256
+        self.off_tsig = self.off_tpart + 2 * self.tp_size * L.MAX_ROWS * self.tile_h * 4
+        nbytes = self.off_tsig + L.MAX_TP * self.tile_flags * 4
         self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
         self.buf.zero_()
         self.hdl = symm_mem.rendezvous(self.buf, self.group)
@@ -81,6 +88,9 @@ class SymmComm(Communicator):
         for r in range(self.tp_size):
             c.part[r] = self.peer_ptrs[r]
             c.sig[r] = self.peer_ptrs[r] + self.off_sig
+            c.tpart[r] = self.peer_ptrs[r] + self.off_tpart
+            c.tsig[r] = self.peer_ptrs[r] + self.off_tsig
+        c.tile_h, c.tile_flags = self.tile_h, self.tile_flags
         c.mc_part = self.multicast_ptr or None
         c.epoch, c.status, c.wait_ns = self.epoch.data_ptr(), self.status.data_ptr(), self.wait_ns
         c.trace = self.trace.data_ptr() if self.trace_enabled else None

@@ -76,4 +76,10 @@ def test_noalloc_gemv_rejects_oversized_and_bad_arguments():
     assert fn(None, p, p, 64, p, 64, 1, 64, 64, 128, 0, None) == -1
     assert fn(p, p, p, 64, p, 64, 9, 64, 64, 128, 0, None) == -1
     assert fn(p, p, p, 64, p, 64, 1, 64, 64, 100, 0, None) == -1
+    # alignment rules: an odd row stride, or pointers off their natural alignment, are refused before any launch
+    assert fn(p, p, p, 65, p, 64, 2, 64, 64, 128, 0, None) == -1
+    assert fn(p, p, p + 2, 64, p, 64, 1, 64, 64, 128, 0, None) == -1
+    assert fn(p + 8, p, p, 64, p, 64, 1, 64, 64, 128, 0, None) == -1
+    assert fn(p, p + 4, p, 64, p, 64, 1, 64, 64, 128, 0, None) == -1
+    assert b"misaligned" in err(-1)
     torch.cuda.synchronize()
