@@ -294,7 +294,9 @@ class EngineConfig:
     use_graph: bool = True
     use_multimem: bool = True
     fused_gemv_ar: bool = True
-    use_chain: bool = False          # consecutive INT4 projections of a decode step run as one persistent launch
+    # consecutive INT4 projections of a decode step run as one persistent launch (csrc/chain.cu);
+    # B200GRAD_CHAIN=0/1 sets the default
+    use_chain: bool = dataclasses.field(default_factory=lambda: os.environ.get("B200GRAD_CHAIN", "0") not in ("0", "false", ""))
     spec_ngram: int = 3
     spec_max_draft: int = 4
     max_step_rows: int = 0           # rows of a batched-decode / verify step (0: 8 per sequence slot)
@@ -320,8 +322,6 @@ class EngineConfig:
             kw["use_graph"] = env["B200GRAD_GRAPH"] not in ("0", "false", "")
         if "B200GRAD_MULTIMEM" in env:
             kw["use_multimem"] = env["B200GRAD_MULTIMEM"] not in ("0", "false", "")
-        if "B200GRAD_CHAIN" in env:
-            kw["use_chain"] = env["B200GRAD_CHAIN"] not in ("0", "false", "")
         if "B200GRAD_DEBUG_GUARDS" in env:
             kw["debug_guards"] = env["B200GRAD_DEBUG_GUARDS"] not in ("0", "false", "")
         return EngineConfig(**kw)

@@ -32,6 +32,8 @@
 //    copies of the same tile and adds them up in rank order.  All tiles are
 //    exchanged concurrently by the warps that finish them; there is no
 //    grid-wide collection point and no serial tail.
+#include <cstdlib>
+#include <cstring>
 #include "chain.cuh"
 
 // ---------------------------------------------------------------------------
@@ -165,6 +167,222 @@ __device__ __forceinline__ int ch_cursor_blocks(const ChCursor& c, int KB) {
     return n < 2 ? n : 2;
 }
 __device__ __forceinline__ void ch_fence_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
+// {value, tag} pairs: written with one 8-byte store, polled with loads that go to L2 every time.
+__device__ __forceinline__ float2 ch_ld_pair(const float2* p) {
+    float2 v;
+    asm volatile("ld.volatile.global.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 ch_ld_pair2(const float2* p) {     // two adjacent pairs (16-byte aligned)
+    float4 v;
+    asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint2 ch_ld_upair(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void ch_st_pair(float2* p, float v, uint32_t tag) {
+    asm volatile("st.volatile.global.v2.f32 [%0], {%1,%2};" :: "l"(p), "f"(v), "f"(__uint_as_float(tag)) : "memory");
+}
+// Poll one pair until its tag matches (bounded).  Returns false on expiry.
+__device__ __forceinline__ bool ch_wait_pair(const float2* p, uint32_t tag, long long budget_ns, float& out) {
+    float2 v = ch_ld_pair(p);
+    if (__float_as_uint(v.y) != tag) {
+        const long long t0 = globaltimer_ns();
+        for (;;) {
+#pragma unroll 1
+            for (int i = 0; i < 32 && __float_as_uint(v.y) != tag; ++i) v = ch_ld_pair(p);
+            if (__float_as_uint(v.y) == tag || globaltimer_ns() - t0 > budget_ns) break;
+        }
+    }
+    out = v.x;
+    return __float_as_uint(v.y) == tag;
+}
+
+// ---------------------------------------------------------------------------
+// Activation staging.  Item (chunk cl, quarter tt) is the B fragment of four lanes: fp16 pairs at
+// k = 32 cl + 2 tt + {0, 8, 16, 24}; the pairs at +16 and +24 are pre-scaled by 1/16 (they meet the
+// high nibbles).  LAZY: x = h * rsqrt(sum(ss)/H + eps) * w formed here.  IT items per thread are
+// loaded (or polled, when the input is a tagged hand-off) before any is used.
+// ---------------------------------------------------------------------------
+template <bool FAST, bool LAZY, int IT>
+__device__ __forceinline__ bool ch_stage(const ChainParams& p, const ChainOp& op, int M, int Mpad, uint4* xf, float2* cs,
+                                         uint32_t itag, long long wait_ns, int c0, int ncl) {
+    // chunks c0 .. c0 + ncl - 1 (modulo the projection's chunk count) are staged at positions 0 .. ncl - 1
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int items = ncl * 4, nCh = 2 * op.KB;
+    auto k_of = [&](int item) -> int {
+        int cl = c0 + (item >> 2);
+        cl = cl >= nCh ? cl - nCh : cl;
+        return cl * 32 + 2 * (item & 3);
+    };
+    bool ok = true;
+    for (int m = 0; m < M; ++m) {
+        const __half* xr = LAZY ? nullptr : op.x + (size_t)m * op.ldx;
+        const float* hr = LAZY ? op.ln.h + (size_t)m * op.ln.H : nullptr;
+        float inv = 0.f;
+        for (int base0 = 0; base0 < items; base0 += CH_THREADS * IT) {
+            float2 hv[LAZY ? IT : 1][4];
+            uint32_t xv16[LAZY ? 1 : IT][4];
+            const bool tagged = LAZY ? op.th_in != nullptr : op.tact_in != nullptr;
+            unsigned long long need = 0;
+#pragma unroll
+            for (int it = 0; it < IT; ++it) {
+                const int item = base0 + it * CH_THREADS + tid;
+                const int k0 = k_of(item);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int k = k0 + 8 * q;
+                    const bool in = item < items && k < op.K;
+                    if (LAZY) hv[it][q] = make_float2(0.f, 0.f); else xv16[it][q] = 0u;
+                    if (!in) continue;
+                    if (tagged) need |= 1ull << (it * 4 + q);
+                    else if (LAZY) hv[it][q] = __ldcg((const float2*)(hr + k));
+                    else xv16[it][q] = __ldcg((const uint32_t*)(xr + k));
+                }
+            }
+            // tagged input: poll until every pair carries this launch's tag of the producing projection
+            long long t0 = 0;
+            while (need) {
+#pragma unroll
+                for (int it = 0; it < IT; ++it) {
+                    const int item = base0 + it * CH_THREADS + tid;
+                    const int k0 = k_of(item);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        if (need & (1ull << (it * 4 + q))) {
+                            const int k = k0 + 8 * q;
+                            if (LAZY) {
+                                const float4 v = ch_ld_pair2(op.th_in + (size_t)m * p.tag_h_cols + k);
+                                if (__float_as_uint(v.y) == itag && __float_as_uint(v.w) == itag) {
+                                    hv[it][q] = make_float2(v.x, v.z);
+                                    need &= ~(1ull << (it * 4 + q));
+                                }
+                            } else {
+                                const uint2 v = ch_ld_upair(op.tact_in + (size_t)m * p.tag_act_cols + k / 2);
+                                if (v.y == itag) { xv16[it][q] = v.x; need &= ~(1ull << (it * 4 + q)); }
+                            }
+                        }
+                    }
+                }
+                if (need) {
+                    if (t0 == 0) t0 = globaltimer_ns();
+                    else if (globaltimer_ns() - t0 > wait_ns) { ok = false; break; }
+                }
+            }
+            if (LAZY && base0 == 0) {
+                // every warp forms 1/rms of the row itself: no block-wide hand-off in front of the loads
+                float s = 0.f;
+                for (int i0 = 0; i0 < op.ln.np; i0 += 128) {
+                    float v[4];
+                    float2 pv[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int i = i0 + u * 32 + lane;
+                        v[u] = 0.f;
+                        pv[u] = make_float2(0.f, __uint_as_float(itag));
+                        if (i < op.ln.np) {
+                            if (op.tss_in) pv[u] = ch_ld_pair(op.tss_in + (size_t)m * p.tag_ss_cols + i);
+                            else v[u] = __ldcg(op.ln.ss + (size_t)m * op.ln.np + i);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int i = i0 + u * 32 + lane;
+                        if (op.tss_in && i < op.ln.np) {
+                            if (__float_as_uint(pv[u].y) == itag) v[u] = pv[u].x;
+                            else if (!ch_wait_pair(op.tss_in + (size_t)m * p.tag_ss_cols + i, itag, wait_ns, v[u])) ok = false;
+                        }
+                        s += v[u];
+                    }
+                }
+                s = warp_sum(s);
+                inv = rsqrtf(s / (float)op.ln.H + op.ln.eps);
+            }
+#pragma unroll
+            for (int it = 0; it < IT; ++it) {
+                const int item = base0 + it * CH_THREADS + tid;
+                const bool valid = item < items;
+                const int tt = item & 3, cl = item >> 2;      // cl: position in the staged window
+                const int k0 = k_of(item);
+                __half2 v[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    if (LAZY) {
+                        const int k = k0 + 8 * q;
+                        float2 wv = make_float2(0.f, 0.f);
+                        if (valid && k < op.K) wv = __half22float2(*(const __half2*)(op.ln.w + k));
+                        v[q] = __floats2half2_rn(hv[it][q].x * inv * wv.x, hv[it][q].y * inv * wv.y);
+                    } else {
+                        v[q] = *(__half2*)&xv16[it][q];
+                    }
+                }
+                const __half2 sixteenth = __float2half2_rn(0.0625f);
+                v[2] = __hmul2(v[2], sixteenth);
+                v[3] = __hmul2(v[3], sixteenth);
+                float2 fa0 = __half22float2(v[0]), fa1 = __half22float2(v[1]);
+                float2 fb0 = __half22float2(v[2]), fb1 = __half22float2(v[3]);
+                float sa = fa0.x + fa0.y + fa1.x + fa1.y;
+                float sb = fb0.x + fb0.y + fb1.x + fb1.y;
+                sa += __shfl_xor_sync(0xffffffffu, sa, 1);
+                sb += __shfl_xor_sync(0xffffffffu, sb, 1);
+                sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+                sb += __shfl_xor_sync(0xffffffffu, sb, 2);
+                if (FAST) {
+                    // a group is four consecutive chunks = sixteen consecutive lanes
+                    sa += __shfl_xor_sync(0xffffffffu, sa, 4);
+                    sb += __shfl_xor_sync(0xffffffffu, sb, 4);
+                    sa += __shfl_xor_sync(0xffffffffu, sa, 8);
+                    sb += __shfl_xor_sync(0xffffffffu, sb, 8);
+                }
+                if (valid) {
+                    uint4 w4;
+                    w4.x = *(uint32_t*)&v[0]; w4.y = *(uint32_t*)&v[1]; w4.z = *(uint32_t*)&v[2]; w4.w = *(uint32_t*)&v[3];
+                    xf[((size_t)cl * M + m) * 4 + tt] = w4;
+                    if (FAST) {
+                        if ((item & 15) == 0) cs[(size_t)(cl >> 2) * Mpad + m] = make_float2(1024.f * (sa + sb), sa + 16.f * sb);
+                    } else if (tt == 0) {
+                        cs[(size_t)cl * Mpad + m] = make_float2(1024.f * (sa + sb), sa + 16.f * sb);
+                    }
+                }
+            }
+        }
+    }
+    return ok;
+}
+
+// Poll N pairs at once: all loads are issued before any tag is checked.
+template <int N>
+__device__ __forceinline__ bool ch_wait_pairs(const float2* const (&ptr)[N], const bool (&want)[N], uint32_t tag,
+                                              long long budget_ns, float (&out)[N]) {
+    float2 v[N];
+    unsigned need = 0;
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        v[i] = make_float2(0.f, 0.f);
+        if (want[i]) v[i] = ch_ld_pair(ptr[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        if (want[i] && __float_as_uint(v[i].y) != tag) need |= 1u << i;
+        out[i] = v[i].x;
+    }
+    if (!need) return true;
+    const long long t0 = globaltimer_ns();
+    for (;;) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+            if (need & (1u << i)) {
+                const float2 w = ch_ld_pair(ptr[i]);
+                if (__float_as_uint(w.y) == tag) { out[i] = w.x; need &= ~(1u << i); }
+            }
+        }
+        if (!need) return true;
+        if (globaltimer_ns() - t0 > budget_ns) return false;
+    }
+}
 
 // ---------------------------------------------------------------------------
 // Epilogue of one finished 64-column tile.  Lane l holds, for every token row m,
@@ -173,12 +391,14 @@ __device__ __forceinline__ void ch_fence_gpu() { asm volatile("fence.acq_rel.gpu
 // Returns false if a peer's tile did not arrive in time.
 // ---------------------------------------------------------------------------
 template <int MT>
-__device__ __forceinline__ bool ch_epilogue(const ChainParams& p, const ChainOp& op, int wt, int lane,
-                                            float (&ya)[MT], float (&yb)[MT], uint32_t epoch, long long wait_ns) {
+__device__ __forceinline__ bool ch_epilogue(const ChainParams& p, const ChainOp& op, int o, int wt, int lane,
+                                            float (&ya)[MT], float (&yb)[MT], uint32_t epoch, uint32_t gen4,
+                                            long long wait_ns) {
     const GemvEpi& e = op.epi;
-    const int M = p.rows;
+    const int M = MT == 1 ? 1 : p.rows;
     const int n0 = wt * 64;
     const int ca = n0 + 16 * (lane >> 3) + (lane & 7), cb = ca + 8;
+    const uint32_t otag = gen4 + (uint32_t)o + 1u;                     // tag of this op's outputs in this launch
     bool ok = true;
     if (e.mode == EPI_STORE_F16) {
         __half* out = (__half*)e.out;
@@ -202,8 +422,23 @@ __device__ __forceinline__ bool ch_epilogue(const ChainParams& p, const ChainOp&
         __half* out = (__half*)e.out;
         const int o = n0 / 2 + 8 * (lane >> 3) + (lane & 7);
 #pragma unroll
-        for (int m = 0; m < MT; ++m)
-            if (m < M && o < e.n_valid) out[(size_t)m * e.ldo + o] = __float2half(silu_f(ya[m]) * yb[m]);
+        for (int m = 0; m < MT; ++m) {
+            if (m < M) {
+                const __half v = __float2half(silu_f(ya[m]) * yb[m]);
+                if (o < e.n_valid) out[(size_t)m * e.ldo + o] = v;
+                if (op.tact_out) {
+                    // the consumer reads fp16 pairs: even lanes store {pair, tag} for themselves and their neighbour
+                    const unsigned short mine = __half_as_ushort(v);
+                    const unsigned short next = (unsigned short)__shfl_down_sync(0xffffffffu, (unsigned)mine, 1);
+                    if (!(lane & 1) && o < e.n_valid) {
+                        uint2 pr;
+                        pr.x = (uint32_t)mine | ((uint32_t)next << 16); pr.y = otag;
+                        asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};"
+                                     :: "l"(op.tact_out + (size_t)m * p.tag_act_cols + o / 2), "r"(pr.x), "r"(pr.y) : "memory");
+                    }
+                }
+            }
+        }
     } else {   // EPI_FINISH
         const CommCtx& c = p.comm;
         const bool va = ca < e.n_valid, vb = cb < e.n_valid;
@@ -214,8 +449,17 @@ __device__ __forceinline__ bool ch_epilogue(const ChainParams& p, const ChainOp&
         for (int m = 0; m < MT; ++m) {
             hra[m] = hrb[m] = 0.f;
             if (m < M) {
-                if (va) hra[m] = __ldcg(e.h + (size_t)m * e.n_valid + ca);
-                if (vb) hrb[m] = __ldcg(e.h + (size_t)m * e.n_valid + cb);
+                if (op.th_res) {
+                    const uint32_t rtag = gen4 + (uint32_t)op.res_op + 1u;
+                    const float2* const ptr[2] = {op.th_res + (size_t)m * p.tag_h_cols + ca, op.th_res + (size_t)m * p.tag_h_cols + cb};
+                    const bool want[2] = {va, vb};
+                    float got[2];
+                    ok = ch_wait_pairs<2>(ptr, want, rtag, wait_ns, got) && ok;
+                    hra[m] = got[0]; hrb[m] = got[1];
+                } else {
+                    if (va) hra[m] = __ldcg(e.h + (size_t)m * e.n_valid + ca);
+                    if (vb) hrb[m] = __ldcg(e.h + (size_t)m * e.n_valid + cb);
+                }
             }
         }
 #pragma unroll
@@ -232,53 +476,58 @@ __device__ __forceinline__ bool ch_epilogue(const ChainParams& p, const ChainOp&
                 }
             }
         }
+        if (e.fin_flags & FIN_SAVE_EXTRA) __threadfence();   // `extra` is read by a later op of this launch: before any tag
         if (!local) {
-            // ---- exchange this tile: store it into every peer's staging area, raise the tile's flag
-            // there, wait for the peers' copies, add in rank order (every rank forms the same sum)
+            // ---- exchange this tile: every value goes to every peer as a {value, epoch} pair in one 8-byte
+            // store over NVLink; the peers' copies are polled in place and added in rank order (every rank
+            // forms the same sum).  No flag, no fence: the data is its own arrival signal.
             const size_t par = (size_t)(epoch & 1) * c.tp * B2_MAX_ROWS * c.tile_h;
             const size_t mine = par + (size_t)c.rank * B2_MAX_ROWS * c.tile_h;
+            if (!(e.fin_flags & FIN_TEST_WITHHOLD_SIGNAL)) {
 #pragma unroll
-            for (int pr = 0; pr < B2_MAX_TP; ++pr) {
-                if (pr < c.tp && pr != c.rank) {
-                    float* dst = c.tpart[pr] + mine;
+                for (int pr = 0; pr < B2_MAX_TP; ++pr) {
+                    if (pr < c.tp && pr != c.rank) {
+                        float2* dst = c.tpart[pr] + mine;
 #pragma unroll
-                    for (int m = 0; m < MT; ++m) {
-                        if (m < M) {
-                            if (va) dst[(size_t)m * c.tile_h + ca] = ya[m];
-                            if (vb) dst[(size_t)m * c.tile_h + cb] = yb[m];
-                        }
-                    }
-                }
-            }
-            __threadfence_system();
-            __syncwarp();
-            if (lane < c.tp && lane != c.rank && !(e.fin_flags & FIN_TEST_WITHHOLD_SIGNAL))
-                st_release_sys_u32(c.tsig[lane] + (size_t)c.rank * c.tile_flags + wt, epoch);
-            bool arrived = true;
-            if (lane < c.tp && lane != c.rank) {
-                arrived = wait_reached(c.tsig[c.rank] + (size_t)lane * c.tile_flags + wt, epoch, wait_ns);
-                if (!arrived) report_timeout(c, B2_KID_CHAIN_TILE, lane, epoch);
-            }
-            ok = __all_sync(0xffffffffu, arrived);
-            asm volatile("fence.acquire.sys;" ::: "memory");
-            if (ok) {
-                const float* src = c.tpart[c.rank] + par;
-#pragma unroll
-                for (int m = 0; m < MT; ++m) {
-                    if (m < M) {
-                        float sa = 0.f, sb = 0.f;
-#pragma unroll
-                        for (int pr = 0; pr < B2_MAX_TP; ++pr) {
-                            if (pr < c.tp) {
-                                const float* q = src + ((size_t)pr * B2_MAX_ROWS + m) * c.tile_h;
-                                sa += pr == c.rank ? ya[m] : (va ? __ldcg(q + ca) : 0.f);
-                                sb += pr == c.rank ? yb[m] : (vb ? __ldcg(q + cb) : 0.f);
+                        for (int m = 0; m < MT; ++m) {
+                            if (m < M) {
+                                if (va) ch_st_pair(dst + (size_t)m * c.tile_h + ca, ya[m], epoch);
+                                if (vb) ch_st_pair(dst + (size_t)m * c.tile_h + cb, yb[m], epoch);
                             }
                         }
-                        ya[m] = sa; yb[m] = sb;
                     }
                 }
             }
+            const float2* src = c.tpart[c.rank] + par;
+            int late = -1;
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                if (m < M) {
+                    // the peers' copies of this row are polled together, then added in rank order
+                    const float2* ptr[2 * B2_MAX_TP];
+                    bool want[2 * B2_MAX_TP];
+                    float got[2 * B2_MAX_TP];
+#pragma unroll
+                    for (int pr = 0; pr < B2_MAX_TP; ++pr) {
+                        const float2* q = src + ((size_t)(pr < c.tp ? pr : 0) * B2_MAX_ROWS + m) * c.tile_h;
+                        ptr[2 * pr] = q + ca; ptr[2 * pr + 1] = q + cb;
+                        want[2 * pr] = pr < c.tp && pr != c.rank && va;
+                        want[2 * pr + 1] = pr < c.tp && pr != c.rank && vb;
+                    }
+                    if (late < 0 && !ch_wait_pairs<2 * B2_MAX_TP>(ptr, want, epoch, wait_ns, got)) late = c.rank == 0 ? 1 : 0;
+                    float sa = 0.f, sb = 0.f;
+#pragma unroll
+                    for (int pr = 0; pr < B2_MAX_TP; ++pr) {
+                        if (pr < c.tp) {
+                            sa += pr == c.rank ? ya[m] : got[2 * pr];
+                            sb += pr == c.rank ? yb[m] : got[2 * pr + 1];
+                        }
+                    }
+                    if (late < 0) { ya[m] = sa; yb[m] = sb; }
+                }
+            }
+            if (late >= 0) { report_timeout(c, B2_KID_CHAIN_TILE, late, epoch); ok = false; }
+            ok = __all_sync(0xffffffffu, ok);
         }
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
@@ -287,8 +536,15 @@ __device__ __forceinline__ bool ch_epilogue(const ChainParams& p, const ChainOp&
                 float ha = 0.f, hb = 0.f;
                 if (va) { ha = hra[m] + ya[m]; e.hout[off + ca] = ha; }
                 if (vb) { hb = hrb[m] + yb[m]; e.hout[off + cb] = hb; }
+                if (op.th_out) {
+                    if (va) ch_st_pair(op.th_out + (size_t)m * p.tag_h_cols + ca, ha, otag);
+                    if (vb) ch_st_pair(op.th_out + (size_t)m * p.tag_h_cols + cb, hb, otag);
+                }
                 const float tot = warp_sum(ha * ha + hb * hb);
-                if (lane == 0) e.ss_part[(size_t)m * e.ss_np + wt] = tot;
+                if (lane == 0) {
+                    e.ss_part[(size_t)m * e.ss_np + wt] = tot;
+                    if (op.tss_out) ch_st_pair(op.tss_out + (size_t)m * p.tag_ss_cols + wt, tot, otag);
+                }
             }
         }
     }
@@ -307,7 +563,7 @@ __device__ __forceinline__ bool ch_epilogue(const ChainParams& p, const ChainOp&
 #define CH_SZ_BYTES 256        // scale/zero pairs of one quantisation group of a warp tile
 
 template <int MT, bool FAST>
-__global__ void __launch_bounds__(CH_THREADS, 1) chain_kernel(const __grid_constant__ ChainParams p) {
+__global__ void __launch_bounds__(CH_THREADS, MT == 1 ? 2 : 1) chain_kernel(const __grid_constant__ ChainParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -320,9 +576,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) chain_kernel(const __grid_const
     const int g_eff = g < M ? g : 0;                                   // token row this lane feeds to the MMA (rows >= M: ignored)
 
     // ---- shared memory carve-up (offsets match b2_chain's size computation)
-    int maxKB = 0;
-    for (int o = 0; o < p.n_ops; ++o) maxKB = p.op[o].KB > maxKB ? p.op[o].KB : maxKB;
-    const int maxCh = 2 * maxKB;
+    const int maxCh = p.xf_chunks;                                     // widest staged window of any projection (32-k chunks)
     uint64_t* bars = (uint64_t*)smem;                                  // [CH_WARPS][CH_MAX_STAGES]
     int* seg_cnt = (int*)(smem + CH_HDR_BYTES - 128);                  // [CH_WARPS] arrivals per shared tile segment
     int* s_abort = (int*)(smem + CH_HDR_BYTES - 64);
@@ -379,39 +633,18 @@ __global__ void __launch_bounds__(CH_THREADS, 1) chain_kernel(const __grid_const
     for (int s = 0; s < NST; ++s) issue_one();
     pdl_launch_dependents();
 
-    uint32_t epoch0 = 0;
+    uint32_t epoch0 = 0, gen4 = 0;
     int n_exchanged = 0;          // exchanges of projections before the current one
     bool failed = false;
 
     for (int o = 0; o < p.n_ops; ++o) {
         const ChainOp& op = p.op[o];
-        // ---- dependency: everything this projection reads has been written
+        // ---- the first projection reads what earlier kernels wrote; the others poll the tagged values
+        // their producer leaves behind, so there is no grid-wide wait between projections
         if (o == 0) {
             pdl_wait();
             if (p.comm.tp > 1) epoch0 = *(volatile uint32_t*)p.comm.epoch;
-        } else {
-            if (tid == 0) {
-                const int* done = p.counters + CH_MAX_OPS * p.cstride + (o - 1);
-                const uint32_t need = (uint32_t)p.op[o - 1].NWT;
-                bool ok = ch_ld_acquire_gpu(done) >= need;
-                if (!ok) {
-                    const long long t0 = globaltimer_ns();
-                    for (;;) {
-#pragma unroll 1
-                        for (int i = 0; i < 64 && !ok; ++i) ok = ch_ld_acquire_gpu(done) >= need;
-                        if (ok || globaltimer_ns() - t0 > wait_ns) break;
-                    }
-                }
-                if (!ok) {
-                    if (atomicCAS(p.comm.status ? p.comm.status : s_abort, B2_STATUS_OK, B2_STATUS_WAIT_TIMEOUT) == B2_STATUS_OK &&
-                        p.comm.status) {
-                        p.comm.status[1] = B2_KID_CHAIN_DEP; p.comm.status[2] = o - 1; p.comm.status[3] = (int)blockIdx.x;
-                    }
-                    *s_abort = 1;
-                }
-            }
-            __syncthreads();
-            if (*s_abort) { failed = true; break; }
+            gen4 = ((volatile unsigned int*)p.counters)[1] << 2;
         }
         long long* pr = p.prof ? p.prof + ((size_t)gw * CH_MAX_OPS + o) * 8 : nullptr;
         long long cyc_wait = 0, cyc_fin = 0, n_stage = 0, cyc_issue = 0;
@@ -420,89 +653,26 @@ __global__ void __launch_bounds__(CH_THREADS, 1) chain_kernel(const __grid_const
         const uint32_t epoch = epoch0 + 1u + (uint32_t)n_exchanged;
 
         // ---- stage the activations in MMA B-fragment order, with the bias sums per 32-k chunk (FAST: per
-        // group of four chunks).  The loads of CH_STAGE_IT items per thread (and of the sums of squares of
-        // a lazily normalised input) are issued before any of them is used.
+        // group of four chunks); all loads of a pass are in flight together
         const int nCh = 2 * op.KB;
-        const int items = nCh * 4;
-        for (int m = 0; m < M; ++m) {
-            const __half* xr = op.x ? op.x + (size_t)m * op.ldx : nullptr;
-            const float* hr = op.ln.h ? op.ln.h + (size_t)m * op.ln.H : nullptr;
-            float inv = 0.f;
-            for (int base0 = 0; base0 < items; base0 += CH_THREADS * CH_STAGE_IT) {
-                float2 hv[CH_STAGE_IT][4];
-                uint32_t xv16[CH_STAGE_IT][4];
-#pragma unroll
-                for (int it = 0; it < CH_STAGE_IT; ++it) {
-                    const int item = base0 + it * CH_THREADS + tid;
-                    const int k0 = (item >> 2) * 32 + 2 * (item & 3);
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int k = k0 + 8 * q;
-                        const bool in = item < items && k < op.K;
-                        hv[it][q] = make_float2(0.f, 0.f);
-                        xv16[it][q] = 0u;
-                        if (in && hr) hv[it][q] = __ldcg((const float2*)(hr + k));
-                        else if (in) xv16[it][q] = __ldcg((const uint32_t*)(xr + k));
-                    }
-                }
-                if (hr && base0 == 0) {
-                    // every warp forms 1/rms of the row itself: no block-wide hand-off in front of the loads
-                    float s = 0.f;
-                    for (int i = lane; i < op.ln.np; i += 32) s += __ldcg(op.ln.ss + (size_t)m * op.ln.np + i);
-                    s = warp_sum(s);
-                    inv = rsqrtf(s / (float)op.ln.H + op.ln.eps);
-                }
-#pragma unroll
-                for (int it = 0; it < CH_STAGE_IT; ++it) {
-                    const int item = base0 + it * CH_THREADS + tid;
-                    const bool valid = item < items;
-                    const int tt = item & 3, cl = item >> 2;
-                    const int k0 = cl * 32 + 2 * tt;
-                    __half2 v[4];
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        if (hr) {
-                            const int k = k0 + 8 * q;
-                            float2 wv = make_float2(0.f, 0.f);
-                            if (valid && k < op.K) wv = __half22float2(*(const __half2*)(op.ln.w + k));
-                            v[q] = __floats2half2_rn(hv[it][q].x * inv * wv.x, hv[it][q].y * inv * wv.y);
-                        } else {
-                            v[q] = *(__half2*)&xv16[it][q];
-                        }
-                    }
-                    const __half2 sixteenth = __float2half2_rn(0.0625f);
-                    v[2] = __hmul2(v[2], sixteenth);
-                    v[3] = __hmul2(v[3], sixteenth);
-                    float2 fa0 = __half22float2(v[0]), fa1 = __half22float2(v[1]);
-                    float2 fb0 = __half22float2(v[2]), fb1 = __half22float2(v[3]);
-                    float sa = fa0.x + fa0.y + fa1.x + fa1.y;
-                    float sb = fb0.x + fb0.y + fb1.x + fb1.y;
-                    sa += __shfl_xor_sync(0xffffffffu, sa, 1);
-                    sb += __shfl_xor_sync(0xffffffffu, sb, 1);
-                    sa += __shfl_xor_sync(0xffffffffu, sa, 2);
-                    sb += __shfl_xor_sync(0xffffffffu, sb, 2);
-                    if (FAST) {
-                        // a group is four consecutive chunks = sixteen consecutive lanes
-                        sa += __shfl_xor_sync(0xffffffffu, sa, 4);
-                        sb += __shfl_xor_sync(0xffffffffu, sb, 4);
-                        sa += __shfl_xor_sync(0xffffffffu, sa, 8);
-                        sb += __shfl_xor_sync(0xffffffffu, sb, 8);
-                    }
-                    if (valid) {
-                        uint4 w4;
-                        w4.x = *(uint32_t*)&v[0]; w4.y = *(uint32_t*)&v[1]; w4.z = *(uint32_t*)&v[2]; w4.w = *(uint32_t*)&v[3];
-                        xf[((size_t)cl * M + m) * 4 + tt] = w4;
-                        if (FAST) {
-                            if ((item & 15) == 0) cs[(size_t)(cl >> 2) * Mpad + m] = make_float2(1024.f * (sa + sb), sa + 16.f * sb);
-                        } else if (tt == 0) {
-                            cs[(size_t)cl * Mpad + m] = make_float2(1024.f * (sa + sb), sa + 16.f * sb);
-                        }
-                    }
-                }
-            }
+        // a CTA without a share of this projection reads none of its input; one whose share is shorter than
+        // a tile's K stages only the window of k it will meet (it may wrap around the end of K)
+        const bool has_share = op.cBase + (cta < op.cRem ? 1 : 0) > 0;
+        int win0 = 0, win_n = nCh;
+        {
+            const int nc = op.cBase + (cta < op.cRem ? 1 : 0);
+            const int u0 = (cta * op.cBase + (cta < op.cRem ? cta : op.cRem)) * op.gsz, un = nc * op.gsz;
+            if (un < op.KB) { win0 = 2 * (u0 % op.KB); win_n = 2 * un; }
+        }
+        if (has_share) {
+            const uint32_t itag = gen4 + (uint32_t)op.in_op + 1u;
+            bool staged;
+            if (op.ln.h) staged = ch_stage<FAST, true, 3>(p, op, M, Mpad, xf, cs, itag, wait_ns, win0, win_n);
+            else staged = ch_stage<FAST, false, 5>(p, op, M, Mpad, xf, cs, itag, wait_ns, win0, win_n);
+            if (!staged) *s_abort = 1;
         }
         if (Mpad != M)
-            for (int cl = tid; cl < (FAST ? nCh / 4 : nCh); cl += CH_THREADS) cs[(size_t)cl * Mpad + M] = make_float2(0.f, 0.f);
+            for (int cl = tid; cl < (FAST ? win_n / 4 : win_n); cl += CH_THREADS) cs[(size_t)cl * Mpad + M] = make_float2(0.f, 0.f);
         __syncthreads();
         if (pr && lane == 0) pr[1] = globaltimer_ns();
 
@@ -579,9 +749,11 @@ __global__ void __launch_bounds__(CH_THREADS, 1) chain_kernel(const __grid_const
                 // the stage is one group: its scale/zero pairs and bias sums are read once
 #pragma unroll
                 for (int i = 0; i < 4; ++i) szc[i] = szs[i * 8];
-                const float4 cv = *(const float4*)(cs + (size_t)(cc.kb >> 1) * Mpad + 2 * t);
+                int rel = 2 * cc.kb - win0;                    // position of the stage's first chunk in the staged window
+                rel = rel < 0 ? rel + nCh : rel;
+                const float4 cv = *(const float4*)(cs + (size_t)(rel >> 2) * Mpad + 2 * t);
                 if (2 * t < Mpad) { c1r0 = cv.x; c2r0 = cv.y; c1r1 = cv.z; c2r1 = cv.w; }
-                const uint4* xp = xfl + (size_t)(2 * cc.kb) * M * 4;
+                const uint4* xp = xfl + (size_t)rel * M * 4;
 #pragma unroll
                 for (int b = 0; b < 2; ++b) {
                     uint4 w[4];
@@ -609,9 +781,11 @@ __global__ void __launch_bounds__(CH_THREADS, 1) chain_kernel(const __grid_const
 #pragma unroll
                             for (int i = 0; i < 4; ++i) szc[i] = szs[((grp - g_lo) * 4 + i) * 8];
                         }
-                        const float4 cv = *(const float4*)(cs + (size_t)cl * Mpad + 2 * t);
+                        int rel = cl - win0;
+                        rel = rel < 0 ? rel + nCh : rel;
+                        const float4 cv = *(const float4*)(cs + (size_t)rel * Mpad + 2 * t);
                         if (2 * t < Mpad) { c1r0 += cv.x; c2r0 += cv.y; c1r1 += cv.z; c2r1 += cv.w; }
-                        mma_chunk(w, j, xfl[(size_t)cl * M * 4]);
+                        mma_chunk(w, j, xfl[(size_t)rel * M * 4]);
                     }
                 }
             }
@@ -689,58 +863,41 @@ __global__ void __launch_bounds__(CH_THREADS, 1) chain_kernel(const __grid_const
             if (carry) {
                 const int cfirst = ch_slice_of(op, tb / op.gsz) / CH_WARPS, clast = ch_slice_of(op, (te - 1) / op.gsz) / CH_WARPS;
                 const int npc = clast - cfirst + 1;
-                int* cnt = p.counters + o * p.cstride + wt;
+                const uint32_t otag = gen4 + (uint32_t)o + 1u;
                 bool epi = true;
                 if (npc > 1 && cta != cfirst) {
-                    float* piece = p.scratch + (((size_t)wt * op.pmax + (cta - cfirst)) * M) * 64;
+                    float2* piece = p.scratch + (((size_t)wt * op.pmax + (cta - cfirst)) * M) * 64;
 #pragma unroll
                     for (int m = 0; m < MT; ++m) {
-                        if (m < M) { piece[m * 64 + la] = ya[m]; piece[m * 64 + la + 8] = yb[m]; }
+                        if (m < M) { ch_st_pair(piece + m * 64 + la, ya[m], otag); ch_st_pair(piece + m * 64 + la + 8, yb[m], otag); }
                     }
-                    ch_fence_gpu();
-                    __syncwarp();
-                    if (lane == 0) atomicAdd(cnt, 1);
                     epi = false;
                 } else if (npc > 1) {
-                    int ok = 1;
-                    if (lane == 0) {
-                        const uint32_t need = (uint32_t)(npc - 1);
-                        bool got = ch_ld_acquire_gpu(cnt) >= need;
-                        if (!got) {
-                            const long long t0 = globaltimer_ns();
-                            for (;;) {
-#pragma unroll 1
-                                for (int i = 0; i < 64 && !got; ++i) got = ch_ld_acquire_gpu(cnt) >= need;
-                                if (got || globaltimer_ns() - t0 > wait_ns) break;
-                            }
+                    const float2* base = p.scratch + ((size_t)wt * op.pmax * M) * 64;
+                    bool ok = true;
+                    for (int q = 1; q < npc && ok; ++q) {
+                        const float2* ptr[2 * MT];
+                        bool want[2 * MT];
+                        float got[2 * MT];
+#pragma unroll
+                        for (int m = 0; m < MT; ++m) {
+                            ptr[2 * m] = base + ((size_t)q * M + (m < M ? m : 0)) * 64 + la;
+                            ptr[2 * m + 1] = ptr[2 * m] + 8;
+                            want[2 * m] = want[2 * m + 1] = m < M;
                         }
-                        *cnt = 0;
-                        ok = got ? 1 : 0;
-                        if (!got && p.comm.status && atomicCAS(p.comm.status, B2_STATUS_OK, B2_STATUS_WAIT_TIMEOUT) == B2_STATUS_OK) {
+                        ok = ch_wait_pairs<2 * MT>(ptr, want, otag, wait_ns, got);
+#pragma unroll
+                        for (int m = 0; m < MT; ++m)
+                            if (m < M) { ya[m] += got[2 * m]; yb[m] += got[2 * m + 1]; }
+                    }
+                    if (!__all_sync(0xffffffffu, ok)) {
+                        if (lane == 0 && p.comm.status && atomicCAS(p.comm.status, B2_STATUS_OK, B2_STATUS_WAIT_TIMEOUT) == B2_STATUS_OK) {
                             p.comm.status[1] = B2_KID_CHAIN_DEP; p.comm.status[2] = o; p.comm.status[3] = (int)blockIdx.x;
                         }
-                    }
-                    ok = __shfl_sync(0xffffffffu, ok, 0);
-                    ch_fence_gpu();
-                    if (ok) {
-                        const float* base = p.scratch + ((size_t)wt * op.pmax * M) * 64;
-                        for (int q = 1; q < npc; ++q) {
-#pragma unroll
-                            for (int m = 0; m < MT; ++m) {
-                                if (m < M) {
-                                    ya[m] += __ldcg(base + ((size_t)q * M + m) * 64 + la);
-                                    yb[m] += __ldcg(base + ((size_t)q * M + m) * 64 + la + 8);
-                                }
-                            }
-                        }
+                        *s_abort = 1;
                     }
                 }
-                if (epi) {
-                    if (!ch_epilogue<MT>(p, op, wt, lane, ya, yb, epoch, wait_ns)) { /* status already recorded; sums stay local */ }
-                    ch_fence_gpu();
-                    __syncwarp();
-                    if (lane == 0) atomicAdd(p.counters + CH_MAX_OPS * p.cstride + o, 1);
-                }
+                if (epi) ch_epilogue<MT>(p, op, o, wt, lane, ya, yb, epoch, gen4, wait_ns);
             }
             if (pr) cyc_fin += clock64() - f0;
         }
@@ -758,19 +915,14 @@ __global__ void __launch_bounds__(CH_THREADS, 1) chain_kernel(const __grid_const
         if (++cslot == NST) { cslot = 0; cphase ^= 1u; }
     }
     __syncthreads();
-    // ---- the last CTA to leave clears the dependency counters and advances the exchange epoch
+    // ---- the last CTA to leave starts the next launch generation and advances the exchange epoch
     if (tid == 0) {
-        int* done = p.counters + CH_MAX_OPS * p.cstride;
         __threadfence();
-        const int old = atomicAdd(done + CH_MAX_OPS, 1);
-        if (old == (int)gridDim.x - 1) {
-            for (int o = 0; o < CH_MAX_OPS; ++o) done[o] = 0;
-            done[CH_MAX_OPS] = 0;
+        const unsigned old = atomicAdd(p.counters, 1u);
+        if (old == gridDim.x - 1) {
+            p.counters[0] = 0;
+            p.counters[1] = (gen4 >> 2) + 1u;
             if (p.comm.tp > 1 && n_exchanged > 0) *p.comm.epoch = epoch0 + (uint32_t)n_exchanged;
-            if (failed) {
-                // a tile count may be left half-way: start the next launch from zero
-                for (int i = 0; i < CH_MAX_OPS * p.cstride; ++i) p.counters[i] = 0;
-            }
             __threadfence();
         }
     }
@@ -799,43 +951,105 @@ static void ch_split(ChainOp& op, int grid) {
     op.pmax = pm < KBg + 1 ? pm : KBg + 1;
 }
 
-// Split-K scratch a projection needs (floats), for the device this is called on.
+// Cross-CTA scratch a projection needs ({value, tag} pairs), for the device this is called on.
 B2_API long long b2_chain_scratch_floats(int KB, int NWT, int rows) {
-    const int grid = ch_grid();
-    if (grid <= 0) return 0;
-    ChainOp op;
-    memset(&op, 0, sizeof(op));
-    op.KB = KB; op.NWT = NWT;
-    ch_split(op, grid);
-    return (long long)NWT * op.pmax * rows * 64;
+    const int sms = ch_grid();
+    if (sms <= 0) return 0;
+    long long need = 0;
+    for (int per = 1; per <= 2; ++per) {          // either grid size may be used, depending on the rows of a launch
+        ChainOp op;
+        memset(&op, 0, sizeof(op));
+        op.KB = KB; op.NWT = NWT;
+        ch_split(op, sms * per);
+        const long long n = (long long)NWT * op.pmax * rows * 64 * 2;
+        need = n > need ? n : need;
+    }
+    return need;
 }
-static size_t ch_fixed_smem(const ChainParams* p) {
-    int maxKB = 0;
-    for (int o = 0; o < p->n_ops; ++o) maxKB = p->op[o].KB > maxKB ? p->op[o].KB : maxKB;
-    const size_t maxCh = 2 * (size_t)maxKB, M = p->rows, Mpad = (M + 1) & ~(size_t)1;
+// CTAs per SM of a launch: the one-row kernels fit two (128 registers, half the shared memory each), which
+// doubles the warps that hide the loop's latencies; more rows need the registers of one CTA per SM.
+static int ch_ctas_per_sm(int rows) { return rows == 1 ? 2 : 1; }
+static size_t ch_smem_limit(int rows) { return ch_ctas_per_sm(rows) == 2 ? (size_t)113 * 1024 : (size_t)227 * 1024; }
+
+// Widest window of 32-k chunks any CTA stages (see the kernel: a share shorter than K stages only its k).
+static int ch_xf_chunks(const ChainParams* p, int grid) {
+    int mx = 0;
+    for (int o = 0; o < p->n_ops; ++o) {
+        ChainOp t = p->op[o];
+        ch_split(t, grid);
+        const int un = (t.cBase + (t.cRem > 0 ? 1 : 0)) * t.gsz;
+        const int ch = 2 * (un < t.KB ? un : t.KB);
+        mx = ch > mx ? ch : mx;
+    }
+    return mx;
+}
+
+static size_t ch_fixed_smem(const ChainParams* p, int grid) {
+    const size_t maxCh = (size_t)ch_xf_chunks(p, grid), M = p->rows, Mpad = (M + 1) & ~(size_t)1;
     size_t s = CH_HDR_BYTES + 2 * CH_WARPS * M * 256;
     s += maxCh * M * 4 * 16;
     s += (maxCh * Mpad + 8) * 8;
     return s + 128;                               // alignment slack before the rings
 }
 
-static int ch_stages(const ChainParams* p) {
-    const size_t fixed = ch_fixed_smem(p);
-    if (fixed >= CH_SMEM_LIMIT) return 0;
-    size_t st = (CH_SMEM_LIMIT - fixed) / ((size_t)CH_WARPS * CH_STAGE_BYTES);
-    return (int)(st > CH_MAX_STAGES ? CH_MAX_STAGES : st);
+static int ch_stages(const ChainParams* p, int grid) {
+    const size_t fixed = ch_fixed_smem(p, grid), limit = ch_smem_limit(p->rows);
+    if (fixed >= limit) return 0;
+    size_t st = (limit - fixed) / ((size_t)CH_WARPS * CH_STAGE_BYTES);
+    // B200GRAD_CHAIN_STAGES caps the ring depth (tuning)
+    static const int cap = [] { const char* e = getenv("B200GRAD_CHAIN_STAGES"); int v = e ? atoi(e) : 0; return v >= CH_MIN_STAGES && v <= CH_MAX_STAGES ? v : CH_MAX_STAGES; }();
+    return (int)(st > (size_t)cap ? (size_t)cap : st);
 }
 
-static bool ch_valid(const ChainParams* p) {
-    if (p->n_ops < 1 || p->n_ops > CH_MAX_OPS || p->rows < 1 || p->rows > B2_MAX_ROWS) return false;
-    for (int o = 0; o < p->n_ops; ++o) {
-        const ChainOp& op = p->op[o];
-        if (!op.qfrag || !op.szfrag || op.KB < 1 || op.NWT < 1 || op.NWT > p->cstride) return false;
+// Wire the hand-off between consecutive projections (each one must read what its predecessor writes)
+// and check the shapes.  Returns false if the projections cannot run as one launch.
+static bool ch_wire(ChainParams* q) {
+    if (q->n_ops < 1 || q->n_ops > CH_MAX_OPS || q->rows < 1 || q->rows > B2_MAX_ROWS) return false;
+    if (!q->scratch || !q->counters) return false;
+    for (int o = 0; o < q->n_ops; ++o) {
+        ChainOp& op = q->op[o];
+        if (!op.qfrag || !op.szfrag || op.KB < 1 || op.NWT < 1) return false;
         if (!op.x && !op.ln.h) return false;
+        op.th_out = nullptr; op.tss_out = nullptr; op.tact_out = nullptr;
+        op.th_in = nullptr; op.tss_in = nullptr; op.tact_in = nullptr; op.th_res = nullptr;
+        op.in_op = op.res_op = 0;
         if (op.epi.mode == EPI_FINISH) {
             if (op.epi.ss_np < op.NWT) return false;
-            const bool comm = p->comm.tp > 1 && !(op.epi.fin_flags & FIN_NO_COMM);
-            if (comm && (p->comm.tile_h < op.epi.n_valid || p->comm.tile_flags < op.NWT || !p->comm.tpart[0])) return false;
+            const bool comm = q->comm.tp > 1 && !(op.epi.fin_flags & FIN_NO_COMM);
+            if (comm && (q->comm.tile_h < op.epi.n_valid || !q->comm.tpart[0])) return false;
+        }
+    }
+    for (int o = 1; o < q->n_ops; ++o) {
+        ChainOp& op = q->op[o];
+        ChainOp& prev = q->op[o - 1];
+        if (op.ln.h && prev.epi.mode == EPI_FINISH && op.ln.h == prev.epi.hout && op.ln.ss == prev.epi.ss_part) {
+            if (!q->tag_h || !q->tag_ss || prev.epi.n_valid > q->tag_h_cols || prev.NWT > q->tag_ss_cols ||
+                op.ln.np != prev.NWT || op.ln.H != prev.epi.n_valid || (q->tag_h_cols & 1))
+                return false;
+            prev.th_out = q->tag_h; prev.tss_out = q->tag_ss;
+            op.th_in = q->tag_h; op.tss_in = q->tag_ss; op.in_op = o - 1;
+        } else if (op.x && prev.epi.mode == EPI_SILU_PAIR && (const void*)op.x == (const void*)prev.epi.out &&
+                   op.ldx == prev.epi.ldo) {
+            if (!q->tag_act || (prev.epi.n_valid + 1) / 2 > q->tag_act_cols || op.K > prev.epi.n_valid) return false;
+            prev.tact_out = q->tag_act;
+            op.tact_in = q->tag_act; op.in_op = o - 1;
+        } else {
+            return false;
+        }
+    }
+    // a FINISH projection whose residual stream is written earlier in the same launch reads the tagged copy
+    for (int o = 1; o < q->n_ops; ++o) {
+        ChainOp& op = q->op[o];
+        if (op.epi.mode != EPI_FINISH) continue;
+        for (int j = o - 1; j >= 0; --j) {
+            const ChainOp& w = q->op[j];
+            if (w.epi.mode == EPI_FINISH && w.epi.hout == op.epi.h) {
+                if (!w.th_out) return false;              // written here but not tagged: cannot be ordered
+                // nothing between j and o may overwrite the tagged copy
+                for (int k = j + 1; k < o; ++k) if (q->op[k].th_out) return false;
+                op.th_res = q->tag_h; op.res_op = j;
+                break;
+            }
         }
     }
     return true;
@@ -844,18 +1058,22 @@ static bool ch_valid(const ChainParams* p) {
 // 1 if the chain can run as one launch (shapes, shared memory for `rows`), else 0: the caller then
 // issues the projections as separate GEMV launches.
 B2_API int b2_chain_feasible(const ChainParams* p) {
-    return ch_valid(p) && ch_grid() > 0 && ch_stages(p) >= CH_MIN_STAGES ? 1 : 0;
+    ChainParams q = *p;
+    const int grid = ch_grid() * ch_ctas_per_sm(p->rows);
+    return ch_wire(&q) && grid > 0 && ch_stages(p, grid) >= CH_MIN_STAGES ? 1 : 0;
 }
 
 B2_API int b2_chain(const ChainParams* p, cudaStream_t stream) {
-    if (!ch_valid(p)) return cudaErrorInvalidValue;
-    const int grid = ch_grid();
+    const int per_sm_want = ch_ctas_per_sm(p->rows);
+    const int grid = ch_grid() * per_sm_want;
     if (grid <= 0) return cudaErrorInvalidDevice;
     ChainParams q = *p;
-    q.stages = ch_stages(p);
+    if (!ch_wire(&q)) return cudaErrorInvalidValue;
+    q.stages = ch_stages(p, grid);
+    q.xf_chunks = ch_xf_chunks(p, grid);
     if (q.stages < CH_MIN_STAGES) return cudaErrorInvalidValue;
     for (int o = 0; o < q.n_ops; ++o) ch_split(q.op[o], grid);
-    const size_t smem = ch_fixed_smem(p) + (size_t)CH_WARPS * q.stages * CH_STAGE_BYTES;
+    const size_t smem = ch_fixed_smem(p, grid) + (size_t)CH_WARPS * q.stages * CH_STAGE_BYTES;
     // groups of 128 k aligned to block pairs in every projection: the loop without group bookkeeping
     bool fast = true;
     for (int o = 0; o < q.n_ops; ++o) fast = fast && q.op[o].gshift == 2 && q.op[o].off32 == 0 && q.op[o].KB % 2 == 0;
@@ -864,7 +1082,7 @@ B2_API int b2_chain(const ChainParams* p, cudaStream_t stream) {
                      : variant == 2 ? (const void*)chain_kernel<B2_MAX_ROWS, false> : (const void*)chain_kernel<B2_MAX_ROWS, true>;
     static SmemOptIn optin[4];
     {
-        cudaError_t e = optin[variant].ensure(kern, CH_SMEM_LIMIT);
+        cudaError_t e = optin[variant].ensure(kern, ch_smem_limit(q.rows));
         if (e != cudaSuccess) return e;
     }
     // the grid's CTAs wait on one another: all of them must be resident at once (one per SM)
@@ -874,9 +1092,9 @@ B2_API int b2_chain(const ChainParams* p, cudaStream_t stream) {
     if (dev < 0 || dev >= B2_MAX_DEVICES) return cudaErrorInvalidDevice;
     if (!resident[variant][dev]) {
         int per_sm = 0;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, CH_THREADS, CH_SMEM_LIMIT);
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, CH_THREADS, smem);
         if (e != cudaSuccess) return e;
-        if (per_sm < 1) return cudaErrorLaunchOutOfResources;
+        if (per_sm < per_sm_want) return cudaErrorLaunchOutOfResources;
         resident[variant][dev] = per_sm;
     }
     cudaLaunchConfig_t cfg = {};

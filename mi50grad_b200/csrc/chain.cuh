@@ -27,15 +27,26 @@ struct ChainOp {
     int pad;
     LazyNorm ln;
     GemvEpi epi;              // epi.ss_np: row stride of ss_part; a FINISH tile writes entry n0/64
+    // Hand-off between the projections of one launch, wired by the launcher: a producer's epilogue
+    // also stores {value, tag} pairs (one 8-byte store each), and its consumer polls those instead of
+    // waiting for a counter: the data is its own arrival flag, nothing is fenced or counted.
+    float2* th_out; float2* tss_out; uint2* tact_out;                  // this op's tagged outputs (null: none)
+    const float2* th_in; const float2* tss_in; const uint2* tact_in;   // tagged input replacing ln.h + ln.ss / x
+    const float2* th_res;     // FINISH: tagged residual stream written by op `res_op` of this launch (null: epi.h)
+    int in_op, res_op;
 };
 
 struct ChainParams {
     int n_ops, rows;
     int stages;               // weight-ring depth per warp (set by the launcher)
-    int cstride;              // ints per op in `counters`
+    int xf_chunks;            // widest activation window any CTA stages, in 32-k chunks (set by the launcher)
     ChainOp op[CH_MAX_OPS];
-    float* scratch;           // split-K pieces: [warp tile][piece][row][64]
-    int* counters;            // [CH_MAX_OPS][cstride] tile arrivals, then done[CH_MAX_OPS], then exit; zero between launches
+    float2* scratch;          // partial tiles that cross CTAs, {value, tag}: [warp tile][piece][row][64]
+    unsigned int* counters;   // [0] CTAs that have left (zero between launches), [1] launch generation (never reset)
+    float2* tag_h;            // [rows][tag_h_cols]   tagged residual stream
+    float2* tag_ss;           // [rows][tag_ss_cols]  tagged per-tile sums of squares
+    uint2* tag_act;           // [rows][tag_act_cols] tagged fp16 pairs of the SiLU output
+    int tag_h_cols, tag_ss_cols, tag_act_cols, pad1;
     long long* prof;          // optional [grid * CH_WARPS][CH_MAX_OPS][8] per-warp timing record (null: off)
     CommCtx comm;
 };

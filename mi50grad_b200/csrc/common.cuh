@@ -33,10 +33,11 @@ struct CommCtx {
     long long* trace;             // optional [8] globaltimer stamps of the last exchange (null: off)
     // Tile-granular exchange of the persistent chain kernel: every 64-column output tile is pushed
     // to the peers by the warp that completes it and announced with its own flag word.
-    float* tpart[B2_MAX_TP];      // [2][tp][B2_MAX_ROWS][tile_h] fp32 partial tiles by (parity, source rank), per rank
-    uint32_t* tsig[B2_MAX_TP];    // [B2_MAX_TP][tile_flags] arrival words by (source rank, tile), per rank
+    float2* tpart[B2_MAX_TP];     // [2][tp][B2_MAX_ROWS][tile_h] {partial, epoch} pairs by (parity, source rank), per rank:
+                                  // every value travels with its arrival tag in one 8-byte store
+    uint32_t* tsig[B2_MAX_TP];    // reserved
     int tile_h;                   // row length the tile area was sized for (0: no tile area)
-    int tile_flags;               // flag words per source rank
+    int tile_flags;               // reserved
 };
 
 // Device-resident description of one token row of a decode/verify step.  A

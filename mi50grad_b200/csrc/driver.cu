@@ -92,7 +92,8 @@ struct ModelDesc {
     float* state0; void* conv0; long long state_layer_stride, conv_layer_stride;
     void* k0; void* v0; long long kv_layer_stride;
     // persistent projection chain (csrc/chain.cu)
-    float* chain_scratch; int* chain_counters; int chain_cstride; int use_chain;
+    void* chain_scratch; unsigned int* chain_counters; int chain_act_cols; int use_chain;
+    void* chain_tag_h; void* chain_tag_ss; void* chain_tag_act;
     CommCtx comm;
 };
 
@@ -179,7 +180,10 @@ static int chain_flush(Driver* d, int rows, cudaStream_t s) {
     const int n = pc.n;
     pc.n = 0;
     pc.cp.n_ops = n; pc.cp.rows = rows;
-    pc.cp.scratch = d->m.chain_scratch; pc.cp.counters = d->m.chain_counters; pc.cp.cstride = d->m.chain_cstride;
+    pc.cp.scratch = (float2*)d->m.chain_scratch; pc.cp.counters = d->m.chain_counters;
+    pc.cp.tag_h = (float2*)d->m.chain_tag_h; pc.cp.tag_ss = (float2*)d->m.chain_tag_ss; pc.cp.tag_act = (uint2*)d->m.chain_tag_act;
+    pc.cp.tag_h_cols = d->m.H; pc.cp.tag_ss_cols = d->m.np; pc.cp.tag_act_cols = d->m.chain_act_cols;
+    pc.cp.stages = 0; pc.cp.xf_chunks = 0; pc.cp.pad1 = 0;
     pc.cp.comm = d->m.comm; pc.cp.prof = nullptr;
     if (d->m.use_chain && d->m.chain_scratch && b2_chain_feasible(&pc.cp)) {
         d->launches++; d->chain_launches++;

@@ -319,11 +319,16 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_int4_kernel(const GemvIn
     const int nb = max(0, wb1 - wb0);
     uint4* rp = (uint4*)(s_flag + 4) + (size_t)warp * (GEMV_STAGES * GEMV_NT * 32) + lane;
     const uint4* gp = p.qfrag + ((size_t)wt * p.KB + wb0) * (GEMV_NT * 32) + lane;
+    // FAST: the 256 bytes of scale/zero pairs of a group ride along with the group's first weight block, so
+    // that nothing in the main loop waits on a global load
+    uint4* szr = (uint4*)(s_flag + 4) + (size_t)(GEMV_THREADS / 32) * (GEMV_STAGES * GEMV_NT * 32) + (size_t)warp * (GEMV_STAGES * 16);
+    const uint4* szg = (const uint4*)(p.szfrag + (size_t)wt * p.G * (GEMV_NT * 8));      // 16 uint4 per group
 #pragma unroll
     for (int s = 0; s < GEMV_STAGES - 1; ++s) {
         if (s < nb) {
 #pragma unroll
             for (int i = 0; i < GEMV_NT; ++i) cp_async16(rp + (s * GEMV_NT + i) * 32, gp + (s * GEMV_NT + i) * 32);
+            if (FAST && !(s & 1) && lane < 16) cp_async16(szr + s * 16 + lane, szg + (size_t)((wb0 + s) >> 1) * 16 + lane);
         }
         cp_async_commit();
     }
@@ -400,10 +405,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_int4_kernel(const GemvIn
     int cur = -1;
     const uint2* szp = p.szfrag + (size_t)wt * p.G * (GEMV_NT * 8) + g;
 
+    int sz_stage = 0;                          // FAST: ring stage that holds the scale/zero pairs of the group being flushed
     auto flush = [&](int grp) {
 #pragma unroll
         for (int i = 0; i < GEMV_NT; ++i) {
-            uint2 sz = ldg_nc_v2(szp + ((size_t)grp * GEMV_NT + i) * 8);
+            uint2 sz = FAST ? ((const uint2*)(szr + sz_stage * 16))[i * 8 + g] : ldg_nc_v2(szp + ((size_t)grp * GEMV_NT + i) * 8);
             float2 s = __half22float2(*(__half2*)&sz.x), z = __half22float2(*(__half2*)&sz.y);
             tot[i][0] += s.x * (acc[i][0] - c1r0 - z.x * c2r0);
             tot[i][1] += s.x * (acc[i][1] - c1r1 - z.x * c2r1);
@@ -430,6 +436,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_int4_kernel(const GemvIn
                     for (int i = 0; i < GEMV_NT; ++i)
                         cp_async16(rp + (((s + GEMV_STAGES - 1) % GEMV_STAGES) * GEMV_NT + i) * 32, gp + i * 32);
                     gp += GEMV_NT * 32;
+                    // block br + 3 is the first of its group exactly when s is odd (the slice starts on an even block)
+                    if (FAST && (s & 1) && lane < 16)
+                        cp_async16(szr + ((s + GEMV_STAGES - 1) % GEMV_STAGES) * 16 + lane,
+                                   szg + (size_t)((wb0 + br + GEMV_STAGES - 1) >> 1) * 16 + lane);
                 }
                 cp_async_commit();
                 cp_async_wait<GEMV_STAGES - 1>();
@@ -459,12 +469,12 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_int4_kernel(const GemvIn
                 }
                 cp4 += 8;
                 // FAST: groups of 128 k aligned to even blocks, so a group ends after every odd block
-                if (FAST && (s & 1)) flush((wb0 + br) >> 1);
+                if (FAST && (s & 1)) { sz_stage = s - 1; flush((wb0 + br) >> 1); }
             }
         }
     }
     cp_async_wait<0>();
-    if (FAST) { if (nb & 1) flush((wb0 + nb - 1) >> 1); }
+    if (FAST) { if (nb & 1) { sz_stage = (nb - 1) % GEMV_STAGES; flush((wb0 + nb - 1) >> 1); } }
     else if (cur >= 0) flush(cur);
 
     // ---- in-CTA reduction over the k-warps into ybuf[row][n_local]
@@ -592,7 +602,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_f16_kernel(const GemvF16Par
 B2_API size_t b2_gemv_int4_smem(int rows, int L) {
     size_t maxCh = 2 * GEMV_WK * (size_t)L;
     return (maxCh * rows + 1) * 64 + maxCh * 64 + (GEMV_WK * GEMV_WN * GEMV_NT * 128 + B2_MAX_ROWS * GEMV_TILE_N + 32 + 4) * 4
-           + (size_t)(GEMV_THREADS / 32) * GEMV_STAGES * GEMV_NT * 512;
+           + (size_t)(GEMV_THREADS / 32) * GEMV_STAGES * (GEMV_NT * 512 + 256);
 }
 
 B2_API int b2_gemv_int4(const GemvInt4Params* p, cudaStream_t stream) {
@@ -690,7 +700,7 @@ static void noalloc_launch_shape(int KB, int NTL, int rows, int* k_splits, int* 
     if (ks < 1) ks = 1;
     auto even = [&](int v) { return (KB >= 2 * GEMV_WK) ? v + (v & 1) : v; };
     int l = even((KB + GEMV_WK * ks - 1) / (GEMV_WK * ks));
-    while ((size_t)2 * GEMV_WK * l * (rows + 1) * 64 > 40000u) {
+    while ((size_t)2 * GEMV_WK * l * (rows + 1) * 64 > 32000u) {
         ++ks;
         l = even((KB + GEMV_WK * ks - 1) / (GEMV_WK * ks));
     }

@@ -336,8 +336,11 @@ class InferenceEngine:
         self.lib.b2_chain_scratch_floats.restype = C.c_longlong
         need = max([int(self.lib.b2_chain_scratch_floats(l.packed.KB, l.packed.NTL // 4, R)) for l in int4] + [1])
         b["chain_scratch"] = f32(need)
-        self.chain_cstride = max([l.packed.NTL // 4 for l in int4] + [1])
-        b["chain_counters"] = i32(L.CH_MAX_OPS * self.chain_cstride + L.CH_MAX_OPS + 4)
+        b["chain_counters"] = i32(8)
+        # tagged hand-off buffers between the projections of one chain launch ({value, tag} pairs)
+        self.chain_act_cols = -(-self.F_pad // 2)
+        b["chain_tag_h"], b["chain_tag_ss"] = f32(R, H, 2), f32(R, self.np, 2)
+        b["chain_tag_act"] = i32(R, self.chain_act_cols, 2)
         b["rows"], b["rows_tmpl"] = i32(R, 6), i32(R, 6)
         b["row_tokens"] = torch.full((R,), -1, dtype=torch.int32, device=dev)
         b["seq_rows"] = i32(self.max_batch + 1 + R)
@@ -392,7 +395,9 @@ class InferenceEngine:
         m.ld_proj, m.ld_attn, m.ld_logits = b["ld_proj"], b["ld_attn"], b["ld_logits"]
         m.np = self.np
         m.chain_scratch, m.chain_counters = b["chain_scratch"].data_ptr(), b["chain_counters"].data_ptr()
-        m.chain_cstride, m.use_chain = self.chain_cstride, int(self.use_chain)
+        m.chain_act_cols, m.use_chain = self.chain_act_cols, int(self.use_chain)
+        m.chain_tag_h, m.chain_tag_ss = b["chain_tag_h"].data_ptr(), b["chain_tag_ss"].data_ptr()
+        m.chain_tag_act = b["chain_tag_act"].data_ptr()
         m.seqs = self.states.seqs.data_ptr()
         m.comm = self._comm_ctx()
         m.max_prefill = self.max_prefill

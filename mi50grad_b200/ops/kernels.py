@@ -129,29 +129,46 @@ def chain_op(pk, x: Optional[torch.Tensor] = None, ln: Optional[L.LazyNorm] = No
     return op
 
 
-def chain_scratch(ops, rows: int, device):
-    """(scratch, counters, cstride) large enough for any chain over the projections in `ops`."""
-    lib = L.lib()
-    need = max(int(lib.b2_chain_scratch_floats(o.KB, o.NWT, rows)) for o in ops)
-    cstride = max(o.NWT for o in ops)
-    return (torch.empty(max(1, need), dtype=torch.float32, device=device),
-            torch.zeros(L.CH_MAX_OPS * cstride + L.CH_MAX_OPS + 4, dtype=torch.int32, device=device), cstride)
+class ChainBuffers:
+    """Work buffers of `chain` launches over a set of projections: cross-CTA scratch, the launch
+    counters, and the tagged hand-off buffers between the projections of one launch."""
+
+    def __init__(self, ops, rows: int, device):
+        lib = L.lib()
+        need = max(int(lib.b2_chain_scratch_floats(o.KB, o.NWT, rows)) for o in ops)
+        self.rows = rows
+        self.scratch = torch.zeros(max(2, need), dtype=torch.float32, device=device)
+        self.counters = torch.zeros(8, dtype=torch.int32, device=device)
+        self.h_cols = max([o.epi.n_valid for o in ops if o.epi.mode == L.EPI_FINISH] + [2])
+        self.h_cols += self.h_cols & 1
+        self.ss_cols = max([o.NWT for o in ops if o.epi.mode == L.EPI_FINISH] + [1])
+        self.act_cols = max([-(-o.epi.n_valid // 2) for o in ops if o.epi.mode == L.EPI_SILU_PAIR] + [1])
+        self.tag_h = torch.zeros(rows, self.h_cols, 2, dtype=torch.float32, device=device)
+        self.tag_ss = torch.zeros(rows, self.ss_cols, 2, dtype=torch.float32, device=device)
+        self.tag_act = torch.zeros(rows, self.act_cols, 2, dtype=torch.int32, device=device)
 
 
-def chain(ops, rows: int, scratch: torch.Tensor, counters: torch.Tensor, cstride: int,
-          comm: Optional[L.CommCtx] = None, prof: Optional[torch.Tensor] = None):
+def chain_scratch(ops, rows: int, device) -> ChainBuffers:
+    return ChainBuffers(ops, rows, device)
+
+
+def chain(ops, rows: int, bufs: ChainBuffers, comm: Optional[L.CommCtx] = None, prof: Optional[torch.Tensor] = None):
     """Run up to four dependent INT4 projections (`chain_op`) as ONE persistent launch
-    (csrc/chain.cu).  Raises if the shapes do not fit the kernel's shared memory."""
+    (csrc/chain.cu): each projection must read what its predecessor writes.  Raises if they
+    cannot run as one launch (shapes, or rows x K too large for shared memory)."""
     lib = L.lib()
     p = L.ChainParams()
-    p.n_ops, p.rows, p.cstride = len(ops), rows, cstride
+    p.n_ops, p.rows = len(ops), rows
     for i, o in enumerate(ops):
         p.op[i] = o
-    p.scratch, p.counters = scratch.data_ptr(), counters.data_ptr()
+    p.scratch, p.counters = bufs.scratch.data_ptr(), bufs.counters.data_ptr()
+    p.tag_h, p.tag_ss, p.tag_act = bufs.tag_h.data_ptr(), bufs.tag_ss.data_ptr(), bufs.tag_act.data_ptr()
+    p.tag_h_cols, p.tag_ss_cols, p.tag_act_cols = bufs.h_cols, bufs.ss_cols, bufs.act_cols
     p.prof = None if prof is None else prof.data_ptr()     # int64 [SMs * 8 warps, 4, 8] per-warp timing record
     p.comm = comm if comm is not None else L.null_comm()
     if not lib.b2_chain_feasible(C.byref(p)):
-        raise ValueError("projection chain does not fit one launch (rows x K too large for shared memory, or bad shapes)")
+        raise ValueError("projection chain does not fit one launch (rows x K too large for shared memory, or "
+                         "projections that do not feed one another)")
     L.check(lib.b2_chain(C.byref(p), L.stream()), "chain")
 
 

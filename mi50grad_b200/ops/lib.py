@@ -78,12 +78,16 @@ class ChainOp(C.Structure):
     _fields_ = [("qfrag", vp), ("szfrag", vp), ("x", vp), ("ldx", i32), ("K", i32), ("KB", i32), ("NWT", i32),
                 ("G", i32), ("off32", i32), ("gshift", i32), ("gsz", i32), ("cBase", i32), ("cRem", i32), ("pmax", i32),
                 ("pad", i32),
-                ("ln", LazyNorm), ("epi", GemvEpi)]
+                ("ln", LazyNorm), ("epi", GemvEpi),
+                ("th_out", vp), ("tss_out", vp), ("tact_out", vp), ("th_in", vp), ("tss_in", vp), ("tact_in", vp),
+                ("th_res", vp), ("in_op", i32), ("res_op", i32)]
 
 
 class ChainParams(C.Structure):
-    _fields_ = [("n_ops", i32), ("rows", i32), ("stages", i32), ("cstride", i32), ("op", ChainOp * CH_MAX_OPS),
-                ("scratch", vp), ("counters", vp), ("prof", vp), ("comm", CommCtx)]
+    _fields_ = [("n_ops", i32), ("rows", i32), ("stages", i32), ("xf_chunks", i32), ("op", ChainOp * CH_MAX_OPS),
+                ("scratch", vp), ("counters", vp), ("tag_h", vp), ("tag_ss", vp), ("tag_act", vp),
+                ("tag_h_cols", i32), ("tag_ss_cols", i32), ("tag_act_cols", i32), ("pad1", i32),
+                ("prof", vp), ("comm", CommCtx)]
 
 
 class AttnParams(C.Structure):
@@ -186,7 +190,8 @@ class ModelDesc(C.Structure):
                 ("spec", SpecStage), ("spec_acc", vp), ("spec_result", vp),
                 ("state0", vp), ("conv0", vp), ("state_layer_stride", i64), ("conv_layer_stride", i64),
                 ("k0", vp), ("v0", vp), ("kv_layer_stride", i64),
-                ("chain_scratch", vp), ("chain_counters", vp), ("chain_cstride", i32), ("use_chain", i32),
+                ("chain_scratch", vp), ("chain_counters", vp), ("chain_act_cols", i32), ("use_chain", i32),
+                ("chain_tag_h", vp), ("chain_tag_ss", vp), ("chain_tag_act", vp),
                 ("comm", CommCtx)]
 
 

@@ -90,7 +90,7 @@ def launch_shape(KB: int, NTL: int, rows: int = 1, slots: int = 2 * NUM_SMS, K: 
     even = lambda v: v + (v & 1) if KB >= 2 * GEMV_WK else v      # even L enables the aligned-group fast path
     L = even(-(-KB // (GEMV_WK * k_splits)))
     # shared-memory bound: activation fragments are 64 bytes per chunk per row
-    while 2 * GEMV_WK * L * (rows + 1) * 64 > 40_000:
+    while 2 * GEMV_WK * L * (rows + 1) * 64 > 32_000:
         k_splits += 1
         L = even(-(-KB // (GEMV_WK * k_splits)))
     k_splits = -(-KB // (GEMV_WK * L))

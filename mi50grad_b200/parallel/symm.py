@@ -16,7 +16,7 @@ Layout of the symmetric block (bytes):
     [0, 2*part_floats*4)            partial-sum staging, double-buffered by epoch parity
     [+0, +gather_floats*4)          two-shot gather area
     [.., +256)                      flag words: [0,8) phase A, [8,16) phase B (uint32, by source rank)
-    [.., +2*tp*8*tile_h*4)          tile staging of the chain kernel: [parity][source rank][row][tile_h] fp32
+    [.., +2*tp*8*tile_h*8)          tile staging of the chain kernel: [parity][source rank][row][tile_h] {fp32, epoch}
     [.., +8*TILE_FLAGS*4)           tile flags: [source rank][tile] uint32
 """
 from __future__ import annotations
@@ -64,7 +64,7 @@ class SymmComm(Communicator):
         self.tile_h = -(-int(hidden) // 64) * 64
         self.tile_flags = max(128, self.tile_h // 64)
         self.off_tpart = self.off_sig + 256
-        self.off_tsig = self.off_tpart + 2 * self.tp_size * L.MAX_ROWS * self.tile_h * 4
+        self.off_tsig = self.off_tpart + 2 * self.tp_size * L.MAX_ROWS * self.tile_h * 8      # {value, epoch} pairs
         nbytes = self.off_tsig + L.MAX_TP * self.tile_flags * 4
         self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
         self.buf.zero_()

@@ -70,14 +70,14 @@ def test_chain_four_projections(K0, H, F, N3, g, rows):
     ]
     # `down` reads F columns of a buffer with row stride Fp
     ops[2].ldx = Fp
-    scratch, counters, cs = K.chain_scratch(ops, rows, d)
-    K.chain(ops, rows, scratch, counters, cs)
+    bufs = K.chain_scratch(ops, rows, d)
+    K.chain(ops, rows, bufs)
     torch.cuda.synchronize()
     assert _rel(act[:, :F].cpu(), ref["act"]) < 4e-3
     assert _rel(h.cpu(), ref["h2"]) < 2e-3
     assert torch.allclose(ss.sum(-1).cpu(), ref["h2"].pow(2).sum(-1), rtol=2e-3)
     assert _rel(out.cpu(), ref["out"]) < 5e-3
-    assert int(counters.abs().sum()) == 0                      # the kernel leaves its counters clean
+    assert bufs.counters[:2].tolist() == [0, 1]                # departures cleared, one launch counted
     # a second launch on the same buffers (counters reused) gives the same bits
     h_b, out_a = h0.clone(), out.clone()
     ops[0] = K.chain_op(pk["o"], x=x0, mode=L.EPI_FINISH, fin_flags=L.FIN_NO_COMM, h=h_b, ss_part=ss)
@@ -85,7 +85,7 @@ def test_chain_four_projections(K0, H, F, N3, g, rows):
     ops[2] = K.chain_op(pk["down"], x=act, mode=L.EPI_FINISH, fin_flags=L.FIN_NO_COMM, h=h_b, ss_part=ss)
     ops[2].ldx = Fp
     ops[3] = K.chain_op(pk["nxt"], ln=K.lazy_norm(h_b, ss, w3), out=out)
-    K.chain(ops, rows, scratch, counters, cs)
+    K.chain(ops, rows, bufs)
     torch.cuda.synchronize()
     assert torch.equal(out, out_a) and torch.equal(h_b, h)
 
@@ -102,8 +102,8 @@ def test_chain_matches_standalone_gemv_and_deferred_flags():
     out_c = torch.zeros(rows, H, dtype=torch.float32, device=d)
     out_g = torch.zeros(rows, H, dtype=torch.float32, device=d)
     op = K.chain_op(pk["o"], x=x0, mode=L.EPI_STORE_F32, out=out_c)
-    scratch, counters, cs = K.chain_scratch([op], rows, d)
-    K.chain([op], rows, scratch, counters, cs)
+    bufs = K.chain_scratch([op], rows, d)
+    K.chain([op], rows, bufs)
     K.gemv(pk["o"], x0, out=out_g, mode=L.EPI_STORE_F32)
     assert _rel(out_c.cpu(), out_g.cpu()) < 1e-4
     # attention partial kept aside (h untouched), then added to the FFN partial
@@ -113,23 +113,27 @@ def test_chain_matches_standalone_gemv_and_deferred_flags():
     y = (ref["h1"] - h0.cpu())
     op1 = K.chain_op(pk["o"], x=x0, mode=L.EPI_FINISH, fin_flags=L.FIN_NO_COMM | L.FIN_NO_H_WRITE | L.FIN_SAVE_EXTRA,
                      h=h, hout=h_tmp, extra=extra, ss_part=ss)
-    K.chain([op1], rows, scratch, counters, cs)
+    K.chain([op1], rows, bufs)
     assert torch.equal(h, h0) and _rel(extra.cpu(), y) < 1e-4 and _rel(h_tmp.cpu(), ref["h1"]) < 1e-4
     op2 = K.chain_op(pk["o"], x=x0, mode=L.EPI_FINISH, fin_flags=L.FIN_NO_COMM | L.FIN_ADD_EXTRA, h=h, extra=extra,
                      ss_part=ss)
-    K.chain([op2], rows, scratch, counters, cs)
+    K.chain([op2], rows, bufs)
     assert _rel(h.cpu(), h0.cpu() + 2 * y) < 1e-4
 
 
-def test_chain_refuses_what_does_not_fit():
-    """Too many rows for the shared-memory budget at a long K: the wrapper raises, nothing is launched."""
+def test_chain_refuses_projections_that_do_not_feed_one_another():
+    """Two projections of one launch must be producer and consumer: anything else is refused by the
+    wrapper before a launch (the step driver then issues them as separate GEMV launches)."""
     from mi50grad_b200.ops import kernels as K
     from mi50grad_b200.ops.packing import random_packed_int4
     d = _dev()
-    pk = random_packed_int4(17408, 128, 128, d)
-    x = torch.zeros(8, 17408, dtype=torch.float16, device=d)
-    out = torch.zeros(8, 128, dtype=torch.float16, device=d)
-    op = K.chain_op(pk, x=x, out=out)
-    scratch, counters, cs = K.chain_scratch([op], 8, d)
+    pk = random_packed_int4(512, 128, 128, d)
+    x = torch.zeros(2, 512, dtype=torch.float16, device=d)
+    out1 = torch.zeros(2, 128, dtype=torch.float16, device=d)
+    out2 = torch.zeros(2, 128, dtype=torch.float16, device=d)
+    ops = [K.chain_op(pk, x=x, out=out1), K.chain_op(pk, x=x, out=out2)]
+    bufs = K.chain_scratch(ops, 2, d)
     with pytest.raises(ValueError):
-        K.chain([op], 8, scratch, counters, cs)
+        K.chain(ops, 2, bufs)
+    K.chain(ops[:1], 2, bufs)                  # each alone is fine
+    torch.cuda.synchronize()
