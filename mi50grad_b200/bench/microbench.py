@@ -138,12 +138,20 @@ def bench_fused(iters: int):
             def fused(i):
                 K.gemv(pks[i], x, mode=L.EPI_FINISH, h=h, ss_part=ss, comm=ctx, scratch=scratch, counters=counters)
 
+            cops = [K.chain_op(pk, x=x, mode=L.EPI_FINISH, h=h, ss_part=torch.zeros(1, H // 64, device=dev)) for pk in pks]
+            cbufs = K.chain_scratch(cops, 1, dev)
+
+            def fused_chain(i):
+                K.chain([cops[i]], 1, cbufs, comm=ctx)
+
             def unfused(i):
                 K.gemv(pks[i], x, out=part, mode=L.EPI_STORE_F32, scratch=scratch, counters=counters)
                 dist.all_reduce(part)
                 K.add_rmsnorm(h, torch.ones(H, dtype=torch.float16, device=dev), part)
             dist.barrier()
             us_f = mx(time_launches(fused, nvar, iters))
+            dist.barrier()
+            us_c = mx(time_launches(fused_chain, nvar, iters))
             dist.barrier()
             us_u = mx(time_launches(unfused, nvar, iters))
             comm.check_status()
@@ -152,6 +160,7 @@ def bench_fused(iters: int):
             t_hbm = pks[0].nbytes() / (hbm * 1e3)
             results.append({"kernel": "int4_gemv_ar_residual", "shape": name, "K_local": Kd, "N": H, "tp": tp,
                             "multimem": comm.has_multimem, "fused_us": round(us_f, 2),
+                            "chain_tile_exchange_us": round(us_c, 2),
                             "gemv+nccl+add_us": round(us_u, 2), "speedup": round(us_u / us_f, 2),
                             "hbm_floor_us": round(t_hbm, 2), "frac_of_roofline": round(t_hbm / us_f, 3),
                             "peak_source": src})
@@ -189,9 +198,70 @@ def bench_fused(iters: int):
     return results
 
 
+def bench_nvlink(iters: int):
+    """NVLink probes (reference: src/kernels/p2p_bandwidth_kernels.hip:187-278 and
+    bench/PCIe4_BANDWIDTH_REPORT.md): read bandwidth from local memory, from a peer's memory with plain
+    loads, through the multicast address with multimem.ld_reduce (payload counted once), write bandwidth
+    into a peer's memory, for 10 KB ... 64 MB; and the latency of dependent loads, local and peer.
+    Run under torch.distributed.run with >= 2 ranks; every figure is the slowest rank's."""
+    import torch.distributed as dist
+    from ..ops import kernels as K
+    from ..parallel.symm import SymmComm
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    tp, rank = dist.get_world_size(), dist.get_rank()
+    dev = torch.device("cuda", local)
+    comm = SymmComm(part_floats=8 * 1024 * 1024, use_multimem=True)          # 64 MB staging region per rank
+    peer = (rank + 1) % tp
+    me_ptr, peer_ptr = comm.peer_ptrs[rank], comm.peer_ptrs[peer]
+    sink = torch.empty(64 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    def mx(v):
+        t = torch.tensor([v], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    res = []
+    for nbytes in (10 * 1024, 160 * 1024, 1024 * 1024, 8 * 1024 * 1024, 64 * 1024 * 1024):
+        ctas = max(1, min(296, nbytes // (16 * 512)))
+        cases = {"local_read": lambda: K.probe_read(me_ptr, nbytes, ctas=ctas),
+                 "peer_read": lambda: K.probe_read(peer_ptr, nbytes, ctas=ctas),
+                 "peer_write": lambda: K.probe_read(sink.data_ptr(), nbytes, dst_ptr=peer_ptr, ctas=ctas)}
+        if comm.has_multimem:
+            cases["multimem_ld_reduce"] = lambda: K.probe_read(comm.multicast_ptr, nbytes, multimem=True, ctas=ctas)
+        row = {"probe": "bandwidth", "bytes": nbytes, "tp": tp, "ctas": ctas}
+        for name, fn in cases.items():
+            dist.barrier()
+            us = mx(time_launches(lambda i: fn(), 1, iters))
+            row[name + "_us"] = round(us, 2)
+            row[name + "_gb_s"] = round(nbytes / us / 1e3, 1)
+        res.append(row)
+        if rank == 0:
+            print(json.dumps(row), flush=True)
+    # dependent-load latency: a chain of indices with a 4 KB stride, walked from local and from peer memory
+    n = 1 << 16
+    chain = ((torch.arange(n, dtype=torch.int64) + 1024) % n).to(torch.int32)
+    region = torch.empty(0)
+    local_view = comm.buf[: n * 4].view(torch.int32)
+    local_view.copy_(chain.to(dev))
+    torch.cuda.synchronize()
+    dist.barrier()
+    lat = {"probe": "latency", "tp": tp, "hops": 2000,
+           "local_ns": round(mx(K.probe_latency(local_view, 2000)), 1),
+           "peer_ns": round(mx(K.probe_latency(local_view, 2000, chain_ptr=peer_ptr)), 1)}
+    res.append(lat)
+    if rank == 0:
+        print(json.dumps(lat), flush=True)
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+    return res
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "fused"])
+    ap.add_argument("what", choices=["gemv", "fused", "nvlink"])
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--iters", type=int, default=20)
@@ -199,6 +269,8 @@ def main(argv=None):
     a = ap.parse_args(argv)
     if a.what == "gemv":
         bench_gemv(a.tp, a.rows, a.iters, a.only)
+    elif a.what == "nvlink":
+        bench_nvlink(a.iters)
     else:
         bench_fused(a.iters)
 

@@ -4,8 +4,13 @@
 
 Each case launches one kernel family a few times on inputs larger than L2 but
 only a few hundred MB in total, brackets the launches of interest with
-cudaProfilerStart/Stop (use `ncu --profile-from-start off`), and with --time
-prints CUDA-event timings taken from a graph replay instead.
+cudaProfilerStart/Stop, and with --time prints CUDA-event timings taken from a
+graph replay instead.  Capture one case and one kernel at a time, after the same
+command has exited 0 without a profiler, and never let the profiler touch the
+clocks of a shared GPU:
+
+    ncu --clock-control none --profile-from-start off -k regex:<kernel> -c 3 \
+        python -m mi50grad_b200.bench.profile_cases <case>
 
 cases: gemv_gateup, gemv_down, gemm_int4, gemm_dense, attn_decode, attn_rows,
        deltanet_step, deltanet_chunk, spec_step, prefill, decode_step, linear_q8

@@ -53,6 +53,11 @@ struct LayerDesc {
     const void* wa; const void* wb; const void* conv_w; void* conv_state; float* state;
     const float* A_log; const void* dt_bias; const void* la_norm;
     int off_q, off_k, off_v, off_z, off_a, off_b;
+    // FFN on the INT8-activation path (quant_format w8a8 / w4a8): gate, up, down
+    int ffn_kind;                 // 0: INT4 weights with fp16 activations, 1: W8A8, 2: W4A8
+    int q8_group, q8_F, pad_q8;   // group size of the W4A8 scales; local FFN width
+    const void* q8_w[3];          // int8 [N][K] or signed nibbles int32 [N][K/8]
+    const void* q8_s[3];          // fp32 [N] (W8A8) or fp16 [K/group][N] (W4A8)
 };
 
 struct ModelDesc {
@@ -94,6 +99,8 @@ struct ModelDesc {
     // persistent projection chain (csrc/chain.cu)
     void* chain_scratch; unsigned int* chain_counters; int chain_act_cols; int use_chain;
     void* chain_tag_h; void* chain_tag_ss; void* chain_tag_act;
+    // INT8-activation FFN work buffers, sized for max(max_rows, max_prefill) rows
+    void* q8_xq; float* q8_sx; void* q8_gate; void* q8_up; float* q8_down; void* q8_xn;
     CommCtx comm;
 };
 
@@ -109,8 +116,11 @@ struct Driver {
     ModelDesc m;
     std::vector<LayerDesc> layers;
     PendingChain pend;
-    long long chain_launches = 0;         // chain kernels issued by the last eager step
-    long long exchanges = 0;              // cross-GPU exchanges issued by the last eager step
+    long long chain_launches = 0;         // chain kernels issued by the last step that was issued or captured
+    long long exchanges = 0;              // cross-GPU exchanges of that step
+    std::vector<int> layer_launches;      // kernels issued inside each layer's part of that step
+    long long graph_launches = 0, graph_exchanges = 0;   // of the captured step
+    long long total_launches = 0, total_exchanges = 0;   // since creation, eager steps and graph replays alike
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     int graph_rows = 0, graph_flags = 0;
@@ -215,6 +225,52 @@ static int chain_add(Driver* d, const LinearDesc& L, const void* x, int ldx, con
     return 0;
 }
 
+// FFN of one layer on the INT8-activation path (reference: src/inference/engine.py:890-991): the
+// normalised input and the SiLU product are quantised per row to int8 in front of the products.
+// `h` holds the residual stream the FFN reads and, afterwards, that stream plus the FFN output
+// (summed over the ranks); `ss` (optional) receives the row sums of squares for lazy consumers.
+static int ffn_q8(Driver* d, const LayerDesc& L, float* h, int rows, float* ss, cudaStream_t s) {
+    const ModelDesc& m = d->m;
+    if (!m.q8_xq || !L.q8_w[0]) return cudaErrorInvalidValue;
+    const int H = m.H, F = L.q8_F;
+    CK(b2_add_rmsnorm(h, nullptr, nullptr, L.ffn_norm, m.q8_xn, nullptr, rows, H, m.eps, s)); d->launches++;
+    ActQuantParams a;
+    memset(&a, 0, sizeof(a));
+    a.x = (const __half*)m.q8_xn; a.xq = (int8_t*)m.q8_xq; a.scale = m.q8_sx; a.T = rows; a.K = H; a.ldx = H;
+    CK(b2_act_quant(&a, s)); d->launches++;
+    auto product = [&](int which, int K, int N, void* out, int f16) -> int {
+        Quant8Params q;
+        memset(&q, 0, sizeof(q));
+        q.w = L.q8_w[which]; q.xq = (const int8_t*)m.q8_xq; q.x_scale = m.q8_sx; q.out = out;
+        if (L.ffn_kind == 1) q.w_scale = (const float*)L.q8_s[which]; else q.g_scale = (const __half*)L.q8_s[which];
+        q.K = K; q.N = N; q.T = rows; q.ldo = N; q.group = L.q8_group; q.out_f16 = f16; q.w4 = L.ffn_kind == 2;
+        d->launches++;
+        return b2_linear_q8(&q, s);
+    };
+    CK(product(0, H, F, m.q8_gate, 1));
+    CK(product(1, H, F, m.q8_up, 1));
+    CK(b2_silu_mul(m.q8_gate, m.q8_up, m.q8_gate, (size_t)rows * F, s)); d->launches++;
+    a.x = (const __half*)m.q8_gate; a.K = F; a.ldx = F;
+    CK(b2_act_quant(&a, s)); d->launches++;
+    CK(product(2, F, H, m.q8_down, 0));
+    if (m.comm.tp > 1) {
+        CollParams c;
+        memset(&c, 0, sizeof(c));
+        c.comm = m.comm; c.in = m.q8_down; c.out = h; c.n = (size_t)rows * H; c.residual = 1;
+        c.twoshot = c.n * 4 > 512 * 1024;
+        for (int r = 0; r < m.comm.tp; ++r) c.gather[r] = m.coll_gather[r];
+        c.mc_gather = m.coll_mc_gather; c.counters = m.coll_counters;
+        d->launches++; d->exchanges++;
+        CK(b2_allreduce(&c, 2 * 148, s));
+        if (ss) { CK(b2_residual_add_ss(h, nullptr, ss, m.np, rows, H, s)); d->launches++; }
+    } else if (ss) {
+        CK(b2_residual_add_ss(h, m.q8_down, ss, m.np, rows, H, s)); d->launches++;
+    } else {
+        CK(b2_residual_add(h, m.q8_down, nullptr, (size_t)rows * H, s)); d->launches++;
+    }
+    return 0;
+}
+
 static void fill_delta(const Driver* d, const LayerDesc& L, DeltaParams& q) {
     const ModelDesc& m = d->m;
     memset(&q, 0, sizeof(q));
@@ -269,6 +325,8 @@ static int step_impl(Driver* d, int rows, int n_seqs, int flags, cudaStream_t s)
     const void* last_norm = m.first_norm;
     for (int li = 0; li < m.n_layers; ++li) {
         const LayerDesc& L = d->layers[li];
+        const long long launched0 = d->launches;
+        struct Count { Driver* d; int li; long long l0; ~Count() { d->layer_launches[li] = (int)(d->launches - l0); } } count{d, li, launched0};
         const LazyNorm ln_in = lazy(d, m.h, L.attn_norm);
         // ---- token mixer
         // the in-projection rides at the end of the previous layer's chain (out_proj, gate/up, down)
@@ -311,6 +369,13 @@ static int step_impl(Driver* d, int rows, int n_seqs, int flags, cudaStream_t s)
         else if (m.ar_mode == 2) { f_attn = FIN_NO_COMM | FIN_NO_H_WRITE | FIN_SAVE_EXTRA; f_ffn = FIN_ADD_EXTRA; h_mid = m.h_tmp; }
         CK(chain_add(d, L.out_proj, m.attn_out, m.ld_attn, no_lazy(), rows, epi_finish(d, f_attn, h_mid), s));
         // ---- FFN
+        if (L.ffn_kind != 0) {
+            if (tp && m.ar_mode != 0) return cudaErrorNotSupported;     // the INT8 path keeps the exact placement
+            CK(chain_flush(d, rows, s));
+            CK(ffn_q8(d, L, m.h, rows, m.ss, s));
+            last_norm = L.next_norm;
+            continue;
+        }
         CK(chain_add(d, L.gate_up, nullptr, 0, lazy(d, h_mid, L.ffn_norm), rows,
                      epi_store(m.act, m.F_pad, m.F_pad, EPI_SILU_PAIR), s));
         CK(chain_add(d, L.down, m.act, m.F_pad, no_lazy(), rows, epi_finish(d, f_ffn, m.h), s));
@@ -401,14 +466,14 @@ static int row_parallel(Driver* d, const LinearDesc& L, const void* x, int ldx, 
     c.twoshot = 1; c.pushed = 1;
     for (int r = 0; r < m.comm.tp; ++r) c.gather[r] = m.coll_gather[r];
     c.mc_gather = m.coll_mc_gather; c.counters = m.coll_counters;
-    d->launches++;
+    d->launches++; d->exchanges++;
     return b2_allreduce(&c, 2 * 148, s);
 }
 
 static int rows_impl(Driver* d, int T, int n_seqs, int flags, cudaStream_t s) {
     const ModelDesc& m = d->m;
     if (T < 1 || T > m.max_prefill) return cudaErrorInvalidValue;
-    d->launches = 0;
+    d->launches = 0; d->chain_launches = 0; d->exchanges = 0;
     CK(b2_prepare_rows(m.p_rows_tmpl, m.seqs, m.p_rows, T, s)); d->launches++;
     if (flags & STEP_EMBED_TOKENS) {
         CK(b2_embed_rmsnorm(m.embed, m.p_row_tokens, m.p_rows, m.seqs, m.first_norm, m.p_h, m.p_xn, nullptr, 0, T,
@@ -417,6 +482,7 @@ static int rows_impl(Driver* d, int T, int n_seqs, int flags, cudaStream_t s) {
     }
     for (int li = 0; li < m.n_layers; ++li) {
         const LayerDesc& L = d->layers[li];
+        struct Count { Driver* d; int li; long long l0; ~Count() { d->layer_launches[li] = (int)(d->launches - l0); } } count{d, li, d->launches};
         if (li > 0) { CK(b2_add_rmsnorm(m.p_h, nullptr, nullptr, L.attn_norm, m.p_xn, nullptr, T, m.H, m.eps, s)); d->launches++; }
         CK(run_gemm(d, L.in_proj, m.p_xn, m.H, T, m.p_proj, m.ld_proj, L.in_proj.N, TC_EPI_STORE_F16, s));
         if (L.type == 0) {
@@ -464,6 +530,7 @@ static int rows_impl(Driver* d, int T, int n_seqs, int flags, cudaStream_t s) {
         }
         // prefill always uses the exact all-reduce placement
         CK(row_parallel(d, L.out_proj, m.p_attn, m.ld_attn, T, s));
+        if (L.ffn_kind != 0) { CK(ffn_q8(d, L, m.p_h, T, nullptr, s)); continue; }
         CK(b2_add_rmsnorm(m.p_h, nullptr, nullptr, L.ffn_norm, m.p_xn, nullptr, T, m.H, m.eps, s)); d->launches++;
         CK(run_gemm(d, L.gate_up, m.p_xn, m.H, T, m.p_act, m.F_pad, m.F_pad, TC_EPI_SILU_PAIR, s));
         CK(row_parallel(d, L.down, m.p_act, m.F_pad, T, s));
@@ -507,15 +574,20 @@ static int run_impl(Driver* d, int rows, int n_seqs, int flags, cudaStream_t s) 
     return (flags & STEP_GEMM_PATH) ? rows_impl(d, rows, n_seqs, flags, s) : step_impl(d, rows, n_seqs, flags, s);
 }
 
-B2_API int b2_driver_prefill(void* h, int T, int flags, cudaStream_t s) { return rows_impl((Driver*)h, T, 1, flags, s); }
+static int counted(Driver* d, int rc) {
+    d->total_launches += d->launches; d->total_exchanges += d->exchanges;
+    return rc;
+}
+B2_API int b2_driver_prefill(void* h, int T, int flags, cudaStream_t s) { return counted((Driver*)h, rows_impl((Driver*)h, T, 1, flags, s)); }
 B2_API int b2_driver_rows(void* h, int T, int n_seqs, int flags, cudaStream_t s) {
-    return rows_impl((Driver*)h, T, n_seqs, flags, s);
+    return counted((Driver*)h, rows_impl((Driver*)h, T, n_seqs, flags, s));
 }
 
 B2_API void* b2_driver_create(const ModelDesc* m, const LayerDesc* layers) {
     Driver* d = new Driver();
     d->m = *m;
     d->layers.assign(layers, layers + m->n_layers);
+    d->layer_launches.assign(m->n_layers, 0);
     return d;
 }
 B2_API void b2_driver_destroy(void* h) {
@@ -526,11 +598,17 @@ B2_API void b2_driver_destroy(void* h) {
     delete d;
 }
 B2_API int b2_driver_step(void* h, int rows, int n_seqs, int flags, cudaStream_t s) {
-    return run_impl((Driver*)h, rows, n_seqs, flags, s);
+    return counted((Driver*)h, run_impl((Driver*)h, rows, n_seqs, flags, s));
 }
+B2_API long long b2_driver_total_launches(void* h) { return ((Driver*)h)->total_launches; }
+B2_API long long b2_driver_total_exchanges(void* h) { return ((Driver*)h)->total_exchanges; }
 B2_API long long b2_driver_launches(void* h) { return ((Driver*)h)->launches; }
 B2_API long long b2_driver_chain_launches(void* h) { return ((Driver*)h)->chain_launches; }
 B2_API long long b2_driver_exchanges(void* h) { return ((Driver*)h)->exchanges; }
+B2_API int b2_driver_layer_launches(void* h, int layer) {
+    Driver* d = (Driver*)h;
+    return layer >= 0 && layer < (int)d->layer_launches.size() ? d->layer_launches[layer] : -1;
+}
 
 // Capture one step into a graph (the stream must be a non-default stream).
 B2_API int b2_driver_capture(void* h, int rows, int n_seqs, int flags, cudaStream_t s) {
@@ -548,6 +626,7 @@ B2_API int b2_driver_capture(void* h, int rows, int n_seqs, int flags, cudaStrea
     e = cudaGraphInstantiate(&d->exec, g, 0);
     if (e != cudaSuccess) return e;
     d->graph_rows = rows; d->graph_flags = flags;
+    d->graph_launches = d->launches; d->graph_exchanges = d->exchanges;
     return 0;
 }
 // Replay the captured step `n` times back to back.
@@ -557,6 +636,7 @@ B2_API int b2_driver_replay(void* h, int n, cudaStream_t s) {
     for (int i = 0; i < n; ++i) {
         cudaError_t e = cudaGraphLaunch(d->exec, s);
         if (e != cudaSuccess) return e;
+        d->total_launches += d->graph_launches; d->total_exchanges += d->graph_exchanges;
     }
     return 0;
 }

@@ -305,6 +305,26 @@ B2_API int b2_residual_add(float* h, const float* d32, const void* d16, size_t n
     return cudaGetLastError();
 }
 
+// h[r] += d32[r] (d32 may be null) and ss[r][0] = sum(h[r]^2), ss[r][1..np) = 0: what a consumer that
+// normalises lazily (LazyNorm) expects from its producer.
+__global__ void __launch_bounds__(256) residual_add_ss_kernel(float* __restrict__ h, const float* __restrict__ d32,
+                                                              float* __restrict__ ss, int np, int H) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    float acc = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = h[(size_t)r * H + i];
+        if (d32) { v += d32[(size_t)r * H + i]; h[(size_t)r * H + i] = v; }
+        acc += v * v;
+    }
+    const float tot = block_sum(acc, red);
+    if (ss) for (int i = threadIdx.x; i < np; i += blockDim.x) ss[(size_t)r * np + i] = i ? 0.f : tot;
+}
+B2_API int b2_residual_add_ss(float* h, const float* d32, float* ss, int np, int n_rows, int H, cudaStream_t s) {
+    residual_add_ss_kernel<<<n_rows, 256, 0, s>>>(h, d32, ss, np, H);
+    return cudaGetLastError();
+}
+
 __global__ void f32_to_f16_kernel(const float* __restrict__ a, __half* __restrict__ b, size_t n) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) b[i] = __float2half(a[i]);

@@ -139,3 +139,25 @@ B2_API int b2_qknorm_rope_cachew(void* qkv, int ld, const void* rows, const void
                                  const float* cos_tab, const float* sin_tab, void* kcache, void* vcache,
                                  int n_rows, int nq, int nkv, int hd, int rot, int max_seq, int interleaved,
                                  float eps, cudaStream_t s);
+
+// ---- INT8-activation products (csrc/quant8.cu) as the step driver uses them
+struct Quant8Params {
+    const void* w;
+    const float* w_scale;
+    const __half* g_scale;
+    const int8_t* xq;
+    const float* x_scale;
+    void* out;
+    int K, N, T, ldo, group, out_f16, w4, pad;
+};
+struct ActQuantParams {
+    const __half* x;
+    int8_t* xq;
+    float* scale;
+    int T, K, ldx, pad;
+};
+B2_API int b2_linear_q8(const Quant8Params* p, cudaStream_t s);
+B2_API int b2_act_quant(const ActQuantParams* p, cudaStream_t s);
+B2_API int b2_silu_mul(const void* gate, const void* up, void* out, size_t n, cudaStream_t s);
+B2_API int b2_residual_add(float* h, const float* d32, const void* d16, size_t n, cudaStream_t s);
+B2_API int b2_residual_add_ss(float* h, const float* d32, float* ss, int np, int n_rows, int H, cudaStream_t s);

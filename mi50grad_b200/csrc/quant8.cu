@@ -24,23 +24,6 @@
 
 #include "kernels.cuh"
 
-struct Quant8Params {
-    const void* w;
-    const float* w_scale;
-    const __half* g_scale;
-    const int8_t* xq;
-    const float* x_scale;
-    void* out;
-    int K, N, T, ldo, group, out_f16, w4, pad;
-};
-
-struct ActQuantParams {
-    const __half* x;
-    int8_t* xq;
-    float* scale;
-    int T, K, ldx, pad;
-};
-
 namespace {
 
 constexpr int Q8_WARPS = 8;

@@ -171,13 +171,18 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const SamplePara
     float* row = p.logits + (size_t)r * p.ld;
     // ---- 1. repetition penalty
     if (p.past && p.rep_penalty != 1.f) {
-        const int np = min(p.n_past[r], min(p.max_past, SAMPLE_MAX_CAND));
-        const int tok = tid < np ? p.past[(size_t)r * p.max_past + tid] - p.vocab_offset : -1;
-        const bool in = tok >= 0 && tok < p.vocab;
-        const float v = in ? row[tok] : 0.f;
-        __syncthreads();
-        if (in) row[tok] = v > 0.f ? v / p.rep_penalty : v * p.rep_penalty;
-        __syncthreads();
+        // any number of past tokens, in blocks of the CTA size.  Within a block all values are read before
+        // any is written, so a token listed twice in one block is penalised once; the generator passes each
+        // distinct past token once, which makes that true across blocks as well.
+        const int np = min(p.n_past[r], p.max_past);
+        for (int base = 0; base < np; base += SAMPLE_THREADS) {
+            const int tok = base + tid < np ? p.past[(size_t)r * p.max_past + base + tid] - p.vocab_offset : -1;
+            const bool in = tok >= 0 && tok < p.vocab;
+            const float v = in ? row[tok] : 0.f;
+            __syncthreads();
+            if (in) row[tok] = v > 0.f ? v / p.rep_penalty : v * p.rep_penalty;
+            __syncthreads();
+        }
     }
     auto block_count = [&](int c) -> int {
 #pragma unroll

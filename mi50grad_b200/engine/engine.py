@@ -97,6 +97,7 @@ class DeviceLayer:
         self.q_norm = self.k_norm = None
         self.wa = self.wb = self.conv_w = self.A_log = self.dt_bias = self.la_norm = None
         self.off = (0, 0, 0, 0, -1, -1)
+        self.ffn_q8 = None            # (kind, group, F, [(w, scale)] * 3) when quant_format is w8a8 / w4a8
 
 
 class InferenceEngine:
@@ -106,8 +107,9 @@ class InferenceEngine:
                  comm=None, max_batch: int = 1):
         if not torch.cuda.is_available():
             raise RuntimeError("InferenceEngine needs a CUDA device; use models.oracle.OracleEngine on CPU")
-        if quant_format != "w4a16":
-            raise NotImplementedError("the whole-model step runs w4a16; w8a8/w4a8 run per layer through engine.ffn_q8.FfnQ8")
+        if quant_format not in ("w4a16", "w8a8", "w4a8"):
+            raise ValueError("quant_format must be w4a16, w8a8 or w4a8")
+        self.quant_format = quant_format
         self.config = config
         self.ecfg = (engine_config or EngineConfig()).replace(
             tp_size=tp_size, tp_rank=tp_rank, max_seq_len=max_seq_len, max_batch=max_batch)
@@ -126,6 +128,7 @@ class InferenceEngine:
         self.final_norm: Optional[torch.Tensor] = None
         self.states = SequenceStates(config, self.spec, max_seq_len, max_batch, self.device)
         self._driver = None
+        self._exch_carry = 0
         self._graph_key = None
         self._tmpl_key = None
         self._ptmpl_key = None
@@ -191,21 +194,40 @@ class InferenceEngine:
             raise NotImplementedError("FFN projections must be INT4 (w4a16)")
         dl.gate_up = DeviceLinear(packed=pack_int4(interleave_gate_up(lw.gate.to(dev), lw.up.to(dev)), dev, rh))
         dl.down = _to_device_linear([lw.down], dev, rh)
+        if self.quant_format != "w4a16":
+            dl.ffn_q8 = self._convert_ffn_q8(lw.gate, lw.up, lw.down)
         self.layers[layer_idx] = dl
-        self._driver = None
+        self._drop_driver()
+
+    def _convert_ffn_q8(self, gate: Int4Linear, up: Int4Linear, down: Int4Linear):
+        """gate / up / down re-quantised for the INT8-activation path (reference:
+        src/model/weight_loader.py:122-249): W8A8 = int8 per output channel, W4A8 = signed nibbles with the
+        checkpoint's group scales.  Returns (kind, group, F, [(w, scale)] * 3) on the device."""
+        from ..utils import quant as Q
+        conv = Q.int4_to_w8a8 if self.quant_format == "w8a8" else Q.int4_to_w4a8
+        dev = self.device
+        out = []
+        for lin in (gate, up, down):
+            need = 64 if self.quant_format == "w8a8" else 128
+            if lin.in_features % need or (self.quant_format == "w4a8" and lin.group_size % 128):
+                raise ValueError(f"{self.quant_format} needs in_features % {need} == 0 (got {lin.in_features})"
+                                 + (" and a group size that is a multiple of 128" if need == 128 else ""))
+            w, sc = conv(lin.to(dev))
+            out.append((w.contiguous(), sc.contiguous()))
+        return (1 if self.quant_format == "w8a8" else 2, gate.group_size, gate.out_features, out)
 
     def load_final_norm(self, w: torch.Tensor):
         self.final_norm = self._h16(torch.as_tensor(w))
-        self._driver = None
+        self._drop_driver()
 
     def load_lm_head(self, w: torch.Tensor):
         """`w` is this rank's vocabulary slice [vocab_local, hidden]."""
         self.lm_head = DeviceLinear(dense=self._h16(torch.as_tensor(w)))
-        self._driver = None
+        self._drop_driver()
 
     def load_embedding(self, w: torch.Tensor):
         self.embed = self._h16(torch.as_tensor(w))
-        self._driver = None
+        self._drop_driver()
 
     def load_model(self, mw: ModelWeights):
         """`mw` must already be this rank's shard."""
@@ -252,6 +274,14 @@ class InferenceEngine:
             if Fp != sp.ffn_local:
                 raise NotImplementedError("random init needs ffn_local % 64 == 0")
             dl.down = rnd(sp.ffn_local, H)
+            if self.quant_format != "w4a16":
+                from ..ops.packing import unpack_fragments
+                gu = unpack_fragments(dl.gate_up.packed)              # gate/up interleaved by 8
+                idx = torch.arange(2 * Fp, device=dev).reshape(-1, 2, 8)
+                take = lambda cols: Int4Linear(gu.qweight[:, cols].contiguous(), gu.scales[:, cols].contiguous(),
+                                               None if gu.zeros is None else gu.zeros[:, cols].contiguous(), gu.group_size, 0)
+                dl.ffn_q8 = self._convert_ffn_q8(take(idx[:, 0].reshape(-1)), take(idx[:, 1].reshape(-1)),
+                                                 unpack_fragments(dl.down.packed))
             self.layers[i] = dl
         # replicated tensors use a rank-independent generator so every rank holds the same values
         g2 = torch.Generator(device=dev)
@@ -260,7 +290,7 @@ class InferenceEngine:
         vl = sp.vocab_local
         self.lm_head = DeviceLinear(dense=(torch.randn(vl, H, device=dev, generator=gen) * embed_std).half())
         self.final_norm = ones(H)
-        self._driver = None
+        self._drop_driver()
 
     def weight_bytes(self) -> int:
         n = sum(l.nbytes() for dl in self.layers for l in (dl.in_proj, dl.out_proj, dl.gate_up, dl.down))
@@ -337,6 +367,13 @@ class InferenceEngine:
         need = max([int(self.lib.b2_chain_scratch_floats(l.packed.KB, l.packed.NTL // 4, R)) for l in int4] + [1])
         b["chain_scratch"] = f32(need)
         b["chain_counters"] = i32(8)
+        # INT8-activation FFN (quant_format w8a8 / w4a8): quantised rows, their scales, gate / up / down outputs
+        if any(dl.ffn_q8 is not None for dl in self.layers):
+            Pq = max(R, min(512, self.max_seq_len))
+            Fq = max(dl.ffn_q8[2] for dl in self.layers if dl.ffn_q8 is not None)
+            b["q8_xq"] = alloc((Pq, max(H, Fq)), torch.int8)
+            b["q8_sx"], b["q8_xn"] = f32(Pq), f16(Pq, H)
+            b["q8_gate"], b["q8_up"], b["q8_down"] = f16(Pq, Fq), f16(Pq, Fq), f32(Pq, H)
         # tagged hand-off buffers between the projections of one chain launch ({value, tag} pairs)
         self.chain_act_cols = -(-self.F_pad // 2)
         b["chain_tag_h"], b["chain_tag_ss"] = f32(R, H, 2), f32(R, self.np, 2)
@@ -398,6 +435,9 @@ class InferenceEngine:
         m.chain_act_cols, m.use_chain = self.chain_act_cols, int(self.use_chain)
         m.chain_tag_h, m.chain_tag_ss = b["chain_tag_h"].data_ptr(), b["chain_tag_ss"].data_ptr()
         m.chain_tag_act = b["chain_tag_act"].data_ptr()
+        for k in ("q8_xq", "q8_sx", "q8_gate", "q8_up", "q8_down", "q8_xn"):
+            if k in b:
+                setattr(m, k, b[k].data_ptr())
         m.seqs = self.states.seqs.data_ptr()
         m.comm = self._comm_ctx()
         m.max_prefill = self.max_prefill
@@ -446,6 +486,10 @@ class InferenceEngine:
                 d.conv_state = self.states.dn.layer_conv(i).data_ptr()
                 d.state = self.states.dn.layer_S(i).data_ptr()
                 d.off_q, d.off_k, d.off_v, d.off_z, d.off_a, d.off_b = dl.off
+            if dl.ffn_q8 is not None:
+                d.ffn_kind, d.q8_group, d.q8_F, ws = dl.ffn_q8
+                for j, (w, sc) in enumerate(ws):
+                    d.q8_w[j], d.q8_s[j] = w.data_ptr(), sc.data_ptr()
         self._model_desc, self._layer_descs = m, descs
         self._driver = self.lib.b2_driver_create(C.byref(m), descs)
         self._graph_key = None
@@ -917,8 +961,25 @@ class InferenceEngine:
         self._launch_counts.clear()
 
     def get_layer_launch_count(self, layer_idx: int) -> int:
-        """Kernels issued per layer and step (reference: src/inference/engine.py:993-1023)."""
-        return 6 if self.layers[layer_idx].type == 0 else 5
+        """Kernels the driver issued inside this layer's part of the most recent step (issued or
+        captured); 0 before the first step (reference: src/inference/engine.py:993-1023).  A chain
+        launch that spans two layers counts for the layer in which it is issued."""
+        self._ensure_driver()
+        return max(0, int(self.lib.b2_driver_layer_launches(C.c_void_p(self._driver), layer_idx)))
+
+    def _drop_driver(self):
+        """Forget the driver plan (weights or settings changed); the counters it kept are carried over."""
+        if getattr(self, "_driver", None) is not None:
+            self._exch_carry += int(self.lib.b2_driver_total_exchanges(C.c_void_p(self._driver)))
+            self.lib.b2_driver_destroy(C.c_void_p(self._driver))
+        self._driver = None
+
+    def exchange_count(self) -> int:
+        """Cross-GPU exchanges (all-reduces fused into kernels) since the driver was built, counted
+        by the driver as it issues or replays steps."""
+        if self._driver is None:
+            return self._exch_carry
+        return self._exch_carry + int(self.lib.b2_driver_total_exchanges(C.c_void_p(self._driver)))
 
     def launches_per_step(self) -> int:
         self._ensure_driver()
@@ -935,7 +996,5 @@ class InferenceEngine:
             self.comm.check_status()
 
     def cleanup(self):
-        if self._driver is not None:
-            self.lib.b2_driver_destroy(C.c_void_p(self._driver))
-            self._driver = None
+        self._drop_driver()
         self.buf = {}

@@ -243,11 +243,9 @@ class TPInferenceEngine:
 
     # ------------------------------------------------------------------ counters
     def get_allreduce_call_count(self) -> int:
-        """All-reduces issued so far (fused into GEMV kernels; counted per step
-        from the layer count and the all-reduce placement)."""
-        per_layer = 2 if self.ecfg.ar_mode == "exact" else 1
-        n = 0 if self.tp_size == 1 else per_layer * self.config.num_hidden_layers * self.engine._steps
-        return n - getattr(self, "_ar_base", 0)
+        """All-reduces issued so far: every exchange fused into a projection or collective kernel, as
+        counted by the step driver while it issues and replays steps."""
+        return self.engine.exchange_count() - getattr(self, "_ar_base", 0)
 
     def reset_allreduce_counter(self):
         self._ar_base = 0
@@ -268,7 +266,7 @@ class TPInferenceEngine:
             raise ValueError(mode)
         self.ecfg = self.ecfg.replace(ar_mode=mode)
         self.engine.ecfg = self.engine.ecfg.replace(ar_mode=mode)
-        self.engine._driver = None
+        self.engine._drop_driver()
 
     def set_graph_dispatch(self, enabled: bool):
         self.ecfg = self.ecfg.replace(use_graph=bool(enabled))

@@ -57,6 +57,15 @@ class TextGenerator:
         greedy = params.temperature == 0 and params.repetition_penalty == 1.0
         past = list(prompt_ids)
         rng = np.random.default_rng(params.seed)
+        # seed of the device sampler for this call: the caller's, or (unseeded, like the host path) a fresh one
+        # from the host generator -- rank 0's under tensor parallelism, so that every rank draws the same tokens
+        self._call_seed = params.seed if params.seed is not None else int(rng.integers(0, 2**31 - 1))
+        if params.seed is None and getattr(self.engine, "tp_size", 1) > 1:
+            import torch.distributed as dist
+            if dist.is_available() and dist.is_initialized():
+                box = [self._call_seed]
+                dist.broadcast_object_list(box, src=0)
+                self._call_seed = int(box[0])
         tok = self.prefill(prompt_ids, seq)
         # on a GPU the sampler runs on the device (only the sampled id crosses PCIe); under tensor
         # parallelism every rank samples the all-gathered logits with the same seed, so all ranks draw
@@ -78,10 +87,11 @@ class TextGenerator:
     def _sample_device(self, params: SamplingParams, past: Sequence[int], step: int) -> int:
         from ..ops import kernels as K
         dev = self.core.device
-        window = list(past)[-1024:]
-        pt = torch.tensor([window], dtype=torch.int32, device=dev) if window else torch.zeros(1, 1, dtype=torch.int32, device=dev)
-        npast = torch.tensor([len(window)], dtype=torch.int32, device=dev)
-        seed = (params.seed if params.seed is not None else 0) * 1000003 + step
+        # the repetition penalty covers every distinct past token once, as the host sampler does
+        uniq = sorted(set(int(t) for t in past))
+        pt = torch.tensor([uniq], dtype=torch.int32, device=dev) if uniq else torch.zeros(1, 1, dtype=torch.int32, device=dev)
+        npast = torch.tensor([len(uniq)], dtype=torch.int32, device=dev)
+        seed = self._call_seed * 1000003 + step
         if getattr(self.engine, "tp_size", 1) > 1:
             logits = self.engine.compute_logits(None).reshape(1, -1).contiguous()
         else:

@@ -439,3 +439,37 @@ def linear_w4a8(w_packed: torch.Tensor, g_scale: torch.Tensor, xq: torch.Tensor,
     Integer accumulation inside a group, fp32 across groups."""
     assert w_packed.dtype == torch.int32 and g_scale.dtype == torch.float16 and g_scale.is_contiguous()
     return _linear_q8(w_packed, xq, x_scale, w_packed.shape[0], out_dtype, g_scale=g_scale, group=group)
+
+
+# -- probes (csrc/comm.cu; reference: src/kernels/p2p_bandwidth_kernels.hip:187-278) ------------------
+
+def probe_read(src_ptr: int, nbytes: int, dst_ptr: Optional[int] = None, multimem: bool = False, ctas: int = 296):
+    """Stream `nbytes` (a multiple of 16) from a device address -- local memory, a peer's mapping, or (with
+    `multimem`) a multicast address read with multimem.ld_reduce -- into registers, or into `dst_ptr`
+    (local or peer) when given.  Launches on the current stream; time it with CUDA events."""
+    L.check(L.lib().b2_probe_read(C.c_void_p(src_ptr), None if dst_ptr is None else C.c_void_p(dst_ptr),
+                                  C.c_size_t(nbytes), int(multimem), ctas, L.stream()), "probe_read")
+
+
+def probe_latency(chain: torch.Tensor, hops: int, chain_ptr: Optional[int] = None) -> float:
+    """Average latency (ns) of `hops` dependent 4-byte loads that walk the index chain stored in `chain`
+    (uint32 indices; `chain_ptr` overrides the address, e.g. with a peer's mapping of the same buffer)."""
+    out = torch.zeros(2, dtype=torch.int64, device=chain.device)
+    L.check(L.lib().b2_probe_latency(C.c_void_p(chain_ptr if chain_ptr is not None else chain.data_ptr()), hops,
+                                     C.c_void_p(out.data_ptr()), L.stream()), "probe_latency")
+    torch.cuda.synchronize(chain.device)
+    return float(out[0].item()) / hops
+
+
+def wait_self_test(wait_us: int = 2000) -> dict:
+    """Run the bounded device wait on a flag that nothing sets and return the status record it leaves
+    ({code, kernel, peer, epoch}): the wait must give up after `wait_us` and the context must stay usable."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    c = L.null_comm()
+    c.status, c.wait_ns = status.data_ptr(), int(wait_us) * 1000
+    L.check(L.lib().b2_wait_test(C.byref(c), C.c_void_p(flag.data_ptr()), L.stream()), "wait_test")
+    torch.cuda.synchronize(dev)
+    st = status.tolist()
+    return {"code": st[0], "kernel": st[1], "peer": st[2], "epoch": st[3]}

@@ -133,7 +133,9 @@ class LayerDesc(C.Structure):
                 ("q_norm", vp), ("k_norm", vp), ("kcache", vp), ("vcache", vp),
                 ("wa", vp), ("wb", vp), ("conv_w", vp), ("conv_state", vp), ("state", vp),
                 ("A_log", vp), ("dt_bias", vp), ("la_norm", vp),
-                ("off_q", i32), ("off_k", i32), ("off_v", i32), ("off_z", i32), ("off_a", i32), ("off_b", i32)]
+                ("off_q", i32), ("off_k", i32), ("off_v", i32), ("off_z", i32), ("off_a", i32), ("off_b", i32),
+                ("ffn_kind", i32), ("q8_group", i32), ("q8_F", i32), ("pad_q8", i32),
+                ("q8_w", vp * 3), ("q8_s", vp * 3)]
 
 
 class SampleParams(C.Structure):
@@ -192,6 +194,7 @@ class ModelDesc(C.Structure):
                 ("k0", vp), ("v0", vp), ("kv_layer_stride", i64),
                 ("chain_scratch", vp), ("chain_counters", vp), ("chain_act_cols", i32), ("use_chain", i32),
                 ("chain_tag_h", vp), ("chain_tag_ss", vp), ("chain_tag_act", vp),
+                ("q8_xq", vp), ("q8_sx", vp), ("q8_gate", vp), ("q8_up", vp), ("q8_down", vp), ("q8_xn", vp),
                 ("comm", CommCtx)]
 
 
@@ -231,6 +234,8 @@ def lib() -> C.CDLL:
     _lib.b2_driver_launches.restype = i64
     _lib.b2_driver_chain_launches.restype = i64
     _lib.b2_driver_exchanges.restype = i64
+    _lib.b2_driver_total_launches.restype = i64
+    _lib.b2_driver_total_exchanges.restype = i64
     _lib.b2_chain_scratch_floats.restype = i64
     _lib.b2_gemv_int4_smem.restype = C.c_size_t
     return _lib

@@ -43,6 +43,59 @@ def scenario_allreduce(multimem: bool):
     return comm.has_multimem
 
 
+def scenario_fused_shapes(multimem: bool):
+    """The fused row-parallel projection (INT4 GEMV + exchange over NVLink + residual add + sums of squares
+    for the next RMSNorm) at the 27B model's shapes, K = 6144 / tp and 17408 / tp -> 5120, one and five token
+    rows, against an fp32 reference: sum over ranks of x_r W_r^T (all-reduced with NCCL) + h.  Both forms
+    are checked: the stand-alone GEMV's finisher and the chain kernel's tile-granular exchange."""
+    from mi50grad_b200.ops import kernels as K
+    from mi50grad_b200.ops import lib as L
+    from mi50grad_b200.ops.packing import pack_int4
+    from mi50grad_b200.parallel.symm import SymmComm
+    from mi50grad_b200.utils.quant import random_int4_linear
+    rank, world = dist.get_rank(), dist.get_world_size()
+    comm = SymmComm(max_rows=8, hidden=5120, use_multimem=multimem)
+    dev, ctx, H = comm.device, comm.ctx(), 5120
+    for Kfull in (6144, 17408):
+        Kd = Kfull // world
+        Kd -= Kd % 64
+        gen = torch.Generator().manual_seed(1000 * Kfull + rank)
+        lin = random_int4_linear(Kd, H, 128, gen)
+        lin.zeros = torch.randint(0, 16, lin.zeros.shape, generator=gen).half()
+        pk = pack_int4(lin, dev)
+        wd = lin.dense().to(dev)
+        for rows in (1, 5):
+            x = torch.randn(rows, Kd, generator=gen).half().to(dev)
+            h0 = torch.randn(rows, H, generator=torch.Generator().manual_seed(9)).to(dev)
+            ref = x.float() @ wd.t()
+            dist.all_reduce(ref)
+            ref = (ref + h0).cpu()
+            # stand-alone GEMV with the finisher
+            h = h0.clone()
+            ss = K.gemv(pk, x, mode=L.EPI_FINISH, h=h, comm=ctx)
+            torch.cuda.synchronize()
+            comm.check_status()
+            assert _rel(h.cpu(), ref) < 2e-4, ("finisher", Kfull, rows, _rel(h.cpu(), ref))
+            assert torch.allclose(ss.sum(-1).cpu(), ref.pow(2).sum(-1), rtol=1e-3)
+            # chain kernel, one projection: every 64-column tile is exchanged by the warp that completes it
+            h2 = h0.clone()
+            ss2 = torch.zeros(rows, H // 64, device=dev)
+            op = K.chain_op(pk, x=x, mode=L.EPI_FINISH, h=h2, ss_part=ss2)
+            bufs = K.chain_scratch([op], rows, dev)
+            for rep in range(3):                      # epochs advance, staging parity alternates
+                h2.copy_(h0)
+                K.chain([op], rows, bufs, comm=ctx)
+            torch.cuda.synchronize()
+            comm.check_status()
+            assert _rel(h2.cpu(), ref) < 2e-4, ("chain", Kfull, rows, _rel(h2.cpu(), ref))
+            assert torch.allclose(ss2.sum(-1).cpu(), ref.pow(2).sum(-1), rtol=1e-3)
+            # every rank holds the same bits
+            hs = [torch.empty_like(h2) for _ in range(world)]
+            dist.all_gather(hs, h2)
+            assert all(torch.equal(hs[0], t) for t in hs)
+    comm.close()
+
+
 def scenario_tp_engine(ar_mode: str, multimem: bool, model: str = "tiny"):
     """Small hybrid model at TP=world on GPUs vs the fp32 CPU oracle.  'medium' has 8 query /
     4 KV heads and 8 / 16 DeltaNet heads, so it shards over 8 ranks with every KV head
@@ -198,6 +251,9 @@ def main():
             extra = f"multimem={mm}"
         elif scenario == "tp_engine":
             scenario_tp_engine(sys.argv[2], sys.argv[3] == "multimem", sys.argv[4] if len(sys.argv) > 4 else "tiny")
+            extra = sys.argv[2]
+        elif scenario == "fused_shapes":
+            scenario_fused_shapes(sys.argv[2] == "multimem")
             extra = sys.argv[2]
         elif scenario == "spec":
             scenario_spec()

@@ -140,6 +140,26 @@ def test_generator_samples_on_device(setup):
     assert a == b and len(a) == 10 and all(0 <= t < cfg.vocab_size for t in a)
     c = gen.generate_ids(_prompt(cfg, 9, seed=11), SamplingParams(temperature=0.8, top_k=20, top_p=0.9, max_tokens=10, seed=6))
     assert c != a or len(set(a)) == 1
+    # unseeded: every call draws its own seed, as the host sampler does, so two generations differ
+    free = SamplingParams(temperature=1.5, top_k=0, top_p=1.0, max_tokens=16)
+    u1 = gen.generate_ids(_prompt(cfg, 9, seed=11), free)
+    u2 = gen.generate_ids(_prompt(cfg, 9, seed=11), free)
+    u3 = gen.generate_ids(_prompt(cfg, 9, seed=11), free)
+    assert not (u1 == u2 == u3)
+    # the repetition penalty reaches every distinct past token, however many there are
+    from mi50grad_b200.generate.sampler import filtered_probs
+    from mi50grad_b200.ops import kernels as K
+    g = torch.Generator().manual_seed(3)
+    logits = torch.randn(1, 4096, generator=g) * 3
+    past = torch.randperm(4096, generator=g)[:2500].tolist()
+    pp = SamplingParams(temperature=1.0, top_k=50, top_p=0.95, repetition_penalty=1.7)
+    ref = filtered_probs(logits[0].numpy(), pp, past)
+    pt = torch.tensor([sorted(set(past))], dtype=torch.int32, device="cuda")
+    ids, probs = K.sample_top_p(logits.cuda().clone(), 1.0, 50, 0.95, 1.7, pt,
+                                torch.tensor([pt.shape[1]], dtype=torch.int32, device="cuda"), seed=1, debug=True)[1:3]
+    got = {int(i): float(p_) for i, p_ in zip(ids[0].tolist(), probs[0].tolist()) if i >= 0}
+    assert set(got) == set(int(i) for i in ref.nonzero()[0])
+    assert all(abs(got[i] - float(ref[i])) < 2e-5 for i in got)
     # after a short prompt (several rows in one step) the logits offered to the sampler are the last row's
     first = gen.prefill(_prompt(cfg, 5, seed=12))
     assert int(eng.logits(1)[0].argmax()) == first
@@ -214,3 +234,40 @@ def test_score_tokens_matches_oracle(setup):
     got = eng.score_tokens(ids).cpu()
     assert got.shape == ref.shape
     assert (got - ref).abs().max() < 0.05 and abs(eng.perplexity(ids) / orc.perplexity(ids) - 1) < 0.02
+
+
+@pytest.mark.parametrize("fmt", ["w8a8", "w4a8"])
+def test_whole_model_int8_activation_formats(fmt):
+    """quant_format w8a8 / w4a8: the FFN of every layer runs on the INT8-activation kernels (decode steps
+    and the many-row prefill path); hidden states stay close to the w4a16 engine's and greedy tokens of
+    the fp32 oracle are reproduced on a well-separated prompt (reference: tests/test_engine_w8a8_w4a8.py)."""
+    from mi50grad_b200.config import tiny_config
+    from mi50grad_b200.engine.engine import InferenceEngine
+    from mi50grad_b200.models.weights import random_model
+    cfg = tiny_config(intermediate_size=768)          # the W4A8 product needs K % 128 == 0 (down: K = FFN width)
+    mw = random_model(cfg, 0)
+    base = InferenceEngine(cfg, max_seq_len=128)
+    base.load_model(mw)
+    eng = InferenceEngine(cfg, max_seq_len=128, quant_format=fmt)
+    eng.load_model(mw)
+    ids = _prompt(cfg, 13, seed=4)
+    for e in (base, eng):
+        e.states.reset()
+        e.step_tokens(ids[:8], logits=False)
+        e.step_tokens(ids[8:], logits=True)
+    n = len(ids) - 8
+    h0, h1 = base.residual_stream(n).float().cpu(), eng.residual_stream(n).float().cpu()
+    for r in range(n):
+        assert cosine(h1[r], h0[r]) > 0.995, (fmt, r, cosine(h1[r], h0[r]))
+    lg0, lg1 = base.logits(n)[n - 1].float().cpu(), eng.logits(n)[n - 1].float().cpu()
+    assert cosine(lg1, lg0) > 0.99
+    # the many-row path (tensor-core projections + the same INT8 FFN) agrees with the step path
+    eng.states.reset()
+    first = eng.prefill_tokens(_prompt(cfg, 40, seed=5))
+    eng2 = InferenceEngine(cfg, max_seq_len=128, quant_format=fmt)
+    eng2.load_model(mw)
+    p40 = _prompt(cfg, 40, seed=5)
+    for i in range(0, 40, 8):
+        out = eng2.step_tokens(p40[i:i + 8], logits=i + 8 >= 40)
+    assert cosine(eng.residual_stream(1)[0].float().cpu(), eng2.residual_stream(8)[7].float().cpu()) > 0.995
+    assert eng.launches_per_step() > 0 and 0 <= first < cfg.vocab_size

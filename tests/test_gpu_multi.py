@@ -41,6 +41,12 @@ def test_tp_engine_tiny_peer_loads():
     _run(2, "tp_engine", "exact", "peer")
 
 
+@pytest.mark.parametrize("mode", ["peer", "multimem"])
+def test_fused_projection_exchange_at_model_shapes(mode):
+    """o_proj and down_proj of the 27B model sharded over every GPU of the box, 1 and 5 rows."""
+    _run(_n(), "fused_shapes", mode)
+
+
 def test_speculative_and_many_row_steps_under_tp():
     _run(2, "spec")
 
