@@ -319,6 +319,8 @@ def main():
                     help="fp16 attention/DeltaNet projections (the checkpoint form the reference ran)")
     ap.add_argument("--no-pp", action="store_true", help="skip the pp512 measurement")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-like-for-like", action="store_true",
+                    help="skip the second timed run with fp16 attention weights (the published numbers' checkpoint layout)")
     ap.add_argument("--mode", default="decode", choices=["decode", "batch-spec"],
                     help="batch-spec: batched decode with per-step draft verification (batch x ctx, --draft tokens)")
     ap.add_argument("--batch", type=int, default=16)
@@ -387,6 +389,9 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
     launches = eng.launches_per_step() * args.steps
+    ar_calls = eng.get_allreduce_call_count()
+    import ctypes as _C
+    chain_per_step = int(eng.engine.lib.b2_driver_chain_launches(_C.c_void_p(eng.engine._driver))) if eng.engine._driver else 0
 
     # ---- end to end through the public generation API: H2D token, step, D2H token, every step
     e2e = None
@@ -443,13 +448,65 @@ def main():
         except Exception as e:                      # an extra: never lose the headline line over it
             deferred = {"ar_mode": "deferred_consistent", "error": str(e)[:200]}
 
+    # ---- like-for-like with the published reference numbers: those ran the GPTQ checkpoint as it ships,
+    # INT4 FFN but fp16 attention / DeltaNet projections (about 10 GB more to stream per token).  The same
+    # timed loop on a second engine with that layout; `vs_baseline` and `vs_reference_same_tp` are computed
+    # from THIS run, the INT4-attention configuration stays the headline `value`.
+    lfl = None
+    streamed = eng.streamed_bytes_per_token()
+    if not args.fp16_attention and not args.no_like_for_like:
+        try:
+            eng.cleanup()
+            del eng
+            torch.cuda.empty_cache()
+            eng = TPInferenceEngine(cfg, device_ids=list(range(world)), max_seq_len=max_seq,
+                                    engine_config=EngineConfig.from_env(ar_mode=args.ar_mode))
+            eng.init_random(seed=0, int4_attention=False)
+            eng.reset()
+            eng.prefill_tokens(prompt)
+            eng.decode_tokens(max(args.warmup, 3), collect=False)
+            barrier_sync()
+            ev0.record()
+            eng.decode_tokens(args.steps, collect=False)
+            ev1.record()
+            barrier_sync()
+            tl = torch.tensor([ev0.elapsed_time(ev1)], device="cuda")
+            if world > 1:
+                dist.all_reduce(tl, op=dist.ReduceOp.MAX)
+            eng.check_status()
+            lms = float(tl.item())
+            lval = args.steps / (lms / 1e3)
+            lfl = {"attention_weights": "fp16 (layout of the GPTQ-Int4 checkpoint the published numbers ran)",
+                   "value": round(lval, 2), "unit": "tok/s", "ms_per_step": round(lms / args.steps, 4),
+                   "streamed_gb_per_token": round(eng.streamed_bytes_per_token() / 1e9, 2),
+                   "hbm_gbs_achieved": round(eng.streamed_bytes_per_token() / (lms / args.steps / 1e3) / 1e9, 1),
+                   "gpu_launches": eng.launches_per_step() * args.steps,
+                   "vs_baseline": round(lval / BASELINE_TG128_TP4, 2),
+                   "vs_reference_same_tp": round(lval / BASELINE_TG[world], 2) if world in BASELINE_TG else None}
+        except Exception as e:                      # an extra: never lose the headline line over it
+            lfl = {"error": str(e)[:200]}
+
     if rank == 0:
         value = args.steps / (ms / 1e3)
+        from mi50grad_b200.utils.metrics import Metrics
+        rec = Metrics(run="tg128", n_gpus=world, tokens=args.steps, steps=args.steps, seconds=ms / 1e3,
+                      prefill_tokens=args.prompt_len, launches_per_step=launches // max(args.steps, 1),
+                      allreduce_calls=ar_calls,
+                      ttft_ms=(e2e or {}).get("ttft_ms", 0.0), prefill_ms=(pp or {}).get("ms", 0.0)).finish()
+        rec.extra = {"ar_mode": args.ar_mode, "chain_launches_per_step": chain_per_step}
+        if os.environ.get("B200GRAD_METRICS_FILE"):
+            rec.dump(os.environ["B200GRAD_METRICS_FILE"])
+        like = lfl if lfl and "value" in lfl else None
         out = {
             "metric": "tg128 decode tok/s (bs1), Qwen3.5-27B GPTQ-Int4", "value": round(value, 2), "unit": "tok/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": round(value / BASELINE_TG128_TP4, 2), "dtype": "fp16 activations / int4 weights / fp32 accumulate",
+            "vs_baseline": like["vs_baseline"] if like else (round(value / BASELINE_TG128_TP4, 2) if args.fp16_attention else None),
+            "vs_baseline_basis": "like_for_like.value (fp16 attention weights, as in the checkpoint behind the published "
+                                 "56.33 tok/s) / 56.33; the INT4-attention `value` has no published counterpart: "
+                                 "vs_baseline_int4_attention",
+            "vs_baseline_int4_attention": round(value / BASELINE_TG128_TP4, 2),
+            "dtype": "fp16 activations / int4 weights / fp32 accumulate",
             "data": "synthetic (random-init weights of the named architecture, random token ids)",
             "impl": "ours",
             "config": {"model": "Qwen3.5-27B GPTQ-Int4 (random init)" if args.model == "27b" else "tiny hybrid",
@@ -457,12 +514,14 @@ def main():
                        "parallelism": f"tp{world}", "ar_mode": args.ar_mode,
                        "attention_weights": "fp16" if args.fp16_attention else "int4",
                        "l2": "inputs larger than L2: every step streams %.1f GB of weights per GPU"
-                             % (eng.streamed_bytes_per_token() / 1e9),
+                             % (streamed / 1e9),
                        "includes": "embedding gather, lm_head, arg-max, KV/DeltaNet state update",
                        "graph": "whole step in one CUDA graph"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
-            "vs_reference_same_tp": round(value / BASELINE_TG[world], 2) if world in BASELINE_TG else None,
-            "hbm_gbs_achieved": round(eng.streamed_bytes_per_token() / (ms / args.steps / 1e3) / 1e9, 1),
+            "vs_reference_same_tp": like["vs_reference_same_tp"] if like else None,
+            "like_for_like": lfl,
+            "hbm_gbs_achieved": round(streamed / (ms / args.steps / 1e3) / 1e9, 1),
+            "metrics": rec.to_dict(),
             "pp512": pp, "one_allreduce_per_layer": deferred,
         }
         print(json.dumps(out))

@@ -204,6 +204,7 @@ struct SmemOptIn {
 #define B2_KID_BARRIER 4
 #define B2_KID_TEST 5
 #define B2_KID_GEMM_RS 6
+#define B2_KID_SAMPLE 10         // distributed sampler: a peer's candidate list did not arrive
 #define B2_KID_CHAIN_DEP 7      // chain kernel: an op's producers did not finish
 #define B2_KID_CHAIN_TILE 8     // chain kernel: a peer's tile did not arrive
 #define B2_KID_CHAIN_COPY 9     // chain kernel: a weight copy did not land

@@ -145,6 +145,8 @@ struct SampleParams {
     int* out_tokens;             // [rows]
     int* dbg_ids;                // optional [rows][SAMPLE_MAX_CAND]: kept candidates (-1 padded)
     float* dbg_probs;            // optional [rows][SAMPLE_MAX_CAND]
+    CommCtx comm;                // tp > 1: `logits` is this rank's vocabulary slice (one row); the ranks exchange
+                                 // their candidate lists through symmetric memory and all draw the same token
 };
 
 __device__ __forceinline__ unsigned ord_key(float f) {
@@ -160,7 +162,20 @@ __device__ __forceinline__ float uniform01(unsigned long long seed, unsigned lon
     return (float)((z >> 40) + 0.5) * (1.0f / 16777216.0f);
 }
 
+// Where candidate (v, id) stands in a list sorted by (value descending, id ascending): the number of
+// entries that come before it.
+__device__ __forceinline__ int rank_in_list(const float* lv, const int* li, int n, float v, int id) {
+    int lo = 0, hi = n;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        const bool before = lv[mid] > v || (lv[mid] == v && li[mid] < id);
+        if (before) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+}
+
 __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const SampleParams p) {
+    extern __shared__ __align__(16) unsigned char dyn_smem[];      // tp > 1: [tp][K] values, [tp][K] ids
     __shared__ float c_val[SAMPLE_MAX_CAND];
     __shared__ int c_id[SAMPLE_MAX_CAND];
     __shared__ float red[32];
@@ -247,7 +262,64 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const SamplePara
             }
             __syncthreads();
         }
-    const int n = min(s_cnt, K);
+    int n = min(s_cnt, K);
+    // ---- 3b. tensor parallel: every rank holds the K best of its vocabulary slice; the K best overall are
+    // among their union.  Each rank publishes its sorted list (values + global ids) in its staging area,
+    // the lists are copied into shared memory and merged by rank counting, so that every rank ends up
+    // with the same K candidates in the same order and, with the same seed, draws the same token.  No
+    // logits are gathered and nothing leaves the device.
+    if (p.comm.tp > 1) {
+        const CommCtx& c = p.comm;
+        __shared__ int s_fail;
+        const uint32_t epoch_next = *c.epoch + 1u;
+        float* mine = c.part[c.rank] + (size_t)(epoch_next & 1) * c.part_stride;      // [0] count, then K values, K ids
+        if (tid == 0) { mine[0] = __int_as_float(n); s_fail = 0; }
+        if (tid < K) {
+            mine[1 + tid] = c_val[tid];
+            mine[1 + K + tid] = __int_as_float(tid < n ? c_id[tid] + p.vocab_offset : 0x7fffffff);
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) *c.epoch = epoch_next;
+        if (tid < c.tp && tid != c.rank) {
+            st_release_sys_u32(c.sig[tid] + c.rank, epoch_next);
+            if (!wait_reached(c.sig[c.rank] + tid, epoch_next, c.wait_ns)) {
+                report_timeout(c, B2_KID_SAMPLE, tid, epoch_next);
+                s_fail = 1;
+            }
+        }
+        __syncthreads();
+        float* lv = (float*)dyn_smem;                      // [tp][K]
+        int* li = (int*)(lv + (size_t)c.tp * K);           // [tp][K]
+        __shared__ int ln[B2_MAX_TP];
+        for (int pr = 0; pr < c.tp; ++pr) {
+            const float* src = c.part[pr] + (size_t)(epoch_next & 1) * c.part_stride;
+            const bool have = pr == c.rank || !s_fail;
+            if (tid == 0) ln[pr] = have ? min(K, max(0, __float_as_int(__ldcg(src)))) : 0;
+            if (tid < K) {
+                lv[pr * K + tid] = have ? __ldcg(src + 1 + tid) : -INFINITY;
+                li[pr * K + tid] = have ? __float_as_int(__ldcg(src + 1 + K + tid)) : 0x7fffffff;
+            }
+        }
+        __syncthreads();
+        c_val[tid] = -INFINITY; c_id[tid] = 0x7fffffff;
+        __syncthreads();
+        int total = 0;
+        for (int pr = 0; pr < c.tp; ++pr) total += ln[pr];
+        for (int pr = 0; pr < c.tp; ++pr) {
+            if (tid < ln[pr]) {
+                const float v = lv[pr * K + tid];
+                const int id = li[pr * K + tid];
+                int pos = tid;                                // entries of its own list that come before it
+                for (int q = 0; q < c.tp; ++q)
+                    if (q != pr) pos += rank_in_list(lv + q * K, li + q * K, ln[q], v, id);
+                if (pos < K) { c_val[pos] = v; c_id[pos] = id; }
+            }
+        }
+        __syncthreads();
+        n = min(total, K);
+    }
+    const int id_offset = p.comm.tp > 1 ? 0 : p.vocab_offset;      // merged ids are global already
     // ---- 4. softmax, scan, top-p, draw
     const float inv_t = 1.f / fmaxf(p.temperature, 1e-6f);
     const float vmax = c_val[0];
@@ -281,16 +353,26 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const SamplePara
     __syncthreads();
     if (tid < keep && cum >= u) atomicMin(&s_cnt, tid);
     __syncthreads();
-    if (tid == 0) p.out_tokens[r] = c_id[s_cnt] + p.vocab_offset;
+    if (tid == 0) p.out_tokens[r] = c_id[s_cnt] + id_offset;
     if (p.dbg_ids) {
-        p.dbg_ids[(size_t)r * SAMPLE_MAX_CAND + tid] = tid < keep ? c_id[tid] + p.vocab_offset : -1;
+        p.dbg_ids[(size_t)r * SAMPLE_MAX_CAND + tid] = tid < keep ? c_id[tid] + id_offset : -1;
         p.dbg_probs[(size_t)r * SAMPLE_MAX_CAND + tid] = tid < keep ? e / kept : 0.f;
     }
 }
 
 B2_API int b2_sample(const SampleParams* p, cudaStream_t s) {
     if (p->n_rows < 1 || p->vocab < 1 || p->temperature <= 0.f || p->top_k < 0 || p->top_p <= 0.f) return cudaErrorInvalidValue;
-    sample_kernel<<<p->n_rows, SAMPLE_THREADS, 0, s>>>(*p);
+    size_t smem = 0;
+    if (p->comm.tp > 1) {
+        // one row per launch under tensor parallelism (the exchange is the launch's only CTA's)
+        const int K = p->top_k > 0 && p->top_k < SAMPLE_MAX_CAND ? p->top_k : SAMPLE_MAX_CAND;
+        if (p->n_rows != 1 || p->comm.part_stride < 1 + 2 * K) return cudaErrorInvalidValue;
+        smem = (size_t)p->comm.tp * K * 8;
+        static SmemOptIn optin;
+        cudaError_t e = optin.ensure(sample_kernel, smem + 16 * 1024);
+        if (e != cudaSuccess) return e;
+    }
+    sample_kernel<<<p->n_rows, SAMPLE_THREADS, smem, s>>>(*p);
     return cudaGetLastError();
 }
 B2_API int b2_sizeof_sample_params() { return (int)sizeof(SampleParams); }

@@ -95,10 +95,16 @@ class TPInferenceEngine:
         return self.engine.prefill_tokens(tokens, seq)
 
     def decode_tokens(self, n_steps: int, seqs=None, graph=None, collect: bool = True):
-        return self.engine.decode_tokens(n_steps, seqs, graph, collect)
+        self._before_step()
+        out = self.engine.decode_tokens(n_steps, seqs, graph, collect)
+        self._after_step()
+        return out
 
     def step_tokens(self, tokens, seq: int = 0, logits: bool = True, commit: bool = True):
-        return self.engine.step_tokens(tokens, seq, logits, commit)
+        self._before_step()
+        out = self.engine.step_tokens(tokens, seq, logits, commit)
+        self._after_step()
+        return out
 
     def score_tokens(self, tokens, seq: int = 0):
         return self.engine.score_tokens(tokens, seq)
@@ -107,10 +113,16 @@ class TPInferenceEngine:
         return self.engine.perplexity(tokens, seq)
 
     def generate_tokens(self, prompt, n_new: int, seq: int = 0, graph=None):
-        return self.engine.generate_tokens(prompt, n_new, seq, graph)
+        self._before_step()
+        out = self.engine.generate_tokens(prompt, n_new, seq, graph)
+        self._after_step()
+        return out
 
     def step_host(self, token: int, seq: int = 0) -> int:
-        return self.engine.step_host(token, seq)
+        self._before_step()
+        out = self.engine.step_host(token, seq)
+        self._after_step()
+        return out
 
     def prefill_step(self, token_embeddings, seq: int = 0):
         return self.engine.prefill_step(token_embeddings, seq)
@@ -134,7 +146,10 @@ class TPInferenceEngine:
     # ------------------------------------------------------------------ speculation
     def spec_step(self, drafts, parents, seqs=None, roots=None):
         """One-pass verify-and-commit for several sequences (engine.InferenceEngine.spec_step)."""
-        return self.engine.spec_step(drafts, parents, seqs, roots)
+        self._before_step()
+        out = self.engine.spec_step(drafts, parents, seqs, roots)
+        self._after_step()
+        return out
 
     def spec_step_tokens(self, root: int, drafts, parents, seq: int = 0):
         return self.engine.spec_step_tokens(root, drafts, parents, seq)
@@ -224,8 +239,85 @@ class TPInferenceEngine:
         self.engine.synchronize()
 
     def check_status(self):
-        if self.comm is not None:
+        """Raise CommTimeout if a bounded device wait expired since the last check; with failure detection
+        on, the expiry is also published so that the peers stop before their next step."""
+        if self.comm is None:
+            return
+        try:
             self.comm.check_status()
+        except Exception as e:
+            hb = getattr(self, "_heartbeat", None)
+            if hb is not None:
+                hb.mark_failed(str(e)[:200])
+            raise
+
+    # ------------------------------------------------------------------ failure detection / recovery
+    def enable_failure_detection(self, store=None, heartbeat_s: float = 0.2, timeout_s: float = 5.0):
+        """Start a heartbeat for this rank and check the peers' before every step: a rank that exited,
+        hung on the host or reported a device-wait expiry makes the others raise `RankFailure` at their
+        next step boundary instead of entering an exchange that cannot complete (the kernels' bounded
+        waits cover the case where the peer dies inside a step).  `store`: any object with set/get
+        (default: the torch.distributed store of the bootstrap)."""
+        from ..utils.watchdog import DictStore, Heartbeat, Watchdog
+        if store is None:
+            if dist.is_available() and dist.is_initialized():
+                store = dist.distributed_c10d._get_default_store()
+            else:
+                store = DictStore()
+        self._heartbeat = Heartbeat(store, self.tp_rank, interval_s=heartbeat_s).start()
+        self._watchdog = Watchdog(store, self.tp_rank, self.tp_size, timeout_s=timeout_s)
+        return self
+
+    def disable_failure_detection(self):
+        hb = getattr(self, "_heartbeat", None)
+        if hb is not None:
+            hb.stop()
+        self._heartbeat = self._watchdog = None
+
+    def _before_step(self):
+        wd = getattr(self, "_watchdog", None)
+        if wd is not None:
+            wd.check(require_present=False)
+
+    def _after_step(self):
+        hb = getattr(self, "_heartbeat", None)
+        if hb is not None:
+            hb.beat(self.engine._steps)
+
+    def snapshot_all(self, seqs=None):
+        """Snapshots of the given sequence slots (default: all), for `recover`."""
+        seqs = range(self.engine.max_batch) if seqs is None else seqs
+        return [self.engine.states.snapshot(s) for s in seqs]
+
+    def recover(self, snapshots=(), group=None):
+        """After a failed exchange (CommTimeout / RankFailure) on a process group that is whole again
+        (the failed rank was restarted, or the ranks re-initialised torch.distributed): throw the old
+        symmetric-memory communicator away, rendezvous a new one on `group` (default: the world), rebuild
+        the step driver on it and put every snapshotted sequence back.  Collective: every rank calls it.
+        The world size must be the one the weights were sharded for."""
+        from ..parallel.symm import SymmComm
+        if self.tp_size > 1:
+            world = dist.get_world_size(group) if group is not None else dist.get_world_size()
+            if world != self.tp_size:
+                raise ValueError(f"recover() on {world} ranks, but the weights are sharded for {self.tp_size}")
+            old = self.comm
+            self.comm = SymmComm(hidden=self.config.hidden_size,
+                                 part_floats=old.part_floats if old is not None else None,
+                                 use_multimem=self.ecfg.use_multimem, wait_us=self.ecfg.wait_budget_us, group=group)
+            if old is not None:
+                old.close()
+            self.engine.comm = self.comm
+        self.engine._drop_driver()
+        self.engine._graph_key = None
+        for s in snapshots:
+            self.engine.states.restore(s)
+        hb = getattr(self, "_heartbeat", None)
+        if hb is not None:
+            hb.clear_failed()
+            hb.beat(self.engine._steps)
+        if self.tp_size > 1:
+            dist.barrier(group)               # every rank has withdrawn its mark before anyone checks again
+        return self.comm
 
     def launches_per_step(self) -> int:
         return self.engine.launches_per_step()
@@ -237,6 +329,7 @@ class TPInferenceEngine:
         self.engine.build_decode_launch_cache()
 
     def cleanup(self):
+        self.disable_failure_detection()
         self.engine.cleanup()
         if self.comm is not None:
             self.comm.close()

@@ -92,12 +92,15 @@ class TextGenerator:
         pt = torch.tensor([uniq], dtype=torch.int32, device=dev) if uniq else torch.zeros(1, 1, dtype=torch.int32, device=dev)
         npast = torch.tensor([len(uniq)], dtype=torch.int32, device=dev)
         seed = self._call_seed * 1000003 + step
-        if getattr(self.engine, "tp_size", 1) > 1:
-            logits = self.engine.compute_logits(None).reshape(1, -1).contiguous()
-        else:
-            logits = self.core.logits(1)
+        # the step left this rank's logits slice on the device; under tensor parallelism the ranks exchange
+        # only their candidate lists (inside the sampling kernel) and draw the same token from the same seed:
+        # no logits gather, no second lm_head pass, no collective call
+        logits = self.core.logits(1)
+        tp = getattr(self.engine, "tp_size", 1) > 1
         tok = K.sample_top_p(logits, params.temperature, params.top_k, params.top_p,
-                             params.repetition_penalty, pt, npast, seed=seed)
+                             params.repetition_penalty, pt, npast, seed=seed,
+                             vocab_offset=self.core.spec.vocab[0] if tp else 0,
+                             comm=self.core._comm_ctx() if tp else None)
         return int(tok[0].item())
 
     def _full_logits(self):

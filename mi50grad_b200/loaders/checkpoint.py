@@ -98,7 +98,10 @@ class CheckpointLoader:
         self.group_size = group_size or (32 if self.fmt == "compressed-tensors"
                                          else self.config.group_size)
         self.quant_format = quant_format
-        self.ck = CheckpointDir(model_dir, SKIP_PREFIXES)
+        # tensors are views of the memory-mapped files: a tensor-parallel rank slices its shard out of them
+        # and only those pages are ever read (the reference reads every full tensor on every GPU's behalf:
+        # src/model/weight_loader.py:300-316)
+        self.ck = CheckpointDir(model_dir, SKIP_PREFIXES, lazy=True)
         self.layer_prefix = self._detect_layer_prefix()
         self.model_prefix = self.layer_prefix.rsplit(".layers.", 1)[0]
 

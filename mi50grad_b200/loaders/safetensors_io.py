@@ -27,8 +27,12 @@ _NAMES = {v[0]: k for k, v in _DTYPES.items()}
 
 
 class SafetensorsFile:
-    def __init__(self, path: str):
+    def __init__(self, path: str, lazy: bool = False):
+        """`lazy`: tensors come back as views of the memory-mapped file (copy-on-write private mapping):
+        nothing is read until a tensor, or the slice of it that a rank keeps, is actually touched."""
         self.path = str(path)
+        self.lazy = lazy
+        self.copied_bytes = 0          # bytes materialised by eager reads (stays 0 in lazy mode)
         with open(self.path, "rb") as f:
             (n,) = struct.unpack("<Q", f.read(8))
             self.header = json.loads(f.read(n))
@@ -49,7 +53,7 @@ class SafetensorsFile:
     def _map(self) -> mmap.mmap:
         if self._mm is None:
             with open(self.path, "rb") as f:
-                self._mm = mmap.mmap(f.fileno(), 0, access=mmap.ACCESS_READ)
+                self._mm = mmap.mmap(f.fileno(), 0, access=mmap.ACCESS_COPY if self.lazy else mmap.ACCESS_READ)
         return self._mm
 
     def get(self, key: str, bf16_to: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -60,16 +64,27 @@ class SafetensorsFile:
             raise ValueError(f"Unsupported dtype: {e['dtype']}")
         dtype, _ = _DTYPES[e["dtype"]]
         start, end = e["data_offsets"]
-        buf = self._map()[self.data_offset + start:self.data_offset + end]
-        t = torch.frombuffer(bytearray(buf), dtype=dtype).reshape(tuple(e["shape"])) \
-            if end > start else torch.empty(tuple(e["shape"]), dtype=dtype)
+        if end <= start:
+            t = torch.empty(tuple(e["shape"]), dtype=dtype)
+        elif self.lazy:
+            n = 1
+            for d in e["shape"]:
+                n *= d
+            t = torch.frombuffer(self._map(), dtype=dtype, count=n, offset=self.data_offset + start).reshape(tuple(e["shape"]))
+        else:
+            buf = self._map()[self.data_offset + start:self.data_offset + end]
+            self.copied_bytes += end - start
+            t = torch.frombuffer(bytearray(buf), dtype=dtype).reshape(tuple(e["shape"]))
         if dtype == torch.bfloat16 and bf16_to is not None:
             t = t.to(bf16_to)
         return t
 
     def close(self):
         if self._mm is not None:
-            self._mm.close()
+            try:
+                self._mm.close()
+            except BufferError:
+                pass                   # lazy tensors still view the mapping: it goes away with the last of them
             self._mm = None
 
 
@@ -103,9 +118,10 @@ class CheckpointDir:
     model.safetensors.index.json when present (reference:
     src/model/weight_loader.py:264-290)."""
 
-    def __init__(self, model_dir: str, skip_prefixes: Tuple[str, ...] = ()):
+    def __init__(self, model_dir: str, skip_prefixes: Tuple[str, ...] = (), lazy: bool = False):
         self.dir = Path(model_dir)
         self.skip_prefixes = skip_prefixes
+        self.lazy = lazy
         self._files: Dict[str, SafetensorsFile] = {}
         self._where: Dict[str, str] = {}
         idx = self.dir / "model.safetensors.index.json"
@@ -118,7 +134,7 @@ class CheckpointDir:
 
     def _open(self, name: str) -> SafetensorsFile:
         if name not in self._files:
-            self._files[name] = SafetensorsFile(self.dir / name)
+            self._files[name] = SafetensorsFile(self.dir / name, lazy=self.lazy)
         return self._files[name]
 
     def keys(self):
@@ -132,6 +148,10 @@ class CheckpointDir:
         if key not in self._where:
             raise FileNotFoundError(f"Cannot find tensor: {key}")
         return self._open(self._where[key]).get(key, bf16_to=bf16_to)
+
+    @property
+    def copied_bytes(self) -> int:
+        return sum(f.copied_bytes for f in self._files.values())
 
     def shape(self, key: str) -> Tuple[int, ...]:
         return self._open(self._where[key]).info(key)[1]

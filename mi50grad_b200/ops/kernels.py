@@ -324,11 +324,14 @@ _tc_status = {}
 
 def sample_top_p(logits: torch.Tensor, temperature: float = 1.0, top_k: int = 50, top_p: float = 0.9,
                  repetition_penalty: float = 1.0, past: Optional[torch.Tensor] = None,
-                 n_past: Optional[torch.Tensor] = None, seed: int = 0, vocab_offset: int = 0, debug: bool = False):
+                 n_past: Optional[torch.Tensor] = None, seed: int = 0, vocab_offset: int = 0, debug: bool = False,
+                 comm: Optional[L.CommCtx] = None):
     """Sample one token per row of fp32 logits [rows, vocab] on the device (temperature > 0).
     `past`: int32 [rows, max_past] token ids for the repetition penalty with counts `n_past`.
     The logits are modified in place by the penalty.  Returns int32 [rows] (and, with `debug`,
-    the kept candidate ids and their probabilities, [rows, 1024] each)."""
+    the kept candidate ids and their probabilities, [rows, 1024] each).  With `comm` (tensor parallel,
+    one row): `logits` is this rank's vocabulary slice starting at `vocab_offset`; the ranks exchange their
+    candidate lists through symmetric memory inside the kernel and all return the same token."""
     n, V = logits.shape
     dev = logits.device
     out = torch.empty(n, dtype=torch.int32, device=dev)
@@ -338,6 +341,7 @@ def sample_top_p(logits: torch.Tensor, temperature: float = 1.0, top_k: int = 50
     if past is not None:
         p.past, p.n_past, p.max_past = past.data_ptr(), n_past.data_ptr(), past.shape[1]
     p.seed, p.out_tokens = seed & 0xFFFFFFFFFFFFFFFF, out.data_ptr()
+    p.comm = comm if comm is not None else L.null_comm()
     ids = probs = None
     if debug:
         ids = torch.empty(n, L.SAMPLE_MAX_CAND, dtype=torch.int32, device=dev)

@@ -30,7 +30,8 @@ import torch.distributed as dist
 from ..ops import lib as L
 from .comm import CommTimeout, Communicator
 
-KERNEL_NAMES = {1: "gemv finisher", 2: "all-reduce", 3: "arg-max", 4: "barrier", 5: "wait self-test", 6: "gemm reduce-scatter"}
+KERNEL_NAMES = {1: "gemv finisher", 2: "all-reduce", 3: "arg-max", 4: "barrier", 5: "wait self-test", 6: "gemm reduce-scatter",
+                7: "chain dependency", 8: "chain tile exchange", 9: "chain weight copy", 10: "distributed sampler"}
 
 
 class CollParams(C.Structure):

@@ -75,7 +75,11 @@ class Heartbeat:
         self.store.set(self.key(), json.dumps({"step": self.step, "t": self.clock()}))
 
     def mark_failed(self, reason: str):
-        self.store.set(f"{self.prefix}/failed/{self.rank}", reason)
+        self.store.set(f"{self.prefix}/failed/{self.rank}", reason or "failed")
+
+    def clear_failed(self):
+        """After a recovery: withdraw this rank's failure mark (an empty mark counts as none)."""
+        self.store.set(f"{self.prefix}/failed/{self.rank}", "")
 
     def start(self):
         self.beat()
@@ -116,7 +120,9 @@ class Watchdog:
                 continue
             fk = f"{self.prefix}/failed/{r}"
             if _has(self.store, fk):
-                raise RankFailure(r, "reported failure: " + bytes(self.store.get(fk)).decode())
+                why = bytes(self.store.get(fk)).decode()
+                if why:
+                    raise RankFailure(r, "reported failure: " + why)
             st = self.peer_state(r)
             if st is None:
                 if require_present:
@@ -140,10 +146,30 @@ class Watchdog:
 
 
 def recover(rebootstrap: Callable[[], object], restore: Callable[[object], None], snapshots) -> object:
-    """`rebootstrap()` destroys the old communicator / process group and returns a new one (the
-    caller decides the new world); `restore(snapshot)` puts one sequence back (KV cache lengths,
-    DeltaNet state, conv history, position).  Returns the new communicator."""
+    """Generic form: `rebootstrap()` destroys the old communicator / process group and returns a new one
+    (the caller decides the new world); `restore(snapshot)` puts one sequence back (KV cache lengths,
+    DeltaNet state, conv history, position).  Returns the new communicator.  The tensor-parallel engine's
+    own `TPInferenceEngine.recover(snapshots)` is this with both callables filled in: a new
+    symmetric-memory communicator, a rebuilt step driver, `SequenceStates.restore`."""
     comm = rebootstrap()
     for s in snapshots:
         restore(s)
     return comm
+
+
+def run_guarded(engine, fn: Callable[[], object], snapshots, retries: int = 1):
+    """Run `fn()` (some steps of a TPInferenceEngine with failure detection on); if an exchange fails
+    (CommTimeout) or a peer is reported down (RankFailure), recover the engine from `snapshots` and try
+    again, up to `retries` times.  Every rank must take the same path: the failure is published through
+    the heartbeat store, so the peers' next step boundary raises too."""
+    from ..parallel.comm import CommTimeout
+    for attempt in range(retries + 1):
+        try:
+            out = fn()
+            engine.synchronize()
+            engine.check_status()
+            return out
+        except (CommTimeout, RankFailure):
+            if attempt == retries:
+                raise
+            engine.recover(snapshots)

@@ -205,9 +205,66 @@ def scenario_wait_timeout():
     assert float(out[0]) == dist.get_world_size()
 
 
+def scenario_failure_detection():
+    """Failure detection and recovery wired into the tensor-parallel engine, with no GPU fault anywhere:
+    (1) recover() -- a new symmetric-memory communicator, a rebuilt driver, sequences restored from
+    snapshots -- continues with exactly the tokens of the uninterrupted run; (2) a rank that leaves between
+    steps (nothing of its in flight) is seen by the other rank before its next launch."""
+    import time
+    from mi50grad_b200.config import EngineConfig, tiny_config
+    from mi50grad_b200.engine.tp_engine import TPInferenceEngine
+    from mi50grad_b200.models.weights import random_model
+    from mi50grad_b200.utils.watchdog import RankFailure
+    rank, world = dist.get_rank(), dist.get_world_size()
+    cfg = tiny_config()
+    eng = TPInferenceEngine(cfg, list(range(world)), max_seq_len=128,
+                            engine_config=EngineConfig(use_multimem=False, wait_budget_us=500_000))
+    eng.load_model(random_model(cfg, 0))
+    eng.enable_failure_detection(heartbeat_s=0.05, timeout_s=3.0)
+    ids = torch.randint(0, cfg.vocab_size, (12,), generator=torch.Generator().manual_seed(2)).tolist()
+    eng.generate_tokens(ids, 4, graph=False)
+    snaps = eng.snapshot_all([0])
+    a = eng.decode_tokens(3, graph=False).cpu().tolist()
+    old = eng.comm
+    eng.recover(snaps)
+    assert eng.comm is not old
+    b = eng.decode_tokens(3, graph=False).cpu().tolist()
+    torch.cuda.synchronize()
+    eng.check_status()
+    assert a == b, (a, b)
+    dist.barrier()
+    if rank == world - 1:
+        eng._heartbeat.mark_failed("leaving between steps")      # this rank issues nothing from here on
+    else:
+        t0, seen = time.time(), None
+        while time.time() - t0 < 10 and seen is None:
+            try:
+                eng._before_step()
+                time.sleep(0.02)
+            except RankFailure as e:
+                seen = e
+        assert seen is not None and seen.rank == world - 1 and "leaving" in seen.reason
+        with pytest_raises(RankFailure):
+            eng.decode_tokens(1, graph=False)                     # refused on the host: no kernel is launched
+    eng.cleanup()
+
+
+class pytest_raises:
+    def __init__(self, exc):
+        self.exc = exc
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, t, v, tb):
+        assert t is not None and issubclass(t, self.exc), f"expected {self.exc.__name__}"
+        return True
+
+
 def scenario_sample():
-    """Non-greedy generation under TP: every rank samples the gathered logits on the device with the
-    same seed; the ranks agree, and the draw equals the device sampler run on the gathered logits."""
+    """Non-greedy generation under TP: every rank samples from its own vocabulary slice and the ranks
+    exchange candidate lists inside the sampling kernel; the ranks agree, and both the kept candidates and
+    the draw equal the one-rank sampler run on the gathered logits."""
     from mi50grad_b200.config import EngineConfig, tiny_config
     from mi50grad_b200.engine.tp_engine import TPInferenceEngine
     from mi50grad_b200.generate.generate import TextGenerator
@@ -237,6 +294,21 @@ def scenario_sample():
     assert int(cold[0]) == int(full.argmax())
     first = gen.prefill(prompt)
     assert first == int(eng.compute_logits(None).argmax())         # gathered logits of the last step
+    # slice-local sampler == one-rank sampler on the gathered logits, for three parameter sets
+    core = eng.engine
+    past = torch.tensor([sorted(set(prompt + ids))], dtype=torch.int32, device="cuda")
+    npast = torch.tensor([past.shape[1]], dtype=torch.int32, device="cuda")
+    for temp, tk, tpp, pen in ((0.8, 40, 0.9, 1.1), (1.3, 0, 0.95, 1.0), (0.5, 7, 1.0, 1.4)):
+        full = eng.compute_logits(None).reshape(1, -1).clone()
+        ref_tok, ref_ids, ref_p = K.sample_top_p(full, temp, tk, tpp, pen, past, npast, seed=77, debug=True)
+        local = core.logits(1).clone()
+        tok, got_ids, got_p = K.sample_top_p(local, temp, tk, tpp, pen, past, npast, seed=77, debug=True,
+                                             vocab_offset=core.spec.vocab[0], comm=core._comm_ctx())
+        torch.cuda.synchronize()
+        eng.check_status()
+        assert int(tok[0]) == int(ref_tok[0]), (temp, tk, tpp, pen)
+        assert torch.equal(got_ids, ref_ids)
+        assert torch.allclose(got_p, ref_p, atol=1e-6)
     eng.cleanup()
 
 
@@ -260,6 +332,9 @@ def main():
             extra = ""
         elif scenario == "sample":
             scenario_sample()
+            extra = ""
+        elif scenario == "failure_detection":
+            scenario_failure_detection()
             extra = ""
         elif scenario == "wait_timeout":
             scenario_wait_timeout()

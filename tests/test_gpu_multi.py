@@ -59,6 +59,10 @@ def test_bounded_wait_times_out_cleanly():
     _run(2, "wait_timeout", env_extra={"NCCL_NVLS_ENABLE": "0"})
 
 
+def test_failure_detection_and_recovery_in_the_tp_engine():
+    _run(2, "failure_detection", env_extra={"NCCL_NVLS_ENABLE": "0"})
+
+
 def test_tp_engine_medium_all_gpus():
     """TP over every GPU of the box (8: KV heads replicated on rank pairs) against the oracle."""
     n = _n()

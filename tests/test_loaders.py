@@ -136,3 +136,10 @@ def test_tp_sharded_load_matches_shard_of_full(tmp_path):
     assert sh.gate.out_features == 352 and sh.down.in_features == 352
     assert torch.equal(sh.down.dense(), full.down.dense()[:, 352:])
     assert ld.load_lm_head(2, 1).shape == (512, 256)
+    # the loader hands out views of the memory-mapped files: a rank's load materialises its shard only
+    assert ld.ck.lazy and ld.ck.copied_bytes == 0
+    qw = ld.ck.get("model.layers.1.mlp.down_proj.qweight" if "model.layers.1.mlp.down_proj.qweight" in ld.ck
+                   else next(k for k in ld.ck.keys() if k.endswith("layers.1.mlp.down_proj.qweight")))
+    # the row shard of down_proj is a window of the mapped file itself: no copy of the full tensor was made
+    assert sh.down.qweight.untyped_storage().data_ptr() == qw.untyped_storage().data_ptr()
+    assert sh.down.qweight.shape[0] * 2 == qw.shape[0]

@@ -122,6 +122,50 @@ def _fail_and_recover(rank, world, port2, fail_step, n_steps):
     return toks, detected
 
 
+def test_run_guarded_recovers_once_and_clears_failure_marks():
+    """The retry wrapper around engine steps: a CommTimeout (or a peer's failure mark) triggers exactly one
+    recover() from the snapshots, after which the step is tried again; a mark that was withdrawn no longer
+    stops the peers."""
+    from mi50grad_b200.parallel.comm import CommTimeout
+    from mi50grad_b200.utils.watchdog import DictStore, Heartbeat, RankFailure, Watchdog, run_guarded
+
+    class FakeEngine:
+        def __init__(self):
+            self.recovered, self.calls = [], 0
+
+        def synchronize(self):
+            pass
+
+        def check_status(self):
+            pass
+
+        def recover(self, snaps):
+            self.recovered.append(list(snaps))
+
+    eng = FakeEngine()
+
+    def step():
+        eng.calls += 1
+        if eng.calls == 1:
+            raise CommTimeout("rank 0: bounded wait expired")
+        return "tokens"
+    assert run_guarded(eng, step, ["snap0"], retries=1) == "tokens"
+    assert eng.recovered == [["snap0"]] and eng.calls == 2
+    eng2 = FakeEngine()
+    with pytest.raises(CommTimeout):
+        run_guarded(eng2, lambda: (_ for _ in ()).throw(CommTimeout("again")), [], retries=1)
+    assert len(eng2.recovered) == 1
+    store = DictStore()
+    hb0, hb1 = Heartbeat(store, 0), Heartbeat(store, 1)
+    hb0.beat(); hb1.beat()
+    wd = Watchdog(store, 0, 2, timeout_s=60)
+    hb1.mark_failed("exchange timed out")
+    with pytest.raises(RankFailure):
+        wd.check()
+    hb1.clear_failed()
+    wd.check()
+
+
 def test_rank_failure_is_detected_and_run_recovers():
     cfg = tiny_config()
     ids = torch.randint(0, cfg.vocab_size, (12,), generator=torch.Generator().manual_seed(0)).tolist()
