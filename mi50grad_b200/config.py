@@ -294,9 +294,10 @@ class EngineConfig:
     use_graph: bool = True
     use_multimem: bool = True
     fused_gemv_ar: bool = True
-    # consecutive INT4 projections of a decode step run as one persistent launch (csrc/chain.cu);
-    # B200GRAD_CHAIN=0/1 sets the default
-    use_chain: bool = dataclasses.field(default_factory=lambda: os.environ.get("B200GRAD_CHAIN", "0") not in ("0", "false", ""))
+    # the persistent projection-chain kernel (csrc/chain.cu) in the decode step: 0 off, 1 consecutive INT4
+    # projections run as one launch, 2 only the projections that exchange across GPUs use it (one launch each),
+    # -1 (default, or B200GRAD_CHAIN unset) = 2 under tensor parallelism, 0 on one GPU
+    use_chain: int = dataclasses.field(default_factory=lambda: int(os.environ.get("B200GRAD_CHAIN", "-1")))
     spec_ngram: int = 3
     spec_max_draft: int = 4
     max_step_rows: int = 0           # rows of a batched-decode / verify step (0: 8 per sequence slot)

@@ -26,6 +26,7 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attn_kernel(const AttnPara
     constexpr int EPL = HD / 32;                 // elements per lane
     const int kvh = blockIdx.x, r = blockIdx.y, sp = blockIdx.z;
     pdl_launch_dependents();
+    pdl_wait();                                  // Q, and the K/V row of this step, come from the kernels before
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int G = p.nq / p.nkv;
     const RowMeta rm = p.rows[r];
@@ -178,10 +179,9 @@ __global__ void __launch_bounds__(ATT_THREADS) decode_attn_kernel(const AttnPara
 B2_API int b2_decode_attn(const AttnParams* p, int hd, cudaStream_t s) {
     if (p->nq % p->nkv || p->nq / p->nkv > ATT_MAX_G || p->splits < 1 || p->splits > 32) return cudaErrorInvalidValue;
     dim3 grid(p->nkv, p->n_rows, p->splits);
-    if (hd == 256) decode_attn_kernel<256><<<grid, ATT_THREADS, 0, s>>>(*p);
-    else if (hd == 128) decode_attn_kernel<128><<<grid, ATT_THREADS, 0, s>>>(*p);
-    else if (hd == 64) decode_attn_kernel<64><<<grid, ATT_THREADS, 0, s>>>(*p);
-    else return cudaErrorInvalidValue;
-    return cudaGetLastError();
+    if (hd == 256) return launch_pdl(decode_attn_kernel<256>, grid, dim3(ATT_THREADS), 0, s, *p);
+    if (hd == 128) return launch_pdl(decode_attn_kernel<128>, grid, dim3(ATT_THREADS), 0, s, *p);
+    if (hd == 64) return launch_pdl(decode_attn_kernel<64>, grid, dim3(ATT_THREADS), 0, s, *p);
+    return cudaErrorInvalidValue;
 }
 B2_API int b2_sizeof_attn_params() { return (int)sizeof(AttnParams); }

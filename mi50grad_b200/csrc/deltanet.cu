@@ -73,7 +73,29 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_step_kernel(const DeltaPa
     const float neg_expA = -__expf(p.A_log[j]);
     const float dtb = __half2float(p.dt_bias[j]);
     const float nw = __half2float(p.norm_w[cb * DN_COLS + vcol]);
+    // The a/b projections' weights (times the norm weights of a lazily normalised input) do not depend on
+    // this step either: the first DN_PRE pairs per thread wait in registers.
+    constexpr int DN_PRE = 10;
+    const bool inkernel_ab = p.off_a < 0;
+    float2 pa[DN_PRE], pb[DN_PRE];
+#pragma unroll
+    for (int k = 0; k < DN_PRE; ++k) {
+        pa[k] = pb[k] = make_float2(0.f, 0.f);
+        const int i = tid * 2 + k * DN_THREADS * 2;
+        if (inkernel_ab && i < p.H) {
+            float2 av = __half22float2(*(const __half2*)(p.wa + (size_t)j * p.H + i));
+            float2 bv = __half22float2(*(const __half2*)(p.wb + (size_t)j * p.H + i));
+            if (p.ln.h) {
+                const float2 ww = __half22float2(*(const __half2*)(p.ln.w + i));
+                av.x *= ww.x; av.y *= ww.y; bv.x *= ww.x; bv.y *= ww.y;
+            }
+            pa[k] = av; pb[k] = bv;
+        }
+    }
     __syncthreads();
+    // Everything above (conv history, state slice, weights) was left by earlier steps; what follows reads
+    // this step's in-projection output and residual stream.
+    pdl_wait();
 
     for (int r = r0; r < r1; ++r) {
         const __half* pr = p.proj + (size_t)r * p.ld;
@@ -81,29 +103,50 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_step_kernel(const DeltaPa
         // a/b projections.  With a lazily normalised input the 1/rms factor is applied to the
         // finished dot products, so nothing here waits on it.
         float sa = 0.f, sb = 0.f;
-        const bool inkernel_ab = p.off_a < 0;
         if (inkernel_ab) {
             const __half* wa = p.wa + (size_t)j * p.H;
             const __half* wb = p.wb + (size_t)j * p.H;
             if (p.ln.h) {
                 const float* hr = p.ln.h + (size_t)r * p.ln.H;
-                for (int i = tid * 2; i < p.H; i += DN_THREADS * 2) {
-                    float2 hv = *(const float2*)(hr + i);
+                float2 hv[DN_PRE];
+#pragma unroll
+                for (int k = 0; k < DN_PRE; ++k) {
+                    const int i = tid * 2 + k * DN_THREADS * 2;
+                    hv[k] = i < p.H ? *(const float2*)(hr + i) : make_float2(0.f, 0.f);
+                }
+#pragma unroll
+                for (int k = 0; k < DN_PRE; ++k) {
+                    sa += hv[k].x * pa[k].x + hv[k].y * pa[k].y;
+                    sb += hv[k].x * pb[k].x + hv[k].y * pb[k].y;
+                }
+                for (int i = tid * 2 + DN_PRE * DN_THREADS * 2; i < p.H; i += DN_THREADS * 2) {
+                    float2 hv2 = *(const float2*)(hr + i);
                     float2 ww = __half22float2(*(const __half2*)(p.ln.w + i));
                     float2 av = __half22float2(*(const __half2*)(wa + i));
                     float2 bv = __half22float2(*(const __half2*)(wb + i));
-                    float x0 = hv.x * ww.x, x1 = hv.y * ww.y;
+                    float x0 = hv2.x * ww.x, x1 = hv2.y * ww.y;
                     sa += x0 * av.x + x1 * av.y;
                     sb += x0 * bv.x + x1 * bv.y;
                 }
             } else {
                 const __half* x = p.xn + (size_t)r * p.ldx;
-                for (int i = tid * 2; i < p.H; i += DN_THREADS * 2) {
-                    float2 xv = __half22float2(*(const __half2*)(x + i));
+                float2 xv[DN_PRE];
+#pragma unroll
+                for (int k = 0; k < DN_PRE; ++k) {
+                    const int i = tid * 2 + k * DN_THREADS * 2;
+                    xv[k] = i < p.H ? __half22float2(*(const __half2*)(x + i)) : make_float2(0.f, 0.f);
+                }
+#pragma unroll
+                for (int k = 0; k < DN_PRE; ++k) {
+                    sa += xv[k].x * pa[k].x + xv[k].y * pa[k].y;
+                    sb += xv[k].x * pb[k].x + xv[k].y * pb[k].y;
+                }
+                for (int i = tid * 2 + DN_PRE * DN_THREADS * 2; i < p.H; i += DN_THREADS * 2) {
+                    float2 xv2 = __half22float2(*(const __half2*)(x + i));
                     float2 av = __half22float2(*(const __half2*)(wa + i));
                     float2 bv = __half22float2(*(const __half2*)(wb + i));
-                    sa += xv.x * av.x + xv.y * av.y;
-                    sb += xv.x * bv.x + xv.y * bv.y;
+                    sa += xv2.x * av.x + xv2.y * av.y;
+                    sb += xv2.x * bv.x + xv2.y * bv.y;
                 }
             }
             sa = warp_sum(sa);
@@ -201,13 +244,17 @@ static int launch_delta(const DeltaParams* p, cudaStream_t s) {
     cfg.blockDim = dim3(DN_THREADS);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CB;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // programmatic dependent launch: the CTAs become resident, load their state slice, conv history and
+    // weights while the in-projection is still finishing, and wait (griddepcontrol.wait) only then
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     return cudaLaunchKernelEx(&cfg, deltanet_step_kernel<DK, DV>, *p);
 }
 

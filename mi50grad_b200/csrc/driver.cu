@@ -208,11 +208,16 @@ static int chain_flush(Driver* d, int rows, cudaStream_t s) {
 
 static int chain_add(Driver* d, const LinearDesc& L, const void* x, int ldx, const LazyNorm& ln, int rows,
                      const GemvEpi& epi, cudaStream_t s) {
-    if (epi.mode == EPI_FINISH && d->m.comm.tp > 1 && !(epi.fin_flags & FIN_NO_COMM)) d->exchanges++;
-    if (L.kind != LIN_INT4) {
+    const bool exchanges = epi.mode == EPI_FINISH && d->m.comm.tp > 1 && !(epi.fin_flags & FIN_NO_COMM);
+    if (exchanges) d->exchanges++;
+    // use_chain 2: only the projections that exchange across GPUs go through the chain kernel, each as a
+    // launch of its own (its tile-granular exchange is faster than the stand-alone GEMV's finisher); the
+    // others stay stand-alone GEMV launches
+    if (L.kind != LIN_INT4 || (d->m.use_chain == 2 && !exchanges)) {
         CK(chain_flush(d, rows, s));
         return run_linear(d, L, x, ldx, ln, rows, epi, s);
     }
+    if (d->m.use_chain == 2) CK(chain_flush(d, rows, s));
     PendingChain& pc = d->pend;
     if (pc.n == CH_MAX_OPS) CK(chain_flush(d, rows, s));
     ChainOp& op = pc.cp.op[pc.n];
@@ -222,6 +227,7 @@ static int chain_add(Driver* d, const LinearDesc& L, const void* x, int ldx, con
     op.ln = ln; op.epi = epi;
     pc.lin[pc.n] = &L;
     pc.n++;
+    if (d->m.use_chain == 2) return chain_flush(d, rows, s);
     return 0;
 }
 

@@ -212,6 +212,7 @@ __global__ void qknorm_rope_cachew_kernel(__half* __restrict__ qkv, int ld, cons
     __shared__ float red[32];
     const int hidx = blockIdx.x, r = blockIdx.y, i = threadIdx.x;
     pdl_launch_dependents();
+    pdl_wait();                             // the in-projection's output
     const RowMeta rm = rows[r];
     __half* row = qkv + (size_t)r * ld;
     const size_t cache_off = (((size_t)rm.seq * max_seq + rm.slot) * nkv) * hd;
@@ -246,10 +247,9 @@ B2_API int b2_qknorm_rope_cachew(void* qkv, int ld, const void* rows, const void
                                  int n_rows, int nq, int nkv, int hd, int rot, int max_seq, int interleaved,
                                  float eps, cudaStream_t s) {
     dim3 grid(nq + 2 * nkv, n_rows);
-    qknorm_rope_cachew_kernel<<<grid, hd, hd * sizeof(float), s>>>(
-        (__half*)qkv, ld, (const RowMeta*)rows, (const __half*)q_norm, (const __half*)k_norm, cos_tab, sin_tab,
-        (__half*)kcache, (__half*)vcache, nq, nkv, hd, rot, max_seq, interleaved, eps);
-    return cudaGetLastError();
+    return launch_pdl(qknorm_rope_cachew_kernel, grid, dim3(hd), hd * sizeof(float), s,
+                      (__half*)qkv, ld, (const RowMeta*)rows, (const __half*)q_norm, (const __half*)k_norm, cos_tab, sin_tab,
+                      (__half*)kcache, (__half*)vcache, nq, nkv, hd, rot, max_seq, interleaved, eps);
 }
 
 // ---------------------------------------------------------------------------

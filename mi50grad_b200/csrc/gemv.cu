@@ -328,7 +328,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_int4_kernel(const GemvIn
         if (s < nb) {
 #pragma unroll
             for (int i = 0; i < GEMV_NT; ++i) cp_async16(rp + (s * GEMV_NT + i) * 32, gp + (s * GEMV_NT + i) * 32);
-            if (FAST && !(s & 1) && lane < 16) cp_async16(szr + s * 16 + lane, szg + (size_t)((wb0 + s) >> 1) * 16 + lane);
+            // slot of a group's pairs: the group's index inside this warp's slice, modulo the ring depth (blocks
+            // b .. b+3 in flight touch at most three groups, so a slot is free again before it is reused)
+            if (FAST && !(s & 1) && lane < 16) cp_async16(szr + ((s >> 1) & (GEMV_STAGES - 1)) * 16 + lane, szg + (size_t)((wb0 + s) >> 1) * 16 + lane);
         }
         cp_async_commit();
     }
@@ -438,7 +440,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_int4_kernel(const GemvIn
                     gp += GEMV_NT * 32;
                     // block br + 3 is the first of its group exactly when s is odd (the slice starts on an even block)
                     if (FAST && (s & 1) && lane < 16)
-                        cp_async16(szr + ((s + GEMV_STAGES - 1) % GEMV_STAGES) * 16 + lane,
+                        cp_async16(szr + (((br + GEMV_STAGES - 1) >> 1) & (GEMV_STAGES - 1)) * 16 + lane,
                                    szg + (size_t)((wb0 + br + GEMV_STAGES - 1) >> 1) * 16 + lane);
                 }
                 cp_async_commit();
@@ -469,12 +471,12 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_int4_kernel(const GemvIn
                 }
                 cp4 += 8;
                 // FAST: groups of 128 k aligned to even blocks, so a group ends after every odd block
-                if (FAST && (s & 1)) { sz_stage = s - 1; flush((wb0 + br) >> 1); }
+                if (FAST && (s & 1)) { sz_stage = (br >> 1) & (GEMV_STAGES - 1); flush((wb0 + br) >> 1); }
             }
         }
     }
     cp_async_wait<0>();
-    if (FAST) { if (nb & 1) { sz_stage = (nb - 1) % GEMV_STAGES; flush((wb0 + nb - 1) >> 1); } }
+    if (FAST) { if (nb & 1) { sz_stage = ((nb - 1) >> 1) & (GEMV_STAGES - 1); flush((wb0 + nb - 1) >> 1); } }
     else if (cur >= 0) flush(cur);
 
     // ---- in-CTA reduction over the k-warps into ybuf[row][n_local]

@@ -140,7 +140,8 @@ struct SampleParams {
     int top_k;                   // 0: no top-k (capped at SAMPLE_MAX_CAND candidates)
     const int* past;             // [rows][max_past] token ids (global), may be null
     const int* n_past;           // [rows]
-    int max_past, pad;
+    int max_past;
+    int vocab_total;             // tp > 1: size of the whole vocabulary (bounds the merged candidate list); 0: `vocab`
     unsigned long long seed;
     int* out_tokens;             // [rows]
     int* dbg_ids;                // optional [rows][SAMPLE_MAX_CAND]: kept candidates (-1 padded)
@@ -306,6 +307,9 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const SamplePara
         __syncthreads();
         int total = 0;
         for (int pr = 0; pr < c.tp; ++pr) total += ln[pr];
+        // the merged list is as long as the one-rank sampler's would be on the whole vocabulary
+        const int vt = p.vocab_total > 0 ? p.vocab_total : p.vocab;
+        const int Kg = min(p.top_k > 0 ? p.top_k : SAMPLE_MAX_CAND, min(SAMPLE_MAX_CAND, vt));
         for (int pr = 0; pr < c.tp; ++pr) {
             if (tid < ln[pr]) {
                 const float v = lv[pr * K + tid];
@@ -313,11 +317,11 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const SamplePara
                 int pos = tid;                                // entries of its own list that come before it
                 for (int q = 0; q < c.tp; ++q)
                     if (q != pr) pos += rank_in_list(lv + q * K, li + q * K, ln[q], v, id);
-                if (pos < K) { c_val[pos] = v; c_id[pos] = id; }
+                if (pos < Kg) { c_val[pos] = v; c_id[pos] = id; }
             }
         }
         __syncthreads();
-        n = min(total, K);
+        n = min(total, Kg);
     }
     const int id_offset = p.comm.tp > 1 ? 0 : p.vocab_offset;      // merged ids are global already
     // ---- 4. softmax, scan, top-p, draw

@@ -362,7 +362,10 @@ class InferenceEngine:
         b["ss"] = f32(R, self.np)
         # persistent projection chain: split-K pieces and tile / dependency counters
         int4 = [l for l in lins if l.packed is not None]
-        self.use_chain = bool(self.ecfg.use_chain and int4)
+        uc = int(self.ecfg.use_chain)
+        self.use_chain = (2 if self.tp_size > 1 else 0) if uc < 0 else uc
+        if not int4:
+            self.use_chain = 0
         self.lib.b2_chain_scratch_floats.restype = C.c_longlong
         need = max([int(self.lib.b2_chain_scratch_floats(l.packed.KB, l.packed.NTL // 4, R)) for l in int4] + [1])
         b["chain_scratch"] = f32(need)
@@ -902,11 +905,28 @@ class InferenceEngine:
     def prefill_step(self, token_embeddings, seq: int = 0):
         """Whole prompt [S, hidden] in, hidden state of the last token out
         (reference: src/inference/engine.py:3009-3294)."""
-        e = self._as_dev(token_embeddings).reshape(-1, self.config.hidden_size)
-        out = None
-        for i in range(0, e.shape[0], self.max_rows):
-            out = self.forward_embeddings(e[i:i + self.max_rows], seq)
-        out = out[-1]
+        e = self._as_dev(token_embeddings).reshape(-1, self.config.hidden_size).contiguous()
+        self._ensure_driver()
+        if self.use_tc_prefill and e.shape[0] >= 16:
+            # many rows: the tensor-core prefill path, max_prefill rows per launch, embeddings loaded
+            # straight into its residual stream (a 512-row prompt is one launch sequence, not 64 decode steps)
+            H, n = self.config.hidden_size, 0
+            for i in range(0, e.shape[0], self.max_prefill):
+                chunk = e[i:i + self.max_prefill]
+                n = chunk.shape[0]
+                L.check(self.lib.b2_load_rmsnorm(None, C.c_void_p(chunk.data_ptr()),
+                                                 C.c_void_p(self.layers[0].attn_norm.data_ptr()),
+                                                 C.c_void_p(self.buf["p_h"].data_ptr()),
+                                                 C.c_void_p(self.buf["p_xn"].data_ptr()), None, 0, n, H,
+                                                 C.c_float(self.config.rms_norm_eps), L.stream()), "load_rmsnorm")
+                self._prefill_rows(n, seq, 0)
+            self.buf["h"][:1].copy_(self.buf["p_h"][n - 1:n])
+            out = self.buf["p_xn"][n - 1]
+        else:
+            out = None
+            for i in range(0, e.shape[0], self.max_rows):
+                out = self.forward_embeddings(e[i:i + self.max_rows], seq)
+            out = out[-1]
         return out.cpu().numpy() if isinstance(token_embeddings, np.ndarray) else out.clone()
 
     def decode_step_batch(self, token_embeddings, batch_size: Optional[int] = None, position: Optional[int] = None,

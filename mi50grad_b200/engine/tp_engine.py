@@ -199,15 +199,22 @@ class TPInferenceEngine:
         first token).  Logits come from the device lm_head, all ranks get the same ids."""
         k = k if k is not None else (getattr(self, "_eagle", None) or {}).get("k_draft", 5)
         eng = self.engine
-        h = torch.as_tensor(hidden_state).float().flatten().to(eng.device)
-        out: List[int] = []
-        for _ in range(k):
-            logits = torch.as_tensor(self.compute_logits(h))
-            t = int(torch.argmax(logits))
-            out.append(t)
-            e = eng.embed[t].float()
-            h = e * torch.rsqrt(e.pow(2).mean() + self.config.rms_norm_eps)
-        return out
+        eng._ensure_driver()
+        from ..ops import kernels as K
+        from ..ops import lib as L
+        # the whole loop stays on the device: lm_head GEMV on this rank's vocabulary slice, arg-max across
+        # the ranks inside the arg-max kernel (symmetric memory), embedding gather + norm; one host read at the end
+        h16 = torch.as_tensor(hidden_state).float().flatten().to(eng.device).half().reshape(1, -1)
+        toks = torch.empty(k, dtype=torch.int32, device=eng.device)
+        ctx = eng._comm_ctx() if self.tp_size > 1 else None
+        for i in range(k):
+            K.gemv(eng.lm_head, h16, out=eng.buf["logits"][:1], mode=L.EPI_STORE_F32,
+                   scratch=eng.buf["gemv_scratch"], counters=eng.buf["gemv_counters"])
+            tok = K.argmax(eng.buf["logits"][:1, :eng.spec.vocab_local], eng.spec.vocab[0], eng.argmax_blocks, ctx)
+            toks[i:i + 1] = tok[:1]
+            e = eng.embed.index_select(0, tok[:1].long()).float()
+            h16 = (e * torch.rsqrt(e.pow(2).mean(-1, keepdim=True) + self.config.rms_norm_eps)).half()
+        return toks.tolist()
 
     def decode_step_eagle(self, hidden_state, position: int, seq: int = 0):
         """Draft with `generate_eagle_drafts`, verify and commit in one pass; returns

@@ -100,7 +100,8 @@ class TextGenerator:
         tok = K.sample_top_p(logits, params.temperature, params.top_k, params.top_p,
                              params.repetition_penalty, pt, npast, seed=seed,
                              vocab_offset=self.core.spec.vocab[0] if tp else 0,
-                             comm=self.core._comm_ctx() if tp else None)
+                             comm=self.core._comm_ctx() if tp else None,
+                             vocab_total=self.core.config.vocab_size if tp else 0)
         return int(tok[0].item())
 
     def _full_logits(self):

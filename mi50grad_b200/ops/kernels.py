@@ -325,7 +325,7 @@ _tc_status = {}
 def sample_top_p(logits: torch.Tensor, temperature: float = 1.0, top_k: int = 50, top_p: float = 0.9,
                  repetition_penalty: float = 1.0, past: Optional[torch.Tensor] = None,
                  n_past: Optional[torch.Tensor] = None, seed: int = 0, vocab_offset: int = 0, debug: bool = False,
-                 comm: Optional[L.CommCtx] = None):
+                 comm: Optional[L.CommCtx] = None, vocab_total: int = 0):
     """Sample one token per row of fp32 logits [rows, vocab] on the device (temperature > 0).
     `past`: int32 [rows, max_past] token ids for the repetition penalty with counts `n_past`.
     The logits are modified in place by the penalty.  Returns int32 [rows] (and, with `debug`,
@@ -342,6 +342,7 @@ def sample_top_p(logits: torch.Tensor, temperature: float = 1.0, top_k: int = 50
         p.past, p.n_past, p.max_past = past.data_ptr(), n_past.data_ptr(), past.shape[1]
     p.seed, p.out_tokens = seed & 0xFFFFFFFFFFFFFFFF, out.data_ptr()
     p.comm = comm if comm is not None else L.null_comm()
+    p.vocab_total = vocab_total
     ids = probs = None
     if debug:
         ids = torch.empty(n, L.SAMPLE_MAX_CAND, dtype=torch.int32, device=dev)

@@ -141,7 +141,7 @@ class LayerDesc(C.Structure):
 class SampleParams(C.Structure):
     _fields_ = [("logits", vp), ("ld", i32), ("n_rows", i32), ("vocab", i32), ("vocab_offset", i32),
                 ("temperature", f32), ("top_p", f32), ("rep_penalty", f32), ("top_k", i32),
-                ("past", vp), ("n_past", vp), ("max_past", i32), ("pad", i32), ("seed", C.c_ulonglong),
+                ("past", vp), ("n_past", vp), ("max_past", i32), ("vocab_total", i32), ("seed", C.c_ulonglong),
                 ("out_tokens", vp), ("dbg_ids", vp), ("dbg_probs", vp), ("comm", CommCtx)]
 
 

@@ -303,7 +303,8 @@ def scenario_sample():
         ref_tok, ref_ids, ref_p = K.sample_top_p(full, temp, tk, tpp, pen, past, npast, seed=77, debug=True)
         local = core.logits(1).clone()
         tok, got_ids, got_p = K.sample_top_p(local, temp, tk, tpp, pen, past, npast, seed=77, debug=True,
-                                             vocab_offset=core.spec.vocab[0], comm=core._comm_ctx())
+                                             vocab_offset=core.spec.vocab[0], comm=core._comm_ctx(),
+                                             vocab_total=cfg.vocab_size)
         torch.cuda.synchronize()
         eng.check_status()
         assert int(tok[0]) == int(ref_tok[0]), (temp, tk, tpp, pen)

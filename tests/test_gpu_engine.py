@@ -79,6 +79,16 @@ def test_embedding_in_hidden_out_api(setup):
     assert cosine(torch.from_numpy(d).float(), d_ref) > 0.999
     lg = eng.compute_logits(d)
     assert cosine(torch.from_numpy(lg), orc.compute_logits(d_ref)) > 0.999
+    # a long prompt given as embeddings takes the tensor-core path (not eight rows per decode-sized step)
+    eng.states.reset(); orc.reset()
+    ids = _prompt(cfg, 40, seed=9)
+    emb = orc.embed(ids)
+    h_ref = orc.prefill_step(emb)
+    h = eng.prefill_step(emb.numpy())
+    assert cosine(torch.from_numpy(h).float(), h_ref) > 0.999 and eng.states.length(0) == 40
+    e1 = orc.embed([7])[0]
+    assert cosine(torch.from_numpy(eng.decode_step(e1.numpy(), position=40)).float(),
+                  orc.decode_step(e1, position=40)) > 0.999
 
 
 def test_two_sequences_with_independent_lengths(setup):
