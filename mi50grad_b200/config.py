@@ -296,8 +296,11 @@ class EngineConfig:
     fused_gemv_ar: bool = True
     # the persistent projection-chain kernel (csrc/chain.cu) in the decode step: 0 off, 1 consecutive INT4
     # projections run as one launch, 2 only the projections that exchange across GPUs use it (one launch each),
-    # -1 (default, or B200GRAD_CHAIN unset) = 2 under tensor parallelism, 0 on one GPU
+    # -1 (default, or B200GRAD_CHAIN unset) = 2 on two to four GPUs, 0 otherwise
     use_chain: int = dataclasses.field(default_factory=lambda: int(os.environ.get("B200GRAD_CHAIN", "-1")))
+    # many-row steps under tensor parallelism: 1 = residual stream sequence-parallel between the row-parallel
+    # projections (reduce-scatter by token rows + norm + fp16 all-gather in one kernel), 0 = all-reduce + norm
+    seq_parallel: int = dataclasses.field(default_factory=lambda: int(os.environ.get("B200GRAD_SEQ_PARALLEL", "1")))
     spec_ngram: int = 3
     spec_max_draft: int = 4
     max_step_rows: int = 0           # rows of a batched-decode / verify step (0: 8 per sequence slot)

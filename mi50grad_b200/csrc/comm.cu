@@ -198,6 +198,151 @@ B2_API int b2_allreduce(const CollParams* p, int max_ctas, cudaStream_t s) {
 B2_API int b2_sizeof_coll_params() { return (int)sizeof(CollParams); }
 
 // ---------------------------------------------------------------------------
+// Reduce-scatter + residual add + RMSNorm + all-gather for many-row steps under tensor parallelism.
+//
+// The row-parallel GEMM before this kernel stored its partial outputs into the staging buffer of the rank
+// that owns each token row (csrc/gemm_tc.cu, TC_EPI_PUSH_F32 with row-aligned slices).  Here every rank sums
+// the tp partials of ITS rows from local memory, adds them to its slice of the fp32 residual stream (which
+// therefore stays sequence-parallel: no rank ever holds other ranks' residual rows again), normalises the
+// rows with the next layer's RMSNorm weights and stores the fp16 result into every rank's activation
+// buffer (one multimem.st, or tp plain peer stores).  The consumer is the next GEMM, whose TMA tensor map
+// covers local memory only.  Against all-reduce + add_rmsnorm this moves half the bytes in the gather
+// phase (fp16 instead of fp32), normalises T / tp rows per rank instead of T, and drops one kernel.
+// One CTA per row; all CTAs wait on flags, so the grid is kept resident by the launcher.
+// The reference gathers full fp16 rows to GPU 0 and broadcasts them back for every prefill layer
+// (reference: src/inference/tp_engine.py:2082-2136).
+// ---------------------------------------------------------------------------
+#define SP_THREADS 256
+#define SP_MAX_IT 4              // H <= 8 * SP_THREADS * SP_MAX_IT
+
+__global__ void __launch_bounds__(SP_THREADS) rs_norm_ag_kernel(const SeqParParams p) {
+    const CommCtx& c = p.comm;
+    const int tp = c.tp, rank = c.rank, tid = threadIdx.x;
+    const uint32_t epoch = *c.epoch + 1u;
+    const size_t poff = (size_t)(epoch & 1) * c.part_stride;
+    __shared__ float red[32];
+    __shared__ int s_last;
+
+    // ---- 1. the partial sums of this rank's rows were stored by every rank's GEMM, which had finished on
+    //         that rank before this kernel started there: raise this rank's flag, wait for the others'
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+        s_last = (atomicAdd(&p.counters[0], 1) == (int)gridDim.x - 1);
+        if (s_last) p.counters[0] = 0;
+        __threadfence();
+    }
+    __syncthreads();
+    if (s_last && !p.test_withhold) signal_all(c, 0, epoch);
+    const bool ok = wait_all(c, 0, epoch, B2_KID_SEQPAR);
+
+    const int lo = rank * p.rows_per, hi = min(p.T, lo + p.rows_per);
+    const float* mine = c.part[rank] + poff;                 // [source rank][rows_per][H]
+    const size_t src_stride = (size_t)p.rows_per * p.H;
+    const int n8 = p.H / 8;
+    for (int row = lo + (int)blockIdx.x; row < hi; row += (int)gridDim.x) {
+        float4 va[SP_MAX_IT], vb[SP_MAX_IT];
+        float ss = 0.f;
+        float* hrow = p.h + (size_t)row * p.H;
+        const float* prow = mine + (size_t)(row - lo) * p.H;
+#pragma unroll
+        for (int it = 0; it < SP_MAX_IT; ++it) {
+            const int i = tid + it * SP_THREADS;
+            if (i < n8) {
+                float4 a = *(const float4*)(hrow + i * 8), b = *(const float4*)(hrow + i * 8 + 4);
+#pragma unroll
+                for (int r = 0; r < B2_MAX_TP; ++r) {
+                    if (r < tp && (ok || r == rank)) {
+                        const float* sp = prow + (size_t)r * src_stride + i * 8;
+                        const float4 x = ld_relaxed_sys_v4(sp), y = ld_relaxed_sys_v4(sp + 4);
+                        a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+                        b.x += y.x; b.y += y.y; b.z += y.z; b.w += y.w;
+                    }
+                }
+                *(float4*)(hrow + i * 8) = a;
+                *(float4*)(hrow + i * 8 + 4) = b;
+                va[it] = a; vb[it] = b;
+                ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+            }
+        }
+        const float inv = rsqrtf(block_sum(ss, red) / (float)p.H + p.eps);
+#pragma unroll
+        for (int it = 0; it < SP_MAX_IT; ++it) {
+            const int i = tid + it * SP_THREADS;
+            if (i < n8) {
+                const uint4 wq = *(const uint4*)(p.norm_w + i * 8);
+                const __half2* w2 = (const __half2*)&wq;
+                const float2 w0 = __half22float2(w2[0]), w1 = __half22float2(w2[1]), w2f = __half22float2(w2[2]), w3 = __half22float2(w2[3]);
+                const float4 a = va[it], b = vb[it];
+                __half2 o0 = __floats2half2_rn(a.x * inv * w0.x, a.y * inv * w0.y);
+                __half2 o1 = __floats2half2_rn(a.z * inv * w1.x, a.w * inv * w1.y);
+                __half2 o2 = __floats2half2_rn(b.x * inv * w2f.x, b.y * inv * w2f.y);
+                __half2 o3 = __floats2half2_rn(b.z * inv * w3.x, b.w * inv * w3.y);
+                float4 u;                                         // eight fp16 values, moved as 16 opaque bytes
+                u.x = __uint_as_float(*(uint32_t*)&o0); u.y = __uint_as_float(*(uint32_t*)&o1);
+                u.z = __uint_as_float(*(uint32_t*)&o2); u.w = __uint_as_float(*(uint32_t*)&o3);
+                const size_t off = (size_t)row * p.H + i * 8;
+                if (p.mc_xn && ok) multimem_st_v4((float*)(p.mc_xn + off), u);
+                else for (int r = 0; r < tp; ++r) if (ok || r == rank) *(float4*)(p.xn[r] + off) = u;
+                if (row == p.T - 1) {
+                    for (int r = 0; r < tp; ++r) {
+                        if (r == rank || !ok) continue;
+                        *(float4*)(p.hlast[r] + i * 8) = a;
+                        *(float4*)(p.hlast[r] + i * 8 + 4) = b;
+                    }
+                }
+            }
+        }
+    }
+    // ---- 2. every rank's rows are in every rank's activation buffer once all flags of the second round are up
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+        s_last = (atomicAdd(&p.counters[1], 1) == (int)gridDim.x - 1);
+        if (s_last) p.counters[1] = 0;
+        __threadfence_system();
+    }
+    __syncthreads();
+    if (s_last && !p.test_withhold) signal_all(c, B2_MAX_TP, epoch);
+    const bool ok2 = ok && wait_all(c, B2_MAX_TP, epoch, B2_KID_SEQPAR);
+    // the residual of the last row (what a caller reads back after a prompt) lands on every rank
+    const int last_owner = (p.T - 1) / p.rows_per;
+    if (blockIdx.x == 0 && ok2 && rank != last_owner) {
+        float* dst = p.h + (size_t)(p.T - 1) * p.H;
+        for (int i = tid; i < p.H / 4; i += SP_THREADS) ((float4*)dst)[i] = ld_relaxed_sys_v4(p.hlast[rank] + i * 4);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        if (atomicAdd(&p.counters[2], 1) == (int)gridDim.x - 1) {
+            p.counters[2] = 0;
+            *c.epoch = epoch;
+        }
+    }
+}
+
+B2_API int b2_rs_norm_ag(const SeqParParams* p, cudaStream_t s) {
+    const int tp = p->comm.tp;
+    if (tp < 2 || p->T < 1 || p->rows_per < 1 || p->rows_per * tp < p->T) return cudaErrorInvalidValue;
+    if (p->H % 8 || p->H > 8 * SP_THREADS * SP_MAX_IT) return cudaErrorInvalidValue;
+    if ((size_t)tp * p->rows_per * p->H > (size_t)p->comm.part_stride) return cudaErrorInvalidValue;
+    // CTAs wait on flags, so the whole grid must be resident: ask the runtime how many fit
+    static int resident = 0;
+    if (!resident) {
+        int dev = 0, sms = 0, per_sm = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rs_norm_ag_kernel, SP_THREADS, 0) != cudaSuccess || per_sm < 1)
+            return cudaErrorLaunchOutOfResources;
+        resident = sms * per_sm;
+    }
+    int ctas = p->rows_per < resident ? p->rows_per : resident;
+    if (ctas > 4 * 148) ctas = 4 * 148;
+    rs_norm_ag_kernel<<<ctas, SP_THREADS, 0, s>>>(*p);
+    return cudaGetLastError();
+}
+B2_API int b2_sizeof_seqpar_params() { return (int)sizeof(SeqParParams); }
+
+// ---------------------------------------------------------------------------
 // Device barrier across ranks (one CTA): flags only, bounded.
 // ---------------------------------------------------------------------------
 __global__ void barrier_kernel(const CommCtx c, int withhold) {

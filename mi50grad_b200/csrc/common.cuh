@@ -102,6 +102,9 @@ __device__ __forceinline__ void cp_async8(void* smem_dst, const void* gmem_src) 
     uint32_t s = (uint32_t)__cvta_generic_to_shared(smem_dst);
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" :: "r"(s), "l"(gmem_src) : "memory");
 }
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
@@ -218,6 +221,7 @@ struct SmemOptIn {
 #define B2_KID_BARRIER 4
 #define B2_KID_TEST 5
 #define B2_KID_GEMM_RS 6
+#define B2_KID_SEQPAR 11         // reduce-scatter + norm + all-gather: a peer never arrived
 #define B2_KID_SAMPLE 10         // distributed sampler: a peer's candidate list did not arrive
 #define B2_KID_CHAIN_DEP 7      // chain kernel: an op's producers did not finish
 #define B2_KID_CHAIN_TILE 8     // chain kernel: a peer's tile did not arrive

@@ -19,6 +19,7 @@
 // The tiny a/b projections (2 rows of length hidden per head) can be computed
 // in-kernel from the normalised activations, saving a launch.
 #include <cooperative_groups.h>
+#include <cstdlib>
 #include "kernels.cuh"
 namespace cg = cooperative_groups;
 
@@ -236,6 +237,216 @@ __global__ void __launch_bounds__(DN_THREADS) deltanet_step_kernel(const DeltaPa
         for (int t = 0; t < 3; ++t) my_hist[c * 3 + t] = __float2half(hist[c][t]);
 }
 
+// ---------------------------------------------------------------------------
+// One CTA per value head (all DV columns: DV/32 groups of four warps).  Same arithmetic and the same
+// state / conv-history layout as deltanet_step_kernel, laid out for latency: a decode step is a chain of
+// short dependent phases, so (1) the sum over the head's columns for the gated RMSNorm goes through shared
+// memory instead of a cluster barrier, (2) everything that earlier steps left (state slice, conv history,
+// weights of the a/b projections) is in registers before the dependency wait, and (3) all loads that
+// depend on this step's in-projection are issued together right after it.
+// ---------------------------------------------------------------------------
+template <int DK, int DV>
+__global__ void __launch_bounds__(DV / 32 * 128) deltanet_head_kernel(const DeltaParams p) {
+    constexpr int CB = DV / DN_COLS;
+    constexpr int KR = 4;                        // warps sharing one 32-column block: state rows kr, kr + KR, ...
+    constexpr int NT = CB * KR * 32;
+    constexpr int RPT = DK / KR;                 // state rows per thread
+    constexpr int NCHB = 2 * DK + DN_COLS;       // channels per private history copy in memory
+    constexpr int NCH = 2 * DK + DV;             // conv channels of the head: q | k | v
+    constexpr int PRE = 5;                       // a/b weight pairs per thread kept in registers
+    pdl_launch_dependents();
+    const int j = blockIdx.x, si = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int cb = warp / KR, kr = warp % KR, col = cb * DN_COLS + lane;
+    const int kh = j / (p.nv / p.nk);
+    const int r0 = p.seq_rows[si], r1 = p.seq_rows[si + 1];
+    if (r0 >= r1) return;
+    const int seq = p.rows[r0].seq;
+
+    __shared__ float cq[DK], ck[DK], cv[DV];
+    __shared__ float red_m[KR][DV], red_q[KR][DV];
+    __shared__ float red_ab[NT / 32][2];
+    __shared__ float red32[8];
+    __shared__ float ss_cb[CB];
+
+    // ---- left by earlier steps: conv history + weights of this thread's channel, state slice, constants
+    const bool has_ch = tid < NCH;
+    int pcol = 0;
+    float h0 = 0.f, h1 = 0.f, h2 = 0.f, w0 = 0.f, w1 = 0.f, w2 = 0.f, w3 = 0.f;
+    __half* hist_base = p.conv_state + (((size_t)seq * p.nv + j) * CB) * NCHB * 3;
+    __half* my_hist = nullptr;
+    if (has_ch) {
+        int gch;
+        if (tid < DK) { gch = kh * DK + tid; pcol = p.off_q + kh * DK + tid; my_hist = hist_base + (size_t)tid * 3; }
+        else if (tid < 2 * DK) { gch = p.nk * DK + kh * DK + (tid - DK); pcol = p.off_k + kh * DK + (tid - DK); my_hist = hist_base + (size_t)tid * 3; }
+        else {
+            const int v = tid - 2 * DK;
+            gch = 2 * p.nk * DK + j * DV + v; pcol = p.off_v + j * DV + v;
+            my_hist = hist_base + ((size_t)(v / DN_COLS) * NCHB + 2 * DK + (v % DN_COLS)) * 3;
+        }
+        h0 = __half2float(my_hist[0]); h1 = __half2float(my_hist[1]); h2 = __half2float(my_hist[2]);
+        const __half* w = p.conv_w + (size_t)gch * 4;
+        w0 = __half2float(w[0]); w1 = __half2float(w[1]); w2 = __half2float(w[2]); w3 = __half2float(w[3]);
+    }
+    float S[RPT];
+    float* sp = p.state + (((size_t)seq * p.nv + j) * DK) * DV + col;
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) S[i] = sp[(size_t)(kr + KR * i) * DV];
+    const float neg_expA = -__expf(p.A_log[j]);
+    const float dtb = __half2float(p.dt_bias[j]);
+    const float nw = __half2float(p.norm_w[col]);
+    const bool inkernel_ab = p.off_a < 0;
+    float2 pa[PRE], pb[PRE];
+#pragma unroll
+    for (int k = 0; k < PRE; ++k) {
+        pa[k] = pb[k] = make_float2(0.f, 0.f);
+        const int i = tid * 2 + k * NT * 2;
+        if (inkernel_ab && i < p.H) {
+            float2 av = __half22float2(*(const __half2*)(p.wa + (size_t)j * p.H + i));
+            float2 bv = __half22float2(*(const __half2*)(p.wb + (size_t)j * p.H + i));
+            if (p.ln.h) {
+                const float2 ww = __half22float2(*(const __half2*)(p.ln.w + i));
+                av.x *= ww.x; av.y *= ww.y; bv.x *= ww.x; bv.y *= ww.y;
+            }
+            pa[k] = av; pb[k] = bv;
+        }
+    }
+    pdl_wait();
+
+    for (int r = r0; r < r1; ++r) {
+        const __half* pr = p.proj + (size_t)r * p.ld;
+        // ---- every load that depends on this step, issued together
+        float2 xin[PRE];
+#pragma unroll
+        for (int k = 0; k < PRE; ++k) {
+            xin[k] = make_float2(0.f, 0.f);
+            const int i = tid * 2 + k * NT * 2;
+            if (inkernel_ab && i < p.H)
+                xin[k] = p.ln.h ? *(const float2*)(p.ln.h + (size_t)r * p.ln.H + i)
+                                : __half22float2(*(const __half2*)(p.xn + (size_t)r * p.ldx + i));
+        }
+        const float xc = has_ch ? __half2float(pr[pcol]) : 0.f;
+        const float z = kr == 0 ? __half2float(pr[p.off_z + j * DV + col]) : 0.f;
+        float ssp = 0.f, a_dir = 0.f, b_dir = 0.f;
+        if (warp == 3) {
+            if (inkernel_ab && p.ln.h) for (int i = lane; i < p.ln.np; i += 32) ssp += p.ln.ss[(size_t)r * p.ln.np + i];
+            if (!inkernel_ab) { a_dir = __half2float(pr[p.off_a + j]); b_dir = __half2float(pr[p.off_b + j]); }
+        }
+        // ---- phase A: partial sums of the a/b projections, conv + SiLU of this thread's channel
+        if (inkernel_ab) {
+            float sa = 0.f, sb = 0.f;
+#pragma unroll
+            for (int k = 0; k < PRE; ++k) {
+                sa += xin[k].x * pa[k].x + xin[k].y * pa[k].y;
+                sb += xin[k].x * pb[k].x + xin[k].y * pb[k].y;
+            }
+            for (int i = tid * 2 + PRE * NT * 2; i < p.H; i += NT * 2) {        // hidden sizes beyond PRE pairs per thread
+                float2 xv = p.ln.h ? *(const float2*)(p.ln.h + (size_t)r * p.ln.H + i)
+                                   : __half22float2(*(const __half2*)(p.xn + (size_t)r * p.ldx + i));
+                float2 av = __half22float2(*(const __half2*)(p.wa + (size_t)j * p.H + i));
+                float2 bv = __half22float2(*(const __half2*)(p.wb + (size_t)j * p.H + i));
+                if (p.ln.h) {
+                    const float2 ww = __half22float2(*(const __half2*)(p.ln.w + i));
+                    av.x *= ww.x; av.y *= ww.y; bv.x *= ww.x; bv.y *= ww.y;
+                }
+                sa += xv.x * av.x + xv.y * av.y;
+                sb += xv.x * bv.x + xv.y * bv.y;
+            }
+            sa = warp_sum(sa);
+            sb = warp_sum(sb);
+            if (lane == 0) { red_ab[warp][0] = sa; red_ab[warp][1] = sb; }
+        }
+        if (has_ch) {
+            float o = silu_f(h0 * w0 + h1 * w1 + h2 * w2 + xc * w3);
+            h0 = h1; h1 = h2; h2 = xc;
+            if (tid < DK) cq[tid] = o; else if (tid < 2 * DK) ck[tid - DK] = o; else cv[tid - 2 * DK] = o;
+        }
+        __syncthreads();
+        // ---- phase B: warps 0..2 the q/k norms and q.k, warp 3 the a/b inputs
+        if (warp < 3) {
+            float s = 0.f;
+            for (int i = lane; i < DK; i += 32) {
+                float a = (warp == 1) ? ck[i] : cq[i], b = (warp == 0) ? cq[i] : ck[i];
+                s += a * b;                      // warp 0: q.q  warp 1: k.k  warp 2: q.k
+            }
+            s = warp_sum(s);
+            if (lane == 0) red32[warp] = s;
+        } else if (warp == 3) {
+            float a_in = a_dir, b_in = b_dir;
+            if (inkernel_ab) {
+                float inv = 1.f;
+                if (p.ln.h) inv = rsqrtf(warp_sum(ssp) / (float)p.ln.H + p.ln.eps);
+                float ta = 0.f, tb = 0.f;
+                for (int w = lane; w < NT / 32; w += 32) { ta += red_ab[w][0]; tb += red_ab[w][1]; }
+                ta = warp_sum(ta); tb = warp_sum(tb);
+                // the unfused path rounds the projection output to fp16: keep that rounding
+                a_in = __half2float(__float2half(ta * inv));
+                b_in = __half2float(__float2half(tb * inv));
+            }
+            if (lane == 0) { red32[3] = a_in; red32[4] = b_in; }
+        }
+        __syncthreads();
+        const float invq = rsqrtf(red32[0] + 1e-6f) * rsqrtf((float)DK);
+        const float invk = rsqrtf(red32[1] + 1e-6f);
+        const float kq = red32[2] * invq * invk;
+        const float a_in = red32[3], b_in = red32[4];
+        float gl = neg_expA * (a_in + dtb > 20.f ? a_in + dtb : log1pf(__expf(a_in + dtb)));
+        gl = fmaxf(gl, -20.f);
+        const float decay = __expf(gl);
+        const float beta = sigmoid_f(b_in);
+        // ---- phase C: single pass over the state slice: m = S^T k, sq = S^T q
+        float mp = 0.f, qp = 0.f;
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) {
+            mp = fmaf(S[i], ck[kr + KR * i], mp);
+            qp = fmaf(S[i], cq[kr + KR * i], qp);
+        }
+        red_m[kr][col] = mp * invk;
+        red_q[kr][col] = qp * invq;
+        __syncthreads();
+        float mm = 0.f, sq = 0.f;
+#pragma unroll
+        for (int w = 0; w < KR; ++w) { mm += red_m[w][col]; sq += red_q[w][col]; }
+        const float delta = (cv[col] - decay * mm) * beta;
+        const float y = decay * sq + delta * kq;
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) S[i] = decay * S[i] + ck[kr + KR * i] * invk * delta;
+        // ---- gated RMSNorm over the head's DV outputs
+        const float ss = warp_sum(y * y);
+        if (kr == 0 && lane == 0) ss_cb[cb] = ss;
+        __syncthreads();
+        if (kr == 0) {
+            float tot = 0.f;
+#pragma unroll
+            for (int c = 0; c < CB; ++c) tot += ss_cb[c];
+            float o = y * rsqrtf(tot / (float)DV + p.eps) * nw * silu_f(z);
+            p.out[(size_t)r * p.ldo + j * DV + col] = __float2half(o);
+        }
+        __syncthreads();                         // this row's shared-memory reads before the next row's writes
+    }
+    if (!p.commit) return;
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) sp[(size_t)(kr + KR * i) * DV] = S[i];
+    if (has_ch) {
+        const __half a0 = __float2half(h0), a1 = __float2half(h1), a2 = __float2half(h2);
+        if (tid < 2 * DK) {
+            // q / k history: every column block keeps its own copy (the chunked scan and the verify kernels read them)
+#pragma unroll
+            for (int c = 0; c < CB; ++c) {
+                __half* d = hist_base + ((size_t)c * NCHB + tid) * 3;
+                d[0] = a0; d[1] = a1; d[2] = a2;
+            }
+        } else {
+            my_hist[0] = a0; my_hist[1] = a1; my_hist[2] = a2;
+        }
+    }
+}
+
+template <int DK, int DV>
+static int launch_delta_head(const DeltaParams* p, cudaStream_t s) {
+    return launch_pdl(deltanet_head_kernel<DK, DV>, dim3(p->nv, p->n_seqs), dim3(DV / 32 * 128), 0, s, *p);
+}
+
 template <int DK, int DV>
 static int launch_delta(const DeltaParams* p, cudaStream_t s) {
     constexpr int CB = DV / DN_COLS;
@@ -260,6 +471,12 @@ static int launch_delta(const DeltaParams* p, cudaStream_t s) {
 
 B2_API int b2_deltanet_step(const DeltaParams* p, int dk, int dv, cudaStream_t s) {
     if (p->nv % p->nk) return cudaErrorInvalidValue;
+    // one CTA per head (deltanet_head_kernel) unless B200GRAD_DELTANET_CLUSTER selects the cluster form
+    static const bool cluster_form = getenv("B200GRAD_DELTANET_CLUSTER") != nullptr;
+    if (!cluster_form) {
+        if (dk == 128 && dv == 128) return launch_delta_head<128, 128>(p, s);
+        if (dk == 64 && dv == 64) return launch_delta_head<64, 64>(p, s);
+    }
     if (dk == 128 && dv == 128) return launch_delta<128, 128>(p, s);
     if (dk == 64 && dv == 64) return launch_delta<64, 64>(p, s);
     return cudaErrorInvalidValue;

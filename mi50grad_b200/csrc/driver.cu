@@ -58,6 +58,7 @@ struct LayerDesc {
     int q8_group, q8_F, pad_q8;   // group size of the W4A8 scales; local FFN width
     const void* q8_w[3];          // int8 [N][K] or signed nibbles int32 [N][K/8]
     const void* q8_s[3];          // fp32 [N] (W8A8) or fp16 [K/group][N] (W4A8)
+    const void* wab;              // DeltaNet: [wa; wb] as one fp16 [2*nv][H] matrix (many-row steps run it as a GEMM)
 };
 
 struct ModelDesc {
@@ -96,6 +97,9 @@ struct ModelDesc {
     SpecStage spec; int* spec_acc; int* spec_result;
     float* state0; void* conv0; long long state_layer_stride, conv_layer_stride;
     void* k0; void* v0; long long kv_layer_stride;
+    // sequence-parallel many-row steps (csrc/comm.cu, rs_norm_ag_kernel): p_xn is then this rank's copy of a
+    // symmetric buffer, xn_sym its address on every rank, hlast_sym a slot of H floats
+    void* xn_sym[B2_MAX_TP]; void* xn_mc; float* hlast_sym[B2_MAX_TP]; int seq_parallel; int pad5;
     // persistent projection chain (csrc/chain.cu)
     void* chain_scratch; unsigned int* chain_counters; int chain_act_cols; int use_chain;
     void* chain_tag_h; void* chain_tag_ss; void* chain_tag_act;
@@ -125,6 +129,8 @@ struct Driver {
     cudaGraphExec_t exec = nullptr;
     int graph_rows = 0, graph_flags = 0;
     long long launches = 0;               // kernels issued by the last eager step
+    int push_rows_per = 0;                // > 0 while a GEMM is issued whose pushed slices are whole token rows
+    bool sp_now = false;                  // the many-row step being issued keeps the residual stream sequence-parallel
 };
 
 #define STEP_EMBED_TOKENS 1     // gather embeddings from tokens (else: h/xn were loaded by the caller)
@@ -454,14 +460,38 @@ static int run_gemm(Driver* d, const LinearDesc& L, const void* x, int ldx, int 
         for (int r = 0; r < c.tp; ++r) p.push[r] = c.part[r];
         p.epoch = c.epoch; p.part_stride = (long long)c.part_stride;
         p.push_tp = c.tp; p.push_rank = c.rank; p.push_per = (unsigned)((n4 + c.tp - 1) / c.tp);
+        if (d->push_rows_per > 0) p.push_per = (unsigned)((size_t)d->push_rows_per * ldo / 4);    // slices of whole token rows
     }
     d->launches++;
     return b2_gemm_int4_tc(&p, x, ldx, s);
 }
 
-static int row_parallel(Driver* d, const LinearDesc& L, const void* x, int ldx, int T, cudaStream_t s) {
+// True when the many-row step keeps the residual stream sequence-parallel: each row-parallel projection is
+// followed by one kernel that reduce-scatters by token rows, adds the residual, applies the NEXT RMSNorm and
+// all-gathers the fp16 result (so the callers skip their add_rmsnorm launches).
+static bool seq_parallel_rows(const ModelDesc& m, int T) {
+    if (m.comm.tp <= 1 || !m.seq_parallel) return false;
+    const int per = (T + m.comm.tp - 1) / m.comm.tp;
+    return (size_t)m.comm.tp * per * m.H <= (size_t)m.comm.part_stride && m.H % 8 == 0 && m.H <= 8192;
+}
+
+static int row_parallel(Driver* d, const LinearDesc& L, const void* x, int ldx, int T, const void* next_norm, cudaStream_t s) {
     const ModelDesc& m = d->m;
     if (m.comm.tp <= 1) return run_gemm(d, L, x, ldx, T, m.p_h, m.H, m.H, TC_EPI_RESID_F32, s);
+    if (d->sp_now) {
+        const int per = (T + m.comm.tp - 1) / m.comm.tp;
+        d->push_rows_per = per;
+        CK(run_gemm(d, L, x, ldx, T, nullptr, m.H, m.H, TC_EPI_PUSH_F32, s));
+        d->push_rows_per = 0;
+        SeqParParams q;
+        memset(&q, 0, sizeof(q));
+        q.comm = m.comm; q.h = m.p_h; q.norm_w = (const __half*)next_norm;
+        for (int r = 0; r < m.comm.tp; ++r) { q.xn[r] = (__half*)m.xn_sym[r]; q.hlast[r] = m.hlast_sym[r]; }
+        q.mc_xn = (__half*)m.xn_mc;
+        q.T = T; q.H = m.H; q.rows_per = per; q.eps = m.eps; q.counters = m.coll_counters;
+        d->launches++; d->exchanges++;
+        return b2_rs_norm_ag(&q, s);
+    }
     // Tensor parallel: the GEMM epilogue pushes every output tile into the staging buffer of the rank
     // that reduces that slice (reduce-scatter traffic overlaps the GEMM); the collective kernel then
     // sums its slice from local memory, multicasts it, and adds the residual.
@@ -486,10 +516,14 @@ static int rows_impl(Driver* d, int T, int n_seqs, int flags, cudaStream_t s) {
                             m.H, m.eps, m.vocab, s));
         d->launches++;
     }
+    // sequence-parallel residual stream: not with INT8-activation FFNs (their kernels read full residual rows)
+    bool sp = seq_parallel_rows(m, T);
+    for (int li = 0; li < m.n_layers && sp; ++li) if (d->layers[li].ffn_kind != 0) sp = false;
+    d->sp_now = sp;
     for (int li = 0; li < m.n_layers; ++li) {
         const LayerDesc& L = d->layers[li];
         struct Count { Driver* d; int li; long long l0; ~Count() { d->layer_launches[li] = (int)(d->launches - l0); } } count{d, li, d->launches};
-        if (li > 0) { CK(b2_add_rmsnorm(m.p_h, nullptr, nullptr, L.attn_norm, m.p_xn, nullptr, T, m.H, m.eps, s)); d->launches++; }
+        if (li > 0 && !sp) { CK(b2_add_rmsnorm(m.p_h, nullptr, nullptr, L.attn_norm, m.p_xn, nullptr, T, m.H, m.eps, s)); d->launches++; }
         CK(run_gemm(d, L.in_proj, m.p_xn, m.H, T, m.p_proj, m.ld_proj, L.in_proj.N, TC_EPI_STORE_F16, s));
         if (L.type == 0) {
             CK(b2_qknorm_rope_cachew(m.p_proj, m.ld_proj, m.p_rows, L.q_norm, L.k_norm, m.cos_tab, m.sin_tab, L.kcache,
@@ -520,7 +554,17 @@ static int rows_impl(Driver* d, int T, int n_seqs, int flags, cudaStream_t s) {
             // else one small dense kernel for all rows into spare columns of the projection buffer
             const void* ab = (const __half*)m.p_proj + (L.off_a >= 0 ? L.off_a : 0);
             if (L.off_a < 0 && m.ab_off >= 0) {
-                CK(b2_ab_proj(m.p_xn, m.H, L.wa, L.wb, m.la_nv, m.H, (__half*)m.p_proj + m.ab_off, m.ld_proj, T, s));
+                if (L.wab && T >= 64 && m.H % 64 == 0) {
+                    // the two small gate projections of all rows as one dense tensor-core GEMM (weights by TMA)
+                    GemmTcParams g;
+                    memset(&g, 0, sizeof(g));
+                    g.K = m.H; g.T = T; g.t_tile = 64;
+                    g.n_valid = 2 * m.la_nv; g.ldo = m.ld_proj; g.epi = TC_EPI_STORE_F16;
+                    g.out = (__half*)m.p_proj + m.ab_off; g.status = m.tc_status;
+                    CK(b2_gemm_f16_tc(&g, L.wab, m.H, m.p_xn, m.H, s));
+                } else {
+                    CK(b2_ab_proj(m.p_xn, m.H, L.wa, L.wb, m.la_nv, m.H, (__half*)m.p_proj + m.ab_off, m.ld_proj, T, s));
+                }
                 d->launches++;
                 ab = (const __half*)m.p_proj + m.ab_off;
                 q.off_a = m.ab_off; q.off_b = m.ab_off + m.la_nv;
@@ -535,15 +579,17 @@ static int rows_impl(Driver* d, int T, int n_seqs, int flags, cudaStream_t s) {
             d->launches++;
         }
         // prefill always uses the exact all-reduce placement
-        CK(row_parallel(d, L.out_proj, m.p_attn, m.ld_attn, T, s));
+        CK(row_parallel(d, L.out_proj, m.p_attn, m.ld_attn, T, L.ffn_norm, s));
         if (L.ffn_kind != 0) { CK(ffn_q8(d, L, m.p_h, T, nullptr, s)); continue; }
-        CK(b2_add_rmsnorm(m.p_h, nullptr, nullptr, L.ffn_norm, m.p_xn, nullptr, T, m.H, m.eps, s)); d->launches++;
+        if (!sp) { CK(b2_add_rmsnorm(m.p_h, nullptr, nullptr, L.ffn_norm, m.p_xn, nullptr, T, m.H, m.eps, s)); d->launches++; }
         CK(run_gemm(d, L.gate_up, m.p_xn, m.H, T, m.p_act, m.F_pad, m.F_pad, TC_EPI_SILU_PAIR, s));
-        CK(row_parallel(d, L.down, m.p_act, m.F_pad, T, s));
+        CK(row_parallel(d, L.down, m.p_act, m.F_pad, T, L.next_norm, s));
     }
     // final norm of every row (hidden-out interface and the lm_head input)
-    CK(b2_add_rmsnorm(m.p_h, nullptr, nullptr, d->layers[m.n_layers - 1].next_norm, m.p_xn, nullptr, T, m.H, m.eps, s));
-    d->launches++;
+    if (!sp) {
+        CK(b2_add_rmsnorm(m.p_h, nullptr, nullptr, d->layers[m.n_layers - 1].next_norm, m.p_xn, nullptr, T, m.H, m.eps, s));
+        d->launches++;
+    }
     if (flags & STEP_LM_HEAD) {
         // logits of every row: the fp16 lm_head goes through the same tcgen05 pipeline, weights by TMA
         if (T > m.p_logit_rows || m.lm_head.kind != LIN_F16) return cudaErrorInvalidValue;

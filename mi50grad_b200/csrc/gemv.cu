@@ -37,6 +37,7 @@ namespace cg = cooperative_groups;
 #define GEMV_WN 2            // warps along n
 #define GEMV_WK 4            // warps along k
 #define GEMV_NT 4            // 16-wide n-tiles per warp
+#define GEMV_STAGE_UN 3         // activation items per thread whose loads are in flight together
 #define GEMV_TILE_N (GEMV_WN * GEMV_NT * 16)   // 128
 #define GEMV_STAGES 4        // cp.async ring depth per warp (k64-blocks in flight)
 
@@ -74,8 +75,9 @@ struct TileCtx {
 __device__ void finish_rows(const GemvEpi& e, const CommCtx& c, int rows, uint32_t epoch_next,
                             float* red);
 
+// h_pre / has_pre: the residual of (row 0, column n0 + tid), read by the caller while the weights streamed.
 __device__ void complete_tile(float* ybuf, const TileCtx& t, const GemvEpi& e, const CommCtx& c,
-                              uint32_t epoch_next, float* red, int* s_flag) {
+                              uint32_t epoch_next, float* red, int* s_flag, float h_pre = 0.f, bool has_pre = false) {
     const int tid = threadIdx.x;
     if (t.k_splits > 1 && t.cluster) {
         // ---- split-K inside a thread-block cluster: the partner CTAs' tiles are read straight from
@@ -117,9 +119,17 @@ __device__ void complete_tile(float* ybuf, const TileCtx& t, const GemvEpi& e, c
         if (!*s_flag) return;
         for (int i = tid; i < t.rows * GEMV_TILE_N; i += GEMV_THREADS) {
             int r = i / GEMV_TILE_N, nl = i % GEMV_TILE_N;
+            // the pieces of up to eight splits are requested together: a load-then-add loop would pay one
+            // trip to L2 per split; the sum keeps the order of the splits
             float s = 0.f;
-            for (int ks = 0; ks < t.k_splits; ++ks)
-                s += ld_cg_f32(&t.scratch[((size_t)ks * t.rows + r) * t.n_pad + t.n0 + nl]);
+            for (int k0 = 0; k0 < t.k_splits; k0 += 8) {
+                float v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    v[u] = (k0 + u < t.k_splits) ? ld_cg_f32(&t.scratch[((size_t)(k0 + u) * t.rows + r) * t.n_pad + t.n0 + nl]) : 0.f;
+#pragma unroll
+                for (int u = 0; u < 8; ++u) s += v[u];
+            }
             ybuf[r * GEMV_TILE_N + nl] = s;
         }
         __syncthreads();
@@ -161,7 +171,7 @@ __device__ void complete_tile(float* ybuf, const TileCtx& t, const GemvEpi& e, c
                         float v = ybuf[r * GEMV_TILE_N + tid];
                         if (e.fin_flags & FIN_ADD_EXTRA) v += e.extra[off];
                         if (e.fin_flags & FIN_SAVE_EXTRA) e.extra[off] = v;
-                        float hv = e.h[off] + v;
+                        float hv = ((has_pre && r == 0) ? h_pre : e.h[off]) + v;
                         e.hout[off] = hv;
                         sq = hv * hv;
                     }
@@ -340,62 +350,89 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_int4_kernel(const GemvIn
     const uint32_t epoch_next = (p.epi.mode == EPI_FINISH && p.comm.tp > 1) ? (*p.comm.epoch + 1u) : 0u;
     if (p.comm.trace && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) p.comm.trace[3] = globaltimer_ns();
 
+    // the residual this tile's epilogue adds (one token row, no exchange): requested now, used at the very end
+    float h_pre = 0.f;
+    bool has_pre = false;
+    if (p.epi.mode == EPI_FINISH && M == 1 && ((p.epi.fin_flags & FIN_NO_COMM) || p.comm.tp <= 1) && tid < GEMV_TILE_N) {
+        const int n = blockIdx.x * GEMV_TILE_N + tid;
+        if (n < p.epi.n_valid) { h_pre = p.epi.h[n]; has_pre = true; }
+    }
+
     // ---- stage activations in MMA B-fragment order, with per-chunk bias sums
     for (int i = tid; i < nCh * 8; i += GEMV_THREADS)
         if ((i & 7) >= M) cs[i] = make_float2(0.f, 0.f);
     if (tid < 4) xf[(size_t)maxCh * M * 4 + tid] = make_uint4(0u, 0u, 0u, 0u);
     const int items = nCh * 4;
     float* s_inv = red32;                       // [rows] 1/rms per row when the input is lazy-normed
-    if (p.ln.h) {
-        if (warp < M) { float v = lazy_inv_rms(p.ln, warp, lane); if (lane == 0) s_inv[warp] = v; }
-        __syncthreads();
-    }
+    // Loads first, arithmetic after: the inputs of up to GEMV_STAGE_UN items per thread (and, under them, the
+    // partial sums of squares of the lazy RMSNorm) are requested before anything waits on one of them, so
+    // staging costs one trip to L2 instead of one per item.
+    bool inv_ready = !p.ln.h;
     for (int m = 0; m < M; ++m) {
         const __half* xr = p.x + (size_t)m * p.ldx;
         const float* hr = p.ln.h ? p.ln.h + (size_t)m * p.ln.H : nullptr;
-        const float inv = p.ln.h ? s_inv[m] : 0.f;
-        for (int base = 0; base < items; base += GEMV_THREADS) {
-            int item = base + tid;
-            bool valid = item < items;
-            int tt = item & 3, cl = item >> 2;
-            int k0 = (cta_b0 * 2 + cl) * 32 + 2 * tt;
-            __half2 a0, a1, b0, b1;
-            a0 = a1 = b0 = b1 = __float2half2_rn(0.f);
-            if (valid && hr) {
-                auto ld = [&](int k) -> __half2 {
-                    float2 hv = *(const float2*)(hr + k);
-                    float2 wv = __half22float2(*(const __half2*)(p.ln.w + k));
-                    return __floats2half2_rn(hv.x * inv * wv.x, hv.y * inv * wv.y);
-                };
-                if (k0 < p.K) a0 = ld(k0);
-                if (k0 + 8 < p.K) a1 = ld(k0 + 8);
-                if (k0 + 16 < p.K) b0 = ld(k0 + 16);
-                if (k0 + 24 < p.K) b1 = ld(k0 + 24);
-            } else if (valid) {
-                if (k0 < p.K) a0 = *(const __half2*)(xr + k0);
-                if (k0 + 8 < p.K) a1 = *(const __half2*)(xr + k0 + 8);
-                if (k0 + 16 < p.K) b0 = *(const __half2*)(xr + k0 + 16);
-                if (k0 + 24 < p.K) b1 = *(const __half2*)(xr + k0 + 24);
+        for (int base0 = 0; base0 < items; base0 += GEMV_STAGE_UN * GEMV_THREADS) {
+            float2 hv[GEMV_STAGE_UN][4];
+            __half2 wv[GEMV_STAGE_UN][4];
+#pragma unroll
+            for (int u = 0; u < GEMV_STAGE_UN; ++u) {
+                const int item = base0 + u * GEMV_THREADS + tid;
+                const bool valid = item < items;
+                const int k0 = (cta_b0 * 2 + (item >> 2)) * 32 + 2 * (item & 3);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int k = k0 + 8 * q;
+                    hv[u][q] = make_float2(0.f, 0.f);
+                    wv[u][q] = __float2half2_rn(0.f);
+                    if (valid && k < p.K) {
+                        if (hr) { hv[u][q] = *(const float2*)(hr + k); wv[u][q] = *(const __half2*)(p.ln.w + k); }
+                        else wv[u][q] = *(const __half2*)(xr + k);
+                    }
+                }
             }
-            const __half2 sixteenth = __float2half2_rn(0.0625f);
-            b0 = __hmul2(b0, sixteenth);
-            b1 = __hmul2(b1, sixteenth);
-            float2 fa0 = __half22float2(a0), fa1 = __half22float2(a1);
-            float2 fb0 = __half22float2(b0), fb1 = __half22float2(b1);
-            float sa = fa0.x + fa0.y + fa1.x + fa1.y;
-            float sb = fb0.x + fb0.y + fb1.x + fb1.y;
-            sa += __shfl_xor_sync(0xffffffffu, sa, 1);
-            sb += __shfl_xor_sync(0xffffffffu, sb, 1);
-            sa += __shfl_xor_sync(0xffffffffu, sa, 2);
-            sb += __shfl_xor_sync(0xffffffffu, sb, 2);
-            if (valid) {
-                uint4 v;
-                v.x = *(uint32_t*)&a0; v.y = *(uint32_t*)&a1; v.z = *(uint32_t*)&b0; v.w = *(uint32_t*)&b1;
-                xf[(cl * M + m) * 4 + tt] = v;
-                if (tt == 0) cs[cl * 8 + m] = make_float2(1024.f * (sa + sb), sa + 16.f * sb);
+            if (!inv_ready) {
+                if (warp < M) { float v = lazy_inv_rms(p.ln, warp, lane); if (lane == 0) s_inv[warp] = v; }
+                __syncthreads();
+                inv_ready = true;
+            }
+            const float inv = hr ? s_inv[m] : 0.f;
+#pragma unroll
+            for (int u = 0; u < GEMV_STAGE_UN; ++u) {
+                const int item = base0 + u * GEMV_THREADS + tid;
+                if (base0 + u * GEMV_THREADS >= items) break;          // uniform: no thread has an item here
+                const bool valid = item < items;
+                const int tt = item & 3, cl = item >> 2;
+                __half2 a0, a1, b0, b1;
+                if (hr) {
+                    auto nrm = [&](int q) -> __half2 {
+                        const float2 w = __half22float2(wv[u][q]);
+                        return __floats2half2_rn(hv[u][q].x * inv * w.x, hv[u][q].y * inv * w.y);
+                    };
+                    a0 = nrm(0); a1 = nrm(1); b0 = nrm(2); b1 = nrm(3);
+                } else {
+                    a0 = wv[u][0]; a1 = wv[u][1]; b0 = wv[u][2]; b1 = wv[u][3];
+                }
+                const __half2 sixteenth = __float2half2_rn(0.0625f);
+                b0 = __hmul2(b0, sixteenth);
+                b1 = __hmul2(b1, sixteenth);
+                float2 fa0 = __half22float2(a0), fa1 = __half22float2(a1);
+                float2 fb0 = __half22float2(b0), fb1 = __half22float2(b1);
+                float sa = fa0.x + fa0.y + fa1.x + fa1.y;
+                float sb = fb0.x + fb0.y + fb1.x + fb1.y;
+                sa += __shfl_xor_sync(0xffffffffu, sa, 1);
+                sb += __shfl_xor_sync(0xffffffffu, sb, 1);
+                sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+                sb += __shfl_xor_sync(0xffffffffu, sb, 2);
+                if (valid) {
+                    uint4 v;
+                    v.x = *(uint32_t*)&a0; v.y = *(uint32_t*)&a1; v.z = *(uint32_t*)&b0; v.w = *(uint32_t*)&b1;
+                    xf[(cl * M + m) * 4 + tt] = v;
+                    if (tt == 0) cs[cl * 8 + m] = make_float2(1024.f * (sa + sb), sa + 16.f * sb);
+                }
             }
         }
     }
+    if (!inv_ready) __syncthreads();               // (no items at all: keep the barrier count uniform)
     __syncthreads();
 
     float acc[GEMV_NT][4], tot[GEMV_NT][4];
@@ -500,7 +537,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_int4_kernel(const GemvIn
     TileCtx tc;
     tc.rows = M; tc.n0 = blockIdx.x * GEMV_TILE_N; tc.n_pad = p.NTL * 16;
     tc.k_splits = p.k_splits; tc.scratch = p.scratch; tc.counters = p.counters; tc.cluster = p.cluster_splitk;
-    complete_tile(ybuf, tc, p.epi, p.comm, epoch_next, red32, s_flag);
+    complete_tile(ybuf, tc, p.epi, p.comm, epoch_next, red32, s_flag, h_pre, has_pre);
 }
 
 // ---------------------------------------------------------------------------
@@ -700,6 +737,7 @@ static void noalloc_launch_shape(int KB, int NTL, int rows, int* k_splits, int* 
     const int ks_max = (KB + GEMV_WK - 1) / GEMV_WK;
     if (ks > ks_max) ks = ks_max;
     if (ks < 1) ks = 1;
+    if (KB <= 24) ks = 1;                          // short K: no cross-CTA split (as ops/packing.py)
     auto even = [&](int v) { return (KB >= 2 * GEMV_WK) ? v + (v & 1) : v; };
     int l = even((KB + GEMV_WK * ks - 1) / (GEMV_WK * ks));
     while ((size_t)2 * GEMV_WK * l * (rows + 1) * 64 > 32000u) {

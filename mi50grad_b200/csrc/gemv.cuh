@@ -32,8 +32,13 @@ struct LazyNorm {
 
 __device__ __forceinline__ float lazy_inv_rms(const LazyNorm& ln, int row, int lane) {
     // one warp: sum the partials in a fixed order
-    float s = 0.f;
-    for (int i = lane; i < ln.np; i += 32) s += ln.ss[(size_t)row * ln.np + i];
+    // (the first four loads of a lane are requested together; the order of the additions is unchanged)
+    float s = 0.f, v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = (lane + 32 * u < ln.np) ? ln.ss[(size_t)row * ln.np + lane + 32 * u] : 0.f;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) s += v[u];
+    for (int i = lane + 128; i < ln.np; i += 32) s += ln.ss[(size_t)row * ln.np + i];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     return rsqrtf(s / (float)ln.H + ln.eps);

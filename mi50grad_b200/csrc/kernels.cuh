@@ -66,6 +66,23 @@ struct CollParams {
                              //    staging buffers ([source rank][slice]); nothing to publish, reduce from local memory
 };
 
+// Sequence-parallel hand-off after a row-parallel many-row projection (csrc/comm.cu, rs_norm_ag_kernel):
+// reduce-scatter by token rows, residual add and RMSNorm on this rank's rows, all-gather of the fp16 result
+// straight into every rank's activation buffer, where the next GEMM's TMA loads find it.
+struct SeqParParams {
+    CommCtx comm;
+    float* h;                    // local residual stream [T][H] fp32: only this rank's rows are read and updated
+    const __half* norm_w;        // weights of the RMSNorm that follows
+    __half* xn[B2_MAX_TP];       // every rank's activation buffer [T][H] fp16 (symmetric memory)
+    __half* mc_xn;               // multicast mapping of that buffer (or null: plain peer stores)
+    float* hlast[B2_MAX_TP];     // every rank's slot [H] for the fp32 residual of row T-1
+    int T, H, rows_per;          // rank r owns rows [r * rows_per, min(T, (r + 1) * rows_per))
+    float eps;
+    int* counters;               // [4] local, zero between launches
+    int test_withhold;           // test hook: never signal, so that the bounded wait expires
+    int pad;
+};
+
 // ---- speculative verification (csrc/speculative.cu)
 #define SPEC_MAX_NODES 16          // rows per sequence in one verify step: the pending token + up to 15 drafts
 
@@ -117,6 +134,7 @@ B2_API int b2_deltanet_commit(const DeltaCommitParams* p, int dk, int dv, cudaSt
 B2_API int b2_spec_accept(const SpecAcceptParams* p, cudaStream_t s);
 B2_API int b2_kv_compact(const KvCompactParams* p, cudaStream_t s);
 B2_API int b2_allreduce(const CollParams* p, int max_ctas, cudaStream_t s);
+B2_API int b2_rs_norm_ag(const SeqParParams* p, cudaStream_t s);
 B2_API int b2_gemv_int4(const GemvInt4Params* p, cudaStream_t stream);
 B2_API int b2_gemv_f16(const GemvF16Params* p, cudaStream_t stream);
 B2_API int b2_decode_attn(const AttnParams* p, int hd, cudaStream_t s);

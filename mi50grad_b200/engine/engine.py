@@ -350,7 +350,7 @@ class InferenceEngine:
         # cache slices per decode-attention row: long contexts need more CTAs than (rows x KV heads) gives
         self.attn_splits = 16 if self.max_seq_len <= 1024 else 32
         G = sp.n_q // sp.n_kv
-        b["attn_scratch"] = f32(R * sp.n_kv * self.attn_splits * G * (cfg.head_dim + 2))
+        b["attn_scratch"] = f32(R * sp.n_kv * self.attn_splits * G * (cfg.head_dim + 4))
         b["attn_counters"] = i32(R * sp.n_kv + 8)
         self.argmax_blocks = max(1, min(64, sp.vocab_local // 2048))
         b["argmax_scratch"] = f32(R * self.argmax_blocks * 2)
@@ -363,7 +363,7 @@ class InferenceEngine:
         # persistent projection chain: split-K pieces and tile / dependency counters
         int4 = [l for l in lins if l.packed is not None]
         uc = int(self.ecfg.use_chain)
-        self.use_chain = (2 if self.tp_size > 1 else 0) if uc < 0 else uc
+        self.use_chain = (2 if 1 < self.tp_size <= 4 else 0) if uc < 0 else uc
         if not int4:
             self.use_chain = 0
         self.lib.b2_chain_scratch_floats.restype = C.c_longlong
@@ -390,6 +390,12 @@ class InferenceEngine:
         P = self.max_prefill = min(512, self.max_seq_len)
         self.use_tc_prefill = all(l.packed is not None for l in lins[:-1])
         b["p_h"], b["p_xn"] = f32(P, H), f16(P, H)
+        # sequence-parallel many-row steps: the activations live in symmetric memory, where every rank's
+        # reduce-scatter + norm + all-gather kernel stores its rows
+        self.seq_parallel = bool(self.ecfg.seq_parallel) and self.tp_size > 1 and self.comm is not None \
+            and hasattr(self.comm, "xn_view") and P * H <= getattr(self.comm, "xn_halves", 0) and H % 8 == 0 and H <= 8192
+        if self.seq_parallel:
+            b["p_xn"] = self.comm.xn_view(P, H)
         b["p_proj"], b["p_attn"], b["p_act"] = f16(P, b["ld_proj"]), f16(P, b["ld_attn"]), f16(P, self.F_pad)
         b["p_partial"] = f32(P, H) if self.tp_size > 1 else f32(1)
         b["p_rows"], b["p_rows_tmpl"] = i32(P, 6), i32(P, 6)
@@ -402,7 +408,7 @@ class InferenceEngine:
         b["p_logits"] = f32(SR, b["ld_logits"])
         b["p_argmax_scratch"], b["p_argmax_counters"] = f32(SR * self.argmax_blocks * 2), i32(SR + 8)
         b["p_out_tokens"] = i32(P)
-        b["p_attn_scratch"] = f32(SR * sp.n_kv * self.attn_splits * G * (cfg.head_dim + 2))
+        b["p_attn_scratch"] = f32(SR * sp.n_kv * self.attn_splits * G * (cfg.head_dim + 4))
         b["p_attn_counters"] = i32(SR * sp.n_kv + 8)
         # speculative verification: staging of the DeltaNet verify kernel, acceptance results
         offs = [C.c_int() for _ in range(4)]
@@ -444,6 +450,9 @@ class InferenceEngine:
         m.seqs = self.states.seqs.data_ptr()
         m.comm = self._comm_ctx()
         m.max_prefill = self.max_prefill
+        if self.seq_parallel:
+            # (a communicator rebuilt by recover() has a new symmetric block)
+            b["p_xn"] = self.comm.xn_view(self.max_prefill, self.config.hidden_size)
         for k in ("p_h", "p_xn", "p_proj", "p_attn", "p_act", "p_partial", "p_rows", "p_rows_tmpl", "p_row_tokens",
                   "tc_status", "coll_counters", "p_ab"):
             setattr(m, k, b[k].data_ptr())
@@ -466,6 +475,12 @@ class InferenceEngine:
             for r in range(self.tp_size):
                 m.coll_gather[r] = self.comm.peer_ptrs[r] + self.comm.off_gather
             m.coll_mc_gather = (self.comm.multicast_ptr + self.comm.off_gather) if self.comm.multicast_ptr else None
+            if self.seq_parallel:
+                for r in range(self.tp_size):
+                    m.xn_sym[r] = self.comm.peer_ptrs[r] + self.comm.off_xn
+                    m.hlast_sym[r] = self.comm.peer_ptrs[r] + self.comm.off_hlast
+                m.xn_mc = (self.comm.multicast_ptr + self.comm.off_xn) if self.comm.multicast_ptr else None
+                m.seq_parallel = 1
         descs = (L.LayerDesc * cfg.num_hidden_layers)()
         for i, dl in enumerate(self.layers):
             d = descs[i]
@@ -484,6 +499,10 @@ class InferenceEngine:
             else:
                 d.wa = None if dl.wa is None else dl.wa.data_ptr()
                 d.wb = None if dl.wb is None else dl.wb.data_ptr()
+                if dl.wa is not None and dl.wb is not None:
+                    if getattr(dl, "wab", None) is None:
+                        dl.wab = torch.cat([dl.wa, dl.wb], dim=0).contiguous()
+                    d.wab = dl.wab.data_ptr()
                 d.conv_w, d.A_log = dl.conv_w.data_ptr(), dl.A_log.data_ptr()
                 d.dt_bias, d.la_norm = dl.dt_bias.data_ptr(), dl.la_norm.data_ptr()
                 d.conv_state = self.states.dn.layer_conv(i).data_ptr()

@@ -212,7 +212,7 @@ def decode_attn(q, rows_meta, kcache, vcache, nq, nkv, hd, gate_off=-1, splits=4
     p.kcache, p.vcache, p.rows = kcache.data_ptr(), vcache.data_ptr(), rows_meta.data_ptr()
     p.out, p.ldo, p.n_rows, p.nq, p.nkv = out.data_ptr(), out.stride(0), n, nq, nkv
     p.max_seq, p.splits, p.scale = kcache.shape[1], splits, 1.0 / hd ** 0.5
-    scratch = torch.empty(n * nkv * splits * G * (hd + 2), dtype=torch.float32, device=dev)
+    scratch = torch.empty(n * nkv * splits * G * (hd + 4), dtype=torch.float32, device=dev)
     counters = torch.zeros(n * nkv + 1, dtype=torch.int32, device=dev)
     p.scratch, p.counters = scratch.data_ptr(), counters.data_ptr()
     L.check(L.lib().b2_decode_attn(C.byref(p), hd, L.stream()), "decode_attn")

@@ -135,7 +135,7 @@ class LayerDesc(C.Structure):
                 ("A_log", vp), ("dt_bias", vp), ("la_norm", vp),
                 ("off_q", i32), ("off_k", i32), ("off_v", i32), ("off_z", i32), ("off_a", i32), ("off_b", i32),
                 ("ffn_kind", i32), ("q8_group", i32), ("q8_F", i32), ("pad_q8", i32),
-                ("q8_w", vp * 3), ("q8_s", vp * 3)]
+                ("q8_w", vp * 3), ("q8_s", vp * 3), ("wab", vp)]
 
 
 class SampleParams(C.Structure):
@@ -192,6 +192,7 @@ class ModelDesc(C.Structure):
                 ("spec", SpecStage), ("spec_acc", vp), ("spec_result", vp),
                 ("state0", vp), ("conv0", vp), ("state_layer_stride", i64), ("conv_layer_stride", i64),
                 ("k0", vp), ("v0", vp), ("kv_layer_stride", i64),
+                ("xn_sym", vp * MAX_TP), ("xn_mc", vp), ("hlast_sym", vp * MAX_TP), ("seq_parallel", i32), ("pad5", i32),
                 ("chain_scratch", vp), ("chain_counters", vp), ("chain_act_cols", i32), ("use_chain", i32),
                 ("chain_tag_h", vp), ("chain_tag_ss", vp), ("chain_tag_act", vp),
                 ("q8_xq", vp), ("q8_sx", vp), ("q8_gate", vp), ("q8_up", vp), ("q8_down", vp), ("q8_xn", vp),

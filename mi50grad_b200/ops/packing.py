@@ -87,6 +87,10 @@ def launch_shape(KB: int, NTL: int, rows: int = 1, slots: int = 2 * NUM_SMS, K: 
         return t
     ctas_n = NTL * 16 // TILE_N
     k_splits = max(1, min(slots // max(ctas_n, 1), -(-KB // GEMV_WK)))
+    if KB <= 24:
+        # short K (a row-parallel shard under tensor parallelism): the cross-CTA split-K round trip costs more
+        # than the few blocks it spreads (measured: K = 768 / 1536 -> 5120: 4.2 / 5.3 us unsplit)
+        k_splits = 1
     even = lambda v: v + (v & 1) if KB >= 2 * GEMV_WK else v      # even L enables the aligned-group fast path
     L = even(-(-KB // (GEMV_WK * k_splits)))
     # shared-memory bound: activation fragments are 64 bytes per chunk per row

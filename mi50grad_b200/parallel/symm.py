@@ -18,6 +18,8 @@ Layout of the symmetric block (bytes):
     [.., +256)                      flag words: [0,8) phase A, [8,16) phase B (uint32, by source rank)
     [.., +2*tp*8*tile_h*8)          tile staging of the chain kernel: [parity][source rank][row][tile_h] {fp32, epoch}
     [.., +8*TILE_FLAGS*4)           tile flags: [source rank][tile] uint32
+    [.., +part_floats*2)            fp16 activations of many-row steps, all-gathered by rs_norm_ag_kernel
+    [.., +hidden*4)                 fp32 residual of the last row of such a step
 """
 from __future__ import annotations
 
@@ -30,8 +32,15 @@ import torch.distributed as dist
 from ..ops import lib as L
 from .comm import CommTimeout, Communicator
 
+class SeqParParams(C.Structure):
+    _fields_ = [("comm", L.CommCtx), ("h", C.c_void_p), ("norm_w", C.c_void_p), ("xn", C.c_void_p * L.MAX_TP),
+                ("mc_xn", C.c_void_p), ("hlast", C.c_void_p * L.MAX_TP), ("T", C.c_int), ("H", C.c_int),
+                ("rows_per", C.c_int), ("eps", C.c_float), ("counters", C.c_void_p), ("test_withhold", C.c_int),
+                ("pad", C.c_int)]
+
+
 KERNEL_NAMES = {1: "gemv finisher", 2: "all-reduce", 3: "arg-max", 4: "barrier", 5: "wait self-test", 6: "gemm reduce-scatter",
-                7: "chain dependency", 8: "chain tile exchange", 9: "chain weight copy", 10: "distributed sampler"}
+                7: "chain dependency", 8: "chain tile exchange", 9: "chain weight copy", 10: "distributed sampler", 11: "reduce-scatter + norm + all-gather"}
 
 
 class CollParams(C.Structure):
@@ -66,7 +75,11 @@ class SymmComm(Communicator):
         self.tile_flags = max(128, self.tile_h // 64)
         self.off_tpart = self.off_sig + 256
         self.off_tsig = self.off_tpart + 2 * self.tp_size * L.MAX_ROWS * self.tile_h * 8      # {value, epoch} pairs
-        nbytes = self.off_tsig + L.MAX_TP * self.tile_flags * 4
+        # sequence-parallel many-row steps (csrc/comm.cu, rs_norm_ag_kernel)
+        self.off_xn = -(-(self.off_tsig + L.MAX_TP * self.tile_flags * 4) // 1024) * 1024
+        self.xn_halves = self.part_floats
+        self.off_hlast = self.off_xn + -(-self.xn_halves * 2 // 256) * 256
+        nbytes = self.off_hlast + self.tile_h * 4
         self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
         self.buf.zero_()
         self.hdl = symm_mem.rendezvous(self.buf, self.group)
@@ -96,6 +109,45 @@ class SymmComm(Communicator):
         c.epoch, c.status, c.wait_ns = self.epoch.data_ptr(), self.status.data_ptr(), self.wait_ns
         c.trace = self.trace.data_ptr() if self.trace_enabled else None
         return c
+
+    def xn_view(self, rows: int, hidden: int) -> torch.Tensor:
+        """This rank's copy of the symmetric fp16 activation buffer of many-row steps, as a [rows, hidden] tensor."""
+        if rows * hidden > self.xn_halves:
+            raise ValueError(f"{rows} x {hidden} activations do not fit the symmetric buffer ({self.xn_halves} halves)")
+        return self.buf[self.off_xn:self.off_xn + rows * hidden * 2].view(torch.float16).view(rows, hidden)
+
+    def reduce_scatter_norm_allgather(self, h: torch.Tensor, norm_w: torch.Tensor, T: int, eps: float,
+                                      withhold_signal: bool = False) -> torch.Tensor:
+        """After every rank stored its partial rows into the owners' staging buffers (row-aligned slices of
+        ceil(T / tp) rows, as the GEMM epilogue does): h[own rows] += sum of partials, normalised fp16 rows of
+        every rank gathered into xn_view() on every rank.  One kernel (csrc/comm.cu, rs_norm_ag_kernel)."""
+        H = h.shape[1]
+        p = SeqParParams()
+        p.comm = self.ctx()
+        p.h, p.norm_w = h.data_ptr(), norm_w.data_ptr()
+        for r in range(self.tp_size):
+            p.xn[r] = self.peer_ptrs[r] + self.off_xn
+            p.hlast[r] = self.peer_ptrs[r] + self.off_hlast
+        p.mc_xn = (self.multicast_ptr + self.off_xn) if self.multicast_ptr else None
+        p.T, p.H, p.rows_per, p.eps = T, H, -(-T // self.tp_size), eps
+        p.counters, p.test_withhold = self.counters.data_ptr(), int(withhold_signal)
+        L.check(self.lib.b2_rs_norm_ag(C.byref(p), L.stream()), "rs_norm_ag")
+        return self.xn_view(T, H)
+
+    def push_rows(self, partial: torch.Tensor):
+        """Test helper: store this rank's [T, H] fp32 partial rows where the GEMM epilogue would have stored
+        them (the staging buffer of each row's owner, parity of the next epoch)."""
+        T, H = partial.shape
+        per = -(-T // self.tp_size)
+        parity = (int(self.epoch.item()) + 1) & 1
+        for r in range(self.tp_size):
+            lo, hi = r * per, min(T, (r + 1) * per)
+            if lo >= hi:
+                continue
+            dst = self.hdl.get_buffer(r, (per * H,), torch.float32,
+                                      parity * self.part_floats + self.tp_rank * per * H)
+            dst[:(hi - lo) * H].copy_(partial[lo:hi].reshape(-1))
+        torch.cuda.synchronize()
 
     def last_exchange_trace(self) -> dict:
         """globaltimer stamps (ns) of the last fused GEMV exchange on this rank, relative to the

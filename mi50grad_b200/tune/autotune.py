@@ -43,7 +43,7 @@ def candidates(KB: int, NTL: int, rows: int = 1):
     for ks in sorted({1, 2, 3, 4, 5, 6, 7, 8, 10, 12, 14, 16, base_ks, base_ks + 1, max(1, base_ks - 1)}):
         Lb = -(-KB // (GEMV_WK * ks))
         Lb += Lb & 1 if KB >= 2 * GEMV_WK else 0
-        if Lb < 1 or 2 * GEMV_WK * Lb * (rows + 1) * 64 > 40_000:
+        if Lb < 1 or 2 * GEMV_WK * Lb * (rows + 1) * 64 > 32_000:
             continue
         ks_eff = -(-KB // (GEMV_WK * Lb))
         if (ks_eff, Lb) in seen:

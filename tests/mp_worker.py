@@ -132,6 +132,64 @@ def scenario_tp_engine(ar_mode: str, multimem: bool, model: str = "tiny"):
     eng.cleanup()
 
 
+def scenario_seq_parallel(multimem: bool):
+    """Reduce-scatter by token rows + residual + RMSNorm + fp16 all-gather in one kernel: stand-alone at the
+    27B prefill shape (and a ragged row count) against an fp32 reference, then the many-row path of the TP
+    engine with the sequence-parallel residual stream against the all-reduce placement."""
+    from mi50grad_b200.parallel.symm import SymmComm
+    rank, world = dist.get_rank(), dist.get_world_size()
+    H = 5120
+    comm = SymmComm(part_floats=512 * H, hidden=H, use_multimem=multimem)
+    dev = comm.device
+    for T in (512, 77, 3):
+        per = -(-T // world)
+        g = torch.Generator().manual_seed(5)
+        h0 = torch.randn(T, H, generator=g)
+        w = (torch.rand(H, generator=g) + 0.5).half()
+        parts = [torch.randn(T, H, generator=torch.Generator().manual_seed(50 + r)) for r in range(world)]
+        href = h0 + sum(parts)
+        xref = href * torch.rsqrt((href * href).mean(-1, keepdim=True) + 1e-6) * w.float()
+        for rep in range(3):                          # epochs advance, parity alternates
+            h = h0.to(dev).clone()
+            comm.push_rows(parts[rank].to(dev))
+            dist.barrier()
+            xn = comm.reduce_scatter_norm_allgather(h, w.to(dev), T, 1e-6)
+            torch.cuda.synchronize()
+            comm.check_status()
+            lo, hi = rank * per, min(T, (rank + 1) * per)
+            assert _rel(xn.cpu(), xref) < 2e-3, (T, rep, _rel(xn.cpu(), xref))
+            if lo < hi:
+                assert _rel(h[lo:hi].cpu(), href[lo:hi]) < 1e-5, (T, rep)
+            assert _rel(h[T - 1].cpu(), href[T - 1]) < 1e-5, (T, rep)       # the last row lands on every rank
+            dist.barrier()
+    comm.close()
+    # the engine: same tokens and hidden states with either placement
+    from mi50grad_b200.config import EngineConfig, tiny_config
+    from mi50grad_b200.engine.tp_engine import TPInferenceEngine
+    from mi50grad_b200.models.weights import random_model
+    cfg = tiny_config(hidden_size=512, intermediate_size=2048, num_attention_heads=8, num_key_value_heads=4,
+                      linear_num_key_heads=8, linear_num_value_heads=16, vocab_size=2048)
+    mw = random_model(cfg, 0)
+    ids = torch.randint(0, cfg.vocab_size, (70,), generator=torch.Generator().manual_seed(0)).tolist()
+    outs = []
+    for sp in (1, 0):
+        eng = TPInferenceEngine(cfg, list(range(world)), max_seq_len=128,
+                                engine_config=EngineConfig(use_multimem=multimem, seq_parallel=sp))
+        eng.load_model(mw)
+        toks = eng.generate_tokens(ids, 6, graph=False)
+        assert bool(eng.engine.seq_parallel) == bool(sp)
+        eng.engine.reset()
+        first = eng.engine.prefill_tokens_tc(ids)
+        xn_last = eng.engine.buf["p_xn"][len(ids) - 1].float().cpu().clone()
+        h_last = eng.engine.buf["h"][0].float().cpu().clone()
+        torch.cuda.synchronize()
+        eng.check_status()
+        outs.append((toks, first, xn_last, h_last))
+        eng.cleanup()
+    assert outs[0][0] == outs[1][0] and outs[0][1] == outs[1][1], (outs[0][0], outs[1][0])
+    assert _rel(outs[0][2], outs[1][2]) < 5e-3 and _rel(outs[0][3], outs[1][3]) < 1e-3
+
+
 def scenario_spec():
     """Speculative verification and many-row steps at TP=world against the oracle: a draft tree
     (GEMV path), three sequences with chains (tensor-core path), batched decode of 10 sequences."""
@@ -331,6 +389,9 @@ def main():
         elif scenario == "spec":
             scenario_spec()
             extra = ""
+        elif scenario == "seq_parallel":
+            scenario_seq_parallel(sys.argv[2] == "multimem")
+            extra = sys.argv[2]
         elif scenario == "sample":
             scenario_sample()
             extra = ""

@@ -47,6 +47,11 @@ def test_fused_projection_exchange_at_model_shapes(mode):
     _run(_n(), "fused_shapes", mode)
 
 
+@pytest.mark.parametrize("mode", ["peer", "multimem"])
+def test_sequence_parallel_reduce_scatter_norm_allgather(mode):
+    _run(_n(), "seq_parallel", mode)
+
+
 def test_speculative_and_many_row_steps_under_tp():
     _run(2, "spec")
 
