@@ -221,6 +221,7 @@ struct SmemOptIn {
 #define B2_KID_BARRIER 4
 #define B2_KID_TEST 5
 #define B2_KID_GEMM_RS 6
+#define B2_KID_GEMV_SPLITK 12     // GEMV: a split-K partner's tagged partial sums did not arrive
 #define B2_KID_SEQPAR 11         // reduce-scatter + norm + all-gather: a peer never arrived
 #define B2_KID_SAMPLE 10         // distributed sampler: a peer's candidate list did not arrive
 #define B2_KID_CHAIN_DEP 7      // chain kernel: an op's producers did not finish

@@ -15,9 +15,12 @@
 // prepare_rows: fill RowMeta from the per-sequence state and a static template.
 // tmpl[r] = {seq, depth, slot_offset, unused, mask}: pos = len+depth, slot = len+slot_offset.
 // ---------------------------------------------------------------------------
+// step_word (optional): the step's generation, advanced by 1024 here; kernels of the step derive tags that
+// no earlier step used from it (csrc/gemv.cu, tagged split-K hand-off).
 __global__ void prepare_rows_kernel(const RowMeta* __restrict__ tmpl, const SeqState* __restrict__ seqs,
-                                    RowMeta* __restrict__ rows, int n) {
+                                    RowMeta* __restrict__ rows, int n, unsigned int* step_word) {
     pdl_launch_dependents();
+    if (step_word && blockIdx.x == 0 && threadIdx.x == 0) *step_word += 1024u;
     int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= n) return;
     RowMeta t = tmpl[r];
@@ -31,8 +34,8 @@ __global__ void prepare_rows_kernel(const RowMeta* __restrict__ tmpl, const SeqS
     rows[r] = o;
 }
 
-B2_API int b2_prepare_rows(const void* tmpl, const void* seqs, void* rows, int n, cudaStream_t s) {
-    prepare_rows_kernel<<<(n + 63) / 64, 64, 0, s>>>((const RowMeta*)tmpl, (const SeqState*)seqs, (RowMeta*)rows, n);
+B2_API int b2_prepare_rows(const void* tmpl, const void* seqs, void* rows, int n, unsigned int* step_word, cudaStream_t s) {
+    prepare_rows_kernel<<<(n + 63) / 64, 64, 0, s>>>((const RowMeta*)tmpl, (const SeqState*)seqs, (RowMeta*)rows, n, step_word);
     return cudaGetLastError();
 }
 

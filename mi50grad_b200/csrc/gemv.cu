@@ -70,7 +70,10 @@ struct TileCtx {
     int cluster;             // split-K partners are one cluster: reduce through distributed shared memory
     float* scratch;
     int* counters;
+    uint32_t tag;            // != 0: tagged hand-off of the split-K partials (see GemvInt4Params::tag_word)
 };
+
+#define GEMV_TAG_POLLS (1 << 20)     // polls of one batch of partners before the merge gives up
 
 __device__ void finish_rows(const GemvEpi& e, const CommCtx& c, int rows, uint32_t epoch_next,
                             float* red);
@@ -98,6 +101,48 @@ __device__ void complete_tile(float* ybuf, const TileCtx& t, const GemvEpi& e, c
         }
         cl.sync();                                   // partners may exit (their shared memory is no longer read)
         if (blockIdx.y != 0) return;
+        __syncthreads();
+    } else
+    // ---- cross-CTA split-K, tagged: slices 1.. store {value, tag} pairs and leave; slice 0 polls them and
+    // sums in the order of the slices (the same order, and therefore the same bits, as the counter protocol)
+    if (t.k_splits > 1 && t.tag) {
+        float2* sc = (float2*)t.scratch;
+        if (blockIdx.y != 0) {
+            for (int i = tid; i < t.rows * GEMV_TILE_N; i += GEMV_THREADS) {
+                const int r = i / GEMV_TILE_N, nl = i % GEMV_TILE_N;
+                float2 v = make_float2(ybuf[r * GEMV_TILE_N + nl], __uint_as_float(t.tag));
+                float2* dst = &sc[((size_t)(blockIdx.y - 1) * t.rows + r) * t.n_pad + t.n0 + nl];
+                asm volatile("st.global.v2.f32 [%0], {%1, %2};" :: "l"(dst), "f"(v.x), "f"(v.y) : "memory");
+            }
+            return;
+        }
+        bool late = false;
+        for (int i = tid; i < t.rows * GEMV_TILE_N; i += GEMV_THREADS) {
+            const int r = i / GEMV_TILE_N, nl = i % GEMV_TILE_N;
+            float s = ybuf[r * GEMV_TILE_N + nl];
+            for (int k0 = 1; k0 < t.k_splits; k0 += 8) {
+                float v[8];
+                unsigned need = 0;
+#pragma unroll
+                for (int u = 0; u < 8; ++u) { v[u] = 0.f; if (k0 + u < t.k_splits) need |= 1u << u; }
+                for (int it = 0; it < GEMV_TAG_POLLS && need; ++it) {
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        if (need & (1u << u)) {
+                            const float2* src = &sc[((size_t)(k0 + u - 1) * t.rows + r) * t.n_pad + t.n0 + nl];
+                            float a, b;
+                            asm volatile("ld.volatile.global.v2.f32 {%0, %1}, [%2];" : "=f"(a), "=f"(b) : "l"(src) : "memory");
+                            if (__float_as_uint(b) == t.tag) { v[u] = a; need &= ~(1u << u); }
+                        }
+                    }
+                }
+                if (need) late = true;
+#pragma unroll
+                for (int u = 0; u < 8; ++u) if (k0 + u < t.k_splits) s += v[u];
+            }
+            ybuf[r * GEMV_TILE_N + nl] = s;
+        }
+        if (late && c.status) report_timeout(c, B2_KID_GEMV_SPLITK, (int)blockIdx.x, t.tag);
         __syncthreads();
     } else
     // ---- cross-CTA split-K: publish, count, last arriver sums in a fixed order
@@ -296,6 +341,27 @@ __device__ void finish_rows(const GemvEpi& e, const CommCtx& c, int rows, uint32
     }
 }
 
+// One warp's share of the L2 prefetch for the next INT4 GEMV of the stream: the streams (CTA, warp) of that
+// launch are dealt round-robin to the warps of this one; lane 0 asks L2 for the first blocks of each.
+__device__ __forceinline__ void prefetch_next_weights(const GemvInt4Params& p, int warp, int lane) {
+    if (!p.pf_q || lane != 0) return;
+    const int my = ((int)blockIdx.y * (int)gridDim.x + (int)blockIdx.x) * (GEMV_THREADS / 32) + warp;
+    const int n_mine = (int)(gridDim.x * gridDim.y) * (GEMV_THREADS / 32);
+    const int n_next = p.pf_nx * p.pf_ks * (GEMV_THREADS / 32);
+    for (int sid = my; sid < n_next; sid += n_mine) {
+        const int cta = sid / (GEMV_THREADS / 32), w = sid % (GEMV_THREADS / 32);
+        const int x = cta % p.pf_nx, y = cta / p.pf_nx;
+        const int wn = w % GEMV_WN, wk = w / GEMV_WN;
+        const int b0 = y * (GEMV_WK * p.pf_L) + wk * p.pf_L;
+        const int b1 = min(min(p.pf_KB, (y + 1) * (GEMV_WK * p.pf_L)), b0 + p.pf_L);
+        const int nb = min(b1 - b0, p.pf_blocks);
+        if (nb <= 0) continue;
+        const uint4* src = p.pf_q + ((size_t)(x * GEMV_WN + wn) * p.pf_KB + b0) * (GEMV_NT * 32);
+        const uint32_t bytes = (uint32_t)nb * (GEMV_NT * 32 * 16);
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(src), "r"(bytes) : "memory");
+    }
+}
+
 // ---------------------------------------------------------------------------
 // INT4 kernel
 // ---------------------------------------------------------------------------
@@ -345,11 +411,14 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_int4_kernel(const GemvIn
         cp_async_commit();
     }
     gp += (GEMV_STAGES - 1) * GEMV_NT * 32;    // next block to prefetch
+    if (nb <= GEMV_STAGES - 1) prefetch_next_weights(p, warp, lane);      // all of this warp's weights are requested
     // Weights do not depend on earlier kernels; everything below does.
     pdl_wait();
     const uint32_t epoch_next = (p.epi.mode == EPI_FINISH && p.comm.tp > 1) ? (*p.comm.epoch + 1u) : 0u;
     if (p.comm.trace && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) p.comm.trace[3] = globaltimer_ns();
 
+    // tag of this launch's split-K pairs (requested now, used at the very end)
+    const uint32_t tag = (p.tag_word && p.k_splits > 1) ? (*p.tag_word + (uint32_t)p.tag_base) : 0u;
     // the residual this tile's epilogue adds (one token row, no exchange): requested now, used at the very end
     float h_pre = 0.f;
     bool has_pre = false;
@@ -475,6 +544,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_int4_kernel(const GemvIn
                     for (int i = 0; i < GEMV_NT; ++i)
                         cp_async16(rp + (((s + GEMV_STAGES - 1) % GEMV_STAGES) * GEMV_NT + i) * 32, gp + i * 32);
                     gp += GEMV_NT * 32;
+                    if (br + GEMV_STAGES == nb) prefetch_next_weights(p, warp, lane);     // that was this warp's last block
                     // block br + 3 is the first of its group exactly when s is odd (the slice starts on an even block)
                     if (FAST && (s & 1) && lane < 16)
                         cp_async16(szr + (((br + GEMV_STAGES - 1) >> 1) & (GEMV_STAGES - 1)) * 16 + lane,
@@ -537,6 +607,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_int4_kernel(const GemvIn
     TileCtx tc;
     tc.rows = M; tc.n0 = blockIdx.x * GEMV_TILE_N; tc.n_pad = p.NTL * 16;
     tc.k_splits = p.k_splits; tc.scratch = p.scratch; tc.counters = p.counters; tc.cluster = p.cluster_splitk;
+    tc.tag = tag;
     complete_tile(ybuf, tc, p.epi, p.comm, epoch_next, red32, s_flag, h_pre, has_pre);
 }
 
@@ -632,6 +703,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_f16_kernel(const GemvF16Par
     TileCtx tc;
     tc.rows = M; tc.n0 = blockIdx.x * GEMV_TILE_N; tc.n_pad = (int)gridDim.x * GEMV_TILE_N;
     tc.k_splits = p.k_splits; tc.scratch = p.scratch; tc.counters = p.counters;
+    tc.cluster = 0; tc.tag = 0;
     complete_tile(ybuf, tc, p.epi, p.comm, epoch_next, red32, s_flag);
 }
 
@@ -667,6 +739,28 @@ B2_API int b2_gemv_int4(const GemvInt4Params* p, cudaStream_t stream) {
     cfg.numAttrs = 1;
     GemvInt4Params q = *p;
     q.cluster_splitk = 0;
+    if (q.tag_word && q.k_splits > 1) {
+        // the tagged hand-off makes one CTA wait for others of the same grid: only with the whole grid resident
+        static std::mutex occ_mu;
+        static int sms = 0, n_cached = 0;
+        static size_t cached_smem[64];
+        static int cached_fast[64], cached_per_sm[64];
+        int per_sm = 0;
+        {
+            std::lock_guard<std::mutex> lock(occ_mu);
+            if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+            for (int i = 0; i < n_cached; ++i)
+                if (cached_smem[i] == smem && cached_fast[i] == (int)fast) per_sm = cached_per_sm[i];
+            if (!per_sm) {
+                int n = 0;
+                cudaError_t e = fast ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemv_int4_kernel<true>, GEMV_THREADS, smem)
+                                     : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemv_int4_kernel<false>, GEMV_THREADS, smem);
+                per_sm = (e == cudaSuccess && n > 0) ? n : -1;
+                if (n_cached < 64) { cached_smem[n_cached] = smem; cached_fast[n_cached] = (int)fast; cached_per_sm[n_cached++] = per_sm; }
+            }
+        }
+        if (per_sm < 0 || (long long)cfg.gridDim.x * cfg.gridDim.y > (long long)sms * per_sm) q.tag_word = nullptr;
+    }
     // Optional: the split-K partners of an output tile as one cluster along grid y, reducing through
     // distributed shared memory.  Measured slower than the scratch + counter path on B200 (down
     // projection 21.0 us against 14.7 us, decode 180.5 against 188.4 tok/s: clusters of 7 CTAs are

@@ -73,9 +73,21 @@ struct GemvInt4Params {
     int k_splits, L;         // CTAs along K, k64-blocks per warp
     int cluster_splitk;      // set by the launcher: the k_splits CTAs of an output tile form a thread-block cluster
                              // and reduce their partial tiles through distributed shared memory
-    int pad1;
+    int tag_base;            // see tag_word
     float* scratch;          // [k_splits][rows][NTL*16] split-K partials
     int* counters;           // [gridDim.x + 1], zero between launches
+    // Tagged split-K hand-off (optional): with tag_word set, the partners of an output tile store their
+    // partial sums as {value, tag} pairs (tag = *tag_word + tag_base, never 0 and never repeated on this
+    // scratch buffer while an older pair can still sit in it) and the CTA of slice 0 polls them: no fence, no
+    // counter, no second trip to L2.  scratch then holds (k_splits - 1) x rows x N such pairs.  The caller
+    // must keep the whole grid resident (the launcher checks and falls back to the counter protocol).
+    const unsigned int* tag_word;
+    // L2 prefetch for the INT4 GEMV that follows in the stream (optional, pf_q != null): when a warp has
+    // requested the last of its own weights it asks L2 for the first pf_blocks k-blocks of "its" warps of the
+    // next launch (grid pf_nx x pf_ks, pf_L blocks per warp, pf_KB blocks per tile), so that HBM keeps
+    // streaming through this kernel's reduction tail and the next kernel's start.
+    const uint4* pf_q;
+    int pf_KB, pf_L, pf_nx, pf_ks, pf_blocks, pf_pad;
     LazyNorm ln;
     GemvEpi epi;
     CommCtx comm;

@@ -144,7 +144,7 @@ B2_API int b2_deltanet_chunk(const DeltaParams* p, const void* ab, int ld_ab, in
 B2_API int b2_ab_proj(const void* x, int ldx, const void* wa, const void* wb, int nv, int H, void* ab, int ld_ab,
                       int rows, cudaStream_t s);
 B2_API int b2_argmax(const ArgmaxParams* p, cudaStream_t s);
-B2_API int b2_prepare_rows(const void* tmpl, const void* seqs, void* rows, int n, cudaStream_t s);
+B2_API int b2_prepare_rows(const void* tmpl, const void* seqs, void* rows, int n, unsigned int* step_word, cudaStream_t s);
 B2_API int b2_advance(void* seqs, const int* add, int n, int add_const, cudaStream_t s);
 B2_API int b2_embed_rmsnorm(const void* embed, const int* row_tokens, const void* rows, const void* seqs,
                             const void* w, float* h, void* xn, float* ss_part, int np, int n_rows, int H,

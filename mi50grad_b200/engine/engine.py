@@ -19,6 +19,7 @@ from __future__ import annotations
 
 import ctypes as C
 import logging
+import os
 import math
 from typing import Dict, List, Optional, Sequence, Union
 
@@ -345,7 +346,9 @@ class InferenceEngine:
         b["act"] = f16(R, self.F_pad)
         b["ld_logits"] = -(-sp.vocab_local // 4) * 4
         b["logits"] = f32(R, b["ld_logits"])
-        b["gemv_scratch"] = f32(max(1, max(l.scratch_floats(R) for l in lins)))
+        # split-K partial sums travel as {value, tag} pairs in the step driver: twice the floats
+        self.tagged_splitk = os.environ.get("B200GRAD_TAGGED_SPLITK", "1") != "0"
+        b["gemv_scratch"] = f32(2 * max(1, max(l.scratch_floats(R) for l in lins)))
         b["gemv_counters"] = i32(8192)
         # cache slices per decode-attention row: long contexts need more CTAs than (rows x KV heads) gives
         self.attn_splits = 16 if self.max_seq_len <= 1024 else 32
@@ -442,6 +445,7 @@ class InferenceEngine:
         m.np = self.np
         m.chain_scratch, m.chain_counters = b["chain_scratch"].data_ptr(), b["chain_counters"].data_ptr()
         m.chain_act_cols, m.use_chain = self.chain_act_cols, int(self.use_chain)
+        m.tagged_splitk = int(self.tagged_splitk)
         m.chain_tag_h, m.chain_tag_ss = b["chain_tag_h"].data_ptr(), b["chain_tag_ss"].data_ptr()
         m.chain_tag_act = b["chain_tag_act"].data_ptr()
         for k in ("q8_xq", "q8_sx", "q8_gate", "q8_up", "q8_down", "q8_xn"):

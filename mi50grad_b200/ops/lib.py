@@ -61,8 +61,10 @@ class GemvEpi(C.Structure):
 class GemvInt4Params(C.Structure):
     _fields_ = [("qfrag", vp), ("szfrag", vp), ("x", vp),
                 ("ldx", i32), ("rows", i32), ("K", i32), ("KB", i32), ("NTL", i32), ("G", i32),
-                ("off32", i32), ("gshift", i32), ("k_splits", i32), ("L", i32), ("cluster_splitk", i32), ("pad1", i32),
-                ("scratch", vp), ("counters", vp), ("ln", LazyNorm), ("epi", GemvEpi), ("comm", CommCtx)]
+                ("off32", i32), ("gshift", i32), ("k_splits", i32), ("L", i32), ("cluster_splitk", i32), ("tag_base", i32),
+                ("scratch", vp), ("counters", vp), ("tag_word", vp),
+                ("pf_q", vp), ("pf_KB", i32), ("pf_L", i32), ("pf_nx", i32), ("pf_ks", i32), ("pf_blocks", i32), ("pf_pad", i32),
+                ("ln", LazyNorm), ("epi", GemvEpi), ("comm", CommCtx)]
 
 
 class GemvF16Params(C.Structure):
@@ -192,7 +194,7 @@ class ModelDesc(C.Structure):
                 ("spec", SpecStage), ("spec_acc", vp), ("spec_result", vp),
                 ("state0", vp), ("conv0", vp), ("state_layer_stride", i64), ("conv_layer_stride", i64),
                 ("k0", vp), ("v0", vp), ("kv_layer_stride", i64),
-                ("xn_sym", vp * MAX_TP), ("xn_mc", vp), ("hlast_sym", vp * MAX_TP), ("seq_parallel", i32), ("pad5", i32),
+                ("xn_sym", vp * MAX_TP), ("xn_mc", vp), ("hlast_sym", vp * MAX_TP), ("seq_parallel", i32), ("tagged_splitk", i32),
                 ("chain_scratch", vp), ("chain_counters", vp), ("chain_act_cols", i32), ("use_chain", i32),
                 ("chain_tag_h", vp), ("chain_tag_ss", vp), ("chain_tag_act", vp),
                 ("q8_xq", vp), ("q8_sx", vp), ("q8_gate", vp), ("q8_up", vp), ("q8_down", vp), ("q8_xn", vp),
