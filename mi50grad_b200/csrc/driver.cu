@@ -132,6 +132,7 @@ struct Driver {
     cudaGraphExec_t exec = nullptr;
     int graph_rows = 0, graph_flags = 0;
     long long launches = 0;               // kernels issued by the last eager step
+    bool gemm_splitk = true;              // split-K in the many-row GEMMs that add into the residual stream
     int pf_blocks = 0;                    // k-blocks per warp of the next projection that a GEMV prefetches into L2 (0: off)
     int gemv_seq = 0;                     // split-K GEMVs issued so far in the step being issued (their tags)
     int push_rows_per = 0;                // > 0 while a GEMM is issued whose pushed slices are whole token rows
@@ -466,14 +467,34 @@ static int run_gemm(Driver* d, const LinearDesc& L, const void* x, int ldx, int 
     // not exceed, one wave of 148 CTAs (one CTA per SM: a second partial wave would double the time)
     const int ctas_n = L.NTL * 16 / 128;
     int tt = T >= 512 ? 512 : ((T + 15) & ~15);
+    int ks = 1;
     if (ctas_n < 148) {
         int parts = 148 / ctas_n;                          // token tiles that still fit one wave
         int need = (T + parts - 1) / parts;
         need = (need + 15) & ~15;
         if (need < 64) need = 64;
         if (need < tt) tt = need;
+        if (epi == TC_EPI_RESID_F32 && d->gemm_splitk) {
+            // ... or split K instead (the partial products meet in the residual stream through atomic adds):
+            // a k-block of a CTA costs about max(0.46, 0.0021 x tokens) us, so few wide token tiles over a
+            // third of K beat many narrow ones over all of it.  Pick the cheapest (token tile, splits) pair.
+            double best = 1e30;
+            const int tmax = T >= 512 ? 512 : ((T + 15) & ~15);
+            for (int tiles = 1; tiles <= 8; ++tiles) {
+                int t1 = ((T + tiles - 1) / tiles + 15) & ~15;
+                if (t1 > tmax) continue;
+                if (t1 < 16) t1 = 16;
+                const int nt = (T + t1 - 1) / t1;
+                int s1 = 148 / (ctas_n * nt);
+                if (s1 < 1) continue;
+                if (s1 > L.KB / 8) s1 = L.KB / 8 > 0 ? L.KB / 8 : 1;
+                const double blk = 0.0021 * t1 > 0.46 ? 0.0021 * t1 : 0.46;
+                const double cost = ((L.KB + s1 - 1) / s1) * blk + (s1 > 1 ? 4.0 : 0.0);
+                if (cost < best) { best = cost; tt = t1; ks = s1; }
+            }
+        }
     }
-    p.T = T; p.t_tile = tt;
+    p.T = T; p.t_tile = tt; p.k_splits = ks;
     p.n_valid = n_valid; p.ldo = ldo; p.epi = epi; p.out = out; p.status = d->m.tc_status;
     if (epi == TC_EPI_PUSH_F32) {
         const CommCtx& c = d->m.comm;
@@ -664,6 +685,8 @@ B2_API void* b2_driver_create(const ModelDesc* m, const LayerDesc* layers) {
     d->layer_launches.assign(m->n_layers, 0);
     // Off by default: measured on B200 (27B, one GPU, tg128) 213.6 tok/s with 4 blocks per warp, 213.1 with 2,
     // 208.7 with 8, against 213.9 without: the gaps between GEMVs are not waiting on HBM.
+    const char* gsk = getenv("B200GRAD_GEMM_SPLITK");
+    d->gemm_splitk = !(gsk && atoi(gsk) == 0);
     const char* pf = getenv("B200GRAD_L2_PREFETCH");
     d->pf_blocks = pf ? atoi(pf) : 0;
     return d;

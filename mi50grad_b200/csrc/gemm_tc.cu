@@ -190,7 +190,10 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const int KB = p.KB;
+    // split-K: this CTA's k-blocks are [kb_lo, kb_lo + KB) of the p.KB blocks of the matrix
+    const int per_kb = (p.KB + (int)gridDim.z - 1) / (int)gridDim.z;
+    const int kb_lo = (int)blockIdx.z * per_kb;
+    const int KB = max(0, min(p.KB, kb_lo + per_kb) - kb_lo);
 
     // Every role walks the stages with running counters (stage index, phase bit, addresses).  The
     // loops of the single-thread roles are chains of dependent instructions, so each instruction
@@ -214,9 +217,9 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
         // packed weights and their scale/zero pairs stream through a cp.async ring: TC_RING-1 of
         // the group's k-blocks are always in flight, each thread later reads back only what it copied
         uint4* my_ring = wring + tid;
-        const uint4* gq = dense ? nullptr : p.qfrag + ((size_t)wt * KB * 4 + ti) * 32 + lane + (size_t)grp * 128;
+        const uint4* gq = dense ? nullptr : p.qfrag + ((size_t)wt * p.KB * 4 + ti) * 32 + lane + (size_t)(kb_lo + grp) * 128;
         const uint2* gs = dense ? nullptr : p.szfrag + ((size_t)wt * p.G * 4 + ti) * 8 + g;
-        int c_issue = p.off32 + 2 * grp;          // 32-k chunk counter of the next k-block to issue
+        int c_issue = p.off32 + 2 * (kb_lo + grp);          // 32-k chunk counter of the next k-block to issue
         int slot_issue = 0;
         auto issue = [&]() {
             uint4* dst = my_ring + slot_issue * 1024;
@@ -327,6 +330,7 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
                             size_t o = (size_t)tt * p.ldo + n;
                             if (p.epi == TC_EPI_STORE_F16) ((__half*)p.out)[o] = __float2half(v);
                             else if (p.epi == TC_EPI_STORE_F32) ((float*)p.out)[o] = v;
+                            else if (gridDim.z > 1) atomicAdd((float*)p.out + o, v);     // split-K partial
                             else ((float*)p.out)[o] += v;
                         }
                     }
@@ -343,7 +347,7 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
             uint32_t ph = 0;
             unsigned char* a = sA;
             unsigned char* b = sB;
-            for (int kb = 0, kx = 0; kb < KB; ++kb, kx += TC_BK) {
+            for (int kb = 0, kx = kb_lo * TC_BK; kb < KB; ++kb, kx += TC_BK) {
                 if (!mbar_wait(&empty[st], ph ^ 1, abort_flag)) break;
                 if (elect_one()) {
                     mbar_arrive_expect_tx(&full[st], tx);
@@ -462,7 +466,10 @@ static int launch_tc(const GemmTcParams* p, const void* w, int ldw, int n_rows_w
         cudaError_t e = optin.ensure(gemm_int4_tc_kernel, smem);
         if (e != cudaSuccess) return e;
     }
-    dim3 grid(q.NTL * 16 / TC_BM, (q.T + q.t_tile - 1) / q.t_tile);
+    int ks = (q.epi == TC_EPI_RESID_F32 && q.k_splits > 1) ? q.k_splits : 1;
+    if (ks > q.KB) ks = q.KB;
+    if (ks > 1) { const int per = (q.KB + ks - 1) / ks; ks = (q.KB + per - 1) / per; }     // no empty split
+    dim3 grid(q.NTL * 16 / TC_BM, (q.T + q.t_tile - 1) / q.t_tile, ks);
     gemm_int4_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(q, map, wmap);
     return cudaGetLastError();
 }

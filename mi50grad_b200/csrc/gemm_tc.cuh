@@ -28,7 +28,8 @@ struct GemmTcParams {
     long long part_stride;       // floats between the two parity halves of a staging buffer
     int push_tp, push_rank;
     unsigned int push_per;       // float4 elements per slice
-    int pad2;
+    int k_splits;                // TC_EPI_RESID_F32 only: CTAs along K per output tile (grid z); their partial
+                                 // products are added to out with atomic adds (0 or 1: no split)
 };
 
 

@@ -36,6 +36,29 @@ def test_gemm_int4_tc_store(K, N, T, g):
     assert _rel(out32.cpu(), 2 * ref) < 2e-3
 
 
+@pytest.mark.parametrize("K,N,T,ks,g", [(1024, 384, 512, 3, 128), (2176, 640, 80, 4, 128), (704, 200, 48, 2, 128),
+                                         (512, 256, 300, 8, 32), (5120, 256, 512, 5, 128)])
+def test_gemm_int4_tc_split_k_adds_into_the_residual(K, N, T, ks, g):
+    """Several CTAs per output tile, each over a slice of K, add their partial products atomically."""
+    from mi50grad_b200.ops import kernels as Kn
+    from mi50grad_b200.ops import lib as L
+    from mi50grad_b200.ops.packing import pack_int4
+    from mi50grad_b200.utils.quant import random_int4_linear
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator().manual_seed(K + N + T + ks)
+    lin = random_int4_linear(K, N, g, gen)
+    lin.zeros = torch.randint(0, 16, lin.zeros.shape, generator=gen).half()
+    x = torch.randn(T, K, generator=gen).half()
+    h0 = torch.randn(T, N, generator=gen)
+    ref = h0 + x.float() @ lin.dense().t()
+    pk = pack_int4(lin, dev)
+    out = h0.to(dev).clone()
+    Kn.gemm_int4_tc(pk, x.to(dev), out, epi=L.TC_EPI_RESID_F32, k_splits=ks)
+    torch.cuda.synchronize()
+    Kn.gemm_tc_check_status()
+    assert _rel(out.cpu(), ref) < 2e-3
+
+
 def test_gemm_int4_tc_silu_pair():
     from mi50grad_b200.ops import kernels as Kn
     from mi50grad_b200.ops import lib as L
