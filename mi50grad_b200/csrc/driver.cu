@@ -132,6 +132,7 @@ struct Driver {
     cudaGraphExec_t exec = nullptr;
     int graph_rows = 0, graph_flags = 0;
     long long launches = 0;               // kernels issued by the last eager step
+    bool attn_tc = true;                  // prompt attention on tcgen05 (csrc/attention_tc.cu)
     bool gemm_splitk = true;              // split-K in the many-row GEMMs that add into the residual stream
     int pf_blocks = 0;                    // k-blocks per warp of the next projection that a GEMV prefetches into L2 (0: off)
     int gemv_seq = 0;                     // split-K GEMVs issued so far in the step being issued (their tags)
@@ -586,8 +587,15 @@ static int rows_impl(Driver* d, int T, int n_seqs, int flags, cudaStream_t s) {
                 sp = sp < 1 ? 1 : (sp > m.attn_splits ? m.attn_splits : sp);
                 a.splits = sp; a.scratch = m.p_attn_scratch;
             }
-            CK(b2_attn_rows(&a, m.seq_rows, n_seqs, m.hd, s));
-            d->launches += a.splits > 1 ? 3 : 2;
+            if (!(flags & STEP_SPEC) && n_seqs == 1 && T >= 64 && d->attn_tc) {
+                // a prompt chunk of one sequence: QK^T and PV on tcgen05 with TMA-fed Q / K tiles
+                a.splits = 1;
+                CK(b2_attn_prefill_tc(&a, 0, T, m.n_seqs_max, m.hd, m.tc_status, s));
+                d->launches += 2;
+            } else {
+                CK(b2_attn_rows(&a, m.seq_rows, n_seqs, m.hd, s));
+                d->launches += a.splits > 1 ? 3 : 2;
+            }
         } else {
             DeltaParams q;
             fill_delta(d, L, q);
@@ -687,6 +695,8 @@ B2_API void* b2_driver_create(const ModelDesc* m, const LayerDesc* layers) {
     // 208.7 with 8, against 213.9 without: the gaps between GEMVs are not waiting on HBM.
     const char* gsk = getenv("B200GRAD_GEMM_SPLITK");
     d->gemm_splitk = !(gsk && atoi(gsk) == 0);
+    const char* atc = getenv("B200GRAD_ATTN_TC");
+    d->attn_tc = !(atc && atoi(atc) == 0);
     const char* pf = getenv("B200GRAD_L2_PREFETCH");
     d->pf_blocks = pf ? atoi(pf) : 0;
     return d;

@@ -139,6 +139,8 @@ B2_API int b2_gemv_int4(const GemvInt4Params* p, cudaStream_t stream);
 B2_API int b2_gemv_f16(const GemvF16Params* p, cudaStream_t stream);
 B2_API int b2_decode_attn(const AttnParams* p, int hd, cudaStream_t s);
 B2_API int b2_attn_rows(const AttnParams* p, const int* seq_rows, int n_seqs, int hd, cudaStream_t s);
+B2_API int b2_attn_prefill_tc(const AttnParams* p, int row_base, int n_rows_seq, int n_slots, int hd, int* status,
+                              cudaStream_t s);
 B2_API int b2_deltanet_step(const DeltaParams* p, int dk, int dv, cudaStream_t s);
 B2_API int b2_deltanet_chunk(const DeltaParams* p, const void* ab, int ld_ab, int dk, int dv, cudaStream_t s);
 B2_API int b2_ab_proj(const void* x, int ldx, const void* wa, const void* wb, int nv, int H, void* ab, int ld_ab,

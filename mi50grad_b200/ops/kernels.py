@@ -237,6 +237,28 @@ def attn_rows(q, rows_meta, seq_rows, kcache, vcache, nq, nkv, hd, gate_off=-1, 
     return out
 
 
+def attn_prefill_tc(q, rows_meta, kcache, vcache, nq, nkv, hd, gate_off=-1, row_base=0, n_rows_seq=None, out=None):
+    """Causal attention of one sequence's prompt rows on the tcgen05 tensor cores (csrc/attention_tc.cu).
+    Rows [row_base, row_base + n_rows_seq) are in position order and carry no draft-tree masks."""
+    n = q.shape[0]
+    dev = q.device
+    if out is None:
+        out = torch.zeros(n, nq * hd, dtype=torch.float16, device=dev)
+    if n_rows_seq is None:
+        n_rows_seq = n - row_base
+    st = _tc_status.get(dev)
+    if st is None:
+        st = _tc_status[dev] = torch.zeros(64, dtype=torch.int32, device=dev)
+    p = L.AttnParams()
+    p.q, p.ldq, p.gate_off = q.data_ptr(), q.stride(0), gate_off
+    p.kcache, p.vcache, p.rows = kcache.data_ptr(), vcache.data_ptr(), rows_meta.data_ptr()
+    p.out, p.ldo, p.n_rows, p.nq, p.nkv = out.data_ptr(), out.stride(0), n, nq, nkv
+    p.max_seq, p.splits, p.scale = kcache.shape[1], 1, 1.0 / hd ** 0.5
+    L.check(L.lib().b2_attn_prefill_tc(C.byref(p), row_base, n_rows_seq, kcache.shape[0], hd,
+                                       C.c_void_p(st.data_ptr()), L.stream()), "attn_prefill_tc")
+    return out
+
+
 def deltanet_step(proj, offs, conv_w, conv_state, state, A_log, dt_bias, norm_w, rows_meta, seq_rows, nk, nv,
                   dk, dv, xn=None, wa=None, wb=None, out=None, commit=True, eps=1e-6, ln=None):
     """offs = (off_q, off_k, off_v, off_z, off_a, off_b)."""

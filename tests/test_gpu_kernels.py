@@ -255,6 +255,32 @@ def test_attn_rows_tensor_core(K, hd, nq, nkv, splits):
         assert _rel(out[r].cpu().view(nq, hd), o[0]) < 4e-3, f"row {r}"
 
 
+@pytest.mark.parametrize("hd,nq,nkv,T,past", [(64, 4, 2, 40, 5), (64, 2, 1, 200, 0), (256, 6, 1, 130, 7),
+                                              (256, 12, 2, 512, 0), (128, 4, 4, 300, 64)])
+def test_attn_prefill_tcgen05(K, hd, nq, nkv, T, past):
+    """Causal prompt attention on tcgen05: T rows of sequence 1 behind `past` cached tokens (partial row
+    and slot tiles), against the fp32 reference, with the sigmoid output gate."""
+    from mi50grad_b200.models import oracle as O
+    gen = torch.Generator().manual_seed(31 + T)
+    d = _dev()
+    max_seq, nseq = 640, 2
+    kc = torch.randn(nseq, max_seq, nkv, hd, generator=gen).half()
+    vc = torch.randn(nseq, max_seq, nkv, hd, generator=gen).half()
+    entries = [(1, past + i, past + i, past + i + 1, 0) for i in range(T)]
+    q = torch.randn(T, 2 * nq * hd, generator=gen).half()
+    out = K.attn_prefill_tc(q.to(d), K.make_rows(entries, d), kc.to(d), vc.to(d), nq, nkv, hd, gate_off=nq * hd)
+    torch.cuda.synchronize()
+    K.gemm_tc_check_status()
+    worst = 0.0
+    for r in list(range(0, T, 7)) + [T - 1]:
+        ctx = past + r + 1
+        o = O.attention(q[r:r + 1, :nq * hd].float().view(1, nq, hd), kc[1, :ctx].float(), vc[1, :ctx].float(),
+                        torch.ones(1, ctx, dtype=torch.bool))
+        o = o * torch.sigmoid(q[r, nq * hd:].float().view(1, nq, hd))
+        worst = max(worst, _rel(out[r].cpu().view(nq, hd), o[0]))
+    assert worst < 4e-3, worst
+
+
 @pytest.mark.parametrize("dk,nk,nv,rows_per_seq,inkernel_ab", [(128, 2, 6, [1], True), (64, 2, 4, [3, 1], False),
                                                               (128, 1, 3, [5], False), (64, 1, 2, [2], "lazy")])
 def test_deltanet_step(K, dk, nk, nv, rows_per_seq, inkernel_ab):

@@ -9,11 +9,14 @@ SOURCES = {p.name: p.read_text() for p in sorted(CSRC.glob("*.cu")) + sorted(CSR
 
 
 def test_blackwell_constructs_present():
-    g = SOURCES["gemm_tc.cu"]
+    # the tcgen05 kernels (GEMM, prompt attention) and the PTX helpers they share
+    g = SOURCES["tc_util.cuh"] + SOURCES["gemm_tc.cu"] + SOURCES["attention_tc.cu"]
     for needle in ("tcgen05.mma.cta_group::1.kind::f16", "tcgen05.alloc", "tcgen05.dealloc", "tcgen05.commit",
                    "tcgen05.ld.sync.aligned.32x32b", "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier",
                    "mbarrier.try_wait.parity", "elect.sync"):
         assert needle in g, needle
+    for name in ("gemm_tc.cu", "attention_tc.cu"):
+        assert "tcgen05.alloc" in SOURCES[name] and "tcgen05.dealloc" in SOURCES[name] and "tc_mma_f16(" in SOURCES[name], name
     assert "multimem.ld_reduce" in SOURCES["common.cuh"] and "multimem.st" in SOURCES["common.cuh"]
     assert "griddepcontrol.launch_dependents" in SOURCES["common.cuh"]
     assert "cluster.map_shared_rank" in SOURCES["deltanet.cu"]
@@ -38,9 +41,13 @@ def test_every_spin_wait_is_bounded():
     c = SOURCES["common.cuh"]
     body = c[c.index("wait_reached"):]
     assert "globaltimer_ns() - t0 > budget_ns" in body
-    g = SOURCES["gemm_tc.cu"]
+    g = SOURCES["tc_util.cuh"]
     w = g[g.index("bool mbar_wait("):g.index("elect_one")]
     assert "TC_WAIT_NS" in w and "abort_flag" in w
+    # the tcgen05 kernels wait on mbarriers only through that bounded helper
+    for name in ("gemm_tc.cu", "attention_tc.cu"):
+        assert "mbar_try_wait(" not in SOURCES[name] and "mbar_wait(" in SOURCES[name], name
+    assert "GEMV_TAG_POLLS" in SOURCES["gemv.cu"]
     for name, text in SOURCES.items():
         for m in re.finditer(r"while\s*\(\s*(true|1)\s*\)|for\s*\(\s*;\s*;\s*\)", text):
             window = text[m.start():m.start() + 700]
