@@ -12,7 +12,7 @@ clocks of a shared GPU:
     ncu --clock-control none --profile-from-start off -k regex:<kernel> -c 3 \
         python -m mi50grad_b200.bench.profile_cases <case>
 
-cases: gemv_gateup, gemv_down, gemm_int4, gemm_dense, attn_decode, attn_rows,
+cases: gemv_gateup, gemv_down, gemm_int4, gemm_dense, attn_decode, attn_rows, attn_prefill,
        deltanet_step, deltanet_chunk, spec_step, prefill, decode_step, linear_q8
 """
 from __future__ import annotations
@@ -95,8 +95,31 @@ def case_gemm(which: str, timed: bool):
     K.gemm_tc_check_status()
 
 
+def case_attn_prefill(timed: bool):
+    """Causal attention of a 512-row prompt (24 query / 4 KV heads of 256): the tcgen05 kernel and, with
+    --time, the mma.sync many-row kernel on the same input."""
+    dev = torch.device("cuda")
+    nq, nkv, hd, T = 24, 4, 256, 512
+    kc = torch.randn(1, T + 64, nkv, hd, device=dev).half()
+    vc = torch.randn(1, T + 64, nkv, hd, device=dev).half()
+    rm = K.make_rows([(0, i, i, i + 1, 0) for i in range(T)], dev)
+    q = torch.randn(T, 2 * nq * hd, device=dev).half()
+    out = torch.zeros(T, nq * hd, dtype=torch.float16, device=dev)
+    run = lambda i=0: K.attn_prefill_tc(q, rm, kc, vc, nq, nkv, hd, gate_off=nq * hd, out=out)
+    flops = 2.0 * 2.0 * nq * hd * T * (T + 1) / 2
+    if timed:
+        _report("attn_prefill tcgen05", time_launches(run, 1, 6), flops=flops)
+        seq_rows = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        run2 = lambda i=0: K.attn_rows(q, rm, seq_rows, kc, vc, nq, nkv, hd, gate_off=nq * hd, splits=1, out=out)
+        _report("attn_prefill mma.sync", time_launches(run2, 1, 6), flops=flops)
+    else:
+        _profiled(run, 1)
+
+
 def case_attn(which: str, timed: bool):
     """attn_decode: 1 row, ctx 4096.  attn_rows: 80 rows (16 sequences x 5 draft rows), ctx 4096."""
+    if which == "attn_prefill":
+        return case_attn_prefill(timed)
     dev = torch.device("cuda")
     nq, nkv, hd, ctx = 24, 4, 256, 4096
     n_seq, per = (1, 1) if which == "attn_decode" else (16, 5)

@@ -9,7 +9,9 @@
 //                    in the same swizzled K-major layout (it is the A operand of the second product);
 //   O_tile = P V     tcgen05.mma, M = 128 rows, N = head dim, K = 64 slots; V is stored in the cache
 //                    with the head dim contiguous, the MMA wants the slots contiguous, so the threads
-//                    transpose the V tile into shared memory while the K tile is in flight;
+//                    transpose the V tile (staged by cp.async) into shared memory while S is computed;
+//   the K tile (TMA, two buffers) and the raw V tile (cp.async) of the next step are requested one step
+//   ahead, so no step waits on global memory;
 //   O = O * corr + O_tile in registers (each of the two warps of a tensor-memory lane quarter keeps half
 //   of the head dim), then 1 / sum, the sigmoid output gate and the fp16 store.
 // Grouped-query heads share the K/V tiles through L2.  Every mbarrier wait is bounded; on expiry the
@@ -45,11 +47,14 @@ attn_prefill_tc_kernel(const AttnParams p, const __grid_constant__ CUtensorMap q
     extern __shared__ __align__(1024) unsigned char at_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)at_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* sQ = smem;                                 // [NB][128 rows][128 B]
-    unsigned char* sK = sQ + (size_t)NB * AT_ROWS * 128;      // [NB][64 slots][128 B]
-    unsigned char* sVt = sK + (size_t)NB * AT_KV * 128;       // [HD rows][128 B]: V transposed (slots contiguous)
+    constexpr int KB_BYTES = NB * AT_KV * 128;                // one K tile
+    constexpr int VR_LD = HD * 2 + 16;                        // bytes per raw V row (padded: conflict-free transposition)
+    unsigned char* sK = sQ + (size_t)NB * AT_ROWS * 128;      // [2][NB][64 slots][128 B]
+    unsigned char* sVt = sK + (size_t)2 * KB_BYTES;           // [HD rows][128 B]: V transposed (slots contiguous)
     unsigned char* sP = sVt + (size_t)HD * 128;               // [128 rows][128 B]
-    uint64_t* bars = (uint64_t*)(sP + (size_t)AT_ROWS * 128); // [0] loads, [1] S ready, [2] O tile ready
-    uint32_t* tmem_slot = (uint32_t*)(bars + 3);
+    unsigned char* sVr = sP + (size_t)AT_ROWS * 128;          // [64 slots][VR_LD]: raw V tile of the next step
+    uint64_t* bars = (uint64_t*)(sVr + (size_t)AT_KV * VR_LD); // [0], [3] K tiles (+ Q), [1] S ready, [2] O tile ready
+    uint32_t* tmem_slot = (uint32_t*)(bars + 4);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -59,7 +64,7 @@ attn_prefill_tc_kernel(const AttnParams p, const __grid_constant__ CUtensorMap q
     constexpr int tmem_cols = HD == 256 ? 512 : (HD == 128 ? 256 : 128);
 
     if (tid == 0) {
-        mbar_init(&bars[0], 1); mbar_init(&bars[1], 1); mbar_init(&bars[2], 1);
+        mbar_init(&bars[0], 1); mbar_init(&bars[1], 1); mbar_init(&bars[2], 1); mbar_init(&bars[3], 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -97,27 +102,61 @@ attn_prefill_tc_kernel(const AttnParams p, const __grid_constant__ CUtensorMap q
     const __half* vbase = p.vcache + ((size_t)seq * p.max_seq) * vstride + (size_t)kvh * HD;
     bool ok = true;
 
+    // K tile t goes to buffer t & 1 on barrier (t & 1 ? 3 : 0); the raw V tile t to sVr
+    auto issue_k = [&](int t) {
+        if (warp == 0 && elect_one()) {
+            uint64_t* bar = &bars[(t & 1) ? 3 : 0];
+            const uint32_t bytes = (uint32_t)KB_BYTES + (t == 0 ? (uint32_t)NB * AT_ROWS * 128 : 0u);
+            mbar_arrive_expect_tx(bar, bytes);
+            if (t == 0)
+                for (int b = 0; b < NB; ++b) tma_load_2d(sQ + (size_t)b * AT_ROWS * 128, &qmap, head * HD + b * 64, r0, bar);
+            for (int b = 0; b < NB; ++b)
+                tma_load_2d(sK + (size_t)(t & 1) * KB_BYTES + (size_t)b * AT_KV * 128, &kmap, kvh * HD + b * 64,
+                            seq * p.max_seq + t * AT_KV, bar);
+        }
+    };
+    auto issue_v = [&](int t) {
+#pragma unroll
+        for (int it = 0; it < HD / 32; ++it) {
+            const int idx = tid + AT_THREADS * it, slot = idx / (HD / 8), ch = idx % (HD / 8);
+            if (t * AT_KV + slot < max_ctx)
+                cp_async16(sVr + (size_t)slot * VR_LD + ch * 16, vbase + (size_t)(t * AT_KV + slot) * vstride + ch * 8);
+        }
+        cp_async_commit();
+    };
+    if (n_tiles > 0) { issue_k(0); issue_v(0); }
+
     for (int tile = 0; tile < n_tiles && ok; ++tile) {
         const int kv0 = tile * AT_KV;
         const uint32_t par = (uint32_t)(tile & 1);
-        // ---- K tile (and, the first time, the Q tile) by TMA; V tile transposed by the threads meanwhile
-        if (warp == 0 && elect_one()) {
-            const uint32_t bytes = (uint32_t)NB * AT_KV * 128 + (tile == 0 ? (uint32_t)NB * AT_ROWS * 128 : 0u);
-            mbar_arrive_expect_tx(&bars[0], bytes);
-            if (tile == 0)
-                for (int b = 0; b < NB; ++b) tma_load_2d(sQ + (size_t)b * AT_ROWS * 128, &qmap, head * HD + b * 64, r0, &bars[0]);
-            for (int b = 0; b < NB; ++b)
-                tma_load_2d(sK + (size_t)b * AT_KV * 128, &kmap, kvh * HD + b * 64, seq * p.max_seq + kv0, &bars[0]);
+        if (tile + 1 < n_tiles) issue_k(tile + 1);             // its buffer was last read by the S product of tile - 1
+        // ---- S = Q K^T (the K tile was requested a step ago)
+        if (warp == 0) {
+            const bool ok0 = mbar_wait(&bars[(tile & 1) ? 3 : 0], (uint32_t)((tile >> 1) & 1), abort_flag);
+            tc_fence_after();
+            if (ok0 && elect_one()) {
+                const uint64_t dKt = dK + (uint64_t)(((tile & 1) * KB_BYTES) >> 4);
+#pragma unroll
+                for (int b = 0; b < NB; ++b)
+#pragma unroll
+                    for (int k16 = 0; k16 < 4; ++k16)
+                        tc_mma_f16(tmem_S, dQ + (uint64_t)((b * AT_ROWS * 128) >> 4) + 2 * k16,
+                                   dKt + (uint64_t)((b * AT_KV * 128) >> 4) + 2 * k16, idesc_s, (b | k16) ? 1u : 0u);
+                tc_commit(&bars[1]);
+            }
+            __syncwarp();
         }
+        // ---- meanwhile: transpose the raw V tile into the layout the second product reads
+        cp_async_wait<0>();
+        __syncthreads();
         {
             const int j = tid & 63;                             // slot of the tile
             const bool live = kv0 + j < max_ctx;
-            const __half* vr = vbase + (size_t)(kv0 + j) * vstride;
 #pragma unroll
             for (int it = 0; it < HD / 32; ++it) {
                 const int d0 = ((tid >> 6) + 4 * it) * 8;
                 uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (live) v = *(const uint4*)(vr + d0);
+                if (live) v = *(const uint4*)(sVr + (size_t)j * VR_LD + d0 * 2);
                 const __half* hv = (const __half*)&v;
 #pragma unroll
                 for (int e = 0; e < 8; ++e)
@@ -126,21 +165,7 @@ attn_prefill_tc_kernel(const AttnParams p, const __grid_constant__ CUtensorMap q
         }
         fence_proxy_async_smem();
         __syncthreads();
-        // ---- S = Q K^T
-        if (warp == 0) {
-            const bool ok0 = mbar_wait(&bars[0], par, abort_flag);
-            tc_fence_after();
-            if (ok0 && elect_one()) {
-#pragma unroll
-                for (int b = 0; b < NB; ++b)
-#pragma unroll
-                    for (int k16 = 0; k16 < 4; ++k16)
-                        tc_mma_f16(tmem_S, dQ + (uint64_t)((b * AT_ROWS * 128) >> 4) + 2 * k16,
-                                   dK + (uint64_t)((b * AT_KV * 128) >> 4) + 2 * k16, idesc_s, (b | k16) ? 1u : 0u);
-                tc_commit(&bars[1]);
-            }
-            __syncwarp();
-        }
+        if (tile + 1 < n_tiles) issue_v(tile + 1);              // flies while this tile is processed
         // (a thread whose wait gave up still walks to the next barrier, where the whole CTA decides to stop)
         const bool ok1 = mbar_wait(&bars[1], par, abort_flag);
         tc_fence_after();
@@ -234,7 +259,8 @@ attn_prefill_tc_kernel(const AttnParams p, const __grid_constant__ CUtensorMap q
 
 static size_t at_smem(int hd) {
     const int nb = hd / 64;
-    return 1024 + (size_t)nb * AT_ROWS * 128 + (size_t)nb * AT_KV * 128 + (size_t)hd * 128 + (size_t)AT_ROWS * 128 + 64;
+    return 1024 + (size_t)nb * AT_ROWS * 128 + (size_t)2 * nb * AT_KV * 128 + (size_t)hd * 128 + (size_t)AT_ROWS * 128 +
+           (size_t)AT_KV * (hd * 2 + 16) + 64;
 }
 
 template <int HD>

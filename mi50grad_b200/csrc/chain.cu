@@ -77,28 +77,17 @@ __device__ __forceinline__ uint32_t ch_ld_acquire_gpu(const int* p) {
 }
 __device__ __forceinline__ void ch_mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                             uint32_t b0, uint32_t b1) {
-#ifdef CH_EXP_NOMMA
-    d[0] += __uint_as_float((a0 ^ b0) & 0x3fffffffu); d[1] += __uint_as_float((a1 ^ b1) & 0x3fffffffu);
-    d[2] += __uint_as_float((a2 ^ b0) & 0x3fffffffu); d[3] += __uint_as_float((a3 ^ b1) & 0x3fffffffu);
-    return;
-#endif
     asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ uint32_t ch_nib_lo(uint32_t w) {      // halves: 1024 + q
-#ifdef CH_EXP_NODEQ
-    return w;
-#endif
     uint32_t r;
     asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(r) : "r"(w));
     return r;
 }
 __device__ __forceinline__ uint32_t ch_nib_hi(uint32_t w) {      // halves: 1024 + 16 q
-#ifdef CH_EXP_NODEQ
-    return w;
-#endif
     uint32_t r;
     asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(r) : "r"(w));
     return r;
