@@ -97,7 +97,7 @@ def bench_gemv(tp: int, rows: int, iters: int, only=None):
 
 
 def bench_fused(iters: int):
-    """BASELINE config 2: row-parallel INT4 GEMV + all-reduce + residual add (+ lazy RMSNorm sums) as ONE
+    """The fused row-parallel projection: INT4 GEMV + all-reduce + residual add (+ lazy RMSNorm sums) as ONE
     kernel at TP = world size, and stand-alone all-reduces of 10 KB / 5 MB, each against NCCL
     all-reduce plus separate kernels.  Run under torch.distributed.run; times are max over ranks."""
     import torch.distributed as dist

@@ -1,6 +1,6 @@
 """Guard bands around scratch and communication buffers (debug builds of a run).
 
-compute-sanitizer is not available where this runs, and the reference found its
+A memory checker is not always at hand on a shared GPU, and the reference found its
 races by symptom (reference: kernel headers of src/kernels/deltanet_v2.hip,
 src/kernels/kernel_p2p_allreduce_rmsnorm.hip:72).  With
 `EngineConfig.debug_guards` every work buffer is allocated with a poisoned band
