@@ -382,7 +382,16 @@ class TPInferenceEngine:
     def set_cached_dispatch(self, enabled: bool): self._note("cached_dispatch", enabled)
     def set_stream_overlap_dispatch(self, enabled: bool): self._note("stream_overlap", enabled)
     def set_threaded_dispatch(self, enabled: bool): self._note("threaded", enabled)
-    def set_persistent_kernel(self, enabled: bool): self._note("persistent_kernel", enabled)
+    def set_persistent_kernel(self, enabled: bool):
+        """Persistent decode dispatch (reference: src/inference/tp_engine.py set_persistent_kernel,
+        src/kernels/persistent_decode.hip:271-468, a stub there).  Here: the projection-chain kernel
+        (csrc/chain.cu) runs the consecutive INT4 projections of the decode step as one resident launch
+        each (`EngineConfig.use_chain = 1`); disabling returns to the default for the rank count."""
+        self._note("persistent_kernel", enabled)
+        want = 1 if enabled else -1
+        if int(self.engine.ecfg.use_chain) != want:
+            self.engine.ecfg.use_chain = want
+            self.engine._drop_driver()
     def set_direct_kv_write(self, enabled: bool): self._note("direct_kv_write", enabled)
     def set_awq_mode(self, enabled: bool = True): self._note("awq", enabled)
     def set_kernel_p2p_allreduce(self, enabled: bool): self._note("kernel_p2p", enabled)
