@@ -390,7 +390,8 @@ class TPInferenceEngine:
         self._note("persistent_kernel", enabled)
         want = 1 if enabled else -1
         if int(self.engine.ecfg.use_chain) != want:
-            self.engine.ecfg.use_chain = want
+            self.engine.ecfg = self.engine.ecfg.replace(use_chain=want)
+            self.ecfg = self.ecfg.replace(use_chain=want)
             self.engine._drop_driver()
     def set_direct_kv_write(self, enabled: bool): self._note("direct_kv_write", enabled)
     def set_awq_mode(self, enabled: bool = True): self._note("awq", enabled)
