@@ -538,7 +538,8 @@ __device__ __forceinline__ void ldsm2(float (&r)[2], const float* row_ptr) {
 __device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.f + __expf(-x)); }
 
 template <int DK, int DV>
-__global__ void __launch_bounds__(DN_THREADS, 2) deltanet_chunk_kernel(const DeltaParams p, const __half* __restrict__ ab, int ld_ab) {
+__global__ void __launch_bounds__(DN_THREADS, 2) deltanet_chunk_kernel(const DeltaParams p, const __half* __restrict__ ab, int ld_ab,
+                                                                      const __half* __restrict__ qk_pre, int ld_qk) {
     constexpr int CB = DV / DN_COLS;
     constexpr int MT = DK / 16;               // 16-row tiles of the state slice, one or two per warp
     constexpr int SPW = (MT + 7) / 8;         // state m-tiles per warp
@@ -623,7 +624,13 @@ __global__ void __launch_bounds__(DN_THREADS, 2) deltanet_chunk_kernel(const Del
             const int c = pc * 8;
             const int ri = rb_ - 3 + row;
             __half* dst = Xr + row * NCH + c;
-            if (ri >= r0 && ri < r1) {
+            if (qk_pre && c < 2 * DK) {
+                // q / k columns: convolved, normalised (q also scaled) rows from the pre-pass; no history rows
+                if (ri >= rb_ && ri < r1)
+                    cp_async16(dst, qk_pre + (size_t)(ri - r0) * ld_qk + (c < DK ? kh * DK + c : p.nk * DK + kh * DK + (c - DK)));
+                else
+                    *(uint4*)dst = make_uint4(0u, 0u, 0u, 0u);
+            } else if (ri >= r0 && ri < r1) {
                 cp_async16(dst, p.proj + (size_t)ri * p.ld + proj_col(c));
             } else if (ri < r0) {
 #pragma unroll
@@ -658,11 +665,19 @@ __global__ void __launch_bounds__(DN_THREADS, 2) deltanet_chunk_kernel(const Del
         for (int item = tid; item < (NCH / 2) * (DC_C / 8); item += DN_THREADS) {
             const int c = 2 * (item % (NCH / 2)), i0 = (item / (NCH / 2)) * 8;
             const float4 wa4 = *(const float4*)&cw[c * 4], wb4 = *(const float4*)&cw[c * 4 + 4];
+            float* dst = (c < DK) ? Qs + c : (c < 2 * DK) ? Ks + (c - DK) : Us + (c - 2 * DK);
+            const int ldd = (c < 2 * DK) ? LDK : DC_LDU;
+            if (qk_pre && c < 2 * DK) {
+                // already convolved and normalised by the pre-pass (fp16 holds exactly the ten mantissa bits the
+                // TF32 products use): widen and store
+#pragma unroll
+                for (int i = i0; i < i0 + 8; ++i)
+                    *(float2*)&dst[i * ldd] = __half22float2(*(const __half2*)&Xr[(i + 3) * NCH + c]);
+                continue;
+            }
             float2 x0 = __half22float2(*(const __half2*)&Xr[(i0 + 0) * NCH + c]);
             float2 x1 = __half22float2(*(const __half2*)&Xr[(i0 + 1) * NCH + c]);
             float2 x2 = __half22float2(*(const __half2*)&Xr[(i0 + 2) * NCH + c]);
-            float* dst = (c < DK) ? Qs + c : (c < 2 * DK) ? Ks + (c - DK) : Us + (c - 2 * DK);
-            const int ldd = (c < 2 * DK) ? LDK : DC_LDU;
 #pragma unroll
             for (int i = i0; i < i0 + 8; ++i) {
                 const float2 x3 = __half22float2(*(const __half2*)&Xr[(i + 3) * NCH + c]);
@@ -709,7 +724,7 @@ __global__ void __launch_bounds__(DN_THREADS, 2) deltanet_chunk_kernel(const Del
             if (DC_C > 32) Gs[lane + DC_C - 32] = b + tot;
         }
 #pragma unroll 1
-        for (int ub = 0; ub < DC_C / 8; ub += 4) {
+        for (int ub = 0; ub < (qk_pre ? 0 : DC_C / 8); ub += 4) {
             // four rows at a time: their loads and the eight reductions overlap
             constexpr int PL = DK / 32;
             float qv[4][PL], kv[4][PL], qq[4], kk[4];
@@ -962,8 +977,67 @@ __global__ void __launch_bounds__(DN_THREADS, 2) deltanet_chunk_kernel(const Del
     }
 }
 
+// ---------------------------------------------------------------------------
+// Pre-pass of the chunked scan: causal conv + SiLU + L2 norm of the q and k channels of every row, once
+// per key head and fully parallel over the rows (the scan kernel would otherwise redo it in each of the
+// dv/32 column CTAs of each of the nv/nk value heads that share a key head, on its sequential path).
+// Output fp16 [rows][2 * nk * DK]: q (scaled by 1/sqrt(DK)) | k.  grid = (row blocks of QP_ROWS, key heads),
+// 2 * DK threads: thread c owns one channel for QP_ROWS rows.
+// ---------------------------------------------------------------------------
+#define QP_ROWS 16
+template <int DK>
+__global__ void __launch_bounds__(2 * DK) deltanet_qk_prep_kernel(const DeltaParams p, __half* __restrict__ qk_pre, int ld_qk,
+                                                                  int cb_copies, int nch) {
+    const int kh = blockIdx.y, c = threadIdx.x, lane = c & 31, warp = c >> 5;
+    const int r0 = p.seq_rows[0], r1 = p.seq_rows[1];
+    const int rb = r0 + blockIdx.x * QP_ROWS;
+    if (rb >= r1) return;
+    const int seq = p.rows[r0].seq;
+    const bool is_q = c < DK;
+    const int gch = is_q ? kh * DK + c : p.nk * DK + kh * DK + (c - DK);
+    const int col = is_q ? p.off_q + kh * DK + c : p.off_k + kh * DK + (c - DK);
+    const __half* w = p.conv_w + (size_t)gch * 4;
+    const float w0 = __half2float(w[0]), w1 = __half2float(w[1]), w2 = __half2float(w[2]), w3 = __half2float(w[3]);
+    // rows before the sequence start come from the saved history of the first value head of this key head
+    const __half* hist = p.conv_state + ((((size_t)seq * p.nv + kh * (p.nv / p.nk)) * cb_copies) * nch + c) * 3;
+    auto input = [&](int ri) -> float {
+        if (ri >= r1) return 0.f;
+        return ri >= r0 ? __half2float(p.proj[(size_t)ri * p.ld + col]) : __half2float(hist[ri - r0 + 3]);
+    };
+    float x[QP_ROWS + 3];
+#pragma unroll
+    for (int i = 0; i < QP_ROWS + 3; ++i) x[i] = input(rb - 3 + i);
+    __shared__ float part[2 * DK / 32][QP_ROWS];
+    float y[QP_ROWS];
+#pragma unroll
+    for (int i = 0; i < QP_ROWS; ++i) {
+        y[i] = silu_fast(x[i] * w0 + x[i + 1] * w1 + x[i + 2] * w2 + x[i + 3] * w3);
+        const float ss = warp_sum(y[i] * y[i]);
+        if (lane == 0) part[warp][i] = ss;
+    }
+    __syncthreads();
+    const int w_lo = is_q ? 0 : DK / 32;
+    const float qscale = is_q ? rsqrtf((float)DK) : 1.f;
+#pragma unroll
+    for (int i = 0; i < QP_ROWS; ++i) {
+        if (rb + i >= r1) break;
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < DK / 32; ++k) ss += part[w_lo + k][i];
+        qk_pre[(size_t)(rb - r0 + i) * ld_qk + (is_q ? kh * DK + c : p.nk * DK + kh * DK + (c - DK))] =
+            __float2half_rn(y[i] * rsqrtf(ss + 1e-6f) * qscale);
+    }
+}
+
 template <int DK, int DV>
-static int launch_delta_chunk(const DeltaParams* p, const void* ab, int ld_ab, cudaStream_t s) {
+static int launch_delta_chunk(const DeltaParams* p, const void* ab, int ld_ab, __half* qk_pre, int ld_qk, int n_rows,
+                              cudaStream_t s) {
+    if (qk_pre) {
+        dim3 grid((n_rows + QP_ROWS - 1) / QP_ROWS, p->nk);
+        deltanet_qk_prep_kernel<DK><<<grid, 2 * DK, 0, s>>>(*p, qk_pre, ld_qk, DV / DN_COLS, 2 * DK + DN_COLS);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
     constexpr int CB = DV / DN_COLS;
     constexpr int NCH = 2 * DK + DN_COLS;
     size_t smem = (size_t)(2 * DC_C * DC_LDK(DK) + DC_C * DC_LDU + 2 * DC_C * DN_COLS + 2 * DC_C * DC_LDA + DN_COLS * DC_LDK(DK) + NCH * 7 +
@@ -985,14 +1059,19 @@ static int launch_delta_chunk(const DeltaParams* p, const void* ab, int ld_ab, c
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, deltanet_chunk_kernel<DK, DV>, *p, (const __half*)ab, ld_ab);
+    return cudaLaunchKernelEx(&cfg, deltanet_chunk_kernel<DK, DV>, *p, (const __half*)ab, ld_ab, (const __half*)qk_pre, ld_qk);
 }
 
 // ab: [rows][ld_ab] fp16 with a at column head and b at column nv + head.
-B2_API int b2_deltanet_chunk(const DeltaParams* p, const void* ab, int ld_ab, int dk, int dv, cudaStream_t s) {
+// qk_scratch (optional): fp16 [n_rows][ld_qk >= 2 * nk * dk] work buffer; with it, and ONE launched sequence of
+// n_rows rows, the q / k convolution and norms run once in a parallel pre-pass instead of inside the scan.
+B2_API int b2_deltanet_chunk(const DeltaParams* p, const void* ab, int ld_ab, void* qk_scratch, int ld_qk, int n_rows,
+                             int dk, int dv, cudaStream_t s) {
     if (p->nv % p->nk || !ab) return cudaErrorInvalidValue;
-    if (dk == 128 && dv == 128) return launch_delta_chunk<128, 128>(p, ab, ld_ab, s);
-    if (dk == 64 && dv == 64) return launch_delta_chunk<64, 64>(p, ab, ld_ab, s);
+    __half* qk = (__half*)qk_scratch;
+    if (qk && (p->n_seqs != 1 || n_rows < 1 || ld_qk < 2 * p->nk * dk || (ld_qk & 7) || ((uintptr_t)qk & 15))) qk = nullptr;
+    if (dk == 128 && dv == 128) return launch_delta_chunk<128, 128>(p, ab, ld_ab, qk, ld_qk, n_rows, s);
+    if (dk == 64 && dv == 64) return launch_delta_chunk<64, 64>(p, ab, ld_ab, qk, ld_qk, n_rows, s);
     return cudaErrorInvalidValue;
 }
 

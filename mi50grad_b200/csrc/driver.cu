@@ -132,6 +132,7 @@ struct Driver {
     cudaGraphExec_t exec = nullptr;
     int graph_rows = 0, graph_flags = 0;
     long long launches = 0;               // kernels issued by the last eager step
+    bool scan_prepass = true;             // q / k convolution and norms of the chunked scan in a parallel pre-pass
     bool attn_tc = true;                  // prompt attention on tcgen05 (csrc/attention_tc.cu)
     bool gemm_splitk = true;              // split-K in the many-row GEMMs that add into the residual stream
     int pf_blocks = 0;                    // k-blocks per warp of the next projection that a GEMV prefetches into L2 (0: off)
@@ -623,7 +624,10 @@ static int rows_impl(Driver* d, int T, int n_seqs, int flags, cudaStream_t s) {
             if (flags & STEP_SPEC) {
                 CK(b2_deltanet_verify(&q, &m.spec, L.type_index, m.la_dk, m.la_dv, s));
             } else if (n_seqs == 1 && T >= 16) {
-                CK(b2_deltanet_chunk(&q, ab, m.ld_proj, m.la_dk, m.la_dv, s));
+                // the FFN activation buffer is idle here: it holds the pre-pass output (q | k of all rows) when it is wide enough
+                void* qk = (d->scan_prepass && m.F_pad >= 2 * m.la_nk * m.la_dk && m.F_pad % 8 == 0) ? m.p_act : nullptr;
+                CK(b2_deltanet_chunk(&q, ab, m.ld_proj, qk, m.F_pad, T, m.la_dk, m.la_dv, s));
+                if (qk) d->launches++;
             } else {
                 CK(b2_deltanet_step(&q, m.la_dk, m.la_dv, s));
             }
@@ -695,6 +699,8 @@ B2_API void* b2_driver_create(const ModelDesc* m, const LayerDesc* layers) {
     // 208.7 with 8, against 213.9 without: the gaps between GEMVs are not waiting on HBM.
     const char* gsk = getenv("B200GRAD_GEMM_SPLITK");
     d->gemm_splitk = !(gsk && atoi(gsk) == 0);
+    const char* spp = getenv("B200GRAD_SCAN_PREPASS");
+    d->scan_prepass = !(spp && atoi(spp) == 0);
     const char* atc = getenv("B200GRAD_ATTN_TC");
     d->attn_tc = !(atc && atoi(atc) == 0);
     const char* pf = getenv("B200GRAD_L2_PREFETCH");

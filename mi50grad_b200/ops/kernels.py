@@ -293,8 +293,9 @@ def ab_proj(x, wa, wb):
 
 
 def deltanet_chunk(proj, offs, ab, conv_w, conv_state, state, A_log, dt_bias, norm_w, rows_meta, seq_rows, nk, nv,
-                   dk, dv, out=None, commit=True, eps=1e-6):
-    """Chunked scan over each sequence's rows; ab: fp16 [rows, >= 2*nv] with a | b."""
+                   dk, dv, out=None, commit=True, eps=1e-6, prepass: bool = False):
+    """Chunked scan over each sequence's rows; ab: fp16 [rows, >= 2*nv] with a | b.  prepass (one sequence):
+    the q / k convolution and norms run once in a parallel kernel instead of inside the scan."""
     n = proj.shape[0]
     if out is None:
         out = torch.empty(n, nv * dv, dtype=torch.float16, device=proj.device)
@@ -305,7 +306,9 @@ def deltanet_chunk(proj, offs, ab, conv_w, conv_state, state, A_log, dt_bias, no
     p.A_log, p.dt_bias, p.norm_w = A_log.data_ptr(), dt_bias.data_ptr(), norm_w.data_ptr()
     p.seq_rows, p.rows, p.out, p.ldo = seq_rows.data_ptr(), rows_meta.data_ptr(), out.data_ptr(), out.stride(0)
     p.nk, p.nv, p.n_seqs, p.eps, p.commit = nk, nv, seq_rows.shape[0] - 1, eps, 1 if commit else 0
-    L.check(L.lib().b2_deltanet_chunk(C.byref(p), _vp(ab), ab.stride(0), dk, dv, L.stream()), "deltanet_chunk")
+    qk = torch.empty(n, 2 * nk * dk, dtype=torch.float16, device=proj.device) if prepass else None
+    L.check(L.lib().b2_deltanet_chunk(C.byref(p), _vp(ab), ab.stride(0), _vp(qk) if qk is not None else None,
+                                      2 * nk * dk, n, dk, dv, L.stream()), "deltanet_chunk")
     return out
 
 

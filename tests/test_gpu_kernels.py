@@ -355,9 +355,12 @@ def test_deltanet_step(K, dk, nk, nv, rows_per_seq, inkernel_ab):
         assert torch.equal(conv_d[s, 0, 0, :dk].cpu(), hist[ch].half())
 
 
-@pytest.mark.parametrize("dk,nk,nv,rows_per_seq", [(128, 1, 3, [150]), (64, 2, 4, [70, 5, 64]), (128, 2, 2, [512])])
-def test_deltanet_chunked_scan(K, dk, nk, nv, rows_per_seq):
-    """Chunked scan == token-serial oracle (outputs, final state, conv history)."""
+@pytest.mark.parametrize("dk,nk,nv,rows_per_seq,prepass", [(128, 1, 3, [150], False), (64, 2, 4, [70, 5, 64], False),
+                                                           (128, 2, 2, [512], False), (128, 1, 3, [150], True),
+                                                           (64, 2, 4, [77], True), (128, 2, 6, [512], True)])
+def test_deltanet_chunked_scan(K, dk, nk, nv, rows_per_seq, prepass):
+    """Chunked scan == token-serial oracle (outputs, final state, conv history), with the q / k convolution
+    and norms inside the scan or in the parallel pre-pass."""
     from mi50grad_b200.models import oracle as O
     gen = torch.Generator().manual_seed(21)
     d = _dev()
@@ -392,7 +395,7 @@ def test_deltanet_chunked_scan(K, dk, nk, nv, rows_per_seq):
     state_d, conv_d = S0.to(d).clone(), conv_state.to(d).clone()
     out = K.deltanet_chunk(proj.to(d), (0, kd, 2 * kd, conv_dim, -1, -1), ab, conv_w.to(d), conv_d, state_d,
                            A_log.to(d), dt_bias.to(d), norm_w.to(d), K.make_rows(entries, d),
-                           torch.tensor(seq_rows, dtype=torch.int32, device=d), nk, nv, dk, dv)
+                           torch.tensor(seq_rows, dtype=torch.int32, device=d), nk, nv, dk, dv, prepass=prepass)
     abh = ab.cpu().float()
     for s_ in range(nseq):
         r0, r1 = seq_rows[s_], seq_rows[s_ + 1]
