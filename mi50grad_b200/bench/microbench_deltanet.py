@@ -30,8 +30,15 @@ def run_case(which: str, timed: bool, profiled, report):
     offs = (0, kd, 2 * kd, conv_dim, -1, -1)
     if which == "deltanet_chunk":
         ab = K.ab_proj(xn, wa, wb)
+        if timed:
+            # the scan alone, with the q / k pre-pass, and with both pre-passes (their launches included)
+            for mode in (0, 1, 2):
+                run = lambda i=0: K.deltanet_chunk(proj, offs, ab, conv_w, conv_state, state, A_log, dt_bias, norm_w, rows,
+                                                   seq_rows, nk, nv, dk, dv, prepass=mode)
+                report(which + f" T={T} prepass={mode}", time_launches(run, 1, 6))
+            return
         run = lambda i=0: K.deltanet_chunk(proj, offs, ab, conv_w, conv_state, state, A_log, dt_bias, norm_w, rows,
-                                           seq_rows, nk, nv, dk, dv)
+                                           seq_rows, nk, nv, dk, dv, prepass=2)
     else:
         run = lambda i=0: K.deltanet_step(proj, offs, conv_w, conv_state, state, A_log, dt_bias, norm_w, rows, seq_rows,
                                           nk, nv, dk, dv, xn=xn, wa=wa, wb=wb)

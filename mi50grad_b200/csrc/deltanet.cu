@@ -539,7 +539,8 @@ __device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.f +
 
 template <int DK, int DV>
 __global__ void __launch_bounds__(DN_THREADS, 2) deltanet_chunk_kernel(const DeltaParams p, const __half* __restrict__ ab, int ld_ab,
-                                                                      const __half* __restrict__ qk_pre, int ld_qk) {
+                                                                      const __half* __restrict__ qk_pre, int ld_qk,
+                                                                      const float* __restrict__ tw_pre, int n_chunks) {
     constexpr int CB = DV / DN_COLS;
     constexpr int MT = DK / 16;               // 16-row tiles of the state slice, one or two per warp
     constexpr int SPW = (MT + 7) / 8;         // state m-tiles per warp
@@ -562,9 +563,8 @@ __global__ void __launch_bounds__(DN_THREADS, 2) deltanet_chunk_kernel(const Del
     float* Us = Ks + DC_C * LDK;              // [C][LDU]  v -> b -> u (in place)
     float* QSs = Us + DC_C * DC_LDU;          // [C][32]   exp(G) Q S0
     float* Ys = QSs + DC_C * DN_COLS;         // [C][32]
-    float* As = Ys + DC_C * DN_COLS;          // [C][LDA]
-    float* Ws = As + DC_C * DC_LDA;           // [C][LDA]
-    float* S0t = Ws + DC_C * DC_LDA;          // [32][LDK]  transposed copy of the state slice (a B operand)
+    float* As0 = Ys + DC_C * DN_COLS;         // [2][2][C][LDA]: (A or T, W) of this chunk and, with the pre-pass, of the next
+    float* S0t = As0 + 4 * DC_C * DC_LDA;     // [32][LDK]  transposed copy of the state slice (a B operand)
     float* hist = S0t + DN_COLS * LDK;        // [NCH][3]
     float* cw = hist + NCH * 3;               // [NCH][4]
     float* Gs = cw + NCH * 4;                 // [C] running log-decay
@@ -641,6 +641,18 @@ __global__ void __launch_bounds__(DN_THREADS, 2) deltanet_chunk_kernel(const Del
         }
         cp_async_commit();
     };
+    // T = (I + A)^-1 and W of a chunk from the pre-pass: 32 x 32 floats each, into the chunk's pair of buffers
+    auto stage_tw = [&](int ci) {
+        if (!tw_pre) return;
+        float* dstb = As0 + (ci & 1) * 2 * DC_C * DC_LDA;
+        const float* src = tw_pre + ((size_t)j * n_chunks + ci) * 2 * DC_C * DC_C;
+        for (int idx = tid; idx < 2 * DC_C * (DC_C / 4); idx += DN_THREADS) {
+            const int mat = idx / (DC_C * (DC_C / 4)), rem = idx % (DC_C * (DC_C / 4));
+            const int row = rem / (DC_C / 4), pc = rem % (DC_C / 4);
+            cp_async16(dstb + mat * DC_C * DC_LDA + row * DC_LDA + pc * 4, src + mat * DC_C * DC_C + row * DC_C + pc * 4);
+        }
+    };
+    stage_tw(0);
     stage_raw(r0);
     // the gate inputs of a chunk are fetched one chunk ahead (a global round trip off the critical path)
     float a_pre = 0.f, b_pre = 0.f;
@@ -700,7 +712,9 @@ __global__ void __launch_bounds__(DN_THREADS, 2) deltanet_chunk_kernel(const Del
             cl_ss[slot * DC_C + tid] = 0.f;
         }
         __syncthreads();
-        if (rb + DC_C < r1) stage_raw(rb + DC_C);          // flies while this chunk is processed
+        if (rb + DC_C < r1) { stage_tw(chunk_idx + 1); stage_raw(rb + DC_C); }          // fly while this chunk is processed
+        float* As = As0 + (tw_pre ? (chunk_idx & 1) * 2 * DC_C * DC_LDA : 0);
+        float* Ws = As + DC_C * DC_LDA;
         fetch_gates(rb + DC_C);
         // output gates of this chunk, needed only at its end
         float zf[DC_C / 8];
@@ -776,7 +790,7 @@ __global__ void __launch_bounds__(DN_THREADS, 2) deltanet_chunk_kernel(const Del
         const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 4;       // A operand addressing
         const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 4;       // B operand, two 8-column tiles
         {
-            for (int tile = kr; tile < MB * (MB + 1); tile += 8) {
+            for (int tile = kr; tile < (tw_pre ? 0 : MB * (MB + 1)); tile += 8) {
                 int mi = 0, ni = tile;                 // row block mi holds tiles ni = 0 .. 2 mi + 1
                 while (ni >= 2 * mi + 2) { ni -= 2 * mi + 2; ++mi; }
                 float kk[4] = {0.f, 0.f, 0.f, 0.f}, qk[4] = {0.f, 0.f, 0.f, 0.f};
@@ -841,6 +855,36 @@ __global__ void __launch_bounds__(DN_THREADS, 2) deltanet_chunk_kernel(const Del
         // ---- P5: (I + A) U = B by forward substitution, 8 rows per block: every warp first removes
         // the contribution of all earlier blocks from its row, then warp 0 solves the 8x8 triangle
         // with one column per lane in registers
+        if (tw_pre) {
+            // U = T B with T = (I + A)^-1 from the pre-pass: one 16x8 tile per warp, split-TF32 operands
+            // (hi + lo parts) so that the product keeps fp32 accuracy like the substitution it replaces
+            const int mi5 = kr % MB, nb5 = (kr / MB) * NTW;
+            float u[NTW][4];
+#pragma unroll
+            for (int n = 0; n < NTW; ++n) u[n][0] = u[n][1] = u[n][2] = u[n][3] = 0.f;
+            const float* ta = As + (16 * mi5 + a_row) * DC_LDA + a_col;
+            for (int k0 = 0; k0 < 16 * (mi5 + 1); k0 += 8) {
+                float fa[4], hi[4], lo[4];
+                ldsm4(fa, ta + k0);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { hi[e] = tf32r(fa[e]); lo[e] = tf32r(fa[e] - hi[e]); }
+#pragma unroll
+                for (int n = 0; n < NTW; ++n) {
+                    const float b0 = Us[(k0 + t) * DC_LDU + 8 * (nb5 + n) + g], b1 = Us[(k0 + t + 4) * DC_LDU + 8 * (nb5 + n) + g];
+                    const float b0h = tf32r(b0), b1h = tf32r(b1);
+                    mma_tf32(u[n], lo[0], lo[1], lo[2], lo[3], b0h, b1h);
+                    mma_tf32(u[n], hi[0], hi[1], hi[2], hi[3], tf32r(b0 - b0h), tf32r(b1 - b1h));
+                    mma_tf32(u[n], hi[0], hi[1], hi[2], hi[3], b0h, b1h);
+                }
+            }
+            __syncthreads();                               // every warp has read B before anyone overwrites it
+#pragma unroll
+            for (int n = 0; n < NTW; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    Us[(16 * mi5 + g + (e >> 1) * 8) * DC_LDU + 8 * (nb5 + n) + 2 * t + (e & 1)] = u[n][e];
+            __syncthreads();
+        } else
         for (int blk = 0; blk < DC_C / 8; ++blk) {
             const int i = 8 * blk + kr;
             float acc = Us[i * DC_LDU + vcol];
@@ -1029,18 +1073,142 @@ __global__ void __launch_bounds__(2 * DK) deltanet_qk_prep_kernel(const DeltaPar
     }
 }
 
+// ---------------------------------------------------------------------------
+// Second pre-pass of the chunked scan: everything of a chunk that does not depend on the state, for every
+// (value head, chunk) in parallel: the gates, A = beta decay (K K^T) below the diagonal, W = decay (Q K^T) on
+// and below it, and T = (I + A)^-1 (forward substitution on the 32 x 32 unit triangle, one column per lane).
+// The scan then replaces its per-chunk products and its sequential triangular solve by loads and U = T B.
+// Output fp32 [nv][n_chunks][T | W][32][32].  grid = (chunks, value heads), 256 threads.
+// ---------------------------------------------------------------------------
+template <int DK>
+__global__ void __launch_bounds__(DN_THREADS) deltanet_tw_prep_kernel(const DeltaParams p, const __half* __restrict__ ab, int ld_ab,
+                                                                      const __half* __restrict__ qk_pre, int ld_qk,
+                                                                      float* __restrict__ tw, int n_chunks) {
+    static_assert(DC_C == 32, "one lane per column of the triangle");
+    constexpr int LDK = DC_LDK(DK);
+    constexpr int MB = DC_C / 16;
+    extern __shared__ __align__(16) float psm[];
+    float* Qs = psm;                          // [C][LDK]
+    float* Ks = Qs + DC_C * LDK;
+    float* As = Ks + DC_C * LDK;              // [C][LDA]
+    float* Ws = As + DC_C * DC_LDA;
+    float* Ts = Ws + DC_C * DC_LDA;
+    float* Gs = Ts + DC_C * DC_LDA;           // [C]
+    float* bs = Gs + DC_C;
+    float* gs = bs + DC_C;
+    const int ci = blockIdx.x, j = blockIdx.y, kh = j / (p.nv / p.nk);
+    const int tid = threadIdx.x, lane = tid & 31, kr = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int r0 = p.seq_rows[0], r1 = p.seq_rows[1];
+    const int rb = r0 + ci * DC_C;
+    if (rb >= r1) return;
+    const int Ce = min(DC_C, r1 - rb);
+    for (int idx = tid; idx < DC_C * (DK / 8) * 2; idx += DN_THREADS) {
+        const int which = idx / (DC_C * (DK / 8)), rem = idx % (DC_C * (DK / 8));
+        const int row = rem / (DK / 8), c = (rem % (DK / 8)) * 8;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row < Ce) v = *(const uint4*)(qk_pre + (size_t)(rb - r0 + row) * ld_qk + (which ? p.nk * DK : 0) + kh * DK + c);
+        const __half2* h2 = (const __half2*)&v;
+        float* dst = (which ? Ks : Qs) + row * LDK + c;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { const float2 f = __half22float2(h2[q]); dst[2 * q] = f.x; dst[2 * q + 1] = f.y; }
+    }
+    if (tid < DC_C) {
+        float gl = 0.f, beta = 0.f;
+        if (tid < Ce) {
+            const __half* abr = ab + (size_t)(rb + tid) * ld_ab;
+            const float sp_ = __half2float(abr[j]) + __half2float(p.dt_bias[j]);
+            gl = fmaxf(-__expf(p.A_log[j]) * (sp_ > 20.f ? sp_ : log1pf(__expf(sp_))), -20.f);
+            beta = sigmoid_f(__half2float(abr[p.nv + j]));
+        }
+        gs[tid] = gl;
+        bs[tid] = beta;
+    }
+    __syncthreads();
+    if (kr == 0) {
+        float a = gs[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float ua = __shfl_up_sync(0xffffffffu, a, o);
+            if (lane >= o) a += ua;
+        }
+        Gs[lane] = a;
+    }
+    __syncthreads();
+    {
+        const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 4;
+        for (int tile = kr; tile < MB * (MB + 1); tile += 8) {
+            int mi = 0, ni = tile;
+            while (ni >= 2 * mi + 2) { ni -= 2 * mi + 2; ++mi; }
+            float kk[4] = {0.f, 0.f, 0.f, 0.f}, qk[4] = {0.f, 0.f, 0.f, 0.f};
+            const float* ka = Ks + (16 * mi + a_row) * LDK + a_col;
+            const float* qa = Qs + (16 * mi + a_row) * LDK + a_col;
+            const float* kb = Ks + (8 * ni + (lane & 7)) * LDK + ((lane >> 3) & 1) * 4;
+#pragma unroll 4
+            for (int k0 = 0; k0 < DK; k0 += 8) {
+                float fa[4], fq[4], fb[2];
+                ldsm4(fa, ka + k0); ldsm4(fq, qa + k0); ldsm2(fb, kb + k0);
+                mma_tf32(kk, fa[0], fa[1], fa[2], fa[3], fb[0], fb[1]);
+                mma_tf32(qk, fq[0], fq[1], fq[2], fq[3], fb[0], fb[1]);
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = 16 * mi + g + (e >> 1) * 8, jj = 8 * ni + 2 * t + (e & 1);
+                const float dec = (jj <= i) ? __expf(Gs[i] - Gs[jj]) : 0.f;
+                As[i * DC_LDA + jj] = (jj < i) ? bs[i] * dec * kk[e] : 0.f;
+                Ws[i * DC_LDA + jj] = tf32r(dec * qk[e]);
+            }
+        }
+        // tiles above the diagonal were not visited: they are zero
+        for (int idx = tid; idx < DC_C * DC_C; idx += DN_THREADS) {
+            const int i = idx / DC_C, jj = idx % DC_C;
+            if ((jj >> 3) > ((i >> 4) * 2 + 1)) { As[i * DC_LDA + jj] = 0.f; Ws[i * DC_LDA + jj] = 0.f; }
+        }
+    }
+    __syncthreads();
+    if (kr == 0) {
+        // column `lane` of T: t_i = [i == lane] - sum_{j < i} A_ij t_j
+        float tc[DC_C];
+#pragma unroll
+        for (int i = 0; i < DC_C; ++i) {
+            float v = (i == lane) ? 1.f : 0.f;
+#pragma unroll
+            for (int jj = 0; jj < DC_C; ++jj)
+                if (jj < i) v = fmaf(-As[i * DC_LDA + jj], tc[jj], v);
+            tc[i] = v;
+            Ts[i * DC_LDA + lane] = v;
+        }
+    }
+    __syncthreads();
+    float* dst = tw + ((size_t)j * n_chunks + ci) * 2 * DC_C * DC_C;
+    for (int idx = tid; idx < 2 * DC_C * DC_C; idx += DN_THREADS) {
+        const int mat = idx / (DC_C * DC_C), rem = idx % (DC_C * DC_C);
+        dst[idx] = (mat ? Ws : Ts)[(rem / DC_C) * DC_LDA + rem % DC_C];
+    }
+}
+
 template <int DK, int DV>
 static int launch_delta_chunk(const DeltaParams* p, const void* ab, int ld_ab, __half* qk_pre, int ld_qk, int n_rows,
-                              cudaStream_t s) {
+                              float* tw, cudaStream_t s) {
     if (qk_pre) {
         dim3 grid((n_rows + QP_ROWS - 1) / QP_ROWS, p->nk);
         deltanet_qk_prep_kernel<DK><<<grid, 2 * DK, 0, s>>>(*p, qk_pre, ld_qk, DV / DN_COLS, 2 * DK + DN_COLS);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
+    const int n_chunks = (n_rows + DC_C - 1) / DC_C;
+    if (qk_pre && tw) {
+        const size_t psm = (size_t)(2 * DC_C * DC_LDK(DK) + 3 * DC_C * DC_LDA + 3 * DC_C) * sizeof(float);
+        static SmemOptIn opt_tw;
+        if (int e = opt_tw.ensure(deltanet_tw_prep_kernel<DK>, psm)) return e;
+        deltanet_tw_prep_kernel<DK><<<dim3(n_chunks, p->nv), DN_THREADS, psm, s>>>(*p, (const __half*)ab, ld_ab, qk_pre, ld_qk, tw, n_chunks);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    } else {
+        tw = nullptr;
+    }
     constexpr int CB = DV / DN_COLS;
     constexpr int NCH = 2 * DK + DN_COLS;
-    size_t smem = (size_t)(2 * DC_C * DC_LDK(DK) + DC_C * DC_LDU + 2 * DC_C * DN_COLS + 2 * DC_C * DC_LDA + DN_COLS * DC_LDK(DK) + NCH * 7 +
+    size_t smem = (size_t)(2 * DC_C * DC_LDK(DK) + DC_C * DC_LDU + 2 * DC_C * DN_COLS + 4 * DC_C * DC_LDA + DN_COLS * DC_LDK(DK) + NCH * 7 +
                            3 * DC_C + 2 * DC_C) * sizeof(float) + (size_t)(DC_C + 3) * NCH * sizeof(__half);
     static SmemOptIn optin;
     {
@@ -1059,21 +1227,27 @@ static int launch_delta_chunk(const DeltaParams* p, const void* ab, int ld_ab, _
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, deltanet_chunk_kernel<DK, DV>, *p, (const __half*)ab, ld_ab, (const __half*)qk_pre, ld_qk);
+    return cudaLaunchKernelEx(&cfg, deltanet_chunk_kernel<DK, DV>, *p, (const __half*)ab, ld_ab, (const __half*)qk_pre, ld_qk,
+                              (const float*)tw, n_chunks);
 }
 
 // ab: [rows][ld_ab] fp16 with a at column head and b at column nv + head.
 // qk_scratch (optional): fp16 [n_rows][ld_qk >= 2 * nk * dk] work buffer; with it, and ONE launched sequence of
 // n_rows rows, the q / k convolution and norms run once in a parallel pre-pass instead of inside the scan.
+// tw_scratch (optional, needs qk_scratch): fp32 [nv][ceil(n_rows / 32)][2][32][32]; with it the state-independent
+// products of every chunk and the inverse of its triangle are computed in a second parallel pre-pass.
 B2_API int b2_deltanet_chunk(const DeltaParams* p, const void* ab, int ld_ab, void* qk_scratch, int ld_qk, int n_rows,
-                             int dk, int dv, cudaStream_t s) {
+                             void* tw_scratch, int dk, int dv, cudaStream_t s) {
     if (p->nv % p->nk || !ab) return cudaErrorInvalidValue;
     __half* qk = (__half*)qk_scratch;
     if (qk && (p->n_seqs != 1 || n_rows < 1 || ld_qk < 2 * p->nk * dk || (ld_qk & 7) || ((uintptr_t)qk & 15))) qk = nullptr;
-    if (dk == 128 && dv == 128) return launch_delta_chunk<128, 128>(p, ab, ld_ab, qk, ld_qk, n_rows, s);
-    if (dk == 64 && dv == 64) return launch_delta_chunk<64, 64>(p, ab, ld_ab, qk, ld_qk, n_rows, s);
+    float* tw = (float*)tw_scratch;
+    if (tw && (!qk || ((uintptr_t)tw & 15))) tw = nullptr;
+    if (dk == 128 && dv == 128) return launch_delta_chunk<128, 128>(p, ab, ld_ab, qk, ld_qk, n_rows, tw, s);
+    if (dk == 64 && dv == 64) return launch_delta_chunk<64, 64>(p, ab, ld_ab, qk, ld_qk, n_rows, tw, s);
     return cudaErrorInvalidValue;
 }
+B2_API long long b2_deltanet_tw_floats(int nv, int n_rows) { return (long long)nv * ((n_rows + DC_C - 1) / DC_C) * 2 * DC_C * DC_C; }
 
 // a/b projections for many rows: ab[r][o] = x[r] . w[o], o < 2 nv (tiny dense weights).  A CTA stages
 // AB_ROWS activation rows in shared memory and computes 8 outputs (one per warp) for all of them:

@@ -132,7 +132,8 @@ struct Driver {
     cudaGraphExec_t exec = nullptr;
     int graph_rows = 0, graph_flags = 0;
     long long launches = 0;               // kernels issued by the last eager step
-    bool scan_prepass = true;             // q / k convolution and norms of the chunked scan in a parallel pre-pass
+    int scan_prepass = 2;                 // chunked scan: 1 = q / k convolution and norms in a parallel pre-pass,
+                                          // 2 = also the state-independent products and the triangle inverse of every chunk
     bool attn_tc = true;                  // prompt attention on tcgen05 (csrc/attention_tc.cu)
     bool gemm_splitk = true;              // split-K in the many-row GEMMs that add into the residual stream
     int pf_blocks = 0;                    // k-blocks per warp of the next projection that a GEMV prefetches into L2 (0: off)
@@ -624,10 +625,17 @@ static int rows_impl(Driver* d, int T, int n_seqs, int flags, cudaStream_t s) {
             if (flags & STEP_SPEC) {
                 CK(b2_deltanet_verify(&q, &m.spec, L.type_index, m.la_dk, m.la_dv, s));
             } else if (n_seqs == 1 && T >= 16) {
-                // the FFN activation buffer is idle here: it holds the pre-pass output (q | k of all rows) when it is wide enough
-                void* qk = (d->scan_prepass && m.F_pad >= 2 * m.la_nk * m.la_dk && m.F_pad % 8 == 0) ? m.p_act : nullptr;
-                CK(b2_deltanet_chunk(&q, ab, m.ld_proj, qk, m.F_pad, T, m.la_dk, m.la_dv, s));
+                // the FFN activation buffer is idle here: it holds the outputs of the two pre-passes (q | k of all rows,
+                // then T | W of every chunk and value head) when it is large enough
+                const int ld_qk = 2 * m.la_nk * m.la_dk;
+                const size_t cap = (size_t)m.max_prefill * m.F_pad * sizeof(__half);
+                const size_t qk_bytes = (((size_t)T * ld_qk * sizeof(__half)) + 255) & ~(size_t)255;
+                const size_t tw_bytes = (size_t)b2_deltanet_tw_floats(m.la_nv, T) * sizeof(float);
+                void* qk = (d->scan_prepass && qk_bytes <= cap) ? m.p_act : nullptr;
+                void* tw = (qk && d->scan_prepass > 1 && qk_bytes + tw_bytes <= cap) ? (void*)((char*)m.p_act + qk_bytes) : nullptr;
+                CK(b2_deltanet_chunk(&q, ab, m.ld_proj, qk, ld_qk, T, tw, m.la_dk, m.la_dv, s));
                 if (qk) d->launches++;
+                if (tw) d->launches++;
             } else {
                 CK(b2_deltanet_step(&q, m.la_dk, m.la_dv, s));
             }
@@ -700,7 +708,7 @@ B2_API void* b2_driver_create(const ModelDesc* m, const LayerDesc* layers) {
     const char* gsk = getenv("B200GRAD_GEMM_SPLITK");
     d->gemm_splitk = !(gsk && atoi(gsk) == 0);
     const char* spp = getenv("B200GRAD_SCAN_PREPASS");
-    d->scan_prepass = !(spp && atoi(spp) == 0);
+    d->scan_prepass = spp ? atoi(spp) : 2;
     const char* atc = getenv("B200GRAD_ATTN_TC");
     d->attn_tc = !(atc && atoi(atc) == 0);
     const char* pf = getenv("B200GRAD_L2_PREFETCH");

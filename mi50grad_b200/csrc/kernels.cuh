@@ -143,7 +143,8 @@ B2_API int b2_attn_prefill_tc(const AttnParams* p, int row_base, int n_rows_seq,
                               cudaStream_t s);
 B2_API int b2_deltanet_step(const DeltaParams* p, int dk, int dv, cudaStream_t s);
 B2_API int b2_deltanet_chunk(const DeltaParams* p, const void* ab, int ld_ab, void* qk_scratch, int ld_qk, int n_rows,
-                             int dk, int dv, cudaStream_t s);
+                             void* tw_scratch, int dk, int dv, cudaStream_t s);
+B2_API long long b2_deltanet_tw_floats(int nv, int n_rows);
 B2_API int b2_ab_proj(const void* x, int ldx, const void* wa, const void* wb, int nv, int H, void* ab, int ld_ab,
                       int rows, cudaStream_t s);
 B2_API int b2_argmax(const ArgmaxParams* p, cudaStream_t s);

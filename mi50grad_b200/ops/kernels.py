@@ -293,9 +293,10 @@ def ab_proj(x, wa, wb):
 
 
 def deltanet_chunk(proj, offs, ab, conv_w, conv_state, state, A_log, dt_bias, norm_w, rows_meta, seq_rows, nk, nv,
-                   dk, dv, out=None, commit=True, eps=1e-6, prepass: bool = False):
+                   dk, dv, out=None, commit=True, eps=1e-6, prepass: int = 0):
     """Chunked scan over each sequence's rows; ab: fp16 [rows, >= 2*nv] with a | b.  prepass (one sequence):
-    the q / k convolution and norms run once in a parallel kernel instead of inside the scan."""
+    1 = the q / k convolution and norms run once in a parallel kernel instead of inside the scan; 2 = also the
+    state-independent products of every chunk and the inverse of its triangle."""
     n = proj.shape[0]
     if out is None:
         out = torch.empty(n, nv * dv, dtype=torch.float16, device=proj.device)
@@ -307,8 +308,10 @@ def deltanet_chunk(proj, offs, ab, conv_w, conv_state, state, A_log, dt_bias, no
     p.seq_rows, p.rows, p.out, p.ldo = seq_rows.data_ptr(), rows_meta.data_ptr(), out.data_ptr(), out.stride(0)
     p.nk, p.nv, p.n_seqs, p.eps, p.commit = nk, nv, seq_rows.shape[0] - 1, eps, 1 if commit else 0
     qk = torch.empty(n, 2 * nk * dk, dtype=torch.float16, device=proj.device) if prepass else None
+    L.lib().b2_deltanet_tw_floats.restype = C.c_longlong
+    tw = torch.empty(int(L.lib().b2_deltanet_tw_floats(nv, n)), dtype=torch.float32, device=proj.device) if int(prepass) > 1 else None
     L.check(L.lib().b2_deltanet_chunk(C.byref(p), _vp(ab), ab.stride(0), _vp(qk) if qk is not None else None,
-                                      2 * nk * dk, n, dk, dv, L.stream()), "deltanet_chunk")
+                                      2 * nk * dk, n, _vp(tw) if tw is not None else None, dk, dv, L.stream()), "deltanet_chunk")
     return out
 
 

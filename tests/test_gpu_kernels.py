@@ -355,12 +355,15 @@ def test_deltanet_step(K, dk, nk, nv, rows_per_seq, inkernel_ab):
         assert torch.equal(conv_d[s, 0, 0, :dk].cpu(), hist[ch].half())
 
 
-@pytest.mark.parametrize("dk,nk,nv,rows_per_seq,prepass", [(128, 1, 3, [150], False), (64, 2, 4, [70, 5, 64], False),
-                                                           (128, 2, 2, [512], False), (128, 1, 3, [150], True),
-                                                           (64, 2, 4, [77], True), (128, 2, 6, [512], True)])
+@pytest.mark.parametrize("dk,nk,nv,rows_per_seq,prepass", [(128, 1, 3, [150], 0), (64, 2, 4, [70, 5, 64], 0),
+                                                           (128, 2, 2, [512], 0), (128, 1, 3, [150], 1),
+                                                           (64, 2, 4, [77], 1), (128, 2, 6, [512], 1),
+                                                           (128, 1, 3, [150], 2), (64, 2, 4, [77], 2),
+                                                           (128, 2, 6, [512], 2), (64, 1, 2, [32], 2)])
 def test_deltanet_chunked_scan(K, dk, nk, nv, rows_per_seq, prepass):
-    """Chunked scan == token-serial oracle (outputs, final state, conv history), with the q / k convolution
-    and norms inside the scan or in the parallel pre-pass."""
+    """Chunked scan == token-serial oracle (outputs, final state, conv history), with everything inside the
+    scan (0), the q / k convolution and norms in a parallel pre-pass (1), and also the state-independent
+    products and the triangle inverse of every chunk (2)."""
     from mi50grad_b200.models import oracle as O
     gen = torch.Generator().manual_seed(21)
     d = _dev()
