@@ -135,6 +135,8 @@ struct Driver {
     int scan_prepass = 2;                 // chunked scan: 1 = q / k convolution and norms in a parallel pre-pass,
                                           // 2 = also the state-independent products and the triangle inverse of every chunk
     bool attn_tc = true;                  // prompt attention on tcgen05 (csrc/attention_tc.cu)
+    bool gemm_m256 = true;                // 256-output GEMM tiles where the grid stays large enough
+    int gemm_m256_min_ctas = 100;
     bool gemm_splitk = true;              // split-K in the many-row GEMMs that add into the residual stream
     int pf_blocks = 0;                    // k-blocks per warp of the next projection that a GEMV prefetches into L2 (0: off)
     int gemv_seq = 0;                     // split-K GEMVs issued so far in the step being issued (their tags)
@@ -498,6 +500,18 @@ static int run_gemm(Driver* d, const LinearDesc& L, const void* x, int ldx, int 
         }
     }
     p.T = T; p.t_tile = tt; p.k_splits = ks;
+    // 256-output tiles (two accumulators sharing each activation tile, weights dequantised once for both) where
+    // they still give the GPU enough CTAs.
+    // Measured (27B, one GPU): with few token rows a weight tile dequantised once for 256 outputs pays (80-row
+    // verify step 26.7 -> 26.1 ms); at 512 rows both forms are bound by the shared-memory traffic of the MMA
+    // operands and the 256-output form is slightly slower in the prompt (41.9 -> 42.5 ms), so it is used below
+    // 256 rows only.
+    if (d->gemm_m256 && T < 256 && (L.NTL * 16) % 256 == 0 &&
+        (epi == TC_EPI_STORE_F16 || epi == TC_EPI_SILU_PAIR || epi == TC_EPI_STORE_F32)) {
+        const int tt2 = T >= 256 ? 256 : ((T + 15) & ~15);
+        const int ctas = (L.NTL * 16 / 256) * ((T + tt2 - 1) / tt2);
+        if (ctas >= d->gemm_m256_min_ctas) { p.m_halves = 2; p.t_tile = tt2; p.k_splits = 1; }
+    }
     p.n_valid = n_valid; p.ldo = ldo; p.epi = epi; p.out = out; p.status = d->m.tc_status;
     if (epi == TC_EPI_PUSH_F32) {
         const CommCtx& c = d->m.comm;
@@ -705,6 +719,9 @@ B2_API void* b2_driver_create(const ModelDesc* m, const LayerDesc* layers) {
     d->layer_launches.assign(m->n_layers, 0);
     // Off by default: measured on B200 (27B, one GPU, tg128) 213.6 tok/s with 4 blocks per warp, 213.1 with 2,
     // 208.7 with 8, against 213.9 without: the gaps between GEMVs are not waiting on HBM.
+    const char* g256 = getenv("B200GRAD_GEMM_M256");
+    d->gemm_m256 = !(g256 && atoi(g256) == 0);
+    if (g256 && atoi(g256) > 1) d->gemm_m256_min_ctas = atoi(g256);
     const char* gsk = getenv("B200GRAD_GEMM_SPLITK");
     d->gemm_splitk = !(gsk && atoi(gsk) == 0);
     const char* spp = getenv("B200GRAD_SCAN_PREPASS");

@@ -67,8 +67,13 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
     const int Tp = (min(p.t_tile, p.T - t0) + 15) & ~15;          // token columns of this CTA
     const int boxes = (Tp + 63) / 64;
     const int b_stage_bytes = ((p.t_tile + 63) / 64) * 64 * 128;
+    // MH = 2: the CTA owns 256 outputs as two M = 128 accumulators that share every activation tile (half the
+    // activation bytes per FLOP, one pass of the dequantising warps per 256 outputs); all 16 producer warps
+    // then work on the same k-block
+    const int MH = p.m_halves == 2 ? 2 : 1;
+    const int a_bytes = MH * TC_A_BYTES;
     unsigned char* sA = smem;
-    unsigned char* sB = smem + (size_t)S * TC_A_BYTES;
+    unsigned char* sB = smem + (size_t)S * a_bytes;
     uint64_t* bars = (uint64_t*)(sB + (size_t)S * b_stage_bytes);
     uint64_t* full = bars;              // [S] operands of the stage are in place: one arrival per producer warp of
                                         // the stage's group (INT4 weights) + 1 arrival with the TMA transaction bytes
@@ -80,9 +85,10 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
 
     int tmem_cols = 32;
     while (tmem_cols < Tp) tmem_cols <<= 1;
+    if (MH == 2) tmem_cols = 512;                  // accumulator h at column 256 h (Tp <= 256)
 
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { mbar_init(&full[s], p.dense ? 1 : TC_GROUP_WARPS + 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < S; ++s) { mbar_init(&full[s], p.dense ? 1 : (MH == 2 ? TC_PRODUCERS : TC_GROUP_WARPS) + 1); mbar_init(&empty[s], 1); }
         mbar_init(acc_full, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -108,10 +114,11 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
         // ================= weight producers =================
         // warp w owns the 16-row tile w of the CTA's 128 outputs: one 16-byte load per k-block and lane
         const int g = lane >> 2, t = lane & 3;
-        const int grp = warp >> 3, w8 = warp & 7;
-        const int wt = blockIdx.x * 2 + (w8 >> 2);
+        // MH = 1: two groups of 8 warps take alternate k-blocks; MH = 2: one group of 16 takes every k-block
+        const int grp = MH == 2 ? 0 : warp >> 3, w8 = MH == 2 ? warp : warp & 7;
+        const int kstep = MH == 2 ? 1 : 2;
+        const int wt = blockIdx.x * (2 * MH) + (w8 >> 2);
         const int ti = w8 & 3;
-        const int tile = wt * 4 + ti;
         const bool dense = p.dense != 0;          // fp16 weights arrive by TMA: nothing to dequantise
         const __half2 sixteenth = __float2half2_rn(0.0625f);
         const __half2 k1024 = __float2half2_rn(1024.f), k64 = __float2half2_rn(64.f);
@@ -125,6 +132,8 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
         uint4* my_ring = wring + tid;
         const uint4* gq = dense ? nullptr : p.qfrag + ((size_t)wt * p.KB * 4 + ti) * 32 + lane + (size_t)(kb_lo + grp) * 128;
         const uint2* gs = dense ? nullptr : p.szfrag + ((size_t)wt * p.G * 4 + ti) * 8 + g;
+        const uint32_t gq_step = 128u * kstep;
+        const int c_step = 2 * kstep;
         int c_issue = p.off32 + 2 * (kb_lo + grp);          // 32-k chunk counter of the next k-block to issue
         int slot_issue = 0;
         auto issue = [&]() {
@@ -132,20 +141,20 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
             cp_async16(dst, gq);
             cp_async8((uint2*)(dst + 512), gs + (size_t)(c_issue >> p.gshift) * 32);
             cp_async8((uint2*)(dst + 512) + 1, gs + (size_t)((c_issue + 1) >> p.gshift) * 32);
-            gq += 256; c_issue += 4;
+            gq += gq_step; c_issue += c_step;
             slot_issue = slot_issue == TC_RING - 1 ? 0 : slot_issue + 1;
         };
 #pragma unroll
         for (int i = 0; i < TC_RING - 1; ++i) {
-            if (grp + 2 * i < KB && !dense) issue();
+            if (grp + kstep * i < KB && !dense) issue();
             cp_async_commit();
         }
         bool ok = true;
         int st = grp, slot = 0;
         uint32_t ph = 0;
-        unsigned char* a_stage = sA + (size_t)grp * TC_A_BYTES + row_lo_off;
-        for (int kb = grp; kb < KB && !dense; kb += 2) {
-            if (kb + 2 * (TC_RING - 1) < KB) issue();
+        unsigned char* a_stage = sA + (size_t)grp * a_bytes + row_lo_off;
+        for (int kb = grp; kb < KB && !dense; kb += kstep) {
+            if (kb + kstep * (TC_RING - 1) < KB) issue();
             cp_async_commit();
             cp_async_wait<TC_RING - 1>();
             const uint4 wv = my_ring[slot * 1024];
@@ -189,8 +198,8 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
             fence_proxy_async_smem();           // generic-proxy stores -> visible to the tensor core
             __syncwarp();
             if (lane == 0) mbar_arrive(&full[st]);
-            st += 2; a_stage += 2 * TC_A_BYTES;       // S is even: a group keeps to the stages of its parity
-            if (st >= S) { st -= S; ph ^= 1; a_stage = sA + (size_t)st * TC_A_BYTES + row_lo_off; }
+            st += kstep; a_stage += kstep * a_bytes;  // two groups: S is even, a group keeps to the stages of its parity
+            if (st >= S) { st -= S; ph ^= 1; a_stage = sA + (size_t)st * a_bytes + row_lo_off; }
         }
         cp_async_wait<0>();
         // ================= epilogue =================
@@ -198,14 +207,15 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
         tc_fence_after();
         if (ok) {
             const int lg = warp & 3;               // tensor-memory lane group this warp may read
-            const int n = blockIdx.x * TC_BM + lg * 32 + lane;
+            for (int hc = 0; hc < MH; ++hc)
             for (int c0 = (warp >> 2) * 32; c0 < Tp; c0 += (TC_PRODUCERS / 4) * 32) {
+                const int n = blockIdx.x * (TC_BM * MH) + hc * TC_BM + lg * 32 + lane;
                 uint32_t r[32];
-                tc_ld32(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)c0, r);
+                tc_ld32(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(hc * 256 + c0), r);
                 tc_wait_ld();
                 if (p.epi == TC_EPI_SILU_PAIR) {
                     const bool is_gate = (lane & 8) == 0;
-                    const int o = blockIdx.x * (TC_BM / 2) + lg * 16 + (lane >> 4) * 8 + (lane & 7);
+                    const int o = blockIdx.x * (TC_BM / 2 * MH) + hc * (TC_BM / 2) + lg * 16 + (lane >> 4) * 8 + (lane & 7);
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
                         float v = __uint_as_float(r[c]);
@@ -247,8 +257,8 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
         // ================= activation producer (TMA) =================
         {
             const bool dense = p.dense != 0;
-            const uint32_t tx = (uint32_t)boxes * 64 * 128 + (dense ? TC_A_BYTES : 0);
-            const int row_w = blockIdx.x * TC_BM;
+            const uint32_t tx = (uint32_t)boxes * 64 * 128 + (dense ? (uint32_t)a_bytes : 0u);
+            const int row_w = blockIdx.x * (TC_BM * MH);
             int st = 0;
             uint32_t ph = 0;
             unsigned char* a = sA;
@@ -257,12 +267,12 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
                 if (!mbar_wait(&empty[st], ph ^ 1, abort_flag)) break;
                 if (elect_one()) {
                     mbar_arrive_expect_tx(&full[st], tx);
-                    if (dense) tma_load_2d(a, &wmap, kx, row_w, &full[st]);
+                    if (dense) for (int hc = 0; hc < MH; ++hc) tma_load_2d(a + hc * TC_A_BYTES, &wmap, kx, row_w + hc * TC_BM, &full[st]);
                     for (int bx = 0; bx < boxes; ++bx)
                         tma_load_2d(b + bx * (64 * 128), &xmap, kx, t0 + bx * 64, &full[st]);
                 }
                 __syncwarp();
-                a += TC_A_BYTES; b += b_stage_bytes;
+                a += a_bytes; b += b_stage_bytes;
                 if (++st == S) { st = 0; ph ^= 1; a = sA; b = sB; }
             }
         }
@@ -274,7 +284,8 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
             const uint32_t idesc1 = make_idesc_f16(n1), idesc2 = make_idesc_f16(n2 > 0 ? n2 : 16);
             // descriptors differ between stages and k16 steps only in the start-address field (16-byte units)
             const uint64_t ad0 = make_desc_sw128(smem_u32(sA)), bd0 = make_desc_sw128(smem_u32(sB));
-            const uint64_t a_step = TC_A_BYTES >> 4, b_step = (uint64_t)(b_stage_bytes >> 4), b_half = (256 * 128) >> 4;
+            const uint64_t a_step = (uint64_t)(a_bytes >> 4), b_step = (uint64_t)(b_stage_bytes >> 4), b_half = (256 * 128) >> 4;
+            const uint64_t a_half = TC_A_BYTES >> 4;
             uint64_t ad = ad0, bd = bd0;
             int st = 0;
             uint32_t ph = 0;
@@ -287,7 +298,8 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
 #pragma unroll
                     for (int k16 = 0; k16 < TC_BK / 16; ++k16) {
                         tc_mma_f16(tmem_base, ad + 2 * k16, bd + 2 * k16, idesc1, (kb | k16) ? 1u : 0u);
-                        if (n2 > 0) tc_mma_f16(tmem_base + 256, ad + 2 * k16, bd + b_half + 2 * k16, idesc2, (kb | k16) ? 1u : 0u);
+                        if (MH == 2) tc_mma_f16(tmem_base + 256, ad + a_half + 2 * k16, bd + 2 * k16, idesc1, (kb | k16) ? 1u : 0u);
+                        else if (n2 > 0) tc_mma_f16(tmem_base + 256, ad + 2 * k16, bd + b_half + 2 * k16, idesc2, (kb | k16) ? 1u : 0u);
                     }
                     tc_commit(&empty[st]);      // stage reusable once these MMAs have read it
                 }
@@ -310,9 +322,10 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
-B2_API size_t b2_gemm_tc_smem(int t_tile, int stages) {
+B2_API size_t b2_gemm_tc_smem(int t_tile, int stages, int m_halves) {
     size_t b = (size_t)((t_tile + 63) / 64) * 64 * 128;
-    return 1024 + (size_t)stages * (TC_A_BYTES + b) + (2 * stages + 1) * 8 + 16 + 16 + (size_t)TC_RING * 2 * (TC_PRODUCERS * 32) * 16;
+    return 1024 + (size_t)stages * ((size_t)(m_halves == 2 ? 2 : 1) * TC_A_BYTES + b) + (2 * stages + 1) * 8 + 16 + 16 +
+           (size_t)TC_RING * 2 * (TC_PRODUCERS * 32) * 16;
 }
 
 // x: [T][ldx] fp16 activations (ldx multiple of 8, base 16-byte aligned).
@@ -343,14 +356,18 @@ static int launch_tc(const GemmTcParams* p, const void* w, int ldw, int n_rows_w
     }
     GemmTcParams q = *p;
     q.dense = w ? 1 : 0;
-    size_t per_stage = TC_A_BYTES + (size_t)((q.t_tile + 63) / 64) * 64 * 128;
+    // 256-output tiles: only with at most 256 tokens per CTA (two accumulators of 256 columns) and a matrix that
+    // is a whole number of such tiles
+    if (q.m_halves == 2 && (q.t_tile > 256 || (q.NTL * 16) % (2 * TC_BM) != 0)) q.m_halves = 1;
+    if (q.m_halves != 2) q.m_halves = 1;
+    size_t per_stage = (size_t)q.m_halves * TC_A_BYTES + (size_t)((q.t_tile + 63) / 64) * 64 * 128;
     // as many stages as shared memory holds next to the weight ring, an even number (the two producer
     // groups alternate stages); deep pipelines matter most for few tokens, where a stage is consumed quickly
     const size_t fixed = 1024 + 256 + (size_t)TC_RING * 2 * (TC_PRODUCERS * 32) * 16;
     int stages = (int)((227 * 1024 - fixed) / per_stage);
     stages = stages > 8 ? 8 : stages;
-    q.stages = stages < 2 ? 2 : (stages & ~1);
-    size_t smem = b2_gemm_tc_smem(q.t_tile, q.stages);
+    q.stages = stages < 2 ? 2 : (q.m_halves == 2 ? stages : (stages & ~1));
+    size_t smem = b2_gemm_tc_smem(q.t_tile, q.stages, q.m_halves);
     static SmemOptIn optin;
     {
         cudaError_t e = optin.ensure(gemm_int4_tc_kernel, smem);
@@ -359,7 +376,7 @@ static int launch_tc(const GemmTcParams* p, const void* w, int ldw, int n_rows_w
     int ks = (q.epi == TC_EPI_RESID_F32 && q.k_splits > 1) ? q.k_splits : 1;
     if (ks > q.KB) ks = q.KB;
     if (ks > 1) { const int per = (q.KB + ks - 1) / ks; ks = (q.KB + per - 1) / per; }     // no empty split
-    dim3 grid(q.NTL * 16 / TC_BM, (q.T + q.t_tile - 1) / q.t_tile, ks);
+    dim3 grid(q.NTL * 16 / (TC_BM * q.m_halves), (q.T + q.t_tile - 1) / q.t_tile, ks);
     gemm_int4_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(q, map, wmap);
     return cudaGetLastError();
 }

@@ -19,7 +19,8 @@ struct GemmTcParams {
     int n_valid, ldo, epi, stages;
     void* out;
     int* status;             // [0] set to 1 when a bounded wait expired
-    int pad;
+    int m_halves;            // 2: CTAs own 256 outputs (two accumulators sharing each activation tile; t_tile <= 256,
+                             // N a multiple of 256); else 128 outputs
     int dense;               // set by the launcher: weights are fp16 and come through a tensor map
     // TC_EPI_PUSH_F32: the flattened output (float4 units) is cut into push_tp slices of push_per; slice o
     // lives on rank o at push[o] + parity offset + (push_rank * push_per + index in slice) * 4 floats

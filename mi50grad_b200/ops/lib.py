@@ -115,7 +115,7 @@ class ArgmaxParams(C.Structure):
 class GemmTcParams(C.Structure):
     _fields_ = [("qfrag", vp), ("szfrag", vp), ("K", i32), ("KB", i32), ("NTL", i32), ("G", i32), ("off32", i32),
                 ("gshift", i32), ("T", i32), ("t_tile", i32), ("n_valid", i32), ("ldo", i32), ("epi", i32),
-                ("stages", i32), ("out", vp), ("status", vp), ("pad", i32), ("dense", i32),
+                ("stages", i32), ("out", vp), ("status", vp), ("m_halves", i32), ("dense", i32),
                 ("push", vp * MAX_TP), ("epoch", vp), ("part_stride", i64), ("push_tp", i32), ("push_rank", i32),
                 ("push_per", C.c_uint), ("k_splits", i32)]
 

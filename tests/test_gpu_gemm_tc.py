@@ -59,6 +59,56 @@ def test_gemm_int4_tc_split_k_adds_into_the_residual(K, N, T, ks, g):
     assert _rel(out.cpu(), ref) < 2e-3
 
 
+@pytest.mark.parametrize("K,N,T,g,ks", [(1024, 512, 512, 128, 1), (2176, 768, 80, 128, 1), (5120, 1024, 700, 128, 1),
+                                         (512, 256, 300, 32, 1), (704, 256, 48, 128, 1), (2048, 512, 512, 128, 3)])
+def test_gemm_int4_tc_256_output_tiles(K, N, T, g, ks):
+    """CTAs that own 256 outputs as two accumulators sharing each activation tile: store, fp32 store, residual
+    add (also with split-K)."""
+    from mi50grad_b200.ops import kernels as Kn
+    from mi50grad_b200.ops import lib as L
+    from mi50grad_b200.ops.packing import pack_int4
+    from mi50grad_b200.utils.quant import random_int4_linear
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator().manual_seed(K + N + T + 1)
+    lin = random_int4_linear(K, N, g, gen)
+    lin.zeros = torch.randint(0, 16, lin.zeros.shape, generator=gen).half()
+    x = torch.randn(T, K, generator=gen).half()
+    ref = x.float() @ lin.dense().t()
+    pk = pack_int4(lin, dev)
+    assert pk.n_pad % 256 == 0
+    out = torch.full((T, N), float("nan"), dtype=torch.float16, device=dev)
+    Kn.gemm_int4_tc(pk, x.to(dev), out, m_halves=2)
+    torch.cuda.synchronize()
+    Kn.gemm_tc_check_status()
+    assert _rel(out.cpu(), ref) < 3e-3
+    h0 = torch.randn(T, N, generator=gen)
+    out32 = h0.to(dev).clone()
+    Kn.gemm_int4_tc(pk, x.to(dev), out32, epi=L.TC_EPI_RESID_F32, k_splits=ks, m_halves=2)
+    torch.cuda.synchronize()
+    Kn.gemm_tc_check_status()
+    assert _rel(out32.cpu(), h0 + ref) < 2e-3
+
+
+def test_gemm_int4_tc_silu_pair_256_output_tiles():
+    from mi50grad_b200.ops import kernels as Kn
+    from mi50grad_b200.ops import lib as L
+    from mi50grad_b200.ops.packing import interleave_gate_up, pack_int4
+    from mi50grad_b200.utils.quant import random_int4_linear
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator().manual_seed(6)
+    K, F, T = 512, 640, 300
+    gate, up = random_int4_linear(K, F, 128, gen), random_int4_linear(K, F, 128, gen)
+    x = torch.randn(T, K, generator=gen).half()
+    ref = torch.nn.functional.silu(x.float() @ gate.dense().t()) * (x.float() @ up.dense().t())
+    pk = pack_int4(interleave_gate_up(gate, up), dev)
+    assert pk.n_pad % 256 == 0
+    out = torch.zeros(T, pk.n_pad // 2, dtype=torch.float16, device=dev)
+    Kn.gemm_int4_tc(pk, x.to(dev), out, epi=L.TC_EPI_SILU_PAIR, m_halves=2)
+    torch.cuda.synchronize()
+    Kn.gemm_tc_check_status()
+    assert _rel(out[:, :F].cpu(), ref) < 4e-3
+
+
 def test_gemm_int4_tc_silu_pair():
     from mi50grad_b200.ops import kernels as Kn
     from mi50grad_b200.ops import lib as L
