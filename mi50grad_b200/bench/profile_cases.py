@@ -70,19 +70,20 @@ def case_gemv(which: str, timed: bool):
 def case_gemm(which: str, timed: bool):
     dev = torch.device("cuda")
     if which == "gemm_int4":
-        # (K, N, T, tokens per CTA, 128-output halves per CTA)
-        shapes = [(17408, 5120, 512, 176, 1), (5120, 34816, 512, 512, 1), (5120, 34816, 80, 80, 1)]
+        # (K, N, T, tokens per CTA, 128-output halves per CTA, CTA pairs)
+        shapes = [(17408, 5120, 512, 176, 1, 0), (5120, 34816, 512, 512, 1, 0), (5120, 34816, 80, 80, 1, 0)]
         if timed:
-            shapes += [(5120, 34816, 512, 256, 2), (5120, 34816, 512, 256, 1), (5120, 16384, 512, 512, 1),
-                       (5120, 16384, 512, 256, 2), (5120, 34816, 80, 80, 2)]
-        for Kd, N, T, tt, mh in shapes:
+            shapes += [(5120, 34816, 512, 512, 1, 1), (5120, 34816, 512, 256, 1, 1), (5120, 34816, 512, 256, 2, 0),
+                       (5120, 16384, 512, 512, 1, 0), (5120, 16384, 512, 512, 1, 1), (5120, 16384, 512, 256, 1, 1),
+                       (5120, 16384, 512, 256, 2, 0), (17408, 5120, 512, 512, 1, 1), (5120, 34816, 80, 80, 2, 0)]
+        for Kd, N, T, tt, mh, pair in shapes:
             pk = random_packed_int4(Kd, N, 128, dev)
             x = torch.randn(T, Kd, device=dev).half()
             out = torch.zeros(T, pk.n_pad, dtype=torch.float32, device=dev)
-            run = lambda i=0: K.gemm_int4_tc(pk, x, out, epi=L.TC_EPI_STORE_F32, t_tile=tt, m_halves=mh)
+            run = lambda i=0: K.gemm_int4_tc(pk, x, out, epi=L.TC_EPI_STORE_F32, t_tile=tt, m_halves=mh, cta_pair=bool(pair))
             if timed:
-                _report(f"gemm_int4 K={Kd} N={N} T={T} t_tile={tt} outputs/CTA={128 * mh}", time_launches(run, 1, 6),
-                        bytes_=pk.nbytes(), flops=2.0 * T * Kd * N)
+                _report(f"gemm_int4 K={Kd} N={N} T={T} t_tile={tt} outputs/CTA={128 * mh}{' CTA pairs' if pair else ''}",
+                        time_launches(run, 1, 6), bytes_=pk.nbytes(), flops=2.0 * T * Kd * N)
             else:
                 _profiled(run, 1)
     else:

@@ -39,7 +39,8 @@
 #define TC_BK 64                 // k per stage (128 bytes of fp16: one swizzle row)
 #define TC_BM 128                // outputs per CTA (MMA M)
 #define TC_A_BYTES (TC_BM * TC_BK * 2)
-#define TC_RING 3                // own k-blocks of packed weights + scales in flight per producer thread (cp.async)
+#define TC_RING_OF(pair) ((pair) ? 2 : 3)     // own k-blocks of packed weights + scales in flight per producer thread (cp.async);
+                                              // CTA pairs trade one for two more pipeline stages (their token stages are half as large)
 
 // ---------------------------------------------------------------------------
 // Kernel
@@ -55,6 +56,9 @@ __device__ __forceinline__ uint32_t tc_nib_hi(uint32_t w) {
     return r;
 }
 
+// PAIR: the kernel of CTA pairs is an instantiation of its own: a kernel that contains cta_group::2 instructions
+// cannot be launched without a cluster (the plain launch is refused with "invalid cluster size").
+template <bool PAIR>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xmap,
                     const __grid_constant__ CUtensorMap wmap) {
@@ -66,10 +70,18 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
     const int t0 = blockIdx.y * p.t_tile;
     const int Tp = (min(p.t_tile, p.T - t0) + 15) & ~15;          // token columns of this CTA
     const int boxes = (Tp + 63) / 64;
-    const int b_stage_bytes = ((p.t_tile + 63) / 64) * 64 * 128;
+    // (CTA pairs: a CTA stages only its half of the token rows)
+    const int b_stage_bytes = ((p.t_tile + 63) / 64) * 64 * 128 / (PAIR ? 2 : 1);
     // MH = 2: the CTA owns 256 outputs as two M = 128 accumulators that share every activation tile (half the
     // activation bytes per FLOP, one pass of the dequantising warps per 256 outputs); all 16 producer warps
     // then work on the same k-block
+    // pair: two CTAs of a cluster (adjacent output tiles) run their MMAs as one cta_group::2 instruction stream,
+    // M = 256 over the two SMs: each CTA dequantises its own 128 weight rows and loads only ITS half of every
+    // 256-token operand tile, so the shared-memory traffic of the token operand per SM halves
+    constexpr bool pair = PAIR;
+    constexpr int TC_RING = TC_RING_OF(PAIR);
+    uint32_t crank = 0u;
+    if constexpr (PAIR) crank = cluster_ctarank();
     const int MH = p.m_halves == 2 ? 2 : 1;
     const int a_bytes = MH * TC_A_BYTES;
     unsigned char* sA = smem;
@@ -79,7 +91,8 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
                                         // the stage's group (INT4 weights) + 1 arrival with the TMA transaction bytes
     uint64_t* empty = bars + S;         // [S] 1 arrival (tcgen05.commit)
     uint64_t* acc_full = bars + 2 * S;  // 1 arrival
-    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * S + 1);
+    uint64_t* peer_full = bars + 2 * S + 1;   // [S] pair mode, leader CTA: the peer's operands of the stage are in place
+    uint32_t* tmem_slot = (uint32_t*)(bars + 3 * S + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     uint4* wring = (uint4*)(((uintptr_t)(tmem_slot + 2) + 15) & ~(uintptr_t)15);   // [TC_RING][2][512 producer threads]: 16 B of nibbles, 2 x 8 B scale/zero
 
@@ -90,13 +103,21 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
     if (tid == 0) {
         for (int s = 0; s < S; ++s) { mbar_init(&full[s], p.dense ? 1 : (MH == 2 ? TC_PRODUCERS : TC_GROUP_WARPS) + 1); mbar_init(&empty[s], 1); }
         mbar_init(acc_full, 1);
+        for (int s = 0; s < S; ++s) mbar_init(&peer_full[s], 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if constexpr (PAIR) cluster_sync_all();       // both CTAs' barriers exist before anyone signals the other
     if (warp == TC_PRODUCERS) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     :: "r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                         :: "r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                         :: "r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -257,7 +278,8 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
         // ================= activation producer (TMA) =================
         {
             const bool dense = p.dense != 0;
-            const uint32_t tx = (uint32_t)boxes * 64 * 128 + (dense ? (uint32_t)a_bytes : 0u);
+            // pair mode: of every 256-token operand tile this CTA loads rows [128 crank, 128 crank + 128)
+            const uint32_t tx = (pair ? (uint32_t)(Tp / 2) * 128u : (uint32_t)boxes * 64 * 128) + (dense ? (uint32_t)a_bytes : 0u);
             const int row_w = blockIdx.x * (TC_BM * MH);
             int st = 0;
             uint32_t ph = 0;
@@ -268,8 +290,14 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
                 if (elect_one()) {
                     mbar_arrive_expect_tx(&full[st], tx);
                     if (dense) for (int hc = 0; hc < MH; ++hc) tma_load_2d(a + hc * TC_A_BYTES, &wmap, kx, row_w + hc * TC_BM, &full[st]);
-                    for (int bx = 0; bx < boxes; ++bx)
-                        tma_load_2d(b + bx * (64 * 128), &xmap, kx, t0 + bx * 64, &full[st]);
+                    if (pair) {
+                        for (int j = 0; j < Tp / 256; ++j)
+                            for (int bx = 0; bx < 2; ++bx)
+                                tma_load_2d(b + j * (128 * 128) + bx * (64 * 128), &xmap, kx, t0 + j * 256 + (int)crank * 128 + bx * 64, &full[st]);
+                    } else {
+                        for (int bx = 0; bx < boxes; ++bx)
+                            tma_load_2d(b + bx * (64 * 128), &xmap, kx, t0 + bx * 64, &full[st]);
+                    }
                 }
                 __syncwarp();
                 a += a_bytes; b += b_stage_bytes;
@@ -290,10 +318,36 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
             int st = 0;
             uint32_t ph = 0;
             bool ok = true;
+            const uint32_t idesc_pair = make_idesc_f16_m256(256);
+            const uint64_t b_pair_half = (128 * 128) >> 4;
             for (int kb = 0; kb < KB; ++kb) {
                 ok = mbar_wait(&full[st], ph, abort_flag);
                 if (!ok) break;
+                if constexpr (PAIR) {
+                    if (crank != 0) {
+                        // peer CTA: its operands of the stage are in place: tell the leader, which issues for both
+                        if (elect_one()) mbar_arrive_remote(&peer_full[st], 0);
+                        __syncwarp();
+                        if (++st == S) { st = 0; ph ^= 1; }
+                        continue;
+                    }
+                    ok = mbar_wait_cluster(&peer_full[st], ph, abort_flag);
+                    if (!ok) break;
+                }
                 tc_fence_after();
+                if constexpr (PAIR) {
+                    if (elect_one()) {
+#pragma unroll
+                        for (int k16 = 0; k16 < TC_BK / 16; ++k16)
+                            for (int j = 0; j < Tp / 256; ++j)
+                                tc_mma_f16_pair(tmem_base + 256 * j, ad + 2 * k16, bd + j * b_pair_half + 2 * k16, idesc_pair, (kb | k16) ? 1u : 0u);
+                        tc_commit_pair(&empty[st]);
+                    }
+                    __syncwarp();
+                    ad += a_step; bd += b_step;
+                    if (++st == S) { st = 0; ph ^= 1; ad = ad0; bd = bd0; }
+                    continue;
+                }
                 if (elect_one()) {
 #pragma unroll
                     for (int k16 = 0; k16 < TC_BK / 16; ++k16) {
@@ -307,7 +361,8 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
                 ad += a_step; bd += b_step;
                 if (++st == S) { st = 0; ph ^= 1; ad = ad0; bd = bd0; }
             }
-            if (ok && elect_one()) tc_commit(acc_full);
+            if constexpr (PAIR) { if (ok && crank == 0 && elect_one()) tc_commit_pair(acc_full); }
+            else { if (ok && elect_one()) tc_commit(acc_full); }
             __syncwarp();
         }
     }
@@ -315,17 +370,21 @@ gemm_int4_tc_kernel(const GemmTcParams p, const __grid_constant__ CUtensorMap xm
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp == TC_PRODUCERS)
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(tmem_cols) : "memory");
+    if constexpr (PAIR) cluster_sync_all();       // neither CTA frees tensor memory (or leaves) while the pair's MMAs or
+                                                  // the other CTA's signals may still touch it
+    if (warp == TC_PRODUCERS) {
+        if constexpr (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(tmem_cols) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(tmem_cols) : "memory");
+    }
 }
 
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
-B2_API size_t b2_gemm_tc_smem(int t_tile, int stages, int m_halves) {
+B2_API size_t b2_gemm_tc_smem(int t_tile, int stages, int m_halves, int ring) {
     size_t b = (size_t)((t_tile + 63) / 64) * 64 * 128;
-    return 1024 + (size_t)stages * ((size_t)(m_halves == 2 ? 2 : 1) * TC_A_BYTES + b) + (2 * stages + 1) * 8 + 16 + 16 +
-           (size_t)TC_RING * 2 * (TC_PRODUCERS * 32) * 16;
+    return 1024 + (size_t)stages * ((size_t)(m_halves == 2 ? 2 : 1) * TC_A_BYTES + b) + (3 * stages + 1) * 8 + 16 + 16 +
+           (size_t)ring * 2 * (TC_PRODUCERS * 32) * 16;
 }
 
 // x: [T][ldx] fp16 activations (ldx multiple of 8, base 16-byte aligned).
@@ -360,24 +419,39 @@ static int launch_tc(const GemmTcParams* p, const void* w, int ldw, int n_rows_w
     // is a whole number of such tiles
     if (q.m_halves == 2 && (q.t_tile > 256 || (q.NTL * 16) % (2 * TC_BM) != 0)) q.m_halves = 1;
     if (q.m_halves != 2) q.m_halves = 1;
-    size_t per_stage = (size_t)q.m_halves * TC_A_BYTES + (size_t)((q.t_tile + 63) / 64) * 64 * 128;
+    dim3 grid(q.NTL * 16 / (TC_BM * q.m_halves), (q.T + q.t_tile - 1) / q.t_tile, 1);
+    // CTA pairs: whole 256-token operand tiles only, an even number of output tiles, 128-output CTAs
+    if (q.cta_pair && (q.m_halves != 1 || (grid.x & 1) || (q.t_tile != 256 && q.t_tile != 512) || q.T % q.t_tile != 0)) q.cta_pair = 0;
+    size_t per_stage = (size_t)q.m_halves * TC_A_BYTES + (size_t)((q.t_tile + 63) / 64) * 64 * 128 / (q.cta_pair ? 2 : 1);
     // as many stages as shared memory holds next to the weight ring, an even number (the two producer
     // groups alternate stages); deep pipelines matter most for few tokens, where a stage is consumed quickly
-    const size_t fixed = 1024 + 256 + (size_t)TC_RING * 2 * (TC_PRODUCERS * 32) * 16;
+    const int ring = TC_RING_OF(q.cta_pair != 0);
+    const size_t fixed = 1024 + 256 + (size_t)ring * 2 * (TC_PRODUCERS * 32) * 16;
     int stages = (int)((227 * 1024 - fixed) / per_stage);
     stages = stages > 8 ? 8 : stages;
     q.stages = stages < 2 ? 2 : (q.m_halves == 2 ? stages : (stages & ~1));
-    size_t smem = b2_gemm_tc_smem(q.t_tile, q.stages, q.m_halves);
+    size_t smem = b2_gemm_tc_smem(q.cta_pair ? q.t_tile / 2 : q.t_tile, q.stages, q.m_halves, ring);
     static SmemOptIn optin;
     {
-        cudaError_t e = optin.ensure(gemm_int4_tc_kernel, smem);
+        cudaError_t e = optin.ensure(gemm_int4_tc_kernel<false>, smem);
         if (e != cudaSuccess) return e;
     }
     int ks = (q.epi == TC_EPI_RESID_F32 && q.k_splits > 1) ? q.k_splits : 1;
     if (ks > q.KB) ks = q.KB;
     if (ks > 1) { const int per = (q.KB + ks - 1) / ks; ks = (q.KB + per - 1) / per; }     // no empty split
-    dim3 grid(q.NTL * 16 / (TC_BM * q.m_halves), (q.T + q.t_tile - 1) / q.t_tile, ks);
-    gemm_int4_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(q, map, wmap);
+    grid.z = ks;
+    if (q.cta_pair) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid; cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        static SmemOptIn optin_pair;
+        if (cudaError_t e = optin_pair.ensure(gemm_int4_tc_kernel<true>, smem)) return e;
+        return cudaLaunchKernelEx(&cfg, gemm_int4_tc_kernel<true>, q, map, wmap);
+    }
+    gemm_int4_tc_kernel<false><<<grid, TC_THREADS, smem, stream>>>(q, map, wmap);
     return cudaGetLastError();
 }
 B2_API int b2_gemm_int4_tc(const GemmTcParams* p, const void* x, int ldx, cudaStream_t stream) {

@@ -31,6 +31,9 @@ struct GemmTcParams {
     unsigned int push_per;       // float4 elements per slice
     int k_splits;                // TC_EPI_RESID_F32 only: CTAs along K per output tile (grid z); their partial
                                  // products are added to out with atomic adds (0 or 1: no split)
+    int cta_pair;                // 1: adjacent output tiles run as CTA pairs (cta_group::2 MMAs, M = 256 over two SMs); needs
+                                 // 128-output CTAs, t_tile 256 or 512 dividing T, an even number of output tiles
+    int pad3;
 };
 
 

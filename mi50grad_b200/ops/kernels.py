@@ -381,7 +381,8 @@ def sample_top_p(logits: torch.Tensor, temperature: float = 1.0, top_k: int = 50
 
 
 def gemm_int4_tc(pk, x: torch.Tensor, out: torch.Tensor, epi: int = L.TC_EPI_STORE_F16,
-                 t_tile: Optional[int] = None, n_valid: Optional[int] = None, k_splits: int = 1, m_halves: int = 1):
+                 t_tile: Optional[int] = None, n_valid: Optional[int] = None, k_splits: int = 1, m_halves: int = 1,
+                 cta_pair: bool = False):
     """out[t][n] (epi) = x[t, :K] @ W for a PackedInt4 matrix on the tcgen05 tensor cores.
     x: fp16 [T, K] (row stride multiple of 8).  SILU_PAIR: out[t][j] = silu(gate_j) * up_j for
     the gate/up-interleaved matrix; RESID_F32: out (fp32) += product, optionally from k_splits CTAs
@@ -399,7 +400,7 @@ def gemm_int4_tc(pk, x: torch.Tensor, out: torch.Tensor, epi: int = L.TC_EPI_STO
     p.K, p.KB, p.NTL, p.G, p.off32, p.gshift = pk.K, pk.KB, pk.NTL, pk.G, pk.off32, pk.gshift
     if m_halves == 2:
         t_tile = min(t_tile, 256)
-    p.T, p.t_tile, p.epi, p.k_splits, p.m_halves = T, t_tile, epi, k_splits, m_halves
+    p.T, p.t_tile, p.epi, p.k_splits, p.m_halves, p.cta_pair = T, t_tile, epi, k_splits, m_halves, int(cta_pair)
     if n_valid is None:
         n_valid = pk.n_pad // 2 if epi == L.TC_EPI_SILU_PAIR else pk.N
     p.n_valid, p.ldo, p.out, p.status = n_valid, out.stride(0), out.data_ptr(), st.data_ptr()

@@ -117,7 +117,7 @@ class GemmTcParams(C.Structure):
                 ("gshift", i32), ("T", i32), ("t_tile", i32), ("n_valid", i32), ("ldo", i32), ("epi", i32),
                 ("stages", i32), ("out", vp), ("status", vp), ("m_halves", i32), ("dense", i32),
                 ("push", vp * MAX_TP), ("epoch", vp), ("part_stride", i64), ("push_tp", i32), ("push_rank", i32),
-                ("push_per", C.c_uint), ("k_splits", i32)]
+                ("push_per", C.c_uint), ("k_splits", i32), ("cta_pair", i32), ("pad3", i32)]
 
 
 TC_EPI_STORE_F16, TC_EPI_SILU_PAIR, TC_EPI_STORE_F32, TC_EPI_RESID_F32 = 0, 1, 2, 3

@@ -89,6 +89,28 @@ def test_gemm_int4_tc_256_output_tiles(K, N, T, g, ks):
     assert _rel(out32.cpu(), h0 + ref) < 2e-3
 
 
+@pytest.mark.parametrize("K,N,T,tt", [(1024, 512, 512, 256), (2176, 768, 256, 256), (5120, 1024, 768, 256),
+                                      (1024, 512, 512, 512), (5120, 1280, 1024, 512)])
+def test_gemm_int4_tc_cta_pairs(K, N, T, tt):
+    """Adjacent output tiles as CTA pairs: cta_group::2 MMAs, each CTA loading its half of the token operand."""
+    from mi50grad_b200.ops import kernels as Kn
+    from mi50grad_b200.ops import lib as L
+    from mi50grad_b200.ops.packing import pack_int4
+    from mi50grad_b200.utils.quant import random_int4_linear
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator().manual_seed(K + N + T + 2)
+    lin = random_int4_linear(K, N, 128, gen)
+    lin.zeros = torch.randint(0, 16, lin.zeros.shape, generator=gen).half()
+    x = torch.randn(T, K, generator=gen).half()
+    ref = x.float() @ lin.dense().t()
+    pk = pack_int4(lin, dev)
+    out32 = torch.zeros(T, N, dtype=torch.float32, device=dev)
+    Kn.gemm_int4_tc(pk, x.to(dev), out32, epi=L.TC_EPI_STORE_F32, t_tile=tt, cta_pair=True)
+    torch.cuda.synchronize()
+    Kn.gemm_tc_check_status()
+    assert _rel(out32.cpu(), ref) < 2e-3
+
+
 def test_gemm_int4_tc_silu_pair_256_output_tiles():
     from mi50grad_b200.ops import kernels as Kn
     from mi50grad_b200.ops import lib as L

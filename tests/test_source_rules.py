@@ -15,6 +15,7 @@ def test_blackwell_constructs_present():
                    "tcgen05.ld.sync.aligned.32x32b", "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier",
                    "mbarrier.try_wait.parity", "elect.sync"):
         assert needle in g, needle
+    assert "tcgen05.mma.cta_group::2.kind::f16" in g and "tcgen05.alloc.cta_group::2" in SOURCES["gemm_tc.cu"]
     for name in ("gemm_tc.cu", "attention_tc.cu"):
         assert "tcgen05.alloc" in SOURCES[name] and "tcgen05.dealloc" in SOURCES[name] and "tc_mma_f16(" in SOURCES[name], name
     assert "multimem.ld_reduce" in SOURCES["common.cuh"] and "multimem.st" in SOURCES["common.cuh"]
