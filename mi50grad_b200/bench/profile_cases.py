@@ -71,9 +71,10 @@ def case_gemm(which: str, timed: bool):
     dev = torch.device("cuda")
     if which == "gemm_int4":
         # (K, N, T, tokens per CTA, 128-output halves per CTA, CTA pairs)
-        shapes = [(17408, 5120, 512, 176, 1, 0), (5120, 34816, 512, 512, 1, 0), (5120, 34816, 80, 80, 1, 0)]
+        shapes = [(17408, 5120, 512, 176, 1, 0), (5120, 34816, 512, 512, 1, 0), (5120, 34816, 80, 80, 1, 0),
+                  (5120, 34816, 512, 512, 1, 1)]
         if timed:
-            shapes += [(5120, 34816, 512, 512, 1, 1), (5120, 34816, 512, 256, 1, 1), (5120, 34816, 512, 256, 2, 0),
+            shapes += [(5120, 34816, 512, 256, 1, 1), (5120, 34816, 512, 256, 2, 0),
                        (5120, 16384, 512, 512, 1, 0), (5120, 16384, 512, 512, 1, 1), (5120, 16384, 512, 256, 1, 1),
                        (5120, 16384, 512, 256, 2, 0), (17408, 5120, 512, 512, 1, 1), (5120, 34816, 80, 80, 2, 0)]
         for Kd, N, T, tt, mh, pair in shapes:
