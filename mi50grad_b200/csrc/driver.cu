@@ -116,6 +116,7 @@ struct PendingChain {
     ChainParams cp;
     const LinearDesc* lin[CH_MAX_OPS];
     const LinearDesc* next[CH_MAX_OPS];   // the projection that follows each one in the stream (L2 prefetch hint)
+    const void* span[CH_MAX_OPS]; long long span_bytes[CH_MAX_OPS];   // other memory the kernel after it reads first
     int n = 0;
 };
 
@@ -138,6 +139,8 @@ struct Driver {
     bool gemm_m256 = true;                // 256-output GEMM tiles where the grid stays large enough
     int gemm_m256_min_ctas = 100;
     bool gemm_splitk = true;              // split-K in the many-row GEMMs that add into the residual stream
+    const void* pf_span = nullptr; long long pf_span_bytes = 0;   // see run_linear
+    bool pf_state = false;                // the in-projection of a DeltaNet layer prefetches that layer's state into L2
     int pf_blocks = 0;                    // k-blocks per warp of the next projection that a GEMV prefetches into L2 (0: off)
     int gemv_seq = 0;                     // split-K GEMVs issued so far in the step being issued (their tags)
     int push_rows_per = 0;                // > 0 while a GEMM is issued whose pushed slices are whole token rows
@@ -169,7 +172,8 @@ static LazyNorm lazy(const Driver* d, const float* h, const void* w) {
 static LazyNorm no_lazy() { LazyNorm ln; memset(&ln, 0, sizeof(ln)); return ln; }
 
 // next: the INT4 projection that follows in the stream (or null): its first weight blocks are prefetched into
-// L2 from inside this launch.
+// L2 from inside this launch.  d->pf_span / pf_span_bytes (consumed by the next INT4 launch): a span of memory the
+// kernel after this one reads first.
 static int run_linear(Driver* d, const LinearDesc& L, const void* x, int ldx, const LazyNorm& ln, int rows,
                       const GemvEpi& epi, cudaStream_t s, const LinearDesc* next = nullptr) {
     d->launches++;
@@ -181,6 +185,7 @@ static int run_linear(Driver* d, const LinearDesc& L, const void* x, int ldx, co
         p.off32 = L.off32; p.gshift = L.gshift; p.k_splits = L.k_splits; p.L = L.L;
         p.scratch = d->m.gemv_scratch; p.counters = d->m.gemv_counters; p.ln = ln; p.epi = epi; p.comm = d->m.comm;
         if (p.k_splits > 1 && d->gemv_seq < 1023 && d->m.tagged_splitk) { p.tag_word = step_word(d->m); p.tag_base = ++d->gemv_seq; }
+        if (d->pf_span) { p.pf_span = d->pf_span; p.pf_span_bytes = d->pf_span_bytes; d->pf_span = nullptr; }
         if (next && next->kind == LIN_INT4 && d->pf_blocks > 0) {
             p.pf_q = (const uint4*)next->w; p.pf_KB = next->KB; p.pf_L = next->L;
             p.pf_nx = next->NTL * 16 / 128; p.pf_ks = next->k_splits; p.pf_blocks = d->pf_blocks;
@@ -230,7 +235,9 @@ static int chain_flush(Driver* d, int rows, cudaStream_t s) {
     }
     for (int i = 0; i < n; ++i) {
         const ChainOp& op = pc.cp.op[i];
+        d->pf_span = pc.span[i]; d->pf_span_bytes = pc.span_bytes[i];
         CK(run_linear(d, *pc.lin[i], op.x, op.ldx, op.ln, rows, op.epi, s, pc.next[i]));
+        d->pf_span = nullptr;
     }
     return 0;
 }
@@ -256,6 +263,8 @@ static int chain_add(Driver* d, const LinearDesc& L, const void* x, int ldx, con
     op.ln = ln; op.epi = epi;
     pc.lin[pc.n] = &L;
     pc.next[pc.n] = next;
+    pc.span[pc.n] = d->pf_span; pc.span_bytes[pc.n] = d->pf_span_bytes;
+    d->pf_span = nullptr;
     pc.n++;
     if (d->m.use_chain == 2) return chain_flush(d, rows, s);
     return 0;
@@ -367,7 +376,11 @@ static int step_impl(Driver* d, int rows, int n_seqs, int flags, cudaStream_t s)
         const LazyNorm ln_in = lazy(d, m.h, L.attn_norm);
         // ---- token mixer
         // the in-projection rides at the end of the previous layer's chain (out_proj, gate/up, down)
+        if (d->pf_state && L.type != 0 && m.n_seqs_max * (long long)m.la_nv * m.la_dk * m.la_dv * 4 <= (8ll << 20)) {
+            d->pf_span = L.state; d->pf_span_bytes = m.n_seqs_max * (long long)m.la_nv * m.la_dk * m.la_dv * 4;
+        }
         CK(chain_add(d, L.in_proj, nullptr, 0, ln_in, rows, epi_store(m.proj, m.ld_proj, L.in_proj.N, EPI_STORE_F16), s, &L.out_proj));
+        d->pf_span = nullptr;
         CK(chain_flush(d, rows, s));
         if (L.type == 0) {
             CK(b2_qknorm_rope_cachew(m.proj, m.ld_proj, m.rows, L.q_norm, L.k_norm, m.cos_tab, m.sin_tab, L.kcache,
@@ -728,6 +741,10 @@ B2_API void* b2_driver_create(const ModelDesc* m, const LayerDesc* layers) {
     d->scan_prepass = spp ? atoi(spp) : 2;
     const char* atc = getenv("B200GRAD_ATTN_TC");
     d->attn_tc = !(atc && atoi(atc) == 0);
+    // Off by default: 214.73 against 214.30 tok/s (27B, one GPU, two runs each): the DeltaNet step's wait for its
+    // state is a small part of its 10 us.
+    const char* pfs = getenv("B200GRAD_PREFETCH_STATE");
+    d->pf_state = pfs && atoi(pfs) != 0;
     const char* pf = getenv("B200GRAD_L2_PREFETCH");
     d->pf_blocks = pf ? atoi(pf) : 0;
     return d;

@@ -344,9 +344,19 @@ __device__ void finish_rows(const GemvEpi& e, const CommCtx& c, int rows, uint32
 // One warp's share of the L2 prefetch for the next INT4 GEMV of the stream: the streams (CTA, warp) of that
 // launch are dealt round-robin to the warps of this one; lane 0 asks L2 for the first blocks of each.
 __device__ __forceinline__ void prefetch_next_weights(const GemvInt4Params& p, int warp, int lane) {
-    if (!p.pf_q || lane != 0) return;
+    if (lane != 0) return;
     const int my = ((int)blockIdx.y * (int)gridDim.x + (int)blockIdx.x) * (GEMV_THREADS / 32) + warp;
     const int n_mine = (int)(gridDim.x * gridDim.y) * (GEMV_THREADS / 32);
+    if (p.pf_span) {
+        // a contiguous span, one slice per warp of this launch
+        const long long per = ((p.pf_span_bytes + n_mine - 1) / n_mine + 15) & ~15ll;
+        const long long off = per * my;
+        if (off < p.pf_span_bytes) {
+            const uint32_t bytes = (uint32_t)min(per, (p.pf_span_bytes - off) & ~15ll);
+            if (bytes) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"((const char*)p.pf_span + off), "r"(bytes) : "memory");
+        }
+    }
+    if (!p.pf_q) return;
     const int n_next = p.pf_nx * p.pf_ks * (GEMV_THREADS / 32);
     for (int sid = my; sid < n_next; sid += n_mine) {
         const int cta = sid / (GEMV_THREADS / 32), w = sid % (GEMV_THREADS / 32);

@@ -88,6 +88,9 @@ struct GemvInt4Params {
     // streaming through this kernel's reduction tail and the next kernel's start.
     const uint4* pf_q;
     int pf_KB, pf_L, pf_nx, pf_ks, pf_blocks, pf_pad;
+    // ... or (pf_span != null) for pf_span_bytes of anything else the next kernel reads first, e.g. the DeltaNet state
+    const void* pf_span;
+    long long pf_span_bytes;
     LazyNorm ln;
     GemvEpi epi;
     CommCtx comm;

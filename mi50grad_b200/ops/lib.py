@@ -63,7 +63,7 @@ class GemvInt4Params(C.Structure):
                 ("ldx", i32), ("rows", i32), ("K", i32), ("KB", i32), ("NTL", i32), ("G", i32),
                 ("off32", i32), ("gshift", i32), ("k_splits", i32), ("L", i32), ("cluster_splitk", i32), ("tag_base", i32),
                 ("scratch", vp), ("counters", vp), ("tag_word", vp),
-                ("pf_q", vp), ("pf_KB", i32), ("pf_L", i32), ("pf_nx", i32), ("pf_ks", i32), ("pf_blocks", i32), ("pf_pad", i32),
+                ("pf_q", vp), ("pf_KB", i32), ("pf_L", i32), ("pf_nx", i32), ("pf_ks", i32), ("pf_blocks", i32), ("pf_pad", i32), ("pf_span", vp), ("pf_span_bytes", i64),
                 ("ln", LazyNorm), ("epi", GemvEpi), ("comm", CommCtx)]
 
 
