@@ -72,6 +72,37 @@ class Communicator:
         return hidden
 
 
+    def reduce_scatter_norm_allgather(self, partial: torch.Tensor, hidden: torch.Tensor, norm_w: torch.Tensor,
+                                      eps: float) -> torch.Tensor:
+        """Sequence-parallel hand-off after a row-parallel projection of T rows: rank r owns rows
+        [r * ceil(T / tp), ...).  hidden[own rows] += sum over ranks of partial[own rows]; returns the RMS-normalised
+        rows (times norm_w) of ALL ranks, fp16.  Only the owner's rows of `hidden` are kept up to date, plus the
+        last row on every rank.  This is the portable composition (reduce-scatter, local norm, all-gather); on
+        GPUs `SymmComm.reduce_scatter_norm_allgather` does it in one kernel (csrc/comm.cu, rs_norm_ag_kernel)."""
+        T, H = partial.shape
+        tp, rank = self.tp_size, self.tp_rank
+        per = -(-T // tp)
+        pad = per * tp - T
+        p32 = partial.float()
+        if pad:
+            p32 = torch.cat([p32, p32.new_zeros(pad, H)])
+        mine = self.reduce_scatter_sum(p32)                              # [per, H]
+        lo, hi = rank * per, min(T, (rank + 1) * per)
+        xn = torch.zeros(per, H, dtype=torch.float16, device=partial.device)
+        last = torch.zeros(H, dtype=torch.float32, device=partial.device)
+        if lo < hi:
+            hidden[lo:hi] += mine[:hi - lo].to(hidden.dtype)
+            h = hidden[lo:hi].float()
+            xn[:hi - lo] = (h * torch.rsqrt((h * h).mean(-1, keepdim=True) + eps) * norm_w.float()).half()
+            if hi == T:
+                last = hidden[T - 1].float().clone()
+        out = torch.cat(self.all_gather(xn))[:T]
+        last = self.all_reduce_sum(last)                                 # only the owner contributes
+        self.allreduce_calls -= 1
+        hidden[T - 1] = last.to(hidden.dtype)
+        return out
+
+
 class SingleComm(Communicator):
     def all_reduce_sum(self, t):
         self.allreduce_calls += 1

@@ -81,6 +81,40 @@ def test_collectives_gloo():
         assert torch.equal(h, 1 + 2 * torch.arange(8.0) + 1)
 
 
+def _seq_parallel(rank, world, T):
+    comm = TorchDistComm()
+    H = 64
+    g = torch.Generator().manual_seed(3)
+    h0 = torch.randn(T, H, generator=g)
+    w = (torch.rand(H, generator=g) + 0.5).half()
+    parts = [torch.randn(T, H, generator=torch.Generator().manual_seed(20 + r)) for r in range(world)]
+    h = h0.clone()
+    xn = comm.reduce_scatter_norm_allgather(parts[rank], h, w, 1e-6)
+    return xn, h
+
+
+@pytest.mark.parametrize("T", [8, 7, 1])
+def test_sequence_parallel_handoff_gloo(T):
+    """Portable form of the reduce-scatter + residual + RMSNorm + all-gather hand-off: every rank gets all
+    normalised rows, keeps its own residual rows and the last row."""
+    world, H = 2, 64
+    g = torch.Generator().manual_seed(3)
+    h0 = torch.randn(T, H, generator=g)
+    w = (torch.rand(H, generator=g) + 0.5).half()
+    parts = [torch.randn(T, H, generator=torch.Generator().manual_seed(20 + r)) for r in range(world)]
+    href = h0 + sum(parts)
+    xref = href * torch.rsqrt((href * href).mean(-1, keepdim=True) + 1e-6) * w.float()
+    res = run_gloo(_seq_parallel, world, T)
+    per = -(-T // world)
+    for rank, (xn, h) in enumerate(res):
+        assert (xn.float() - xref).abs().max() < 3e-3 * xref.abs().max()
+        lo, hi = rank * per, min(T, (rank + 1) * per)
+        if lo < hi:
+            assert torch.allclose(h[lo:hi], href[lo:hi], atol=1e-5)
+        assert torch.allclose(h[T - 1], href[T - 1], atol=1e-5)
+    assert torch.equal(res[0][0], res[1][0])
+
+
 def test_shard_spec_tp8_replicates_kv_heads():
     cfg = qwen35_27b()
     assert cfg.max_tp() == 8
