@@ -72,8 +72,8 @@ class Communicator:
         return hidden
 
 
-    def reduce_scatter_norm_allgather(self, partial: torch.Tensor, hidden: torch.Tensor, norm_w: torch.Tensor,
-                                      eps: float) -> torch.Tensor:
+    def sequence_parallel_handoff(self, partial: torch.Tensor, hidden: torch.Tensor, norm_w: torch.Tensor,
+                                  eps: float) -> torch.Tensor:
         """Sequence-parallel hand-off after a row-parallel projection of T rows: rank r owns rows
         [r * ceil(T / tp), ...).  hidden[own rows] += sum over ranks of partial[own rows]; returns the RMS-normalised
         rows (times norm_w) of ALL ranks, fp16.  Only the owner's rows of `hidden` are kept up to date, plus the

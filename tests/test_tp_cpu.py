@@ -89,7 +89,7 @@ def _seq_parallel(rank, world, T):
     w = (torch.rand(H, generator=g) + 0.5).half()
     parts = [torch.randn(T, H, generator=torch.Generator().manual_seed(20 + r)) for r in range(world)]
     h = h0.clone()
-    xn = comm.reduce_scatter_norm_allgather(parts[rank], h, w, 1e-6)
+    xn = comm.sequence_parallel_handoff(parts[rank], h, w, 1e-6)
     return xn, h
 
 
