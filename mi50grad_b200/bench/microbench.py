@@ -155,6 +155,12 @@ def bench_fused(iters: int):
             dist.barrier()
             us_u = mx(time_launches(unfused, nvar, iters))
             comm.check_status()
+            # in-kernel time stamps of one finisher launch (globaltimer, relative to the kernel's start)
+            comm.trace_enabled = True
+            K.gemv(pks[0], x, mode=L.EPI_FINISH, h=h, ss_part=ss, comm=comm.ctx(), scratch=scratch, counters=counters)
+            torch.cuda.synchronize()
+            trace = comm.last_exchange_trace()
+            comm.trace_enabled = False
             # roofline: the slower of streaming this rank's weight shard from HBM and moving the
             # partial vectors over NVLink (20 KB per peer, latency bound: reported for context)
             t_hbm = pks[0].nbytes() / (hbm * 1e3)
@@ -163,7 +169,7 @@ def bench_fused(iters: int):
                             "chain_tile_exchange_us": round(us_c, 2),
                             "gemv+nccl+add_us": round(us_u, 2), "speedup": round(us_u / us_f, 2),
                             "hbm_floor_us": round(t_hbm, 2), "frac_of_roofline": round(t_hbm / us_f, 3),
-                            "peak_source": src})
+                            "finisher_trace_ns": trace, "peak_source": src})
             if rank == 0:
                 print(json.dumps(results[-1]), flush=True)
         for n, label in ((H, "10KB fp16 payload (5120 elems)"), (512 * H, "5MB fp16 payload (512x5120)")):
